@@ -1,0 +1,112 @@
+"""ctypes binding of ``libtessera_sm100.so`` (the C ABI declared in ``include/tessera_sm100.h``).
+
+There is no fallback: if the shared library is missing or a call returns non-zero, an exception
+is raised. ``TESSERA_SM100_LIB`` overrides the library path (the same pattern as the reference's
+``TESSERA_NVIDIA_GEMM_LIB``, python/tessera/runtime.py:2169).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import POINTER, c_char_p, c_float, c_int, c_longlong, c_size_t, c_void_p
+from pathlib import Path
+
+_LIB = None
+
+F32, BF16, F16 = 0, 1, 2
+
+
+class BackendError(RuntimeError):
+    """A C-ABI call returned a non-zero code."""
+
+    def __init__(self, fn: str, rc: int, detail: str):
+        self.fn, self.rc, self.detail = fn, rc, detail
+        kind = {1: "bad argument", 2: "no usable GPU", 3: "device operation failed"}.get(rc, "error")
+        super().__init__(f"{fn}: rc={rc} ({kind}): {detail}")
+
+
+def lib_path() -> Path:
+    env = os.environ.get("TESSERA_SM100_LIB")
+    if env:
+        return Path(env)
+    return Path(__file__).resolve().parent / "lib" / "libtessera_sm100.so"
+
+
+_VP = c_void_p
+_SIGNATURES = {
+    "tessera_sm100_version": (c_char_p, []),
+    "tessera_sm100_last_error": (c_char_p, []),
+    "tessera_sm100_device_count": (c_int, [POINTER(c_int)]),
+    "tessera_sm100_set_device": (c_int, [c_int]),
+    "tessera_sm100_sm_count": (c_int, [POINTER(c_int)]),
+    "tessera_sm100_consume_device_error": (c_int, [POINTER(c_int)]),
+    "tessera_sm100_launch_count": (c_longlong, []),
+    "tessera_sm100_device_alloc": (c_int, [POINTER(_VP), c_size_t]),
+    "tessera_sm100_device_free": (c_int, [_VP]),
+    "tessera_sm100_device_memset": (c_int, [_VP, c_int, c_size_t, _VP]),
+    "tessera_sm100_device_upload": (c_int, [_VP, _VP, c_size_t, _VP]),
+    "tessera_sm100_device_download": (c_int, [_VP, _VP, c_size_t, _VP]),
+    "tessera_sm100_device_copy": (c_int, [_VP, _VP, c_size_t, _VP]),
+    "tessera_sm100_host_alloc": (c_int, [POINTER(_VP), c_size_t]),
+    "tessera_sm100_host_free": (c_int, [_VP]),
+    "tessera_sm100_stream_create": (c_int, [POINTER(_VP)]),
+    "tessera_sm100_stream_destroy": (c_int, [_VP]),
+    "tessera_sm100_stream_synchronize": (c_int, [_VP]),
+    "tessera_sm100_device_synchronize": (c_int, []),
+    "tessera_sm100_event_create": (c_int, [POINTER(_VP)]),
+    "tessera_sm100_event_destroy": (c_int, [_VP]),
+    "tessera_sm100_event_record": (c_int, [_VP, _VP]),
+    "tessera_sm100_event_synchronize": (c_int, [_VP]),
+    "tessera_sm100_event_elapsed_ms": (c_int, [_VP, _VP, POINTER(c_float)]),
+    "tessera_sm100_flush_l2": (c_int, [_VP]),
+    "tessera_sm100_mma_gemm_bf16": (c_int, [_VP, _VP, _VP, c_int, c_int, c_int]),
+    "tessera_sm100_mma_gemm_f16": (c_int, [_VP, _VP, _VP, c_int, c_int, c_int]),
+    "tessera_sm100_mma_gemm_bf16_device": (c_int, [_VP, _VP, _VP, c_int, c_int, c_int, _VP]),
+    "tessera_sm100_mma_gemm_f16_device": (c_int, [_VP, _VP, _VP, c_int, c_int, c_int, _VP]),
+    "tessera_sm100_gemm": (c_int, [_VP, _VP, _VP, c_int, c_int, c_int, c_int, c_int, c_int]),
+    "tessera_sm100_gemm_device": (c_int, [_VP, _VP, _VP, c_int, c_int, c_int, c_int, c_int, c_int,
+                                          _VP]),
+    "tessera_sm100_gemm_strided_device": (c_int, [_VP, _VP, _VP, c_int, c_int, c_int, c_int,
+                                                  c_longlong, c_longlong, c_longlong, c_longlong,
+                                                  c_longlong, c_longlong, c_int, c_int, _VP]),
+    "tessera_sm100_grouped_gemm_device": (c_int, [_VP, _VP, _VP, _VP, c_int, c_int, c_int, c_int,
+                                                  c_int, c_int, _VP]),
+    "tessera_sm100_grouped_swiglu_device": (c_int, [_VP, _VP, _VP, _VP, _VP, c_int, c_int, c_int,
+                                                    c_int, c_int, c_int, _VP]),
+}
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library once; raise if it is not there."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = lib_path()
+    if not path.exists():
+        raise BackendError("load", 2, f"{path} not found; run `python -m tessera_b200.build`")
+    lib = ctypes.CDLL(str(path))
+    for name, (res, args) in _SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the library lacks a declared symbol
+        fn.restype = res
+        fn.argtypes = args
+    _LIB = lib
+    return lib
+
+
+def exported_symbols() -> list[str]:
+    return sorted(_SIGNATURES)
+
+
+def last_error() -> str:
+    return (load().tessera_sm100_last_error() or b"").decode("utf-8", "replace")
+
+
+def check(fn_name: str, rc: int) -> None:
+    if rc != 0:
+        raise BackendError(fn_name, rc, last_error())
+
+
+def call(fn_name: str, *args):
+    """Call an int-returning entry point and raise on a non-zero code."""
+    rc = getattr(load(), fn_name)(*args)
+    check(fn_name, rc)

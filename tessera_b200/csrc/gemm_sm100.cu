@@ -1,0 +1,365 @@
+// Host side of the tcgen05 GEMM: tensor-map construction, launch, and the C entry points.
+#include "gemm_sm100.cuh"
+
+#include <algorithm>
+#include <mutex>
+
+#include "../../include/tessera_sm100.h"
+#include "device_ctx.h"
+
+namespace tsb {
+namespace gemm {
+
+namespace {
+
+size_t out_size(int out_dtype) { return out_dtype == TESSERA_SM100_F32 ? 4 : 2; }
+
+template <typename OutT, int kMode>
+int launch_kernel(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2,
+                  const CUtensorMap& tD, const Params& p, int grid, cudaStream_t stream) {
+  // The attribute is per device; setting it on every call is cheap and keeps multi-device
+  // processes correct.
+  TSB_CUDA_OK(cudaFuncSetAttribute(gemm_kernel<OutT, kMode>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));
+  gemm_kernel<OutT, kMode><<<grid, NUM_THREADS, SMEM_ALLOC, stream>>>(tA, tB, tB2, tD, p);
+  TSB_CUDA_OK(cudaGetLastError());
+  note_launch();
+  return kOk;
+}
+
+template <int kMode>
+int dispatch_out(int out_dtype, const CUtensorMap& tA, const CUtensorMap& tB,
+                 const CUtensorMap& tB2, const CUtensorMap& tD, const Params& p, int grid,
+                 cudaStream_t stream) {
+  switch (out_dtype) {
+    case TESSERA_SM100_F32:
+      if constexpr (kMode == kGroupedSwiGLU) break;
+      else return launch_kernel<float, kMode>(tA, tB, tB2, tD, p, grid, stream);
+    case TESSERA_SM100_BF16:
+      return launch_kernel<__nv_bfloat16, kMode>(tA, tB, tB2, tD, p, grid, stream);
+    case TESSERA_SM100_F16:
+      return launch_kernel<__half, kMode>(tA, tB, tB2, tD, p, grid, stream);
+    default:
+      break;
+  }
+  set_last_error("unsupported output dtype %d for this GEMM mode", out_dtype);
+  return kBadArg;
+}
+
+CUtensorMapDataType tm_dtype(int dt) {
+  switch (dt) {
+    case TESSERA_SM100_BF16: return CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    case TESSERA_SM100_F16: return CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    default: return CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  }
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+// Dense (optionally batched) GEMM on device pointers with explicit leading dimensions and
+// batch strides, all in elements. Every stride must make a 16-byte multiple.
+int launch_plain(const void* A, const void* B, void* D, int batch, int M, int N, int K,
+                 long long lda, long long ldb, long long ldd, long long sA, long long sB,
+                 long long sD, int in_dtype, int out_dtype, cudaStream_t stream) {
+  if (!A || !B || !D || batch <= 0 || M <= 0 || N <= 0 || K <= 0) {
+    set_last_error("gemm: null pointer or non-positive size (batch %d M %d N %d K %d)", batch, M,
+                   N, K);
+    return kBadArg;
+  }
+  if (in_dtype != TESSERA_SM100_BF16 && in_dtype != TESSERA_SM100_F16) {
+    set_last_error("gemm: input dtype must be bf16 or f16");
+    return kBadArg;
+  }
+  const size_t osz = out_size(out_dtype);
+  if (!aligned16(A) || !aligned16(B) || !aligned16(D) || (lda * 2) % 16 || (ldb * 2) % 16 ||
+      (ldd * (long long)osz) % 16 || (sA * 2) % 16 || (sB * 2) % 16 || (sD * (long long)osz) % 16) {
+    set_last_error("gemm: operands must be 16-byte aligned with 16-byte-multiple strides");
+    return kBadArg;
+  }
+  if (batch == 1) {  // any legal stride will do for a single batch
+    sA = (long long)M * lda;
+    sB = (long long)K * ldb;
+    sD = (long long)M * ldd;
+  }
+  CUtensorMap tA, tB, tD;
+  {
+    uint64_t dims[3] = {(uint64_t)K, (uint64_t)M, (uint64_t)batch};
+    uint64_t str[2] = {(uint64_t)lda * 2, (uint64_t)sA * 2};
+    uint32_t box[3] = {BK, BM, 1};
+    if (!encode_tmap(&tA, tm_dtype(in_dtype), 3, A, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return kBadArg;
+  }
+  {
+    uint64_t dims[3] = {(uint64_t)N, (uint64_t)K, (uint64_t)batch};
+    uint64_t str[2] = {(uint64_t)ldb * 2, (uint64_t)sB * 2};
+    uint32_t box[3] = {64, BK, 1};
+    if (!encode_tmap(&tB, tm_dtype(in_dtype), 3, B, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return kBadArg;
+  }
+  {
+    uint64_t dims[3] = {(uint64_t)N, (uint64_t)M, (uint64_t)batch};
+    uint64_t str[2] = {(uint64_t)ldd * osz, (uint64_t)sD * osz};
+    uint32_t box[3] = {(uint32_t)(128 / osz), 32, 1};
+    if (!encode_tmap(&tD, tm_dtype(out_dtype), 3, D, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return kBadArg;
+  }
+  Params p{};
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.batch = batch;
+  p.m_tiles = (M + BM - 1) / BM;
+  p.n_tiles = (N + BN - 1) / BN;
+  p.idesc = make_idesc_f16(in_dtype == TESSERA_SM100_BF16, false, true, BM, BN);
+  p.group_offsets = nullptr;
+  p.D = D;
+  p.ldd = ldd;
+  p.err = device_err_word();
+  if (!p.err) return kDeviceFailed;
+  const long long total = (long long)p.m_tiles * p.n_tiles * batch;
+  const int grid = (int)std::min<long long>(total, sm_count());
+  return dispatch_out<kPlain>(out_dtype, tA, tB, tB, tD, p, grid, stream);
+}
+
+// Ragged grouped GEMM on device pointers. x[T,K] rows sorted by group, w[E,K,N] (and w2 for
+// the SwiGLU form), offsets[E+1] int32 in device memory, out[T,N]. K and N multiples of 8.
+int launch_grouped(const void* x, const void* w, const void* w2, const int* offsets, void* out,
+                   int T, int K, int N, int E, int in_dtype, int out_dtype, bool swiglu,
+                   cudaStream_t stream) {
+  if (!x || !w || !offsets || !out || (swiglu && !w2) || T < 0 || K <= 0 || N <= 0 || E <= 0) {
+    set_last_error("grouped_gemm: null pointer or bad size (T %d K %d N %d E %d)", T, K, N, E);
+    return kBadArg;
+  }
+  if (T == 0) return kOk;
+  if (in_dtype != TESSERA_SM100_BF16 && in_dtype != TESSERA_SM100_F16) {
+    set_last_error("grouped_gemm: input dtype must be bf16 or f16");
+    return kBadArg;
+  }
+  const size_t osz = out_size(out_dtype);
+  if ((K % 8) || (N % 8) || !aligned16(x) || !aligned16(w) || !aligned16(out) ||
+      (swiglu && !aligned16(w2))) {
+    set_last_error("grouped_gemm: K and N must be multiples of 8 and pointers 16-byte aligned");
+    return kBadArg;
+  }
+  CUtensorMap tA, tB, tB2, tD;
+  {
+    uint64_t dims[3] = {(uint64_t)K, (uint64_t)T, 1};
+    uint64_t str[2] = {(uint64_t)K * 2, (uint64_t)T * K * 2};
+    uint32_t box[3] = {BK, BM, 1};
+    if (!encode_tmap(&tA, tm_dtype(in_dtype), 3, x, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return kBadArg;
+  }
+  {
+    uint64_t dims[3] = {(uint64_t)N, (uint64_t)K, (uint64_t)E};
+    uint64_t str[2] = {(uint64_t)N * 2, (uint64_t)K * N * 2};
+    uint32_t box[3] = {64, BK, 1};
+    if (!encode_tmap(&tB, tm_dtype(in_dtype), 3, w, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return kBadArg;
+    if (swiglu) {
+      if (!encode_tmap(&tB2, tm_dtype(in_dtype), 3, w2, dims, str, box,
+                       CU_TENSOR_MAP_SWIZZLE_128B))
+        return kBadArg;
+    } else {
+      tB2 = tB;
+    }
+  }
+  {
+    uint64_t dims[3] = {(uint64_t)N, (uint64_t)T, 1};
+    uint64_t str[2] = {(uint64_t)N * osz, (uint64_t)T * N * osz};
+    uint32_t box[3] = {(uint32_t)(128 / osz), 32, 1};
+    if (!encode_tmap(&tD, tm_dtype(out_dtype), 3, out, dims, str, box,
+                     CU_TENSOR_MAP_SWIZZLE_128B))
+      return kBadArg;
+  }
+  Params p{};
+  p.M = T;
+  p.N = N;
+  p.K = K;
+  p.batch = E;
+  const int out_w = swiglu ? BN / 2 : BN;
+  p.m_tiles = 0;
+  p.n_tiles = (N + out_w - 1) / out_w;
+  p.idesc = make_idesc_f16(in_dtype == TESSERA_SM100_BF16, false, true, BM, BN);
+  p.group_offsets = offsets;
+  p.D = out;
+  p.ldd = N;
+  p.err = device_err_word();
+  if (!p.err) return kDeviceFailed;
+  // Upper bound on the number of tiles: every group may add one partial m-tile.
+  const long long max_tiles = ((long long)(T + BM - 1) / BM + E) * p.n_tiles;
+  const int grid = (int)std::min<long long>(max_tiles, sm_count());
+  if (swiglu) return dispatch_out<kGroupedSwiGLU>(out_dtype, tA, tB, tB2, tD, p, grid, stream);
+  return dispatch_out<kGrouped>(out_dtype, tA, tB, tB2, tD, p, grid, stream);
+}
+
+// ---------------------------------------------------------------------------------------
+// Row-pitch conversion kernels for operands whose natural row stride is not a 16-byte
+// multiple (the TMA requirement). `esz` is the element size in bytes.
+__global__ void repitch_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                               long long rows, long long row_bytes, long long src_pitch,
+                               long long dst_pitch) {
+  const long long total = rows * row_bytes;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / row_bytes;
+    const long long c = i - r * row_bytes;
+    dst[r * dst_pitch + c] = src[r * src_pitch + c];
+  }
+}
+
+int repitch(const void* src, void* dst, long long rows, long long row_bytes, long long src_pitch,
+            long long dst_pitch, cudaStream_t stream) {
+  const long long total = rows * row_bytes;
+  if (total == 0) return kOk;
+  const int block = 256;
+  const int grid = (int)std::min<long long>((total + block - 1) / block, 148 * 16);
+  repitch_kernel<<<grid, block, 0, stream>>>(static_cast<const uint8_t*>(src),
+                                             static_cast<uint8_t*>(dst), rows, row_bytes,
+                                             src_pitch, dst_pitch);
+  TSB_CUDA_OK(cudaGetLastError());
+  note_launch();
+  return kOk;
+}
+
+long long round_up8(long long v) { return (v + 7) & ~7ll; }
+
+// Dense row-major batched GEMM on device pointers; pads through scratch when K or N is not
+// a multiple of 8 (that path synchronises the stream before it frees the scratch).
+int gemm_device(const void* A, const void* B, void* D, int batch, int M, int N, int K,
+                int in_dtype, int out_dtype, cudaStream_t stream) {
+  if (!A || !B || !D || batch <= 0 || M <= 0 || N <= 0 || K <= 0) {
+    set_last_error("gemm: null pointer or non-positive size (batch %d M %d N %d K %d)", batch, M,
+                   N, K);
+    return kBadArg;
+  }
+  const size_t osz = out_size(out_dtype);
+  const bool direct = (K % 8 == 0) && (N % 8 == 0) && aligned16(A) && aligned16(B) && aligned16(D);
+  if (direct) {
+    return launch_plain(A, B, D, batch, M, N, K, K, N, N, (long long)M * K, (long long)K * N,
+                        (long long)M * N, in_dtype, out_dtype, stream);
+  }
+  const long long Kp = round_up8(K), Np = round_up8(N);
+  void* pA = pool_alloc((size_t)batch * M * Kp * 2);
+  void* pB = pool_alloc((size_t)batch * K * Np * 2);
+  void* pD = pool_alloc((size_t)batch * M * Np * osz);
+  int rc = kOk;
+  if (!pA || !pB || !pD) rc = kDeviceFailed;
+  if (rc == kOk) rc = repitch(A, pA, (long long)batch * M, (long long)K * 2, (long long)K * 2, Kp * 2, stream);
+  if (rc == kOk) rc = repitch(B, pB, (long long)batch * K, (long long)N * 2, (long long)N * 2, Np * 2, stream);
+  if (rc == kOk)
+    rc = launch_plain(pA, pB, pD, batch, M, N, K, Kp, Np, Np, (long long)M * Kp,
+                      (long long)K * Np, (long long)M * Np, in_dtype, out_dtype, stream);
+  if (rc == kOk)
+    rc = repitch(pD, D, (long long)batch * M, (long long)N * osz, Np * (long long)osz,
+                 (long long)N * osz, stream);
+  if (cudaStreamSynchronize(stream) != cudaSuccess && rc == kOk) {
+    set_last_error("gemm: stream synchronise failed: %s", cudaGetErrorString(cudaGetLastError()));
+    rc = kDeviceFailed;
+  }
+  pool_free(pA);
+  pool_free(pB);
+  pool_free(pD);
+  return rc;
+}
+
+// Host-pointer form: upload (re-pitching rows on the way), run, download.
+int gemm_host(const void* A, const void* B, void* D, int batch, int M, int N, int K, int in_dtype,
+              int out_dtype) {
+  if (!A || !B || !D || batch <= 0 || M <= 0 || N <= 0 || K <= 0) {
+    set_last_error("gemm: null pointer or non-positive size (batch %d M %d N %d K %d)", batch, M,
+                   N, K);
+    return kBadArg;
+  }
+  if (int rc = ensure_device()) return rc;
+  const size_t osz = out_size(out_dtype);
+  const long long Kp = round_up8(K), Np = round_up8(N);
+  void* pA = pool_alloc((size_t)batch * M * Kp * 2);
+  void* pB = pool_alloc((size_t)batch * K * Np * 2);
+  void* pD = pool_alloc((size_t)batch * M * Np * osz);
+  int rc = (pA && pB && pD) ? kOk : kDeviceFailed;
+  cudaStream_t st = nullptr;
+  auto fail = [&](const char* what) {
+    set_last_error("gemm: %s failed: %s", what, cudaGetErrorString(cudaGetLastError()));
+    rc = kDeviceFailed;
+  };
+  if (rc == kOk && cudaMemcpy2DAsync(pA, Kp * 2, A, (size_t)K * 2, (size_t)K * 2,
+                                     (size_t)batch * M, cudaMemcpyHostToDevice, st) != cudaSuccess)
+    fail("upload of A");
+  if (rc == kOk && cudaMemcpy2DAsync(pB, Np * 2, B, (size_t)N * 2, (size_t)N * 2,
+                                     (size_t)batch * K, cudaMemcpyHostToDevice, st) != cudaSuccess)
+    fail("upload of B");
+  if (rc == kOk)
+    rc = launch_plain(pA, pB, pD, batch, M, N, K, Kp, Np, Np, (long long)M * Kp,
+                      (long long)K * Np, (long long)M * Np, in_dtype, out_dtype, st);
+  if (rc == kOk && cudaMemcpy2DAsync(D, (size_t)N * osz, pD, Np * osz, (size_t)N * osz,
+                                     (size_t)batch * M, cudaMemcpyDeviceToHost, st) != cudaSuccess)
+    fail("download of D");
+  if (cudaStreamSynchronize(st) != cudaSuccess && rc == kOk) fail("synchronise");
+  if (rc == kOk) {
+    int e[4];
+    if (consume_device_err(e) != 0) {
+      set_last_error("gemm: kernel wait expired (code %d, block %d, detail %d)", e[0], e[1], e[2]);
+      rc = kDeviceFailed;
+    }
+  }
+  pool_free(pA);
+  pool_free(pB);
+  pool_free(pD);
+  return rc;
+}
+
+}  // namespace gemm
+}  // namespace tsb
+
+using namespace tsb;
+
+extern "C" {
+
+int tessera_sm100_mma_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K) {
+  return gemm::gemm_host(A, B, D, 1, M, N, K, TESSERA_SM100_BF16, TESSERA_SM100_F32);
+}
+int tessera_sm100_mma_gemm_f16(const void* A, const void* B, void* D, int M, int N, int K) {
+  return gemm::gemm_host(A, B, D, 1, M, N, K, TESSERA_SM100_F16, TESSERA_SM100_F32);
+}
+int tessera_sm100_mma_gemm_bf16_device(const void* A, const void* B, void* D, int M, int N, int K,
+                                       void* stream) {
+  return gemm::gemm_device(A, B, D, 1, M, N, K, TESSERA_SM100_BF16, TESSERA_SM100_F32,
+                           static_cast<cudaStream_t>(stream));
+}
+int tessera_sm100_mma_gemm_f16_device(const void* A, const void* B, void* D, int M, int N, int K,
+                                      void* stream) {
+  return gemm::gemm_device(A, B, D, 1, M, N, K, TESSERA_SM100_F16, TESSERA_SM100_F32,
+                           static_cast<cudaStream_t>(stream));
+}
+int tessera_sm100_gemm(const void* A, const void* B, void* D, int batch, int M, int N, int K,
+                       int in_dtype, int out_dtype) {
+  return gemm::gemm_host(A, B, D, batch, M, N, K, in_dtype, out_dtype);
+}
+int tessera_sm100_gemm_device(const void* A, const void* B, void* D, int batch, int M, int N,
+                              int K, int in_dtype, int out_dtype, void* stream) {
+  return gemm::gemm_device(A, B, D, batch, M, N, K, in_dtype, out_dtype,
+                           static_cast<cudaStream_t>(stream));
+}
+int tessera_sm100_gemm_strided_device(const void* A, const void* B, void* D, int batch, int M,
+                                      int N, int K, long long lda, long long ldb, long long ldd,
+                                      long long strideA, long long strideB, long long strideD,
+                                      int in_dtype, int out_dtype, void* stream) {
+  return gemm::launch_plain(A, B, D, batch, M, N, K, lda, ldb, ldd, strideA, strideB, strideD,
+                            in_dtype, out_dtype, static_cast<cudaStream_t>(stream));
+}
+int tessera_sm100_grouped_gemm_device(const void* x, const void* w, const int* offsets, void* out,
+                                      int T, int K, int N, int E, int in_dtype, int out_dtype,
+                                      void* stream) {
+  return gemm::launch_grouped(x, w, nullptr, offsets, out, T, K, N, E, in_dtype, out_dtype, false,
+                              static_cast<cudaStream_t>(stream));
+}
+int tessera_sm100_grouped_swiglu_device(const void* x, const void* w_gate, const void* w_up,
+                                        const int* offsets, void* out, int T, int K, int F, int E,
+                                        int in_dtype, int out_dtype, void* stream) {
+  return gemm::launch_grouped(x, w_gate, w_up, offsets, out, T, K, F, E, in_dtype, out_dtype, true,
+                              static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -99,6 +99,64 @@ int tessera_sm100_grouped_swiglu_device(const void* x, const void* w_gate, const
                                         const int* offsets, void* out, int T, int K, int F, int E,
                                         int in_dtype, int out_dtype, void* stream);
 
+/* ---- MoE layer pieces --------------------------------------------------------------------
+ * Router: top-k over f32 gate logits [T,E]; selection order and tie rule of route_tokens
+ * (python/tessera/distributed/moe.py:160-172: descending, the higher expert index first on a
+ * tie); weights are f32 softmax probabilities, renormalised over the top-k when `normalize`.
+ * assignment [T,top_k] int32, weights [T,top_k] f32. */
+int tessera_sm100_moe_route_device(const float* logits, int T, int E, int top_k, int normalize,
+                                   int* assignment, float* weights, void* stream);
+/* Stable expert sort of the token-major slots with the capacity rule of route_tokens
+ * (python/tessera/distributed/moe.py:185-199; capacity < 0 = unlimited; dropped slots get
+ * assignment -1 / weight 0 in place). Outputs are the canonical int32 transport arrays
+ * (python/tessera/compiler/moe_transport.py:75-134): token_of_slot, expert_of_slot,
+ * weight_of_slot (length = kept slots), group_sizes[E], group_offsets[E+1], plus
+ * slot_of_assignment[T*top_k] (sorted position of each slot, -1 if dropped). E <= 256. */
+int tessera_sm100_moe_permute_device(int* assignment, float* weights, int T, int top_k, int E,
+                                     int capacity, int* token_of_slot, int* expert_of_slot,
+                                     float* weight_of_slot, int* group_sizes, int* group_offsets,
+                                     int* slot_of_assignment, void* stream);
+/* o[s,:] = x[tok[s],:]: the dispatch gather, argument order of tessera_nvidia_moe_dispatch_f32
+ * (x, tok, o, T, S, H) (python/tessera/compiler/emit/nvidia_cuda.py:1530). */
+int tessera_sm100_moe_dispatch_device(const void* x, const int* tok, void* o, int T, int S, int H,
+                                      int dtype, void* stream);
+/* out[t,:] = sum_j weights[t,j] * y[slot_of_assignment[t,j],:] in j order (deterministic); the
+ * combine of python/tessera/nn/functional.py:487-490. */
+int tessera_sm100_moe_combine_device(const void* y, const int* slot_of_assignment,
+                                     const float* weights, void* out, int T, int top_k, int H,
+                                     int y_dtype, int out_dtype, void* stream);
+/* o[tok[s],:] += w[s] * x[s,:] after zeroing o: tessera_nvidia_moe_combine_f32's contract
+ * (x, tok, w, o, T, S, H) (python/tessera/compiler/emit/nvidia_cuda.py:1531) on device memory. */
+int tessera_sm100_moe_combine_scatter_f32_device(const float* x, const int* tok, const float* w,
+                                                 float* o, int T, int S, int H, void* stream);
+/* Whole layer: route -> permute -> dispatch -> grouped SwiGLU GEMM -> grouped down GEMM ->
+ * combine (python/tessera/nn/functional.py:403-490 with the router logits given). x [T,H],
+ * w_gate/w_up [E,H,F], w_down [E,F,H] in `dtype` (bf16/f16), logits f32 [T,E], out [T,H].
+ * `workspace` is device scratch of tessera_sm100_moe_workspace_bytes() bytes; the routing
+ * products stay in it and can be located with tessera_sm100_moe_workspace_views(). */
+size_t tessera_sm100_moe_workspace_bytes(int T, int H, int F, int E, int top_k);
+int tessera_sm100_moe_layer_device(const void* x, const float* logits, const void* w_gate,
+                                   const void* w_up, const void* w_down, void* out, int T, int H,
+                                   int F, int E, int top_k, int normalize, int capacity, int dtype,
+                                   int out_dtype, void* workspace, void* stream);
+int tessera_sm100_moe_workspace_views(void* workspace, int T, int H, int F, int E, int top_k,
+                                      void** assignment, void** weights, void** token_of_slot,
+                                      void** expert_of_slot, void** weight_of_slot,
+                                      void** group_sizes, void** group_offsets,
+                                      void** slot_of_assignment);
+
+/* ---- decode attention --------------------------------------------------------------------
+ * One query token per sequence against a KV cache: Q,O [B,Hq,1,D], K,V [B,Hkv,Sk,D] bf16,
+ * D = 128, query head hq reads KV head hq / (Hq/Hkv) (python/tessera/nn/functional.py:349-356;
+ * the reference's CUDA lane has the same mapping, python/tessera/compiler/emit/nvidia_cuda.py:265).
+ * splits <= 0 lets the library choose; with more than one split `scratch` must hold
+ * tessera_sm100_attn_decode_scratch_bytes(B, Hq, splits) bytes of device memory. */
+int tessera_sm100_attn_decode_splits(int B, int Hq, int Hkv, int Sk);
+size_t tessera_sm100_attn_decode_scratch_bytes(int B, int Hq, int splits);
+int tessera_sm100_attn_decode_device(const void* Q, const void* K, const void* V, void* O, int B,
+                                     int Hq, int Hkv, int Sk, int D, float scale, int splits,
+                                     void* scratch, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -73,6 +73,23 @@ _SIGNATURES = {
                                                   c_int, c_int, _VP]),
     "tessera_sm100_grouped_swiglu_device": (c_int, [_VP, _VP, _VP, _VP, _VP, c_int, c_int, c_int,
                                                     c_int, c_int, c_int, _VP]),
+    "tessera_sm100_moe_route_device": (c_int, [_VP, c_int, c_int, c_int, c_int, _VP, _VP, _VP]),
+    "tessera_sm100_moe_permute_device": (c_int, [_VP, _VP, c_int, c_int, c_int, c_int, _VP, _VP,
+                                                 _VP, _VP, _VP, _VP, _VP]),
+    "tessera_sm100_moe_dispatch_device": (c_int, [_VP, _VP, _VP, c_int, c_int, c_int, c_int, _VP]),
+    "tessera_sm100_moe_combine_device": (c_int, [_VP, _VP, _VP, _VP, c_int, c_int, c_int, c_int,
+                                                 c_int, _VP]),
+    "tessera_sm100_moe_combine_scatter_f32_device": (c_int, [_VP, _VP, _VP, _VP, c_int, c_int,
+                                                             c_int, _VP]),
+    "tessera_sm100_moe_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
+    "tessera_sm100_moe_layer_device": (c_int, [_VP, _VP, _VP, _VP, _VP, _VP, c_int, c_int, c_int,
+                                               c_int, c_int, c_int, c_int, c_int, c_int, _VP, _VP]),
+    "tessera_sm100_moe_workspace_views": (c_int, [_VP, c_int, c_int, c_int, c_int, c_int]
+                                          + [POINTER(_VP)] * 8),
+    "tessera_sm100_attn_decode_splits": (c_int, [c_int, c_int, c_int, c_int]),
+    "tessera_sm100_attn_decode_scratch_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "tessera_sm100_attn_decode_device": (c_int, [_VP, _VP, _VP, _VP, c_int, c_int, c_int, c_int,
+                                                 c_int, c_float, c_int, _VP, _VP]),
 }
 
 

@@ -1,0 +1,417 @@
+// GQA decode attention (one query token per sequence) for sm_100a: a bandwidth-bound
+// split-KV flash-decode kernel.
+//
+//   O[b,hq,:] = softmax(scale * Q[b,hq,:] . K[b,hk,:,:]^T) V[b,hk,:,:],   hk = hq / (Hq/Hkv)
+//
+// (python/tessera/nn/functional.py:349-356 on top of python/tessera/__init__.py:1304-1356; for a
+// single query token the causal mask removes nothing, python/tessera/__init__.py:1344-1349.)
+//
+// Grid = (kv splits, Hkv * head-groups, B). A CTA streams its KV range through a 3-stage
+// TMA + mbarrier ring (64 positions of K and V per stage, 128-byte swizzle) fed by one producer
+// warp. Four consumer warps each own 16 of the 64 positions. The up-to-8 query heads that share
+// a KV head ride in the N dimension of mma.sync.m16n8k16 (tcgen05 needs M >= 64, which would be
+// >= 87% padding here; the kernel is HBM-bound, not tensor-bound):
+//     S^T[16 pos x 8 heads]  = K[16 x 128] . Q^T[128 x 8]
+//     O^T[128 d  x 8 heads] += V^T[128 x 16 pos] . P^T[16 x 8]     (V via ldmatrix.trans,
+//                                                                   P^T via movmatrix)
+// Online softmax keeps fp32 running max / sum per head; the max over positions is a
+// warp-shuffle reduction. Warps are merged through shared memory, splits through a small
+// fp32 partial buffer and a second kernel (the merge of
+// python/tessera/_block_attnres_ops.py:104-146).
+#include <cuda_bf16.h>
+
+#include <algorithm>
+#include <cmath>
+
+#include "../../include/tessera_sm100.h"
+#include "device_ctx.h"
+#include "sm100_ptx.cuh"
+
+namespace tsb {
+namespace attn_decode {
+
+constexpr int D = 128;
+constexpr int TILE = 64;      // KV positions per stage
+constexpr int STAGES = 3;
+constexpr int CONSUMERS = 4;  // warps; each owns TILE / 4 = 16 positions
+constexpr int THREADS = (CONSUMERS + 1) * 32;
+constexpr int HALF_BYTES = TILE * 64 * 2;        // one [64 pos][64 d] swizzled block
+constexpr int KV_BYTES = 2 * HALF_BYTES;         // K or V tile
+constexpr int STAGE_BYTES = 2 * KV_BYTES;        // K + V
+constexpr int SMEM_BAR_OFF = STAGES * STAGE_BYTES;
+constexpr int SMEM_BYTES = SMEM_BAR_OFF + 64;
+constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;
+constexpr int MAX_SPLITS = 64;
+
+struct Params {
+  const __nv_bfloat16* Q;  // [B, Hq, D]
+  __nv_bfloat16* O;        // [B, Hq, D]
+  float* part_o;           // [B, Hq, splits, D]   (unnormalised)
+  float* part_ml;          // [B, Hq, splits, 2]   (max in log2 units, sum)
+  int B, Hq, Hkv, Sk, G;   // G = Hq / Hkv
+  int groups_per_kv;       // ceil(G / 8)
+  int splits, tiles_total, tiles_per_split;
+  float scale_log2;        // scale * log2(e)
+  int* err;
+};
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                               uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+      "{%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ void consumer_bar() {
+  asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory");
+}
+
+__global__ void __launch_bounds__(THREADS, 2)
+decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+              const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bars = smem_base + SMEM_BAR_OFF;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + SMEM_BAR_OFF + 8 * 2 * STAGES);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int split = blockIdx.x;
+  const int kvh = blockIdx.y / p.groups_per_kv;
+  const int hgroup = blockIdx.y - kvh * p.groups_per_kv;
+  const int b = blockIdx.z;
+  const int head0 = kvh * p.G + hgroup * 8;             // first query head of this CTA
+  const int nheads = min(8, p.G - hgroup * 8);          // valid heads in the N dimension
+  const int tile_begin = split * p.tiles_per_split;
+  const int tile_end = min(p.tiles_total, tile_begin + p.tiles_per_split);
+  const int ntiles = max(0, tile_end - tile_begin);
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), CONSUMERS);
+    }
+    fence_mbar_init();
+  }
+  __syncthreads();
+
+  if (warp == CONSUMERS) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int i = 0; i < ntiles; ++i) {
+        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.err, kErrWaitEmpty, i)) break;
+        mbar_arrive_expect_tx(full_bar(stage), STAGE_BYTES);
+        const int pos0 = (tile_begin + i) * TILE;
+        const uint32_t dst = smem_base + stage * STAGE_BYTES;
+        tma_load_4d(dst, &tmK, full_bar(stage), 0, pos0, kvh, b);
+        tma_load_4d(dst + HALF_BYTES, &tmK, full_bar(stage), 64, pos0, kvh, b);
+        tma_load_4d(dst + KV_BYTES, &tmV, full_bar(stage), 0, pos0, kvh, b);
+        tma_load_4d(dst + KV_BYTES + HALF_BYTES, &tmV, full_bar(stage), 64, pos0, kvh, b);
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+    return;  // the producer warp takes no part in the consumer barriers below
+  }
+
+  // -------------------------------------------------------------- consumers
+  const int g = lane >> 2;  // fragment row group
+  const int t = lane & 3;   // fragment column pair
+  // Q^T B-fragments for the 8 k-steps over d: head = g (zero beyond nheads).
+  uint32_t qb[8][2];
+  {
+    const bool live = g < nheads;
+    const uint32_t* qrow = reinterpret_cast<const uint32_t*>(
+        p.Q + (static_cast<long long>(b) * p.Hq + head0 + (live ? g : 0)) * D);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      qb[ks][0] = live ? qrow[(16 * ks + 2 * t) >> 1] : 0u;
+      qb[ks][1] = live ? qrow[(16 * ks + 8 + 2 * t) >> 1] : 0u;
+    }
+  }
+  float o[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY;  // running max (log2 units) for heads 2t, 2t+1
+  float l0 = 0.f, l1 = 0.f;              // per-lane partial sums
+
+  int stage = 0;
+  uint32_t phase = 0;
+  bool ok = true;
+  for (int i = 0; i < ntiles; ++i) {
+    if (!mbar_wait(full_bar(stage), phase, abort_flag, p.err, kErrWaitFull, i)) {
+      ok = false;
+      break;
+    }
+    const uint32_t kbase = smem_base + stage * STAGE_BYTES;
+    const uint32_t vbase = kbase + KV_BYTES;
+    // S^T = K . Q^T for this warp's 16 positions
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      uint32_t a[4];
+      const uint32_t row = 16 * warp + (lane & 15);
+      const uint32_t chunk = (ks & 3) * 2 + (lane >> 4);
+      ldmatrix_x4(kbase + (ks >> 2) * HALF_BYTES + swz128(row, chunk), a);
+      mma_bf16_16816(c, a, qb[ks][0], qb[ks][1]);
+    }
+    const int pos_a = (tile_begin + i) * TILE + 16 * warp + g;  // rows g and g + 8
+    const bool va = pos_a < p.Sk, vb = (pos_a + 8) < p.Sk;
+    float s0 = va ? c[0] * p.scale_log2 : -INFINITY;
+    float s1 = va ? c[1] * p.scale_log2 : -INFINITY;
+    float s2 = vb ? c[2] * p.scale_log2 : -INFINITY;
+    float s3 = vb ? c[3] * p.scale_log2 : -INFINITY;
+    float mx0 = fmaxf(s0, s2), mx1 = fmaxf(s1, s3);
+#pragma unroll
+    for (int sh = 4; sh <= 16; sh <<= 1) {
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, sh));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, sh));
+    }
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    const float mu0 = (mn0 == -INFINITY) ? 0.f : mn0;
+    const float mu1 = (mn1 == -INFINITY) ? 0.f : mn1;
+    const float al0 = exp2f(m0 - mu0), al1 = exp2f(m1 - mu1);
+    const float p0 = exp2f(s0 - mu0), p1 = exp2f(s1 - mu1);
+    const float p2 = exp2f(s2 - mu0), p3 = exp2f(s3 - mu1);
+    m0 = mn0;
+    m1 = mn1;
+    l0 = l0 * al0 + p0 + p2;
+    l1 = l1 * al1 + p1 + p3;
+    const uint32_t pb0 = movmatrix_trans(pack_bf16(p0, p1));
+    const uint32_t pb1 = movmatrix_trans(pack_bf16(p2, p3));
+#pragma unroll
+    for (int dt = 0; dt < 8; ++dt) {
+      o[dt][0] *= al0;
+      o[dt][1] *= al1;
+      o[dt][2] *= al0;
+      o[dt][3] *= al1;
+      uint32_t a[4];
+      const uint32_t mat = lane >> 3;
+      const uint32_t row = 16 * warp + (lane & 7) + ((mat & 2) ? 8 : 0);
+      const uint32_t chunk = (dt & 3) * 2 + (mat & 1);
+      ldmatrix_x4_trans(vbase + (dt >> 2) * HALF_BYTES + swz128(row, chunk), a);
+      mma_bf16_16816(o[dt], a, pb0, pb1);
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty_bar(stage));
+    if (++stage == STAGES) {
+      stage = 0;
+      phase ^= 1u;
+    }
+  }
+  (void)ok;
+  // finish the per-warp row sums (lanes with equal t hold partial sums of the same heads)
+#pragma unroll
+  for (int sh = 4; sh <= 16; sh <<= 1) {
+    l0 += __shfl_xor_sync(0xffffffffu, l0, sh);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, sh);
+  }
+  // ---- merge the four warps through shared memory (the stage buffers are free now)
+  consumer_bar();
+  float* s_o = reinterpret_cast<float*>(smem_gen);                 // [4][8][128]
+  float* s_m = s_o + CONSUMERS * 8 * D;                            // [4][8]
+  float* s_l = s_m + CONSUMERS * 8;                                // [4][8]
+  if (g == 0) {
+    s_m[warp * 8 + 2 * t] = m0;
+    s_m[warp * 8 + 2 * t + 1] = m1;
+    s_l[warp * 8 + 2 * t] = l0;
+    s_l[warp * 8 + 2 * t + 1] = l1;
+  }
+#pragma unroll
+  for (int dt = 0; dt < 8; ++dt) {
+    float* base = s_o + (warp * 8) * D;
+    base[(2 * t) * D + 16 * dt + g] = o[dt][0];
+    base[(2 * t + 1) * D + 16 * dt + g] = o[dt][1];
+    base[(2 * t) * D + 16 * dt + g + 8] = o[dt][2];
+    base[(2 * t + 1) * D + 16 * dt + g + 8] = o[dt][3];
+  }
+  consumer_bar();
+  const int d = threadIdx.x;  // 0..127
+  for (int h = 0; h < nheads; ++h) {
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < CONSUMERS; ++w) m = fmaxf(m, s_m[w * 8 + h]);
+    const float mu = (m == -INFINITY) ? 0.f : m;
+    float acc = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < CONSUMERS; ++w) {
+      const float f = exp2f(s_m[w * 8 + h] - mu);
+      acc += f * s_o[(w * 8 + h) * D + d];
+      l += f * s_l[w * 8 + h];
+    }
+    const long long row = static_cast<long long>(b) * p.Hq + head0 + h;
+    if (p.splits == 1) {
+      p.O[row * D + d] = __float2bfloat16_rn(acc / l);
+    } else {
+      p.part_o[(row * p.splits + split) * D + d] = acc;
+      if (d == 0) {
+        p.part_ml[(row * p.splits + split) * 2] = m;
+        p.part_ml[(row * p.splits + split) * 2 + 1] = l;
+      }
+    }
+  }
+}
+
+// One CTA per (b, hq): merges the split partials and writes bf16.
+__global__ void merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                             __nv_bfloat16* __restrict__ O, int splits) {
+  const long long row = blockIdx.x;
+  const int d = threadIdx.x;
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(row * splits + s) * 2]);
+  const float mu = (m == -INFINITY) ? 0.f : m;
+  float acc = 0.f, l = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float f = exp2f(part_ml[(row * splits + s) * 2] - mu);
+    acc += f * part_o[(row * splits + s) * D + d];
+    l += f * part_ml[(row * splits + s) * 2 + 1];
+  }
+  O[row * D + d] = __float2bfloat16_rn(acc / l);
+}
+
+int choose_splits(int B, int Hkv, int groups_per_kv, int tiles_total) {
+  // Aim for about four waves of two CTAs per SM, at least 4 tiles per CTA.
+  const long long base = (long long)B * Hkv * groups_per_kv;
+  const long long target = (long long)sm_count() * 2 * 4;
+  long long s = (target + base - 1) / base;
+  s = std::min<long long>(s, std::max(1, tiles_total / 4));
+  s = std::max<long long>(1, std::min<long long>(s, MAX_SPLITS));
+  return (int)s;
+}
+
+size_t scratch_bytes(int B, int Hq, int splits) {
+  return (size_t)B * Hq * splits * (D + 2) * sizeof(float);
+}
+
+// K, V: [B, Hkv, Sk, D] bf16 device pointers; Q, O: [B, Hq, 1, D]. `scratch` must hold
+// scratch_bytes(B, Hq, splits) bytes when splits > 1.
+int launch(const void* Q, const void* K, const void* V, void* O, int B, int Hq, int Hkv, int Sk,
+           int Dh, float scale, int splits, void* scratch, cudaStream_t st) {
+  if (!Q || !K || !V || !O || B <= 0 || Hq <= 0 || Hkv <= 0 || Sk <= 0) {
+    set_last_error("attn_decode: null pointer or non-positive size");
+    return kBadArg;
+  }
+  if (Dh != D) {
+    set_last_error("attn_decode: head dimension must be %d (got %d)", D, Dh);
+    return kBadArg;
+  }
+  if (Hq % Hkv) {
+    set_last_error("attn_decode: Hq (%d) must be divisible by Hkv (%d)", Hq, Hkv);
+    return kBadArg;
+  }
+  if ((reinterpret_cast<uintptr_t>(K) & 15) || (reinterpret_cast<uintptr_t>(V) & 15) ||
+      (reinterpret_cast<uintptr_t>(Q) & 3)) {
+    set_last_error("attn_decode: K and V must be 16-byte aligned");
+    return kBadArg;
+  }
+  Params p{};
+  p.Q = static_cast<const __nv_bfloat16*>(Q);
+  p.O = static_cast<__nv_bfloat16*>(O);
+  p.B = B;
+  p.Hq = Hq;
+  p.Hkv = Hkv;
+  p.Sk = Sk;
+  p.G = Hq / Hkv;
+  p.groups_per_kv = (p.G + 7) / 8;
+  p.tiles_total = (Sk + TILE - 1) / TILE;
+  if (splits <= 0) splits = choose_splits(B, Hkv, p.groups_per_kv, p.tiles_total);
+  splits = std::min(splits, std::min(p.tiles_total, MAX_SPLITS));
+  p.tiles_per_split = (p.tiles_total + splits - 1) / splits;
+  splits = (p.tiles_total + p.tiles_per_split - 1) / p.tiles_per_split;  // no empty splits
+  p.splits = splits;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.err = device_err_word();
+  if (!p.err) return kDeviceFailed;
+  if (splits > 1) {
+    if (!scratch) {
+      set_last_error("attn_decode: %d splits need a scratch buffer", splits);
+      return kBadArg;
+    }
+    p.part_o = static_cast<float*>(scratch);
+    p.part_ml = p.part_o + (size_t)B * Hq * splits * D;
+  }
+  CUtensorMap tK, tV;
+  uint64_t dims[4] = {(uint64_t)D, (uint64_t)Sk, (uint64_t)Hkv, (uint64_t)B};
+  uint64_t str[3] = {(uint64_t)D * 2, (uint64_t)Sk * D * 2, (uint64_t)Hkv * Sk * D * 2};
+  uint32_t box[4] = {64, TILE, 1, 1};
+  if (!encode_tmap(&tK, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, K, dims, str, box,
+                   CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !encode_tmap(&tV, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, V, dims, str, box,
+                   CU_TENSOR_MAP_SWIZZLE_128B))
+    return kBadArg;
+  TSB_CUDA_OK(cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   SMEM_ALLOC));
+  dim3 grid(splits, Hkv * p.groups_per_kv, B);
+  decode_kernel<<<grid, THREADS, SMEM_ALLOC, st>>>(tK, tV, p);
+  TSB_CUDA_OK(cudaGetLastError());
+  note_launch();
+  if (splits > 1) {
+    merge_kernel<<<B * Hq, D, 0, st>>>(p.part_o, p.part_ml, p.O, splits);
+    TSB_CUDA_OK(cudaGetLastError());
+    note_launch();
+  }
+  return kOk;
+}
+
+}  // namespace attn_decode
+}  // namespace tsb
+
+using namespace tsb;
+
+extern "C" {
+
+int tessera_sm100_attn_decode_splits(int B, int Hq, int Hkv, int Sk) {
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Sk <= 0 || Hq % Hkv) return 1;
+  if (ensure_device()) return 1;
+  const int G = Hq / Hkv;
+  const int tiles = (Sk + attn_decode::TILE - 1) / attn_decode::TILE;
+  int s = attn_decode::choose_splits(B, Hkv, (G + 7) / 8, tiles);
+  s = std::min(s, std::min(tiles, attn_decode::MAX_SPLITS));
+  const int tps = (tiles + s - 1) / s;
+  return (tiles + tps - 1) / tps;
+}
+
+size_t tessera_sm100_attn_decode_scratch_bytes(int B, int Hq, int splits) {
+  return attn_decode::scratch_bytes(B, Hq, splits);
+}
+
+int tessera_sm100_attn_decode_device(const void* Q, const void* K, const void* V, void* O, int B,
+                                     int Hq, int Hkv, int Sk, int D, float scale, int splits,
+                                     void* scratch, void* stream) {
+  return attn_decode::launch(Q, K, V, O, B, Hq, Hkv, Sk, D, scale, splits, scratch,
+                             static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -157,6 +157,16 @@ int tessera_sm100_attn_decode_device(const void* Q, const void* K, const void* V
                                      int Hq, int Hkv, int Sk, int D, float scale, int splits,
                                      void* scratch, void* stream);
 
+/* ---- flash-attention forward (prefill) ----------------------------------------------------
+ * O = softmax(scale * Q K^T [+ bottom-right causal mask]) V with fp32 statistics:
+ * tessera.ops.flash_attn (python/tessera/__init__.py:1304-1356). Q,O [B,Hq,Sq,D], K,V [B,Hkv,Sk,D]
+ * bf16, D = 128, query head h reads KV head h / (Hq/Hkv) (python/tessera/nn/functional.py:349-356).
+ * Argument order follows the reference's flash-forward ABI (q,k,v,o,B,Hq,Hkv,Sq,Sk,D,scale,causal)
+ * (python/tessera/compiler/emit/nvidia_cuda.py:274), without its bias/window/softcap extras. */
+int tessera_sm100_flash_attn_fwd_device(const void* Q, const void* K, const void* V, void* O, int B,
+                                        int Hq, int Hkv, int Sq, int Sk, int D, float scale,
+                                        int causal, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,438 @@
+// Flash-attention forward (prefill) for sm_100a with tcgen05 MMA and TMEM accumulators.
+//
+//   O[b,h] = softmax(scale * Q[b,h] K[b,hk]^T + causal mask) V[b,hk],   hk = h / (H/Hkv)
+//
+// Semantics of tessera.ops.flash_attn (python/tessera/__init__.py:1304-1356): the causal mask is
+// bottom-right aligned (key j is visible to query i when j <= i + max(Sk - Sq, 0)); softmax
+// statistics are fp32. Head dimension 128, bf16 in / bf16 out.
+//
+// One CTA owns 256 query rows of one (b, h) as two 128-row tiles and walks the KV sequence in
+// blocks of 128. Ten warps:
+//   warps 0-3  softmax group for tile 0   (thread r owns row r: TMEM lane r)
+//   warps 4-7  softmax group for tile 1
+//   warp  8    MMA issuer (one lane) + TMEM owner
+//   warp  9    TMA producer (one lane)
+// TMEM (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each. P (bf16) overwrites the first
+// 64 columns of its S and is fed back as the A operand of the P.V MMA straight from TMEM.
+// The MMA warp alternates tiles (S0, S1, then per KV block PV0, S0', PV1, S1') so one tile's
+// softmax overlaps the other tile's MMAs. The running maximum is only raised (and O rescaled
+// in TMEM) when it grows by more than 2^8, which keeps exp2 arguments bounded while making the
+// rescale rare; the final O / l normalisation is exact regardless.
+#include <cuda_bf16.h>
+
+#include <algorithm>
+#include <cmath>
+
+#include "../../include/tessera_sm100.h"
+#include "device_ctx.h"
+#include "sm100_ptx.cuh"
+
+namespace tsb {
+namespace attn_prefill {
+
+constexpr int D = 128;
+constexpr int BQ = 128;    // rows per Q tile
+constexpr int BKV = 128;   // KV positions per block
+constexpr int TILE_BYTES = 128 * 128 * 2;  // any 128 x 128 bf16 tile = two 16 KB swizzled blocks
+constexpr int HALF_BYTES = TILE_BYTES / 2;
+constexpr int SMEM_Q_OFF = 0;                       // Q0, Q1 (reused for the O store)
+constexpr int SMEM_K_OFF = 2 * TILE_BYTES;          // K stages 0, 1
+constexpr int SMEM_V_OFF = 4 * TILE_BYTES;          // V stages 0, 1
+constexpr int SMEM_BAR_OFF = 6 * TILE_BYTES;
+constexpr int SMEM_BYTES = SMEM_BAR_OFF + 256;
+constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;
+constexpr int THREADS = 320;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+struct Params {
+  int B, H, Hkv, Sq, Sk;
+  int causal;
+  float scale_log2;
+  int* err;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+               const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+               const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t sQ = smem_base + SMEM_Q_OFF;
+  const uint32_t sK = smem_base + SMEM_K_OFF;
+  const uint32_t sV = smem_base + SMEM_V_OFF;
+  const uint32_t bars = smem_base + SMEM_BAR_OFF;
+  // barriers: q_full[2] k_full[2] k_empty[2] v_full[2] v_empty[2] s_full[2] p_full[2] o_full[2]
+  auto q_full = [&](int i) { return bars + 8u * (0 + i); };
+  auto k_full = [&](int s) { return bars + 8u * (2 + s); };
+  auto k_empty = [&](int s) { return bars + 8u * (4 + s); };
+  auto v_full = [&](int s) { return bars + 8u * (6 + s); };
+  auto v_empty = [&](int s) { return bars + 8u * (8 + s); };
+  auto s_full = [&](int i) { return bars + 8u * (10 + i); };
+  auto p_full = [&](int i) { return bars + 8u * (12 + i); };
+  auto o_full = [&](int i) { return bars + 8u * (14 + i); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + SMEM_BAR_OFF + 128);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + SMEM_BAR_OFF + 132);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int qpair = gridDim.x - 1 - blockIdx.x;  // heaviest (latest) query rows first
+  const int h = blockIdx.y;
+  const int b = blockIdx.z;
+  const int hk = h / (p.H / p.Hkv);
+  const int q_base = qpair * 2 * BQ;
+  const int shift = p.causal ? max(p.Sk - p.Sq, 0) : 0;
+  const int nblk_total = (p.Sk + BKV - 1) / BKV;
+  int nblk[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int qi0 = q_base + i * BQ;
+    if (qi0 >= p.Sq) {
+      nblk[i] = 0;
+    } else if (p.causal) {
+      const int last_row = min(qi0 + BQ - 1, p.Sq - 1);
+      nblk[i] = min(nblk_total, (last_row + shift) / BKV + 1);
+    } else {
+      nblk[i] = nblk_total;
+    }
+  }
+  const int n_iter = max(nblk[0], nblk[1]);
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(q_full(i), 1);
+      mbar_init(k_full(i), 1);
+      mbar_init(k_empty(i), 1);
+      mbar_init(v_full(i), 1);
+      mbar_init(v_empty(i), 1);
+      mbar_init(s_full(i), 1);
+      mbar_init(p_full(i), 128);
+      mbar_init(o_full(i), 1);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 8) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // TMEM columns
+  auto tS = [&](int i) { return tmem_base + static_cast<uint32_t>(i * 128); };
+  auto tO = [&](int i) { return tmem_base + static_cast<uint32_t>(256 + i * 128); };
+
+  if (warp == 9) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      for (int i = 0; i < 2; ++i) {
+        if (nblk[i] == 0) continue;
+        mbar_arrive_expect_tx(q_full(i), TILE_BYTES);
+        tma_load_4d(sQ + i * TILE_BYTES, &tmQ, q_full(i), 0, q_base + i * BQ, h, b);
+        tma_load_4d(sQ + i * TILE_BYTES + HALF_BYTES, &tmQ, q_full(i), 64, q_base + i * BQ, h, b);
+      }
+      for (int j = 0; j < n_iter; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(k_empty(st), ph ^ 1u, abort_flag, p.err, kErrWaitEmpty, j)) break;
+        mbar_arrive_expect_tx(k_full(st), TILE_BYTES);
+        tma_load_4d(sK + st * TILE_BYTES, &tmK, k_full(st), 0, j * BKV, hk, b);
+        tma_load_4d(sK + st * TILE_BYTES + HALF_BYTES, &tmK, k_full(st), 64, j * BKV, hk, b);
+        if (!mbar_wait(v_empty(st), ph ^ 1u, abort_flag, p.err, kErrWaitEmpty, 1000 + j)) break;
+        mbar_arrive_expect_tx(v_full(st), TILE_BYTES);
+        tma_load_4d(sV + st * TILE_BYTES, &tmV, v_full(st), 0, j * BKV, hk, b);
+        tma_load_4d(sV + st * TILE_BYTES + HALF_BYTES, &tmV, v_full(st), 64, j * BKV, hk, b);
+      }
+    }
+  } else if (warp == 8) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_f16(true, false, false, BQ, BKV);  // Q K^T, both K-major
+      const uint32_t idesc_pv = make_idesc_f16(true, false, true, BQ, D);    // P (TMEM) V (N-major)
+      auto issue_s = [&](int i, int kst) {
+        const uint32_t a_base = sQ + i * TILE_BYTES;
+        const uint32_t b_base = sK + kst * TILE_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
+          umma_f16_ss(tS(i), make_smem_desc(a_base + off, 16, 1024),
+                      make_smem_desc(b_base + off, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+        }
+        umma_commit(s_full(i));
+      };
+      auto issue_pv = [&](int i, int vst, bool accumulate) {
+        const uint32_t b_base = sV + vst * TILE_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < BKV / 16; ++ks) {
+          // A: P rows in TMEM lanes, 16 bf16 of K per 8 columns. B: V[kv][d], 16 kv rows = 2048 B;
+          // the two 64-wide d blocks are HALF_BYTES apart.
+          umma_f16_ts(tO(i), tS(i) + 8u * ks, make_smem_desc(b_base + ks * 2048, HALF_BYTES, 1024),
+                      idesc_pv, (accumulate || ks > 0) ? 1u : 0u);
+        }
+      };
+      bool ok = true;
+      for (int i = 0; i < 2 && ok; ++i)
+        if (nblk[i] > 0) ok = mbar_wait(q_full(i), 0, abort_flag, p.err, kErrWaitFull, 2000 + i);
+      if (ok && n_iter > 0) {
+        ok = mbar_wait(k_full(0), 0, abort_flag, p.err, kErrWaitFull, 0);
+        if (ok) {
+          tc_fence_after();
+          if (nblk[0] > 0) issue_s(0, 0);
+          if (nblk[1] > 0) issue_s(1, 0);
+          umma_commit(k_empty(0));
+        }
+      }
+      for (int j = 0; j < n_iter && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const int nst = (j + 1) & 1;
+        const uint32_t nph = ((j + 1) >> 1) & 1;
+        const bool has_next = (j + 1) < n_iter;
+        if (!(ok = mbar_wait(v_full(st), ph, abort_flag, p.err, kErrWaitFull, 3000 + j))) break;
+        bool next_k_ready = false;
+        for (int i = 0; i < 2 && ok; ++i) {
+          if (j >= nblk[i]) continue;
+          if (!(ok = mbar_wait(p_full(i), j & 1, abort_flag, p.err, kErrWaitOther, 4000 + j))) break;
+          tc_fence_after();
+          issue_pv(i, st, j > 0);
+          if (j == nblk[i] - 1) umma_commit(o_full(i));
+          if (j + 1 < nblk[i]) {
+            if (!next_k_ready) {
+              if (!(ok = mbar_wait(k_full(nst), nph, abort_flag, p.err, kErrWaitFull, 5000 + j))) break;
+              tc_fence_after();
+              next_k_ready = true;
+            }
+            issue_s(i, nst);
+          }
+        }
+        if (!ok) break;
+        umma_commit(v_empty(st));
+        if (has_next) umma_commit(k_empty(nst));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax groups
+    const int i = warp >> 2;                    // tile
+    const int r = (warp & 3) * 32 + lane;       // row inside the tile == TMEM lane
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const int qi0 = q_base + i * BQ;
+    const int row_q = qi0 + r;
+    const int kv_limit = p.causal ? min(row_q + shift, p.Sk - 1) : (p.Sk - 1);  // last visible key
+    float m_used = -INFINITY;
+    float l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nblk[i] && ok; ++j) {
+      if (!(ok = mbar_wait(s_full(i), j & 1, abort_flag, p.err, kErrWaitTmemFull, j))) break;
+      tc_fence_after();
+      const int kv0 = j * BKV;
+      const bool need_mask = (kv0 + BKV - 1 > qi0 + shift && p.causal) || (kv0 + BKV > p.Sk);
+      const uint32_t t_s = tS(i) + lane_base;
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(t_s + c * 32, v);
+        tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+          for (int k = 0; k < 32; ++k)
+            mx = fmaxf(mx, (kv0 + c * 32 + k <= kv_limit) ? __uint_as_float(v[k]) : -INFINITY);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) mx = fmaxf(mx, __uint_as_float(v[k]));
+        }
+      }
+      const float m_new = fmaxf(m_used, mx * p.scale_log2);
+      const bool need = m_new > m_used + kRescaleThreshold;
+      if (j == 0) {
+        m_used = m_new;
+      } else if (__any_sync(0xffffffffu, need)) {
+        const float alpha = need ? ex2(m_used - m_new) : 1.0f;
+        if (need) {
+          m_used = m_new;
+          l *= alpha;
+        }
+        const uint32_t t_o = tO(i) + lane_base;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(t_o + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int k = 0; k < 32; ++k) v[k] = __float_as_uint(__uint_as_float(v[k]) * alpha);
+          tmem_st_32x32b_x32(t_o + c * 32, v);
+        }
+        tmem_st_wait();
+      }
+      // pass 2: P = exp2(S * scale - m), row sum, bf16 P back into the first 64 columns of S
+      const float neg_m = -m_used;
+#pragma unroll 1
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t pk[32];
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(t_s + hh * 64 + q * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int k = 0; k < 32; k += 2) {
+            float e0 = ex2(fmaf(__uint_as_float(v[k]), p.scale_log2, neg_m));
+            float e1 = ex2(fmaf(__uint_as_float(v[k + 1]), p.scale_log2, neg_m));
+            if (need_mask) {
+              const int kv = kv0 + hh * 64 + q * 32 + k;
+              if (kv > kv_limit) e0 = 0.f;
+              if (kv + 1 > kv_limit) e1 = 0.f;
+            }
+            l += e0 + e1;
+            pk[q * 16 + (k >> 1)] = pack_bf16(e0, e1);
+          }
+        }
+        tmem_st_32x32b_x32(t_s + hh * 32, pk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(p_full(i));
+    }
+    // ---- epilogue: O / l -> bf16 -> swizzled smem (the Q tile's buffer) -> TMA store
+    if (ok && nblk[i] > 0) ok = mbar_wait(o_full(i), 0, abort_flag, p.err, kErrWaitTmemFull, 9000);
+    if (nblk[i] > 0) {
+      tc_fence_after();
+      const float inv = 1.0f / l;
+      const uint32_t t_o = tO(i) + lane_base;
+      const uint32_t obuf = sQ + i * TILE_BYTES;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(t_o + c * 32, v);
+        tmem_ld_wait();
+        const uint32_t blk = obuf + (c >> 1) * HALF_BYTES;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            w[e] = pack_bf16(__uint_as_float(v[ch * 8 + 2 * e]) * inv,
+                             __uint_as_float(v[ch * 8 + 2 * e + 1]) * inv);
+          const uint32_t addr = blk + swz128(r, (c & 1) * 4 + ch);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]),
+                       "r"(w[2]), "r"(w[3])
+                       : "memory");
+        }
+      }
+      fence_proxy_async_smem();
+      asm volatile("bar.sync %0, 128;" ::"r"(1 + i) : "memory");
+      if (r == 0 && ok) {
+        tma_store_4d(&tmO, obuf, 0, qi0, h, b);
+        tma_store_4d(&tmO, obuf + HALF_BYTES, 64, qi0, h, b);
+        tma_store_commit();
+        tma_store_wait<0>();
+      }
+    }
+  }
+
+  // -------------------------------------------------------------------- tear-down
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int k = 0; k < 64; ++k) __nanosleep(10000);
+    __syncthreads();
+  }
+  if (warp == 8) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+int launch(const void* Q, const void* K, const void* V, void* O, int B, int H, int Hkv, int Sq,
+           int Sk, int Dh, float scale, int causal, cudaStream_t st) {
+  if (!Q || !K || !V || !O || B <= 0 || H <= 0 || Hkv <= 0 || Sq <= 0 || Sk <= 0) {
+    set_last_error("attn_prefill: null pointer or non-positive size");
+    return kBadArg;
+  }
+  if (Dh != D) {
+    set_last_error("attn_prefill: head dimension must be %d (got %d)", D, Dh);
+    return kBadArg;
+  }
+  if (H % Hkv) {
+    set_last_error("attn_prefill: H (%d) must be divisible by Hkv (%d)", H, Hkv);
+    return kBadArg;
+  }
+  if (!(scale > 0.f)) {
+    set_last_error("attn_prefill: scale must be positive");
+    return kBadArg;
+  }
+  for (const void* ptr : {Q, K, V, (const void*)O})
+    if (reinterpret_cast<uintptr_t>(ptr) & 15) {
+      set_last_error("attn_prefill: pointers must be 16-byte aligned");
+      return kBadArg;
+    }
+  CUtensorMap tQ, tK, tV, tO;
+  uint32_t box[4] = {64, 128, 1, 1};
+  {
+    uint64_t dims[4] = {(uint64_t)D, (uint64_t)Sq, (uint64_t)H, (uint64_t)B};
+    uint64_t str[3] = {(uint64_t)D * 2, (uint64_t)Sq * D * 2, (uint64_t)H * Sq * D * 2};
+    if (!encode_tmap(&tQ, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, Q, dims, str, box,
+                     CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !encode_tmap(&tO, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, O, dims, str, box,
+                     CU_TENSOR_MAP_SWIZZLE_128B))
+      return kBadArg;
+  }
+  {
+    uint64_t dims[4] = {(uint64_t)D, (uint64_t)Sk, (uint64_t)Hkv, (uint64_t)B};
+    uint64_t str[3] = {(uint64_t)D * 2, (uint64_t)Sk * D * 2, (uint64_t)Hkv * Sk * D * 2};
+    if (!encode_tmap(&tK, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, K, dims, str, box,
+                     CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !encode_tmap(&tV, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, V, dims, str, box,
+                     CU_TENSOR_MAP_SWIZZLE_128B))
+      return kBadArg;
+  }
+  Params p{};
+  p.B = B;
+  p.H = H;
+  p.Hkv = Hkv;
+  p.Sq = Sq;
+  p.Sk = Sk;
+  p.causal = causal ? 1 : 0;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.err = device_err_word();
+  if (!p.err) return kDeviceFailed;
+  TSB_CUDA_OK(cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   SMEM_ALLOC));
+  dim3 grid((Sq + 2 * BQ - 1) / (2 * BQ), H, B);
+  prefill_kernel<<<grid, THREADS, SMEM_ALLOC, st>>>(tQ, tK, tV, tO, p);
+  TSB_CUDA_OK(cudaGetLastError());
+  note_launch();
+  return kOk;
+}
+
+}  // namespace attn_prefill
+}  // namespace tsb
+
+using namespace tsb;
+
+extern "C" {
+
+int tessera_sm100_flash_attn_fwd_device(const void* Q, const void* K, const void* V, void* O, int B,
+                                        int Hq, int Hkv, int Sq, int Sk, int D, float scale,
+                                        int causal, void* stream) {
+  return attn_prefill::launch(Q, K, V, O, B, Hq, Hkv, Sq, Sk, D, scale, causal,
+                              static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

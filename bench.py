@@ -1,0 +1,482 @@
+"""Benchmark of the dense-contraction hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload ...]
+
+Headline (one JSON line on stdout, rank 0): dense bf16 GEMM M=N=K=8192, fp32 accumulate, bf16
+output. With N > 1 GPUs the GEMM is column-parallel (W split on N, A replicated) and followed by an
+all-gather of Y, total work fixed ("strong" scaling). The same line carries, under "workloads",
+the other configurations of the hot path (causal prefill attention, GQA decode attention, the MoE
+layer), each with its own roofline entry.
+
+A step is one pass over synthetic inputs that are resident in HBM before the timed region. Every
+timed step is preceded (outside its CUDA-event bracket) by an L2 flush. Times are CUDA events on
+the launching stream; with several ranks the per-step maximum over ranks is what counts.
+``e2e`` is the same GEMM through the public ``tessera_b200.ops.gemm`` call with pinned host
+buffers, host<->device copies inside the timed region.
+
+``--impl reference`` times the reference's CPU implementation of the same configuration (its
+numpy path, restated in oracle/) on the host cores of this machine.
+
+Multi-GPU runs are launched as ``python -m torch.distributed.run --nproc-per-node N bench.py
+--gpus N ...``; torch.distributed (gloo) is used for rank plumbing only.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
+# summarised under profiles/; None where no capture exists yet.
+NCU_TRAFFIC_BYTES = {"gemm_8192": None, "attn_prefill": None, "attn_decode": None, "moe": None}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return {k: float(d[k]) for k in FALLBACK_PEAKS}, "measured"
+    except Exception:
+        return dict(FALLBACK_PEAKS), "fallback"
+
+
+# ------------------------------------------------------------------------------ clocks sampling
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.rows, self.proc = gpu_index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-i",
+                 str(self.gpu), "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip())
+
+    def mark(self):
+        return len(self.rows)
+
+    def stop(self):
+        if self.proc:
+            self.proc.terminate()
+
+    def summary(self, lo: int = 0, hi=None):
+        sm, mx, reasons = [], [], set()
+        for row in self.rows[lo:hi]:
+            parts = [p.strip() for p in row.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                  "sw_power_cap"), parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------ rank plumbing
+class Ranks:
+    def __init__(self, n_gpus: int):
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        self.dist = None
+        if self.world > 1:
+            import torch.distributed as dist
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group("gloo")
+            self.dist = dist
+
+    def barrier(self):
+        if self.dist:
+            self.dist.barrier()
+
+    def gather(self, obj):
+        if not self.dist:
+            return [obj]
+        out = [None] * self.world
+        self.dist.all_gather_object(out, obj)
+        return out
+
+    def bcast(self, obj):
+        if not self.dist:
+            return obj
+        box = [obj]
+        self.dist.broadcast_object_list(box, src=0)
+        return box[0]
+
+    def close(self):
+        if self.dist:
+            self.dist.barrier()
+            self.dist.destroy_process_group()
+
+
+def timed_steps(ranks, device, fn, steps, warmup, flush=True):
+    """W warm-ups, then K steps; each step bracketed by CUDA events on the launching stream, an
+    L2 flush before every bracket. Returns per-step times (ms) as the max over ranks."""
+    for _ in range(warmup):
+        fn()
+    device.synchronize()
+    ranks.barrier()
+    ev = [(device.Event(), device.Event()) for _ in range(steps)]
+    for a, b in ev:
+        if flush:
+            device.flush_l2()
+        a.record()
+        fn()
+        b.record()
+    device.synchronize()
+    ranks.barrier()
+    mine = [a.elapsed_ms(b) for a, b in ev]
+    device.check_device_error("bench")
+    allr = ranks.gather(mine)
+    return [max(r[i] for r in allr) for i in range(steps)]
+
+
+def tiled_normal(rng, shape, tile_axis_len, scale, dtype):
+    """N(0,1)*scale values; drawn for `tile_axis_len` entries of axis 0 and repeated along it
+    (same distribution, a fraction of the host time)."""
+    base = (rng.standard_normal((tile_axis_len,) + tuple(shape[1:]), dtype=np.float32) * scale).astype(dtype)
+    reps = -(-shape[0] // tile_axis_len)
+    return np.concatenate([np.roll(base, r, axis=-1) for r in range(reps)], axis=0)[:shape[0]]
+
+
+# ------------------------------------------------------------------------------ workloads
+def bench_gemm(ranks, args, peaks, peak_kind, sampler):
+    import tessera_b200 as tessera
+    from tessera_b200 import _lib, collectives, device, parallel
+    from tessera_b200.device import DeviceArray, PinnedArray, bfloat16
+    n = 8192
+    W = ranks.world
+    rng = np.random.default_rng(1002)
+    A = (rng.standard_normal((n, n), dtype=np.float32) / np.sqrt(n)).astype(bfloat16)
+    B = (rng.standard_normal((n, n), dtype=np.float32) / np.sqrt(n)).astype(bfloat16)
+    c0, nb = parallel.tp_column_range(n, W, ranks.rank)
+    dA = DeviceArray.from_host(A)
+    dB = DeviceArray.from_host(B)            # full W on every rank; a rank reads its column block
+    dY = DeviceArray.zeros((n, n), bfloat16)
+    comm = None
+    stage = gathered = None
+    if W > 1:
+        uid = ranks.bcast(collectives.Communicator.unique_id() if ranks.rank == 0 else None)
+        comm = collectives.Communicator.from_unique_id(uid, W, ranks.rank)
+        stage = DeviceArray((n, nb), bfloat16)
+        gathered = DeviceArray((W, n, nb), bfloat16)
+
+    def gemm_only():
+        if W == 1:
+            _lib.call("tessera_sm100_gemm_device", dA.ptr, dB.ptr, dY.ptr, 1, n, n, n, _lib.BF16,
+                      _lib.BF16, None)
+        else:
+            _lib.call("tessera_sm100_gemm_strided_device", dA.ptr, dB.ptr + c0 * 2, stage.ptr, 1, n, nb,
+                      n, n, n, nb, 0, 0, 0, _lib.BF16, _lib.BF16, None)
+
+    def step():
+        gemm_only()
+        if W > 1:
+            comm.all_gather(stage, gathered)
+            for r in range(W):   # [W, M, nb] -> row-major Y[M, N]
+                _lib.call("tessera_sm100_device_copy_2d", dY.ptr + r * nb * 2, n * 2,
+                          gathered.ptr + r * n * nb * 2, nb * 2, nb * 2, n, None)
+
+    l0 = device.launch_count()
+    m0 = sampler.mark()
+    times = timed_steps(ranks, device, step, args.steps, args.warmup)
+    m1 = sampler.mark()
+    launches = (device.launch_count() - l0) * args.steps // (args.steps + args.warmup)
+    kernel_times = timed_steps(ranks, device, gemm_only, max(3, args.steps // 2), 1)
+    flops = 2.0 * n * n * n
+    ms = statistics.mean(times)
+    k_ms = statistics.mean(kernel_times)
+    achieved = flops / W / k_ms / 1e9        # per-GPU kernel TFLOP/s
+    # correctness spot check of what was just timed
+    rows = [0, 4097, n - 1]
+    got = dY.download()[rows].astype(np.float32)
+    ref = A[rows].astype(np.float32) @ B.astype(np.float32)
+    rel = float(np.abs(got - ref).max() / np.abs(ref).max())
+
+    # end to end through the public op with pinned host buffers
+    e2e = None
+    try:
+        pA, pB = PinnedArray((n, n), bfloat16), PinnedArray((n, nb), bfloat16)
+        pY = PinnedArray((n, nb), bfloat16)
+        pA.array[...] = A
+        pB.array[...] = B[:, c0:c0 + nb]
+        e2e_steps = max(2, min(args.steps, 5))
+        tessera.ops.gemm(pA.array, pB.array, out_dtype=bfloat16, out=pY.array)
+        ranks.barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            tessera.ops.gemm(pA.array, pB.array, out_dtype=bfloat16, out=pY.array)
+        device.synchronize()
+        dt = (time.perf_counter() - t0) / e2e_steps
+        dt = max(ranks.gather(dt))
+        e2e = {"value": flops / dt / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": int(pA.nbytes + pB.nbytes),
+               "d2h_bytes_per_step": int(pY.nbytes), "ms_per_step": dt * 1e3,
+               "api": "tessera_b200.ops.gemm(host, host) -> tessera_sm100_gemm",
+               "note": "per rank: upload A and its column block of W, GEMM, download its block of Y"}
+    except Exception as exc:  # keep the headline even if pinned allocation fails
+        e2e = {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+               "error": str(exc)}
+    if comm:
+        comm.close()
+    return {
+        "value": flops / ms / 1e9, "ms_per_step": ms, "gpu_launches": int(launches * W),
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"],
+                     "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
+                     "traffic": NCU_TRAFFIC_BYTES["gemm_8192"], "peak_kind": f"burst cuBLAS bf16, of {peak_kind}",
+                     "kernel_ms": k_ms, "kernel": "gemm_kernel<bf16,plain> (tcgen05 128x256x64, 4-stage TMA)"},
+        "e2e": e2e, "check_max_rel_err": rel, "clock_marks": (m0, m1),
+    }
+
+
+def bench_attn_prefill(ranks, args, peaks, peak_kind):
+    import ctypes
+    from tessera_b200 import _lib, device
+    from tessera_b200.device import DeviceArray, bfloat16
+    B, H, S, D = 8, 32, 4096, 128
+    W = ranks.world
+    Hl = H // W
+    rng = np.random.default_rng(1003 + ranks.rank)
+    q, k, v = (tiled_normal(rng, (B, Hl, S, D), 2, 1.0, bfloat16) for _ in range(3))
+    dq, dk, dv = (DeviceArray.from_host(t) for t in (q, k, v))
+    do = DeviceArray.zeros((B, Hl, S, D), bfloat16)
+    scale = ctypes.c_float(1.0 / np.sqrt(D))
+    fn = lambda: _lib.call("tessera_sm100_flash_attn_fwd_device", dq.ptr, dk.ptr, dv.ptr, do.ptr, B, Hl,
+                           Hl, S, S, D, scale, 1, None)
+    times = timed_steps(ranks, device, fn, args.steps, args.warmup)
+    ms = statistics.mean(times)
+    flops = 4.0 * B * H * S * S * D / 2
+    ach = flops / W / ms / 1e9
+    return {"metric": "causal flash-attention forward TFLOP/s", "value": flops / ms / 1e9, "unit": "TFLOP/s",
+            "ms_per_step": ms, "config": f"B={B} H={H} S={S} D={D} bf16 causal, heads sharded /{W}",
+            "flops_convention": "4*B*H*S^2*D/2",
+            "roofline": {"bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": ach / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC_BYTES["attn_prefill"],
+                         "peak_kind": f"burst cuBLAS bf16, of {peak_kind}"}}
+
+
+def bench_attn_decode(ranks, args, peaks, peak_kind):
+    import ctypes
+    from tessera_b200 import _lib, device
+    from tessera_b200.device import DeviceArray, bfloat16
+    B, Hq, Hkv, S, D = 64, 32, 8, 8192, 128
+    W = ranks.world
+    Bl = B // W
+    rng = np.random.default_rng(1004 + ranks.rank)
+    q = rng.standard_normal((Bl, Hq, 1, D), dtype=np.float32).astype(bfloat16)
+    k = tiled_normal(rng, (Bl, Hkv, S, D), 2, 1.0, bfloat16)
+    v = tiled_normal(rng, (Bl, Hkv, S, D), 2, 1.0, bfloat16)
+    dq, dk, dv = (DeviceArray.from_host(t) for t in (q, k, v))
+    do = DeviceArray.zeros((Bl, Hq, 1, D), bfloat16)
+    lib = _lib.load()
+    ns = lib.tessera_sm100_attn_decode_splits(Bl, Hq, Hkv, S)
+    scr = DeviceArray((max(1, lib.tessera_sm100_attn_decode_scratch_bytes(Bl, Hq, ns)),), np.uint8)
+    scale = ctypes.c_float(1.0 / np.sqrt(D))
+    fn = lambda: _lib.call("tessera_sm100_attn_decode_device", dq.ptr, dk.ptr, dv.ptr, do.ptr, Bl, Hq, Hkv,
+                           S, D, scale, ns, scr.ptr, None)
+    times = timed_steps(ranks, device, fn, args.steps, args.warmup)
+    ms = statistics.mean(times)
+    nbytes = 2.0 * B * Hkv * S * D * 2
+    ach = nbytes / W / ms / 1e6
+    return {"metric": "GQA decode attention GB/s (K+V bytes)", "value": nbytes / ms / 1e6, "unit": "GB/s",
+            "ms_per_step": ms, "config": f"batch={B} Hq={Hq} Hkv={Hkv} KV={S} D={D} bf16, batch sharded /{W}",
+            "splits": ns,
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": ach / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES["attn_decode"],
+                         "peak_kind": f"copy bandwidth, of {peak_kind}"}}
+
+
+def bench_moe(ranks, args, peaks, peak_kind):
+    from tessera_b200 import _lib, collectives, device, parallel
+    from tessera_b200.device import DeviceArray, bfloat16
+    T, H, F, E, k = 8192, 4096, 14336, 8, 2
+    W = ranks.world
+    rng = np.random.default_rng(1005)
+    x = rng.standard_normal((T, H), dtype=np.float32).astype(bfloat16)
+    logits = rng.standard_normal((T, E), dtype=np.float32)
+    Ep = E // W
+    rngw = np.random.default_rng(2005 + ranks.rank)
+    wg = tiled_normal(rngw, (Ep, H, F), 1, 1 / np.sqrt(H), bfloat16)
+    wu = tiled_normal(rngw, (Ep, H, F), 1, 1 / np.sqrt(H), bfloat16)
+    wd = tiled_normal(rngw, (Ep, F, H), 1, 1 / np.sqrt(F), bfloat16)
+    dwg, dwu, dwd = (DeviceArray.from_host(t) for t in (wg, wu, wd))
+    flops = 3 * 2.0 * T * k * H * F
+    if W == 1:
+        dx, dl = DeviceArray.from_host(x), DeviceArray.from_host(logits)
+        out = DeviceArray.zeros((T, H), bfloat16)
+        ws = DeviceArray((_lib.load().tessera_sm100_moe_workspace_bytes(T, H, F, E, k),), np.uint8)
+        fn = lambda: _lib.call("tessera_sm100_moe_layer_device", dx.ptr, dl.ptr, dwg.ptr, dwu.ptr, dwd.ptr,
+                               out.ptr, T, H, F, E, k, 1, -1, _lib.BF16, _lib.BF16, ws.ptr, None)
+        comm = None
+    else:
+        uid = ranks.bcast(collectives.Communicator.unique_id() if ranks.rank == 0 else None)
+        comm = collectives.Communicator.from_unique_id(uid, W, ranks.rank)
+        Tl = T // W
+        sl = slice(ranks.rank * Tl, (ranks.rank + 1) * Tl)
+        dxl = DeviceArray.from_host(x[sl])
+        ll = np.ascontiguousarray(logits[sl])
+        moe = parallel.ExpertParallelMoE(E, k, parallel.NcclTransport(comm, ranks.gather),
+                                         parallel.GpuMoeBackend(dwg, dwu, dwd))
+        fn = lambda: moe.forward(dxl, ll)
+    times = timed_steps(ranks, device, fn, max(2, args.steps // 2), min(args.warmup, 3))
+    if comm:
+        comm.close()
+    ms = statistics.mean(times)
+    ach = flops / W / ms / 1e9
+    return {"metric": "MoE FFN layer TFLOP/s (routed slots, unpadded)", "value": flops / ms / 1e9,
+            "unit": "TFLOP/s", "ms_per_step": ms,
+            "config": f"T={T} H={H} F={F} E={E} top-{k} bf16, " + ("single GPU" if W == 1 else f"expert-parallel /{W}, ragged all-to-all"),
+            "roofline": {"bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops_sustained"],
+                         "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops_sustained"],
+                         "traffic": NCU_TRAFFIC_BYTES["moe"],
+                         "peak_kind": f"sustained cuBLAS bf16 (two multi-ms GEMMs per step), of {peak_kind}"}}
+
+
+# ------------------------------------------------------------------------------ CPU baseline
+def cpu_gemm_baseline(target_seconds: float = 10.0, max_reps: int = 10):
+    from oracle import tessera_oracle as orc
+    inp = orc.make_inputs("gemm_bf16")
+    A, B = inp["A"].astype(np.float32), inp["B"].astype(np.float32)
+    t0 = time.perf_counter()
+    orc.gemm(A, B)
+    first = time.perf_counter() - t0
+    reps = int(min(max_reps, max(1, round(target_seconds / max(first, 1e-3)))))
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        orc.gemm(A, B)
+    dt = (time.perf_counter() - t0) / reps
+    flops = 2.0 * 8192 ** 3
+    return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"{reps} x full 8192^3 fp32 matmul of bf16-rounded operands (numpy, all host threads), "
+                      f"{dt:.2f} s each", "seconds_per_step": dt}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import tessera_oracle as orc
+    inp = orc.make_inputs("gemm_bf16")
+    A, B = inp["A"].astype(np.float32), inp["B"].astype(np.float32)
+    for _ in range(args.warmup):
+        orc.gemm(A, B)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        orc.gemm(A, B)
+    dt = (time.perf_counter() - t0) / args.steps
+    val = 2.0 * 8192 ** 3 / dt / 1e12
+    line = {"impl": "reference", "metric": "bf16 GEMM TFLOP/s (M=N=K=8192)", "value": val, "unit": "TFLOP/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": "gemm_bf16_8192: A[8192,8192] x B[8192,8192], bf16 operands, fp32 accumulate"},
+            "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+                             "sample": "each step = the full 8192^3 product: the reference's tessera.ops.gemm "
+                                       "(np.matmul) on fp32 arrays holding bf16 values, all host threads"},
+            "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------ main
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="all", choices=["all", "gemm", "attn_prefill", "attn_decode", "moe"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", "29541", os.path.abspath(__file__)] + sys.argv[1:]
+        sys.exit(subprocess.call(cmd))
+
+    ranks = Ranks(args.gpus)
+    from tessera_b200 import device
+    device.set_device(ranks.local_rank)
+    peaks, peak_kind = load_peaks()
+    sampler = ClockSampler(ranks.local_rank)
+    if ranks.rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+
+    g = bench_gemm(ranks, args, peaks, peak_kind, sampler)
+    extras = {}
+    if args.workload in ("all", "attn_prefill", "attn_decode", "moe"):
+        for name, fn in (("attn_prefill", bench_attn_prefill), ("attn_decode", bench_attn_decode),
+                         ("moe", bench_moe)):
+            if args.workload not in ("all", name):
+                continue
+            try:
+                extras[name] = fn(ranks, args, peaks, peak_kind)
+            except Exception as exc:
+                extras[name] = {"error": f"{type(exc).__name__}: {exc}"}
+                ranks.barrier() if False else None
+    clocks = sampler.summary(*g.pop("clock_marks")) if ranks.rank == 0 else None
+    sampler.stop()
+
+    cpu = None
+    if ranks.rank == 0 and ranks.world == 1 and not args.no_cpu_baseline:
+        cpu = cpu_gemm_baseline()
+
+    if ranks.rank == 0:
+        W = ranks.world
+        line = {
+            "metric": "bf16 GEMM TFLOP/s (M=N=K=8192)", "value": g["value"], "unit": "TFLOP/s",
+            "n_gpus": W, "steps": args.steps, "warmup": args.warmup, "ms_per_step": g["ms_per_step"],
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (seeded N(0,1)/sqrt(K) operands)",
+            "config": {"workload": "gemm_bf16_8192: A[8192,8192] x B[8192,8192] -> Y bf16, fp32 accumulate",
+                       "parallelism": "single GPU" if W == 1 else f"column-parallel tp{W}: W split on N, "
+                                      f"NCCL all-gather of Y + strided copies into row-major Y",
+                       "l2": "L2 flushed (256 MiB write) before every timed step, outside the event bracket",
+                       "timing": "CUDA events per step on the launching stream, max over ranks, mean of steps"},
+            "roofline": g["roofline"], "e2e": g["e2e"], "gpu_launches": g["gpu_launches"],
+            "clocks": clocks, "check_max_rel_err": g["check_max_rel_err"], "workloads": extras,
+        }
+        if cpu:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    ranks.close()
+
+
+if __name__ == "__main__":
+    main()

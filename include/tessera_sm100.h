@@ -24,6 +24,8 @@ extern "C" {
 #define TESSERA_SM100_F32 0
 #define TESSERA_SM100_BF16 1
 #define TESSERA_SM100_F16 2
+#define TESSERA_SM100_U8 3  /* collectives only */
+#define TESSERA_SM100_I32 4 /* collectives only */
 
 /* ---- library / device management ------------------------------------------------------ */
 const char* tessera_sm100_version(void);
@@ -45,6 +47,9 @@ int tessera_sm100_device_memset(void* ptr, int value, size_t bytes, void* stream
 int tessera_sm100_device_upload(void* dst, const void* src, size_t bytes, void* stream);
 int tessera_sm100_device_download(void* dst, const void* src, size_t bytes, void* stream);
 int tessera_sm100_device_copy(void* dst, const void* src, size_t bytes, void* stream);
+/* Strided device-to-device copy of `rows` rows of `width_bytes` bytes. */
+int tessera_sm100_device_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
+                                 size_t width_bytes, size_t rows, void* stream);
 int tessera_sm100_host_alloc(void** out, size_t bytes); /* pinned host memory */
 int tessera_sm100_host_free(void* ptr);
 int tessera_sm100_stream_create(void** out);
@@ -166,6 +171,66 @@ int tessera_sm100_attn_decode_device(const void* Q, const void* K, const void* V
 int tessera_sm100_flash_attn_fwd_device(const void* Q, const void* K, const void* V, void* O, int B,
                                         int Hq, int Hkv, int Sq, int Sk, int D, float scale,
                                         int causal, void* stream);
+
+/* Attention forward that picks the kernel: Sq == 1 -> split-KV decode (scratch taken from the
+ * library's pool, recycled in stream order), otherwise the tcgen05 prefill kernel. The
+ * host-pointer form uploads Q,K,V, runs, synchronises and downloads O; it is what the Python
+ * tessera.ops.flash_attn / nn.functional.gqa_attention binding calls
+ * (python/tessera/__init__.py:1304-1356, python/tessera/nn/functional.py:349-356), in the manner
+ * of run_flash_attention_forward (python/tessera/compiler/emit/nvidia_cuda.py:313-361). */
+int tessera_sm100_flash_attn_device(const void* Q, const void* K, const void* V, void* O, int B,
+                                    int Hq, int Hkv, int Sq, int Sk, int D, float scale, int causal,
+                                    void* stream);
+int tessera_sm100_flash_attn(const void* Q, const void* K, const void* V, void* O, int B, int Hq,
+                             int Hkv, int Sq, int Sk, int D, float scale, int causal);
+
+/* Host-pointer MoE layer (upload, tessera_sm100_moe_layer_device, download): the GPU lane of
+ * tessera.nn.functional.moe_layer (python/tessera/nn/functional.py:403-490). Optional outputs
+ * may be null. */
+int tessera_sm100_moe_layer(const void* x, const float* logits, const void* w_gate,
+                            const void* w_up, const void* w_down, void* out, int T, int H, int F,
+                            int E, int top_k, int normalize, int capacity, int dtype, int out_dtype,
+                            int* assignment_out, float* weights_out, int* group_sizes_out,
+                            int* token_of_slot_out);
+
+/* out = silu(a) * b elementwise: tessera.ops.silu_mul (python/tessera/__init__.py:559-574). */
+int tessera_sm100_silu_mul_device(const void* a, const void* b, void* out, long long n, int dtype,
+                                  void* stream);
+
+/* ---- collectives (NCCL over NVLink / NVSwitch) ---------------------------------------------
+ * Device-resident, typed, asynchronous on the given stream. They stand where the reference has
+ * NCCLAdapter::all_reduce / reduce_scatter / all_gather / all_to_all
+ * (src/collectives/include/tessera/Dialect/Collective/Runtime/Adapters.h:295-394) and the ctypes
+ * executor of python/tessera/collectives.py:516-628. A communicator handle is created either per
+ * process (unique id + init_rank; the current CUDA device is the rank's GPU) or for several
+ * devices of one process (init_all). Reduction op: 0 sum, 1 max, 2 min, 3 prod. */
+int tessera_sm100_nccl_version(int* version);
+int tessera_sm100_comm_unique_id(void* out128);
+int tessera_sm100_comm_init_rank(const void* id128, int world, int rank, void** comm_out);
+int tessera_sm100_comm_init_all(int ndev, const int* devices, void** comms_out);
+int tessera_sm100_comm_destroy(void* comm);
+int tessera_sm100_comm_abort(void* comm);
+int tessera_sm100_comm_info(void* comm, int* rank, int* world, int* device);
+int tessera_sm100_comm_async_error(void* comm);
+int tessera_sm100_group_start(void);
+int tessera_sm100_group_end(void);
+int tessera_sm100_all_gather(void* comm, const void* send, void* recv, size_t count_per_rank,
+                             int dtype, void* stream);
+int tessera_sm100_all_reduce(void* comm, const void* send, void* recv, size_t count, int dtype,
+                             int op, void* stream);
+int tessera_sm100_reduce_scatter(void* comm, const void* send, void* recv, size_t recv_count,
+                                 int dtype, int op, void* stream);
+int tessera_sm100_all_to_all(void* comm, const void* send, void* recv, size_t bytes_per_peer,
+                             void* stream);
+/* Ragged all-to-all in bytes; the four arrays are host arrays of length world. Expert-parallel
+ * MoE dispatch/combine need it (python/tessera/distributed/moe.py:252-315 gives the counts). */
+int tessera_sm100_all_to_all_v(void* comm, const void* send, const size_t* send_bytes,
+                               const size_t* send_offs, void* recv, const size_t* recv_bytes,
+                               const size_t* recv_offs, void* stream);
+/* CUDA IPC handles (64 bytes) so that one rank's kernel can store into another rank's buffer. */
+int tessera_sm100_ipc_get_handle(void* device_ptr, void* handle64);
+int tessera_sm100_ipc_open_handle(const void* handle64, void** device_ptr);
+int tessera_sm100_ipc_close_handle(void* device_ptr);
 
 #ifdef __cplusplus
 }

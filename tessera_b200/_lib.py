@@ -13,7 +13,7 @@ from pathlib import Path
 
 _LIB = None
 
-F32, BF16, F16 = 0, 1, 2
+F32, BF16, F16, U8, I32 = 0, 1, 2, 3, 4
 
 
 class BackendError(RuntimeError):
@@ -47,6 +47,7 @@ _SIGNATURES = {
     "tessera_sm100_device_upload": (c_int, [_VP, _VP, c_size_t, _VP]),
     "tessera_sm100_device_download": (c_int, [_VP, _VP, c_size_t, _VP]),
     "tessera_sm100_device_copy": (c_int, [_VP, _VP, c_size_t, _VP]),
+    "tessera_sm100_device_copy_2d": (c_int, [_VP, c_size_t, _VP, c_size_t, c_size_t, c_size_t, _VP]),
     "tessera_sm100_host_alloc": (c_int, [POINTER(_VP), c_size_t]),
     "tessera_sm100_host_free": (c_int, [_VP]),
     "tessera_sm100_stream_create": (c_int, [POINTER(_VP)]),
@@ -92,6 +93,32 @@ _SIGNATURES = {
                                                  c_int, c_float, c_int, _VP, _VP]),
     "tessera_sm100_flash_attn_fwd_device": (c_int, [_VP, _VP, _VP, _VP, c_int, c_int, c_int, c_int,
                                                     c_int, c_int, c_float, c_int, _VP]),
+    "tessera_sm100_flash_attn_device": (c_int, [_VP, _VP, _VP, _VP, c_int, c_int, c_int, c_int,
+                                                c_int, c_int, c_float, c_int, _VP]),
+    "tessera_sm100_flash_attn": (c_int, [_VP, _VP, _VP, _VP, c_int, c_int, c_int, c_int, c_int,
+                                         c_int, c_float, c_int]),
+    "tessera_sm100_moe_layer": (c_int, [_VP, _VP, _VP, _VP, _VP, _VP, c_int, c_int, c_int, c_int,
+                                        c_int, c_int, c_int, c_int, c_int, _VP, _VP, _VP, _VP]),
+    "tessera_sm100_silu_mul_device": (c_int, [_VP, _VP, _VP, c_longlong, c_int, _VP]),
+    "tessera_sm100_nccl_version": (c_int, [POINTER(c_int)]),
+    "tessera_sm100_comm_unique_id": (c_int, [_VP]),
+    "tessera_sm100_comm_init_rank": (c_int, [_VP, c_int, c_int, POINTER(_VP)]),
+    "tessera_sm100_comm_init_all": (c_int, [c_int, POINTER(c_int), POINTER(_VP)]),
+    "tessera_sm100_comm_destroy": (c_int, [_VP]),
+    "tessera_sm100_comm_abort": (c_int, [_VP]),
+    "tessera_sm100_comm_info": (c_int, [_VP, POINTER(c_int), POINTER(c_int), POINTER(c_int)]),
+    "tessera_sm100_comm_async_error": (c_int, [_VP]),
+    "tessera_sm100_group_start": (c_int, []),
+    "tessera_sm100_group_end": (c_int, []),
+    "tessera_sm100_all_gather": (c_int, [_VP, _VP, _VP, c_size_t, c_int, _VP]),
+    "tessera_sm100_all_reduce": (c_int, [_VP, _VP, _VP, c_size_t, c_int, c_int, _VP]),
+    "tessera_sm100_reduce_scatter": (c_int, [_VP, _VP, _VP, c_size_t, c_int, c_int, _VP]),
+    "tessera_sm100_all_to_all": (c_int, [_VP, _VP, _VP, c_size_t, _VP]),
+    "tessera_sm100_all_to_all_v": (c_int, [_VP, _VP, POINTER(c_size_t), POINTER(c_size_t), _VP,
+                                           POINTER(c_size_t), POINTER(c_size_t), _VP]),
+    "tessera_sm100_ipc_get_handle": (c_int, [_VP, _VP]),
+    "tessera_sm100_ipc_open_handle": (c_int, [_VP, POINTER(_VP)]),
+    "tessera_sm100_ipc_close_handle": (c_int, [_VP]),
 }
 
 

@@ -84,6 +84,14 @@ int tessera_sm100_device_copy(void* dst, const void* src, size_t bytes, void* st
                               static_cast<cudaStream_t>(stream)));
   return kOk;
 }
+int tessera_sm100_device_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
+                                 size_t width_bytes, size_t rows, void* stream) {
+  if (!dst || !src) return kBadArg;
+  if (width_bytes == 0 || rows == 0) return kOk;
+  TSB_CUDA_OK(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows,
+                                cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)));
+  return kOk;
+}
 int tessera_sm100_host_alloc(void** out, size_t bytes) {
   if (!out) return kBadArg;
   if (int rc = ensure_device()) return rc;

@@ -1,0 +1,362 @@
+"""``tessera.ops`` for the B200 backend: the dense-contraction ops, executed on the GPU.
+
+Same names, arguments and error behaviour as the reference's numpy ops
+(python/tessera/__init__.py:239-254 ``gemm``/``matmul``/``batched_gemm``, :291-351
+``grouped_gemm``, :559-616 ``silu_mul``/``swiglu``/``moe_swiglu_block``, :1304-1356 ``flash_attn``,
+python/tessera/nn/functional.py:349-356 ``gqa_attention``), but every op here calls the sm_100a
+kernels through the C ABI. There is no CPU fallback: without the shared library or a GPU the
+call raises ``BackendError``.
+
+Host arrays (numpy, or anything with ``._data`` / ``.numpy()``) go in and numpy arrays come out;
+``DeviceArray`` inputs stay on the device and produce ``DeviceArray`` outputs, so a chain of ops
+moves no data across PCIe.
+
+Differences from the numpy reference, all on the side of what its own GPU lanes do:
+* 16-bit GEMM operands accumulate in fp32 and the result is float32 unless ``out_dtype`` is
+  given (the reference's shipped GEMM symbols return fp32,
+  src/compiler/codegen/tessera_gpu_backend_NVIDIA/runtime/cuda/tessera_nvidia_gemm.cpp:41-60).
+* float32 host operands are not accepted by the tensor-core ops unless ``compute_dtype`` says
+  which 16-bit format to round them to.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Any, Optional
+
+import numpy as np
+
+from . import _lib, device
+from .device import DeviceArray, bfloat16
+
+GROUPED_KINDS = ("contiguous", "dense", "masked", "k_grouped")
+SUPPORTED_GROUPED_KINDS = ("contiguous", "dense")
+
+
+def _unwrap(x: Any) -> Any:
+    """DeviceArray stays; everything else becomes a numpy array (reference `_as_numpy`,
+    python/tessera/runtime.py:44377-44384)."""
+    if isinstance(x, DeviceArray):
+        return x
+    if hasattr(x, "_data"):
+        return np.asarray(x._data)
+    if hasattr(x, "numpy") and callable(x.numpy):
+        return np.asarray(x.numpy())
+    return np.asarray(x)
+
+
+def _storage_dtype(arrs, compute_dtype: Optional[str], op: str) -> np.dtype:
+    dts = {np.dtype(a.dtype) for a in arrs}
+    if compute_dtype is not None:
+        name = {"bf16": bfloat16, "bfloat16": bfloat16, "f16": np.dtype(np.float16),
+                "fp16": np.dtype(np.float16), "float16": np.dtype(np.float16)}.get(compute_dtype)
+        if name is None:
+            raise ValueError(f"{op}: compute_dtype must be 'bf16' or 'f16', got {compute_dtype!r}")
+        return np.dtype(name)
+    if len(dts) != 1:
+        raise TypeError(f"{op}: operands must share one dtype, got {sorted(map(str, dts))}")
+    dt = dts.pop()
+    if dt == np.float16 or dt == bfloat16:
+        return dt
+    raise TypeError(f"{op}: operands must be float16 or bfloat16 (got {dt}); pass "
+                    f"compute_dtype='bf16' to round float32 operands")
+
+
+def _to_device(x, dt: np.dtype) -> DeviceArray:
+    if isinstance(x, DeviceArray):
+        if x.dtype != dt:
+            raise TypeError(f"device operand has dtype {x.dtype}, expected {dt}")
+        return x
+    return DeviceArray.from_host(np.ascontiguousarray(x).astype(dt, copy=False))
+
+
+def _any_device(*xs) -> bool:
+    return any(isinstance(x, DeviceArray) for x in xs)
+
+
+def _out_code(out_dtype, default: int) -> int:
+    if out_dtype is None:
+        return default
+    return device.dtype_code(out_dtype)
+
+
+# --------------------------------------------------------------------------------- GEMM
+def gemm(A, B, epilogue=None, *, out_dtype=None, compute_dtype: Optional[str] = None, stream=None,
+         out=None):
+    """Matrix multiply ``A @ B``; leading dimensions are a batch (python/tessera/__init__.py:239-248).
+    ``out`` (host operands only) is an optional preallocated result array, e.g. pinned memory."""
+    if epilogue:
+        raise NotImplementedError("gemm: fused epilogues are not part of the sm_100a backend yet")
+    A, B = _unwrap(A), _unwrap(B)
+    if A.ndim < 2 or B.ndim < 2:
+        raise ValueError(f"gemm: operands must be at least 2-D, got {A.shape} @ {B.shape}")
+    if A.shape[-1] != B.shape[-2]:
+        raise ValueError(f"gemm: K mismatch — {A.shape} @ {B.shape}")
+    dt = _storage_dtype((A, B), compute_dtype, "gemm")
+    in_code = device.dtype_code(dt)
+    out_code = _out_code(out_dtype, _lib.F32)
+    M, K, N = A.shape[-2], A.shape[-1], B.shape[-1]
+    batch_shape = A.shape[:-2]
+    if B.shape[:-2] != batch_shape:
+        if _any_device(A, B):
+            raise ValueError("gemm: device operands must have identical batch dimensions")
+        bs = np.broadcast_shapes(A.shape[:-2], B.shape[:-2])
+        A = np.broadcast_to(A, bs + A.shape[-2:])
+        B = np.broadcast_to(B, bs + B.shape[-2:])
+        batch_shape = bs
+    batch = int(np.prod(batch_shape, dtype=np.int64)) if batch_shape else 1
+    out_shape = tuple(batch_shape) + (M, N)
+    if batch == 0 or M == 0 or N == 0:
+        return np.zeros(out_shape, device.code_dtype(out_code))
+    if K == 0:
+        return np.zeros(out_shape, device.code_dtype(out_code))
+    if _any_device(A, B):
+        dA, dB = _to_device(A, dt), _to_device(B, dt)
+        out = DeviceArray(out_shape, device.code_dtype(out_code))
+        _lib.call("tessera_sm100_gemm_device", dA.ptr, dB.ptr, out.ptr, batch, M, N, K, in_code,
+                  out_code, device._stream_handle(stream))
+        return out
+    a = np.ascontiguousarray(A).astype(dt, copy=False)
+    b = np.ascontiguousarray(B).astype(dt, copy=False)
+    if out is None:
+        out = np.empty(out_shape, device.code_dtype(out_code))
+    elif out.shape != out_shape or out.dtype != device.code_dtype(out_code) or not out.flags.c_contiguous:
+        raise ValueError(f"gemm: out must be a contiguous {device.code_dtype(out_code)} array of shape {out_shape}")
+    _lib.call("tessera_sm100_gemm", a.ctypes.data, b.ctypes.data, out.ctypes.data, batch, M, N, K,
+              in_code, out_code)
+    return out
+
+
+def matmul(A, B, epilogue=None, **kw):
+    return gemm(A, B, epilogue=epilogue, **kw)
+
+
+def batched_gemm(A, B, epilogue=None, **kw):
+    return gemm(A, B, epilogue=epilogue, **kw)
+
+
+# --------------------------------------------------------------------------------- attention
+def flash_attn(Q, K=None, V=None, scale=None, causal: bool = False, cache=None,
+               dropout_p: float = 0.0, params=None, deterministic=None, seed=None, attn_bias=None,
+               kv_state=None, *, stream=None):
+    """``softmax(scale * Q K^T, causal) V`` (python/tessera/__init__.py:1304-1356). Q [B,Hq,Sq,D],
+    K/V [B,Hkv,Sk,D] bfloat16, D = 128; Hkv may divide Hq (grouped-query attention)."""
+    if kv_state is not None or cache is not None:
+        raise NotImplementedError("flash_attn: paged / cached KV state is not part of this backend")
+    if not 0.0 <= dropout_p < 1.0:
+        raise ValueError("dropout_p must be in [0.0, 1.0)")
+    if dropout_p > 0.0 or attn_bias is not None:
+        raise NotImplementedError("flash_attn: dropout and attn_bias are not part of this backend")
+    if K is None or V is None:
+        raise ValueError("flash_attn: K and V are required")
+    Q, K, V = _unwrap(Q), _unwrap(K), _unwrap(V)
+    squeeze = 0
+    while Q.ndim < 4:  # (S, D) or (H, S, D) like numpy broadcasting would accept
+        if _any_device(Q, K, V):
+            raise ValueError("flash_attn: device operands must be 4-D [B, H, S, D]")
+        Q, K, V = Q[None], K[None], V[None]
+        squeeze += 1
+    if Q.ndim != 4 or K.ndim != 4 or V.ndim != 4:
+        raise ValueError(f"flash_attn: expected [B, H, S, D] operands, got {Q.shape}, {K.shape}, {V.shape}")
+    Bq, Hq, Sq, D = Q.shape
+    Bk, Hkv, Sk, Dk = K.shape
+    if V.shape != K.shape or Bk != Bq or Dk != D:
+        raise ValueError(f"flash_attn: incompatible shapes Q {Q.shape}, K {K.shape}, V {V.shape}")
+    if Hq % Hkv:
+        raise ValueError("num_query_heads must be divisible by num_kv_heads")
+    dt = _storage_dtype((Q, K, V), None, "flash_attn")
+    if dt != bfloat16:
+        raise TypeError("flash_attn: the sm_100a attention kernels take bfloat16 operands")
+    if scale is None:
+        scale = 1.0 / np.sqrt(D)
+    cscale = ctypes.c_float(float(scale))
+    if _any_device(Q, K, V):
+        dq, dk, dv = _to_device(Q, dt), _to_device(K, dt), _to_device(V, dt)
+        out = DeviceArray(Q.shape, dt)
+        _lib.call("tessera_sm100_flash_attn_device", dq.ptr, dk.ptr, dv.ptr, out.ptr, Bq, Hq, Hkv, Sq,
+                  Sk, D, cscale, int(bool(causal)), device._stream_handle(stream))
+        return out
+    q, k, v = (np.ascontiguousarray(t) for t in (Q, K, V))
+    out = np.empty(q.shape, dt)
+    _lib.call("tessera_sm100_flash_attn", q.ctypes.data, k.ctypes.data, v.ctypes.data, out.ctypes.data,
+              Bq, Hq, Hkv, Sq, Sk, D, cscale, int(bool(causal)))
+    for _ in range(squeeze):
+        out = out[0]
+    return out
+
+
+def gqa_attention(Q, K, V, num_query_heads: int, num_kv_heads: int, **kwargs):
+    """Grouped-query attention (python/tessera/nn/functional.py:349-356). The KV heads are shared
+    inside the kernel instead of being repeated in memory."""
+    if num_query_heads % num_kv_heads != 0:
+        raise ValueError("num_query_heads must be divisible by num_kv_heads")
+    q, k = _unwrap(Q), _unwrap(K)
+    if q.shape[1] != num_query_heads or k.shape[1] != num_kv_heads:
+        raise ValueError(f"gqa_attention: Q has {q.shape[1]} heads and K has {k.shape[1]}, expected "
+                         f"{num_query_heads} and {num_kv_heads}")
+    return flash_attn(Q, K, V, **kwargs)
+
+
+def mqa_attention(Q, K, V, **kwargs):
+    return gqa_attention(Q, K, V, num_query_heads=_unwrap(Q).shape[1], num_kv_heads=1, **kwargs)
+
+
+# --------------------------------------------------------------------------------- MoE
+def _group_offsets(group_sizes, T: int, op: str) -> np.ndarray:
+    gs = np.asarray(group_sizes).astype(np.int64).reshape(-1)
+    if int(gs.sum()) != T:
+        raise ValueError(f"{op}: group_sizes sum {int(gs.sum())} != T={T}")
+    if np.any(gs < 0):
+        raise ValueError(f"{op}: group_sizes must be non-negative")
+    off = np.zeros(gs.shape[0] + 1, np.int32)
+    off[1:] = np.cumsum(gs)
+    return off
+
+
+def _check_kind(kind: str, alignment, group_sizes, quant, op: str) -> None:
+    if kind not in GROUPED_KINDS:
+        raise ValueError(f"{op}: unknown kind {kind!r}; expected one of {GROUPED_KINDS}")
+    if kind not in SUPPORTED_GROUPED_KINDS:
+        raise NotImplementedError(f"{op}: kind={kind!r} is not implemented yet")
+    if quant is not None:
+        raise NotImplementedError(f"{op}: quantised grouped GEMM is not part of this backend")
+    if alignment is not None:
+        gs = np.asarray(group_sizes).astype(np.int64).reshape(-1)
+        if np.any(gs % int(alignment)):
+            raise ValueError(f"{op}: every group size must be a multiple of alignment={alignment}")
+
+
+def grouped_gemm(x, weights, group_sizes, *, kind="contiguous", alignment=None, quant=None,
+                 out_dtype=None, stream=None):
+    """Ragged grouped matmul: row block e of ``x`` (T, K) times ``weights[e]`` (E, K, N)
+    (python/tessera/__init__.py:291-351). Output dtype follows ``x``."""
+    _check_kind(kind, alignment, group_sizes, quant, "grouped_gemm")
+    x, w = _unwrap(x), _unwrap(weights)
+    if x.ndim != 2:
+        raise ValueError(f"grouped_gemm: x must be (T, K); got {x.shape}")
+    gs_len = np.asarray(group_sizes).reshape(-1).shape[0]
+    if w.ndim != 3 or w.shape[0] != gs_len:
+        raise ValueError(f"grouped_gemm: weights {w.shape} must be (E, K, N) with "
+                         f"E == len(group_sizes)={gs_len}")
+    if w.shape[1] != x.shape[1]:
+        raise ValueError(f"grouped_gemm: K mismatch — x K={x.shape[1]}, weights K={w.shape[1]}")
+    T, K = x.shape
+    E, _, N = w.shape
+    off = _group_offsets(group_sizes, T, "grouped_gemm")
+    dt = _storage_dtype((x, w), None, "grouped_gemm")
+    out_code = _out_code(out_dtype, device.dtype_code(dt))
+    on_device = _any_device(x, w)
+    dx, dw = _to_device(x, dt), _to_device(w, dt)
+    doff = DeviceArray.from_host(off)
+    out = DeviceArray.zeros((T, N), device.code_dtype(out_code))
+    _lib.call("tessera_sm100_grouped_gemm_device", dx.ptr, dw.ptr, doff.ptr, out.ptr, T, K, N, E,
+              device.dtype_code(dt), out_code, device._stream_handle(stream))
+    return out if on_device else _finish(out)
+
+
+def _finish(out: DeviceArray) -> np.ndarray:
+    host = out.download()
+    device.check_device_error("kernel")
+    return host
+
+
+def silu_mul(a, b, *, stream=None):
+    """``silu(a) * b`` elementwise (python/tessera/__init__.py:559-574)."""
+    a, b = _unwrap(a), _unwrap(b)
+    if a.shape != b.shape:
+        raise ValueError(f"silu_mul: shape mismatch {a.shape} vs {b.shape}")
+    on_device = _any_device(a, b)
+    dt = np.dtype(a.dtype)
+    da, db = _to_device(a, dt), _to_device(b, dt)
+    out = DeviceArray(a.shape, dt)
+    _lib.call("tessera_sm100_silu_mul_device", da.ptr, db.ptr, out.ptr, int(da.size),
+              device.dtype_code(dt), device._stream_handle(stream))
+    return out if on_device else _finish(out)
+
+
+def moe_swiglu_block(x, w_gate, w_up, w_down, group_sizes, *, kind="contiguous", alignment=None,
+                     quant=None, stream=None):
+    """Expert FFN over grouped tokens: gate and up grouped GEMMs fused with ``silu_mul`` in one
+    kernel, then the down grouped GEMM (python/tessera/__init__.py:592-616)."""
+    _check_kind(kind, alignment, group_sizes, quant, "moe_swiglu_block")
+    x, wg, wu, wd = _unwrap(x), _unwrap(w_gate), _unwrap(w_up), _unwrap(w_down)
+    if x.ndim != 2 or wg.ndim != 3 or wu.shape != wg.shape or wd.ndim != 3:
+        raise ValueError("moe_swiglu_block: expected x (T,K), w_gate/w_up (E,K,F), w_down (E,F,N)")
+    T, K = x.shape
+    E, Kw, F = wg.shape
+    if Kw != K or wd.shape[0] != E or wd.shape[1] != F:
+        raise ValueError(f"moe_swiglu_block: shape mismatch x {x.shape}, w_gate {wg.shape}, "
+                         f"w_down {wd.shape}")
+    N = wd.shape[2]
+    off = _group_offsets(group_sizes, T, "moe_swiglu_block")
+    if off.shape[0] != E + 1:
+        raise ValueError(f"moe_swiglu_block: len(group_sizes)={off.shape[0] - 1} != E={E}")
+    dt = _storage_dtype((x, wg, wu, wd), None, "moe_swiglu_block")
+    code = device.dtype_code(dt)
+    on_device = _any_device(x, wg, wu, wd)
+    dx, dg, du, dd = (_to_device(t, dt) for t in (x, wg, wu, wd))
+    doff = DeviceArray.from_host(off)
+    hidden = DeviceArray.zeros((T, F), dt)
+    out = DeviceArray.zeros((T, N), dt)
+    sh = device._stream_handle(stream)
+    _lib.call("tessera_sm100_grouped_swiglu_device", dx.ptr, dg.ptr, du.ptr, doff.ptr, hidden.ptr, T,
+              K, F, E, code, code, sh)
+    _lib.call("tessera_sm100_grouped_gemm_device", hidden.ptr, dd.ptr, doff.ptr, out.ptr, T, F, N, E,
+              code, code, sh)
+    return out if on_device else _finish(out)
+
+
+def swiglu(x, W_gate, W_up, W_down, *, stream=None):
+    """Dense SwiGLU MLP ``(silu(x Wg) * (x Wu)) Wd`` (python/tessera/__init__.py:576-590), run as a
+    one-expert ``moe_swiglu_block`` so gate, up and the activation share a kernel."""
+    x_, wg, wu, wd = _unwrap(x), _unwrap(W_gate), _unwrap(W_up), _unwrap(W_down)
+    lead = x_.shape[:-1]
+    x2 = x_.reshape((-1, x_.shape[-1]))
+    out = moe_swiglu_block(x2, wg.reshape((1,) + tuple(wg.shape)), wu.reshape((1,) + tuple(wu.shape)),
+                           wd.reshape((1,) + tuple(wd.shape)), [x2.shape[0]], stream=stream)
+    return out.reshape(tuple(lead) + (wd.shape[-1],)) if isinstance(out, np.ndarray) else out
+
+
+def moe_layer_from_logits(x, logits, W_gate, W_up, W_down, *, top_k: int = 1,
+                          normalize_weights: bool = True, capacity: Optional[int] = None,
+                          out_dtype=None, return_routing: bool = False):
+    """Route (given router logits) -> permute -> expert FFN -> combine, all on the GPU. Returns
+    the (T, N) output, plus a dict of routing products when ``return_routing`` is set."""
+    x, wg, wu, wd = _unwrap(x), _unwrap(W_gate), _unwrap(W_up), _unwrap(W_down)
+    logits = np.ascontiguousarray(_unwrap(logits), dtype=np.float32)
+    T, H = x.shape
+    E, Hw, F = wg.shape
+    if Hw != H or wu.shape != wg.shape or wd.shape != (E, F, H) or logits.shape != (T, E):
+        raise ValueError(f"moe_layer: shape mismatch x {x.shape}, logits {logits.shape}, w_gate "
+                         f"{wg.shape}, w_up {wu.shape}, w_down {wd.shape}")
+    if not 1 <= top_k <= E:
+        raise ValueError(f"top_k must be in [1, num_experts={E}], got {top_k}")
+    dt = _storage_dtype((x, wg, wu, wd), None, "moe_layer")
+    code = device.dtype_code(dt)
+    out_code = _out_code(out_dtype, code)
+    xh, g, u, d = (np.ascontiguousarray(t) for t in (x, wg, wu, wd))
+    out = np.empty((T, H), device.code_dtype(out_code))
+    assignment = np.empty((T, top_k), np.int32)
+    weights = np.empty((T, top_k), np.float32)
+    group_sizes = np.empty((E,), np.int32)
+    token_of_slot = np.empty((T * top_k,), np.int32)
+    _lib.call("tessera_sm100_moe_layer", xh.ctypes.data, logits.ctypes.data, g.ctypes.data,
+              u.ctypes.data, d.ctypes.data, out.ctypes.data, T, H, F, E, int(top_k),
+              int(bool(normalize_weights)), -1 if capacity is None else int(capacity), code, out_code,
+              assignment.ctypes.data, weights.ctypes.data, group_sizes.ctypes.data,
+              token_of_slot.ctypes.data)
+    if not return_routing:
+        return out
+    kept = int(group_sizes.sum())
+    return out, dict(assignment=assignment.astype(np.int64), weights=weights,
+                     group_sizes=group_sizes, token_of_slot=token_of_slot[:kept])
+
+
+_RUNTIME_KERNELS: dict[str, Any] = {}
+
+
+def register_runtime_kernel(name: str, fn) -> None:
+    """Op registry seam (python/tessera/__init__.py:182-186): expose ``fn`` as ``ops.<name>``."""
+    if not callable(fn):
+        raise TypeError("runtime kernel must be callable")
+    _RUNTIME_KERNELS[name] = fn
+    globals()[name] = fn

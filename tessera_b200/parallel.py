@@ -1,0 +1,227 @@
+"""Multi-GPU forms of the hot path, one process per GPU.
+
+* ``tp_column_range`` / ``TensorParallelGemm`` — column-parallel GEMM: W split on N, A replicated,
+  ``Y = all_gather(A @ W_r, axis=1)`` (python/tessera/compiler/tensor_parallel.py:118-123).
+* ``ep_plan`` / ``ExpertParallelMoE`` — expert-parallel MoE forward partitioned like
+  ``megamoe_forward`` (python/tessera/distributed/moe.py:358-483): tokens row-sharded, rank r owns
+  experts [r*Ep, (r+1)*Ep), a dispatch exchange, the local expert FFN, a combine exchange and a
+  weighted sum per token. Unlike the reference nothing is padded to a capacity: the exchanges are
+  ragged, sized from the routing histogram (``plan_all_to_all``, :252-315).
+
+The planning code is plain numpy and independent of where the arithmetic runs. ``ExpertParallelMoE``
+takes a *transport* (how ranks exchange rows) and a *compute backend* (how rows are gathered and
+the expert FFN is evaluated); on a GPU job these are NCCL + the sm_100a kernels
+(``NcclTransport`` / ``GpuMoeBackend``), while the CPU tests drive the very same planning and
+sequencing with ``torch.distributed`` (gloo) and a numpy backend.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Protocol, Sequence
+
+import numpy as np
+
+
+# ---------------------------------------------------------------------------- tensor parallel
+def tp_column_range(n: int, world: int, rank: int) -> tuple:
+    """Column block of rank ``rank`` when N is split evenly over ``world`` ranks."""
+    if n % world:
+        raise ValueError(f"N={n} is not divisible by the tensor-parallel size {world}")
+    nb = n // world
+    return rank * nb, nb
+
+
+# ---------------------------------------------------------------------------- expert parallel
+@dataclass
+class EPPlan:
+    world: int
+    rank: int
+    experts_per_rank: int
+    top_k: int
+    # send side (this rank's tokens)
+    send_token: np.ndarray          # (Ssend,) int32 local token of each sent row, in send order
+    send_counts: np.ndarray         # (world,) rows sent to each destination rank
+    slot_of_assignment: np.ndarray  # (Tl, k) int32 position in send order of slot (t, j), -1 dropped
+    send_expert_counts: np.ndarray  # (world, Ep) rows per destination and local expert
+
+
+def ep_plan(assignment: np.ndarray, num_experts: int, world: int, rank: int) -> EPPlan:
+    """Send-side plan from this rank's routing table (``assignment`` (Tl, k), -1 = dropped).
+    Rows go out ordered by (destination rank, expert, token-major slot), so every receiver gets
+    from every source a block that is already sorted by its local expert id."""
+    assignment = np.asarray(assignment)
+    if num_experts % world:
+        raise ValueError(f"num_experts={num_experts} must be divisible by world_size={world}")
+    Ep = num_experts // world
+    Tl, k = assignment.shape
+    flat = assignment.reshape(-1).astype(np.int64)
+    kept = np.nonzero(flat >= 0)[0]
+    order = kept[np.argsort(flat[kept], kind="stable")]      # by expert == by (dst, local expert)
+    send_token = (order // k).astype(np.int32)
+    slot_of = np.full(Tl * k, -1, np.int32)
+    slot_of[order] = np.arange(order.shape[0], dtype=np.int32)
+    counts = np.bincount(flat[order], minlength=num_experts).reshape(world, Ep).astype(np.int64)
+    return EPPlan(world, rank, Ep, k, send_token, counts.sum(axis=1), slot_of.reshape(Tl, k), counts)
+
+
+@dataclass
+class EPRecvPlan:
+    recv_counts: np.ndarray    # (world,) rows received from each source
+    group_sizes: np.ndarray    # (Ep,) rows per local expert
+    group_offsets: np.ndarray  # (Ep+1,) int32
+    to_grouped: np.ndarray     # (Srecv,) int32: grouped row i comes from received row to_grouped[i]
+    from_grouped: np.ndarray   # (Srecv,) int32: received row i sits at grouped row from_grouped[i]
+
+
+def ep_recv_plan(all_expert_counts: np.ndarray, rank: int) -> EPRecvPlan:
+    """Receive-side plan from the gathered ``send_expert_counts`` of every rank
+    (shape (world_src, world_dst, Ep)). Received rows arrive source-major; the expert FFN wants
+    them expert-major (source-major inside an expert), which is the stable expert sort the
+    single-device layer applies."""
+    counts = np.asarray(all_expert_counts)[:, rank, :]        # (src, Ep) rows bound for this rank
+    world, Ep = counts.shape
+    recv_counts = counts.sum(axis=1)
+    total = int(recv_counts.sum())
+    src_base = np.concatenate(([0], np.cumsum(recv_counts)[:-1]))
+    in_src = np.concatenate((np.zeros((world, 1), np.int64), np.cumsum(counts, axis=1)[:, :-1]), axis=1)
+    to_grouped = np.empty(total, np.int32)
+    pos = 0
+    for e in range(Ep):
+        for s in range(world):
+            n = int(counts[s, e])
+            start = int(src_base[s] + in_src[s, e])
+            to_grouped[pos:pos + n] = np.arange(start, start + n, dtype=np.int32)
+            pos += n
+    from_grouped = np.empty(total, np.int32)
+    from_grouped[to_grouped] = np.arange(total, dtype=np.int32)
+    group_sizes = counts.sum(axis=0).astype(np.int32)
+    offsets = np.zeros(Ep + 1, np.int32)
+    offsets[1:] = np.cumsum(group_sizes)
+    return EPRecvPlan(recv_counts, group_sizes, offsets, to_grouped, from_grouped)
+
+
+class Transport(Protocol):
+    rank: int
+    world: int
+
+    def all_gather_small(self, arr: np.ndarray) -> np.ndarray: ...
+    def exchange_rows(self, rows, send_counts: Sequence[int], recv_counts: Sequence[int]): ...
+
+
+class MoeBackend(Protocol):
+    def route(self, logits: np.ndarray, top_k: int, normalize: bool): ...       # -> (assignment, weights) host
+    def gather_rows(self, rows, index: np.ndarray): ...
+    def expert_ffn(self, rows, group_offsets: np.ndarray): ...
+    def combine(self, rows, slot_of: np.ndarray, weights: np.ndarray, num_tokens: int): ...
+
+
+class ExpertParallelMoE:
+    """Sequencing of the expert-parallel forward for ONE rank."""
+
+    def __init__(self, num_experts: int, top_k: int, transport: Transport, backend: MoeBackend,
+                 normalize_weights: bool = True) -> None:
+        if num_experts % transport.world:
+            raise ValueError("num_experts must be divisible by the number of ranks")
+        self.E, self.k = num_experts, top_k
+        self.t, self.b = transport, backend
+        self.normalize = normalize_weights
+
+    def forward(self, x_local, logits_local: np.ndarray):
+        """``x_local`` (Tl, H) rows of this rank, ``logits_local`` (Tl, E) router logits. Returns
+        the (Tl, H) output rows of this rank (backend array type)."""
+        t, b = self.t, self.b
+        assignment, weights = b.route(logits_local, self.k, self.normalize)
+        plan = ep_plan(assignment, self.E, t.world, t.rank)
+        all_counts = t.all_gather_small(plan.send_expert_counts)          # (world, world, Ep)
+        rplan = ep_recv_plan(all_counts, t.rank)
+        send_rows = b.gather_rows(x_local, plan.send_token)               # dispatch pack
+        recv_rows = t.exchange_rows(send_rows, plan.send_counts, rplan.recv_counts)
+        grouped = b.gather_rows(recv_rows, rplan.to_grouped)              # expert-major
+        y_grouped = b.expert_ffn(grouped, rplan.group_offsets)
+        y_recv_order = b.gather_rows(y_grouped, rplan.from_grouped)       # back to source-major
+        y_back = t.exchange_rows(y_recv_order, rplan.recv_counts, plan.send_counts)
+        return b.combine(y_back, plan.slot_of_assignment, weights, int(np.asarray(logits_local).shape[0]))
+
+
+# ---------------------------------------------------------------------------- GPU pieces
+class NcclTransport:
+    """Row exchange over a ``collectives.Communicator``; small host metadata travels through a
+    caller-supplied ``gather_host`` (e.g. ``torch.distributed.all_gather_object`` over gloo)."""
+
+    def __init__(self, comm, gather_host, stream=None) -> None:
+        self.comm, self.rank, self.world = comm, comm.rank, comm.world
+        self._gather_host = gather_host
+        self.stream = stream
+
+    def all_gather_small(self, arr: np.ndarray) -> np.ndarray:
+        return np.stack(self._gather_host(np.asarray(arr)))
+
+    def exchange_rows(self, rows, send_counts, recv_counts):
+        from .device import DeviceArray
+        width = rows.shape[1]
+        row_bytes = width * rows.dtype.itemsize
+        out = DeviceArray((int(np.sum(recv_counts)), width), rows.dtype)
+        self.comm.all_to_all_v(rows.ptr, [int(c) * row_bytes for c in send_counts], out.ptr,
+                               [int(c) * row_bytes for c in recv_counts], self.stream)
+        return out
+
+
+class GpuMoeBackend:
+    """Expert FFN and row movement on the sm_100a kernels for one rank's local experts."""
+
+    def __init__(self, w_gate, w_up, w_down, stream=None) -> None:
+        from . import device
+        self.wg, self.wu, self.wd = w_gate, w_up, w_down          # DeviceArrays (Ep, H, F) / (Ep, F, H)
+        self.stream = stream
+        self._code = device.dtype_code(w_gate.dtype)
+
+    def route(self, logits, top_k, normalize):
+        from . import _lib
+        from .device import DeviceArray, _stream_handle
+        logits = np.ascontiguousarray(logits, np.float32)
+        T, E = logits.shape
+        dl = DeviceArray.from_host(logits)
+        da, dw = DeviceArray((T, top_k), np.int32), DeviceArray((T, top_k), np.float32)
+        _lib.call("tessera_sm100_moe_route_device", dl.ptr, T, E, top_k, int(normalize), da.ptr, dw.ptr,
+                  _stream_handle(self.stream))
+        return da.download(), dw.download()
+
+    def gather_rows(self, rows, index):
+        from . import _lib
+        from .device import DeviceArray, _stream_handle
+        index = np.ascontiguousarray(index, np.int32)
+        S, H = int(index.shape[0]), rows.shape[1]
+        out = DeviceArray((S, H), rows.dtype)
+        if S:
+            didx = DeviceArray.from_host(index)
+            _lib.call("tessera_sm100_moe_dispatch_device", rows.ptr, didx.ptr, out.ptr, rows.shape[0], S,
+                      H, self._code, _stream_handle(self.stream))
+        return out
+
+    def expert_ffn(self, rows, group_offsets):
+        from . import _lib
+        from .device import DeviceArray, _stream_handle
+        S, H = rows.shape
+        Ep, _, F = self.wg.shape
+        doff = DeviceArray.from_host(np.ascontiguousarray(group_offsets, np.int32))
+        hidden = DeviceArray((max(S, 1), F), rows.dtype)
+        out = DeviceArray((S, self.wd.shape[2]), rows.dtype)
+        if S:
+            sh = _stream_handle(self.stream)
+            _lib.call("tessera_sm100_grouped_swiglu_device", rows.ptr, self.wg.ptr, self.wu.ptr, doff.ptr,
+                      hidden.ptr, S, H, F, Ep, self._code, self._code, sh)
+            _lib.call("tessera_sm100_grouped_gemm_device", hidden.ptr, self.wd.ptr, doff.ptr, out.ptr, S, F,
+                      self.wd.shape[2], Ep, self._code, self._code, sh)
+        return out
+
+    def combine(self, rows, slot_of, weights, num_tokens):
+        from . import _lib
+        from .device import DeviceArray, _stream_handle
+        k = slot_of.shape[1]
+        H = rows.shape[1]
+        dso = DeviceArray.from_host(np.ascontiguousarray(slot_of, np.int32))
+        dw = DeviceArray.from_host(np.ascontiguousarray(weights, np.float32))
+        out = DeviceArray((num_tokens, H), rows.dtype)
+        _lib.call("tessera_sm100_moe_combine_device", rows.ptr, dso.ptr, dw.ptr, out.ptr, num_tokens, k, H,
+                  self._code, self._code, _stream_handle(self.stream))
+        return out

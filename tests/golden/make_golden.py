@@ -1,0 +1,141 @@
+"""Generates the golden fixtures in this directory by running the REFERENCE implementation.
+
+Run it where the reference checkout is available (it cannot run on a machine without it):
+
+    TESSERA_REFERENCE=/path/to/tessera python tests/golden/make_golden.py
+
+It imports the reference's own ``tessera`` package (pure Python + numpy) and records inputs and
+outputs of the hot-path functions at small sizes:
+
+  gemm.npz        tessera.ops.gemm / MatmulRegion.reference       (python/tessera/__init__.py:239-254,
+                                                                   python/tessera/compiler/fusion_core.py:398-405)
+  attention.npz   tessera.ops.flash_attn, nn.functional.gqa_attention, softmax_merge/finalize
+                                                                  (python/tessera/__init__.py:1304-1356,
+                                                                   python/tessera/nn/functional.py:349-356,
+                                                                   python/tessera/_block_attnres_ops.py:104-146)
+  moe.npz         distributed.moe.route_tokens, stdlib.moe.plan_dispatch +
+                  compiler.moe_transport.descriptor_from_dispatch_plan, ops.grouped_gemm,
+                  ops.moe_swiglu_block, nn.functional.moe_layer, distributed.moe.megamoe_layer
+
+The committed .npz files are what ``tests/test_oracle_golden.py`` pins the oracle against.
+"""
+import os
+import sys
+
+import numpy as np
+
+REF = os.environ.get("TESSERA_REFERENCE", "/root/reference")
+sys.dont_write_bytecode = True
+sys.path.insert(0, os.path.join(REF, "python"))
+sys.path.insert(1, REF)
+
+import ml_dtypes  # noqa: E402
+import tessera  # noqa: E402  (the reference package)
+from tessera.compiler import fusion_core  # noqa: E402
+from tessera.compiler.moe_transport import descriptor_from_dispatch_plan  # noqa: E402
+from tessera.distributed import moe as dmoe  # noqa: E402
+from tessera.nn import functional as F  # noqa: E402
+from tessera.stdlib import moe as smoe  # noqa: E402
+from tessera._block_attnres_ops import softmax_finalize, softmax_merge  # noqa: E402
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+bf16 = ml_dtypes.bfloat16
+
+
+def rt(x, dt):
+    """Round to 16-bit storage and return float32 (what the reference holds for 'bf16')."""
+    return np.asarray(x, np.float32).astype(dt).astype(np.float32)
+
+
+def gemm():
+    rng = np.random.default_rng(101)
+    out = {}
+    for i, (b, M, N, K, dt) in enumerate([(1, 17, 9, 31, "bf16"), (3, 48, 40, 56, "f16"),
+                                          (1, 128, 128, 256, "bf16"), (2, 33, 64, 72, "bf16")]):
+        st = bf16 if dt == "bf16" else np.float16
+        A = rt(rng.standard_normal((b, M, K)) / np.sqrt(K), st)
+        B = rt(rng.standard_normal((b, K, N)) / np.sqrt(K), st)
+        Y = np.asarray(tessera.ops.gemm(A, B), np.float32)  # f32 arrays holding 16-bit values
+        region = fusion_core.MatmulRegion(dtype="bfloat16" if dt == "bf16" else "float16")
+        Yr = np.stack([region.reference(A[j], B[j]) for j in range(b)])
+        out[f"A{i}"], out[f"B{i}"], out[f"Y{i}"], out[f"Yregion{i}"] = A, B, Y, Yr
+        out[f"dtype{i}"] = np.array(dt)
+    out["n"] = np.array(4)
+    np.savez_compressed(os.path.join(HERE, "gemm.npz"), **out)
+
+
+def attention():
+    rng = np.random.default_rng(202)
+    out = {}
+    cases = [(1, 2, 2, 40, 40, 128, True), (2, 2, 2, 33, 70, 128, True), (1, 2, 2, 70, 33, 128, True),
+             (1, 3, 3, 50, 50, 128, False), (2, 4, 2, 1, 97, 128, False), (1, 8, 2, 24, 24, 128, True)]
+    for i, (B, Hq, Hkv, Sq, Sk, D, causal) in enumerate(cases):
+        Q = rt(rng.standard_normal((B, Hq, Sq, D)), bf16)
+        K = rt(rng.standard_normal((B, Hkv, Sk, D)), bf16)
+        V = rt(rng.standard_normal((B, Hkv, Sk, D)), bf16)
+        if Hq == Hkv:
+            O = tessera.ops.flash_attn(Q, K, V, causal=causal)
+        else:
+            O = F.gqa_attention(Q, K, V, Hq, Hkv, causal=causal)
+        out[f"Q{i}"], out[f"K{i}"], out[f"V{i}"] = Q, K, V
+        out[f"O{i}"] = np.asarray(O, np.float32)
+        out[f"meta{i}"] = np.array([B, Hq, Hkv, Sq, Sk, D, int(causal)])
+    out["n"] = np.array(len(cases))
+    # split-KV merge states
+    oa, ob = rng.standard_normal((2, 5, 16)).astype(np.float32)
+    ma, mb = rng.standard_normal((2, 5)).astype(np.float32)
+    la, lb = (rng.random((2, 5)) + 0.5).astype(np.float32)
+    o, m, l = softmax_merge(oa, ma, la, ob, mb, lb)
+    out.update(merge_oa=oa, merge_ob=ob, merge_ma=ma, merge_mb=mb, merge_la=la, merge_lb=lb,
+               merge_o=o, merge_m=m, merge_l=l, merge_final=softmax_finalize(o, l))
+    np.savez_compressed(os.path.join(HERE, "attention.npz"), **out)
+
+
+def moe():
+    rng = np.random.default_rng(303)
+    out = {}
+    # routing + permutation, with and without capacity
+    cases = [(64, 8, 2, None), (100, 8, 2, 20), (37, 4, 1, 6), (50, 16, 4, None)]
+    for i, (T, E, k, cap) in enumerate(cases):
+        logits = rng.standard_normal((T, E)).astype(np.float32)
+        cfg = dmoe.MoEConfig(num_experts=E, top_k=k, capacity_factor=1e9)
+        r = dmoe.route_tokens(logits, cfg, capacity=cap if cap is not None else T * k + 1)
+        # the transport descriptor is built from the un-dropped routing plus the same capacity
+        r0 = dmoe.route_tokens(logits, cfg, capacity=T * k + 1)
+        plan = smoe.plan_dispatch(r0.assignment, r0.weights, E, capacity=cap)
+        desc = descriptor_from_dispatch_plan(plan)
+        out[f"logits{i}"] = logits
+        out[f"meta{i}"] = np.array([T, E, k, -1 if cap is None else cap])
+        out[f"assignment{i}"], out[f"weights{i}"] = r.assignment, r.weights
+        out[f"load{i}"], out[f"overflow{i}"] = r.load, np.array(r.overflow)
+        out[f"token_of_slot{i}"], out[f"expert_of_slot{i}"] = desc.token_of_slot, desc.expert_of_slot
+        out[f"combine_weights{i}"] = desc.combine_weights
+        out[f"group_sizes{i}"], out[f"group_offsets{i}"] = desc.group_sizes, desc.group_offsets
+    out["n_route"] = np.array(len(cases))
+    # grouped GEMM / SwiGLU block / full layer / expert-parallel layer
+    T, H, Fdim, E, k = 48, 32, 64, 4, 2
+    x = rt(rng.standard_normal((T, H)), bf16)
+    Wr = rt(rng.standard_normal((H, E)) / np.sqrt(H), bf16)
+    Wg = rt(rng.standard_normal((E, H, Fdim)) / np.sqrt(H), bf16)
+    Wu = rt(rng.standard_normal((E, H, Fdim)) / np.sqrt(H), bf16)
+    Wd = rt(rng.standard_normal((E, Fdim, H)) / np.sqrt(Fdim), bf16)
+    gs = np.array([10, 0, 25, 13], np.int64)
+    out.update(x=x, Wr=Wr, Wg=Wg, Wu=Wu, Wd=Wd, gs=gs)
+    out["grouped_gemm"] = np.asarray(tessera.ops.grouped_gemm(x, Wg, gs), np.float32)
+    out["swiglu_block"] = np.asarray(tessera.ops.moe_swiglu_block(x, Wg, Wu, Wd, gs), np.float32)
+    out["moe_layer_k1"] = np.asarray(F.moe_layer(x, Wr, Wg, Wu, Wd, top_k=1), np.float32)
+    out["moe_layer_k2"] = np.asarray(F.moe_layer(x, Wr, Wg, Wu, Wd, top_k=2), np.float32)
+    cfg = dmoe.MoEConfig(num_experts=E, top_k=k, capacity_factor=1e9)
+    for R in (2, 4):
+        y, dropped = dmoe.megamoe_layer(x, Wr, Wg, Wu, Wd, world_size=R, config=cfg,
+                                        capacity=T * k)
+        out[f"megamoe_w{R}"] = np.asarray(y, np.float32)
+        out[f"megamoe_dropped_w{R}"] = np.array(dropped)
+    np.savez_compressed(os.path.join(HERE, "moe.npz"), **out)
+
+
+if __name__ == "__main__":
+    gemm()
+    attention()
+    moe()
+    print("wrote", sorted(f for f in os.listdir(HERE) if f.endswith(".npz")))

@@ -39,8 +39,11 @@ sys.path.insert(0, ROOT)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
-# summarised under profiles/; None where no capture exists yet.
-NCU_TRAFFIC_BYTES = {"gemm_8192": None, "attn_prefill": None, "attn_decode": None, "moe": None}
+# summarised under profiles/. The GEMM capture is the benchmark size itself; the attention and MoE
+# captures ran a quarter-size case (heads, batch, experts x slots) and are scaled x4, the traffic
+# of these kernels being proportional to those counts. The MoE figure is the sum of its two
+# grouped GEMM launches.
+NCU_TRAFFIC_BYTES = {"gemm_8192": 1.154e9, "attn_prefill": 1.007e9, "attn_decode": 2.171e9, "moe": 4.78e9}
 
 
 def load_peaks():
@@ -66,7 +69,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-i",
-                 str(self.gpu), "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 str(self.gpu), "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except Exception:
             self.proc = None
@@ -162,6 +165,21 @@ def timed_steps(ranks, device, fn, steps, warmup, flush=True):
     return [max(r[i] for r in allr) for i in range(steps)]
 
 
+def clock_probe(device, sampler, fn, seconds=0.4):
+    """Runs `fn` back to back for `seconds` and returns the sampler marks around it: the clocks
+    the GPU holds under this load (single timed steps are shorter than one nvidia-smi sample)."""
+    fn()
+    device.synchronize()
+    time.sleep(0.05)
+    m0 = sampler.mark()
+    t0 = time.perf_counter()
+    while time.perf_counter() - t0 < seconds:
+        for _ in range(8):
+            fn()
+        device.synchronize()
+    return m0, sampler.mark()
+
+
 def tiled_normal(rng, shape, tile_axis_len, scale, dtype):
     """N(0,1)*scale values; drawn for `tile_axis_len` entries of axis 0 and repeated along it
     (same distribution, a fraction of the host time)."""
@@ -185,12 +203,26 @@ def bench_gemm(ranks, args, peaks, peak_kind, sampler):
     dB = DeviceArray.from_host(B)            # full W on every rank; a rank reads its column block
     dY = DeviceArray.zeros((n, n), bfloat16)
     comm = None
-    stage = gathered = None
+    stage = gathered = fused = None
+    tp_mode = "single"
     if W > 1:
         uid = ranks.bcast(collectives.Communicator.unique_id() if ranks.rank == 0 else None)
         comm = collectives.Communicator.from_unique_id(uid, W, ranks.rank)
         stage = DeviceArray((n, nb), bfloat16)
         gathered = DeviceArray((W, n, nb), bfloat16)
+        tp_mode = "nccl"
+        if args.tp_mode == "fused":
+            try:
+                fused = parallel.TensorParallelGemm(n, n, n, W, ranks.rank, ranks.gather, bfloat16, bfloat16)
+                dY = fused.Y
+                tp_mode = "fused"
+            except Exception as exc:
+                fused = None
+                tp_mode = f"nccl (fused set-up failed: {exc})"
+            # every rank must take the same path
+            modes = ranks.gather(tp_mode)
+            if any(m != "fused" for m in modes):
+                fused, tp_mode = None, next(m for m in modes if m != "fused")
 
     def gemm_only():
         if W == 1:
@@ -201,6 +233,9 @@ def bench_gemm(ranks, args, peaks, peak_kind, sampler):
                       n, n, n, nb, 0, 0, 0, _lib.BF16, _lib.BF16, None)
 
     def step():
+        if fused is not None:
+            fused(dA, dB)
+            return
         gemm_only()
         if W > 1:
             comm.all_gather(stage, gathered)
@@ -212,6 +247,7 @@ def bench_gemm(ranks, args, peaks, peak_kind, sampler):
     m0 = sampler.mark()
     times = timed_steps(ranks, device, step, args.steps, args.warmup)
     m1 = sampler.mark()
+    probe_marks = clock_probe(device, sampler, step)
     launches = (device.launch_count() - l0) * args.steps // (args.steps + args.warmup)
     kernel_times = timed_steps(ranks, device, gemm_only, max(3, args.steps // 2), 1)
     flops = 2.0 * n * n * n
@@ -255,7 +291,8 @@ def bench_gemm(ranks, args, peaks, peak_kind, sampler):
                      "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
                      "traffic": NCU_TRAFFIC_BYTES["gemm_8192"], "peak_kind": f"burst cuBLAS bf16, of {peak_kind}",
                      "kernel_ms": k_ms, "kernel": "gemm_kernel<bf16,plain> (tcgen05 128x256x64, 4-stage TMA)"},
-        "e2e": e2e, "check_max_rel_err": rel, "clock_marks": (m0, m1),
+        "e2e": e2e, "check_max_rel_err": rel, "clock_marks": (m0, m1), "probe_marks": probe_marks,
+        "tp_mode": tp_mode,
     }
 
 
@@ -408,6 +445,60 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------------------------------------------ small cases for ncu
+def profile_case(name: str) -> None:
+    """One warm-up and two launches of one kernel on a small case (inputs larger than L2, well
+    under a few GB): what `ncu --set full -k regex:<kernel> -c 2` is pointed at."""
+    import ctypes
+    from tessera_b200 import _lib, device
+    from tessera_b200.device import DeviceArray, bfloat16
+    device.set_device(0)
+    rng = np.random.default_rng(1)
+
+    def dev_normal(shape, scale=1.0):
+        return DeviceArray.from_host(tiled_normal(rng, shape, min(shape[0], 2), scale, bfloat16))
+
+    if name == "gemm":
+        n = 8192
+        a, b = dev_normal((n, n), 1 / np.sqrt(n)), dev_normal((n, n), 1 / np.sqrt(n))
+        d = DeviceArray.zeros((n, n), bfloat16)
+        fn = lambda: _lib.call("tessera_sm100_gemm_device", a.ptr, b.ptr, d.ptr, 1, n, n, n, _lib.BF16,
+                               _lib.BF16, None)
+    elif name == "attn_prefill":
+        B, H, S, D = 4, 16, 4096, 128
+        q, k, v = (dev_normal((B, H, S, D)) for _ in range(3))
+        o = DeviceArray.zeros((B, H, S, D), bfloat16)
+        fn = lambda: _lib.call("tessera_sm100_flash_attn_fwd_device", q.ptr, k.ptr, v.ptr, o.ptr, B, H, H, S,
+                               S, D, ctypes.c_float(1 / np.sqrt(D)), 1, None)
+    elif name == "attn_decode":
+        B, Hq, Hkv, S, D = 16, 32, 8, 8192, 128
+        q = dev_normal((B, Hq, 1, D))
+        k, v = dev_normal((B, Hkv, S, D)), dev_normal((B, Hkv, S, D))
+        o = DeviceArray.zeros((B, Hq, 1, D), bfloat16)
+        lib = _lib.load()
+        ns = lib.tessera_sm100_attn_decode_splits(B, Hq, Hkv, S)
+        scr = DeviceArray((max(1, lib.tessera_sm100_attn_decode_scratch_bytes(B, Hq, ns)),), np.uint8)
+        fn = lambda: _lib.call("tessera_sm100_attn_decode_device", q.ptr, k.ptr, v.ptr, o.ptr, B, Hq, Hkv, S,
+                               D, ctypes.c_float(1 / np.sqrt(D)), ns, scr.ptr, None)
+    elif name == "moe":
+        T, H, F, E, k = 2048, 4096, 14336, 2, 2
+        x = dev_normal((T, H))
+        logits = DeviceArray.from_host(rng.standard_normal((T, E), dtype=np.float32))
+        wg, wu = dev_normal((E, H, F), 1 / np.sqrt(H)), dev_normal((E, H, F), 1 / np.sqrt(H))
+        wd = dev_normal((E, F, H), 1 / np.sqrt(F))
+        out = DeviceArray.zeros((T, H), bfloat16)
+        ws = DeviceArray((_lib.load().tessera_sm100_moe_workspace_bytes(T, H, F, E, k),), np.uint8)
+        fn = lambda: _lib.call("tessera_sm100_moe_layer_device", x.ptr, logits.ptr, wg.ptr, wu.ptr, wd.ptr,
+                               out.ptr, T, H, F, E, k, 1, -1, _lib.BF16, _lib.BF16, ws.ptr, None)
+    else:
+        raise SystemExit(f"unknown profile case {name}")
+    for _ in range(3):
+        fn()
+    device.synchronize()
+    device.check_device_error("profile case")
+    print(f"profile case {name}: 3 launches done")
+
+
 # ------------------------------------------------------------------------------ main
 def main():
     ap = argparse.ArgumentParser()
@@ -417,7 +508,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="all", choices=["all", "gemm", "attn_prefill", "attn_decode", "moe"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tp-mode", default="fused", choices=["fused", "nccl"],
+                    help="N>1 GEMM: all-gather fused into the epilogue (peer TMA stores) or NCCL after it")
+    ap.add_argument("--profile-case", default=None,
+                    help="run three launches of one kernel on a small case and exit (for ncu)")
     args = ap.parse_args()
+    if args.profile_case:
+        profile_case(args.profile_case)
+        return
     args.warmup = max(args.warmup, 3)
 
     if args.impl == "reference":
@@ -449,8 +547,19 @@ def main():
                 extras[name] = fn(ranks, args, peaks, peak_kind)
             except Exception as exc:
                 extras[name] = {"error": f"{type(exc).__name__}: {exc}"}
-                ranks.barrier() if False else None
-    clocks = sampler.summary(*g.pop("clock_marks")) if ranks.rank == 0 else None
+    timed_marks, probe_marks = g.pop("clock_marks"), g.pop("probe_marks")
+    clocks = None
+    if ranks.rank == 0:
+        under_load = sampler.summary(*probe_marks)
+        in_steps = sampler.summary(*timed_marks)
+        whole = sampler.summary()
+        clocks = {"sm_mhz": under_load["sm_mhz"], "sm_max_mhz": under_load["sm_max_mhz"] or whole["sm_max_mhz"],
+                  "reasons": sorted(set(under_load["reasons"]) | set(in_steps["reasons"]) | set(whole["reasons"])),
+                  "samples": under_load["samples"],
+                  "how": "median SM clock while the timed step runs back to back for 0.4 s right after the "
+                         "timed region (one timed step is shorter than an nvidia-smi sample); reasons are the "
+                         "union over the whole run",
+                  "sm_mhz_during_timed_steps": in_steps["sm_mhz"], "samples_during_timed_steps": in_steps["samples"]}
     sampler.stop()
 
     cpu = None
@@ -465,8 +574,11 @@ def main():
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic (seeded N(0,1)/sqrt(K) operands)",
             "config": {"workload": "gemm_bf16_8192: A[8192,8192] x B[8192,8192] -> Y bf16, fp32 accumulate",
-                       "parallelism": "single GPU" if W == 1 else f"column-parallel tp{W}: W split on N, "
-                                      f"NCCL all-gather of Y + strided copies into row-major Y",
+                       "parallelism": "single GPU" if W == 1 else (
+                           f"column-parallel tp{W}: W split on N, all-gather of Y fused into the GEMM "
+                           f"epilogue (TMA stores into every rank's Y over NVLink)" if g["tp_mode"] == "fused"
+                           else f"column-parallel tp{W}: W split on N, NCCL all-gather of Y + strided copies "
+                                f"into row-major Y [{g['tp_mode']}]"),
                        "l2": "L2 flushed (256 MiB write) before every timed step, outside the event bracket",
                        "timing": "CUDA events per step on the launching stream, max over ranks, mean of steps"},
             "roofline": g["roofline"], "e2e": g["e2e"], "gpu_launches": g["gpu_launches"],

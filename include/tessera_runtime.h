@@ -137,6 +137,11 @@ TsrStatus tsrDestroyKernel(tsrKernel kernel);
  * TSR_STATUS_UNIMPLEMENTED when none handles (target, kernel name). */
 TsrStatus tsrLaunchKernel(tsrStream s, tsrKernel kernel, void** args, size_t nargs);
 TsrStatus tsrRegisterGpuLauncher(tsrGpuLauncherFn fn, void* user);
+/* The library's own launcher for target "nvidia_sm100" (kernel names tessera.sm100.*), exported
+ * so that a runtime with the same registry, such as the reference's libtessera_runtime
+ * (src/runtime/src/tessera_runtime.cpp:1210-1222), can register it. */
+TsrStatus tessera_sm100_gpu_launcher(const char* target, const char* kernel_name,
+                                     const tsrGpuLaunchParams* params, void* user);
 
 #ifdef __cplusplus
 }

@@ -88,6 +88,15 @@ int tessera_sm100_gemm_strided_device(const void* A, const void* B, void* D, int
                                       int N, int K, long long lda, long long ldb, long long ldd,
                                       long long strideA, long long strideB, long long strideD,
                                       int in_dtype, int out_dtype, void* stream);
+/* Column-parallel GEMM with the all-gather of Y fused into the epilogue
+ * (Y = all_gather(A @ W_r, axis=1), python/tessera/compiler/tensor_parallel.py:118-123): rank r
+ * multiplies columns [r*N/world, (r+1)*N/world) of the full B[K,N] and TMA-stores every output
+ * tile into all `world` copies of Y. Y_ptrs[i] is rank i's Y base (a CUDA-IPC-mapped peer pointer
+ * for i != rank, see tessera_sm100_ipc_*). Each copy is complete once every rank's kernel has
+ * finished, so ranks synchronise their streams and then meet at a host barrier. world <= 8. */
+int tessera_sm100_gemm_allgather_device(const void* A, const void* B, void* const* Y_ptrs, int world,
+                                        int rank, int M, int N_total, int K, int in_dtype,
+                                        int out_dtype, void* stream);
 
 /* ---- MoE grouped GEMM ------------------------------------------------------------------
  * out[T,N] = rows of group e of x[T,K] times w[e] (w is [E,K,N]); offsets[E+1] int32 row

@@ -16,12 +16,13 @@ size_t out_size(int out_dtype) { return out_dtype == TESSERA_SM100_F32 ? 4 : 2; 
 
 template <typename OutT, int kMode>
 int launch_kernel(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2,
-                  const CUtensorMap& tD, const Params& p, int grid, cudaStream_t stream) {
+                  const CUtensorMap& tD, const PeerMaps& peers, const Params& p, int grid,
+                  cudaStream_t stream) {
   // The attribute is per device; setting it on every call is cheap and keeps multi-device
   // processes correct.
   TSB_CUDA_OK(cudaFuncSetAttribute(gemm_kernel<OutT, kMode>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));
-  gemm_kernel<OutT, kMode><<<grid, NUM_THREADS, SMEM_ALLOC, stream>>>(tA, tB, tB2, tD, p);
+  gemm_kernel<OutT, kMode><<<grid, NUM_THREADS, SMEM_ALLOC, stream>>>(tA, tB, tB2, tD, peers, p);
   TSB_CUDA_OK(cudaGetLastError());
   note_launch();
   return kOk;
@@ -29,16 +30,16 @@ int launch_kernel(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMa
 
 template <int kMode>
 int dispatch_out(int out_dtype, const CUtensorMap& tA, const CUtensorMap& tB,
-                 const CUtensorMap& tB2, const CUtensorMap& tD, const Params& p, int grid,
-                 cudaStream_t stream) {
+                 const CUtensorMap& tB2, const CUtensorMap& tD, const PeerMaps& peers,
+                 const Params& p, int grid, cudaStream_t stream) {
   switch (out_dtype) {
     case TESSERA_SM100_F32:
       if constexpr (kMode == kGroupedSwiGLU) break;
-      else return launch_kernel<float, kMode>(tA, tB, tB2, tD, p, grid, stream);
+      else return launch_kernel<float, kMode>(tA, tB, tB2, tD, peers, p, grid, stream);
     case TESSERA_SM100_BF16:
-      return launch_kernel<__nv_bfloat16, kMode>(tA, tB, tB2, tD, p, grid, stream);
+      return launch_kernel<__nv_bfloat16, kMode>(tA, tB, tB2, tD, peers, p, grid, stream);
     case TESSERA_SM100_F16:
-      return launch_kernel<__half, kMode>(tA, tB, tB2, tD, p, grid, stream);
+      return launch_kernel<__half, kMode>(tA, tB, tB2, tD, peers, p, grid, stream);
     default:
       break;
   }
@@ -62,7 +63,8 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 // batch strides, all in elements. Every stride must make a 16-byte multiple.
 int launch_plain(const void* A, const void* B, void* D, int batch, int M, int N, int K,
                  long long lda, long long ldb, long long ldd, long long sA, long long sB,
-                 long long sD, int in_dtype, int out_dtype, cudaStream_t stream) {
+                 long long sD, int in_dtype, int out_dtype, cudaStream_t stream,
+                 void* const* peer_D = nullptr, int num_peers = 0) {
   if (!A || !B || !D || batch <= 0 || M <= 0 || N <= 0 || K <= 0) {
     set_last_error("gemm: null pointer or non-positive size (batch %d M %d N %d K %d)", batch, M,
                    N, K);
@@ -105,11 +107,35 @@ int launch_plain(const void* A, const void* B, void* D, int batch, int M, int N,
     if (!encode_tmap(&tD, tm_dtype(out_dtype), 3, D, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
       return kBadArg;
   }
+  static PeerMaps no_peers{};
+  PeerMaps peer_maps;
+  const PeerMaps* peers = &no_peers;
+  if (num_peers > 0) {
+    if (num_peers > MAX_PEERS || !peer_D) {
+      set_last_error("gemm: at most %d output copies are supported", MAX_PEERS);
+      return kBadArg;
+    }
+    uint64_t dims[3] = {(uint64_t)N, (uint64_t)M, (uint64_t)batch};
+    uint64_t str[2] = {(uint64_t)ldd * osz, (uint64_t)sD * osz};
+    uint32_t box[3] = {(uint32_t)(128 / osz), 32, 1};
+    for (int i = 0; i < num_peers; ++i) {
+      if (!peer_D[i] || !aligned16(peer_D[i])) {
+        set_last_error("gemm: output copy %d is null or not 16-byte aligned", i);
+        return kBadArg;
+      }
+      if (!encode_tmap(&peer_maps.m[i], tm_dtype(out_dtype), 3, peer_D[i], dims, str, box,
+                       CU_TENSOR_MAP_SWIZZLE_128B))
+        return kBadArg;
+    }
+    for (int i = num_peers; i < MAX_PEERS; ++i) peer_maps.m[i] = peer_maps.m[0];
+    peers = &peer_maps;
+  }
   Params p{};
   p.M = M;
   p.N = N;
   p.K = K;
   p.batch = batch;
+  p.num_peers = num_peers;
   p.m_tiles = (M + BM - 1) / BM;
   p.n_tiles = (N + BN - 1) / BN;
   p.idesc = make_idesc_f16(in_dtype == TESSERA_SM100_BF16, false, true, BM, BN);
@@ -120,7 +146,7 @@ int launch_plain(const void* A, const void* B, void* D, int batch, int M, int N,
   if (!p.err) return kDeviceFailed;
   const long long total = (long long)p.m_tiles * p.n_tiles * batch;
   const int grid = (int)std::min<long long>(total, sm_count());
-  return dispatch_out<kPlain>(out_dtype, tA, tB, tB, tD, p, grid, stream);
+  return dispatch_out<kPlain>(out_dtype, tA, tB, tB, tD, *peers, p, grid, stream);
 }
 
 // Ragged grouped GEMM on device pointers. x[T,K] rows sorted by group, w[E,K,N] (and w2 for
@@ -190,8 +216,10 @@ int launch_grouped(const void* x, const void* w, const void* w2, const int* offs
   // Upper bound on the number of tiles: every group may add one partial m-tile.
   const long long max_tiles = ((long long)(T + BM - 1) / BM + E) * p.n_tiles;
   const int grid = (int)std::min<long long>(max_tiles, sm_count());
-  if (swiglu) return dispatch_out<kGroupedSwiGLU>(out_dtype, tA, tB, tB2, tD, p, grid, stream);
-  return dispatch_out<kGrouped>(out_dtype, tA, tB, tB2, tD, p, grid, stream);
+  static PeerMaps no_peers{};
+  if (swiglu)
+    return dispatch_out<kGroupedSwiGLU>(out_dtype, tA, tB, tB2, tD, no_peers, p, grid, stream);
+  return dispatch_out<kGrouped>(out_dtype, tA, tB, tB2, tD, no_peers, p, grid, stream);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -348,6 +376,37 @@ int tessera_sm100_gemm_strided_device(const void* A, const void* B, void* D, int
                                       int in_dtype, int out_dtype, void* stream) {
   return gemm::launch_plain(A, B, D, batch, M, N, K, lda, ldb, ldd, strideA, strideB, strideD,
                             in_dtype, out_dtype, static_cast<cudaStream_t>(stream));
+}
+// Column-parallel GEMM with the all-gather fused into the epilogue. B is the full [K, N_total]
+// weight (rank r multiplies its columns [r*nb, (r+1)*nb), nb = N_total / world); Y_ptrs[i] is the
+// base of rank i's [M, N_total] output (peer pointers for i != rank). Every tile is stored into
+// all `world` copies, so when every rank's kernel has finished each copy holds the whole Y.
+int tessera_sm100_gemm_allgather_device(const void* A, const void* B, void* const* Y_ptrs, int world,
+                                        int rank, int M, int N_total, int K, int in_dtype,
+                                        int out_dtype, void* stream) {
+  if (!Y_ptrs || world <= 0 || world > gemm::MAX_PEERS || rank < 0 || rank >= world ||
+      N_total % world) {
+    set_last_error("gemm_allgather: bad arguments (world %d rank %d N %d; world <= %d, N %% world == 0)",
+                   world, rank, N_total, gemm::MAX_PEERS);
+    return kBadArg;
+  }
+  const int nb = N_total / world;
+  const size_t osz = out_dtype == TESSERA_SM100_F32 ? 4 : 2;
+  if (nb % 8) {
+    set_last_error("gemm_allgather: N / world (%d) must be a multiple of 8", nb);
+    return kBadArg;
+  }
+  void* outs[gemm::MAX_PEERS];
+  for (int i = 0; i < world; ++i) {
+    if (!Y_ptrs[i]) {
+      set_last_error("gemm_allgather: Y_ptrs[%d] is null", i);
+      return kBadArg;
+    }
+    outs[i] = static_cast<char*>(Y_ptrs[i]) + (size_t)rank * nb * osz;
+  }
+  const char* Bblk = static_cast<const char*>(B) + (size_t)rank * nb * 2;
+  return gemm::launch_plain(A, Bblk, outs[rank], 1, M, nb, K, K, N_total, N_total, 0, 0, 0, in_dtype,
+                            out_dtype, static_cast<cudaStream_t>(stream), outs, world);
 }
 int tessera_sm100_grouped_gemm_device(const void* x, const void* w, const int* offsets, void* out,
                                       int T, int K, int N, int E, int in_dtype, int out_dtype,

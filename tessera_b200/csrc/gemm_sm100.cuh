@@ -56,7 +56,15 @@ struct Params {
   const int* group_offsets;  // grouped modes: batch + 1 row offsets (device memory)
   void* D;                   // grouped modes: output base for masked stores
   long long ldd;             // grouped modes: output leading dimension (elements)
+  int num_peers;             // plain mode: > 0 = store each tile through peers.m[0..num_peers)
   int* err;
+};
+
+// Output tensor maps of the other ranks (column-parallel GEMM whose epilogue stores every tile
+// into each rank's copy of Y: the all-gather fused into the GEMM).
+constexpr int MAX_PEERS = 8;
+struct PeerMaps {
+  CUtensorMap m[MAX_PEERS];
 };
 
 struct Tile {
@@ -152,7 +160,7 @@ template <typename OutT, int kMode>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmD,
-            const Params p) {
+            const __grid_constant__ PeerMaps peers, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -357,7 +365,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           __syncwarp();
           if (lane == 0) {
             const int d_b = (kMode == kPlain) ? tile.b : 0;
-            tma_store_3d(&tmD, buf, col0, row0, d_b);
+            if (kMode == kPlain && p.num_peers > 0) {
+              // Same tile into every rank's Y (this rank's own copy is one of the maps); plain
+              // TMA stores, no multicast. One bulk group covers all of them.
+              for (int i = 0; i < p.num_peers; ++i) tma_store_3d(&peers.m[i], buf, col0, row0, d_b);
+            } else {
+              tma_store_3d(&tmD, buf, col0, row0, d_b);
+            }
             tma_store_commit();
           }
         } else {

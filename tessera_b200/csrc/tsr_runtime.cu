@@ -540,6 +540,13 @@ TsrStatus tsrDestroyKernel(tsrKernel k) {
   return TSR_STATUS_SUCCESS;
 }
 
+// The built-in launcher as a public symbol, so another runtime that implements the same
+// registry (the reference's libtessera_runtime) can register it.
+TsrStatus tessera_sm100_gpu_launcher(const char* target, const char* kernel_name,
+                                     const tsrGpuLaunchParams* params, void* user) {
+  return builtin_launcher(target, kernel_name, params, user);
+}
+
 TsrStatus tsrRegisterGpuLauncher(tsrGpuLauncherFn fn, void* user) {
   std::lock_guard<std::mutex> lk(g_mu);
   g_launcher = fn ? fn : (g_init ? builtin_launcher : nullptr);

@@ -131,6 +131,10 @@ class DeviceArray:
     def size(self) -> int:
         return int(np.prod(self.shape, dtype=np.int64))
 
+    @property
+    def ndim(self) -> int:
+        return len(self.shape)
+
     @classmethod
     def from_host(cls, arr: np.ndarray, stream=None) -> "DeviceArray":
         arr = np.ascontiguousarray(arr)

@@ -31,6 +31,49 @@ def tp_column_range(n: int, world: int, rank: int) -> tuple:
     return rank * nb, nb
 
 
+class TensorParallelGemm:
+    """Column-parallel GEMM whose epilogue is the all-gather: rank r multiplies its column block of
+    the full W and stores every output tile into every rank's Y over NVLink
+    (``tessera_sm100_gemm_allgather_device``). ``gather_host`` exchanges the 64-byte CUDA IPC
+    handles of the Y buffers (e.g. ``torch.distributed.all_gather_object`` over gloo). After a
+    call, synchronise the stream and pass a host barrier before reading ``self.Y``."""
+
+    def __init__(self, M: int, N: int, K: int, world: int, rank: int, gather_host, dtype, out_dtype):
+        import ctypes
+        from . import _lib, device
+        from .device import DeviceArray
+        tp_column_range(N, world, rank)
+        self.M, self.N, self.K, self.world, self.rank = M, N, K, world, rank
+        self._in, self._out = device.dtype_code(dtype), device.dtype_code(out_dtype)
+        self.Y = DeviceArray.zeros((M, N), out_dtype)
+        device.synchronize()
+        handle = ctypes.create_string_buffer(64)
+        _lib.call("tessera_sm100_ipc_get_handle", self.Y.ptr, handle)
+        handles = gather_host(handle.raw)
+        self._opened = []
+        ptrs = []
+        for r in range(world):
+            if r == rank:
+                ptrs.append(self.Y.ptr)
+            else:
+                p = ctypes.c_void_p()
+                _lib.call("tessera_sm100_ipc_open_handle", ctypes.c_char_p(handles[r]), ctypes.byref(p))
+                self._opened.append(p.value)
+                ptrs.append(p.value)
+        self._ptrs = (ctypes.c_void_p * world)(*ptrs)
+
+    def __call__(self, A, W_full, stream=None) -> None:
+        from . import _lib, device
+        _lib.call("tessera_sm100_gemm_allgather_device", A.ptr, W_full.ptr, self._ptrs, self.world,
+                  self.rank, self.M, self.N, self.K, self._in, self._out, device._stream_handle(stream))
+
+    def close(self) -> None:
+        from . import _lib
+        for p in self._opened:
+            _lib.call("tessera_sm100_ipc_close_handle", p)
+        self._opened = []
+
+
 # ---------------------------------------------------------------------------- expert parallel
 @dataclass
 class EPPlan:

@@ -1,0 +1,115 @@
+"""Two-GPU runs (one process per GPU, NCCL): collectives through the C ABI, the column-parallel
+GEMM with the all-gather fused into its epilogue, and the expert-parallel MoE forward, each
+against the single-device oracle. Skipped when fewer than two GPUs are visible."""
+import multiprocessing as mp
+import socket
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, q):
+    try:
+        import torch.distributed as dist
+
+        from oracle import tessera_oracle as orc
+        from tessera_b200 import collectives, device, parallel
+        from tessera_b200.device import DeviceArray, bfloat16
+        device.set_device(rank)
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+
+        def gather(obj):
+            out = [None] * world
+            dist.all_gather_object(out, obj)
+            return out
+
+        box = [collectives.Communicator.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        comm = collectives.Communicator.from_unique_id(box[0], world, rank)
+        errs = {}
+        # --- collectives
+        x = np.arange(8, dtype=np.float32) + 100 * rank
+        dx, dg = DeviceArray.from_host(x), DeviceArray((world * 8,), np.float32)
+        comm.all_gather(dx, dg)
+        dr = DeviceArray((8,), np.float32)
+        comm.all_reduce(dx, dr, "sum")
+        device.synchronize()
+        want = np.concatenate([np.arange(8, dtype=np.float32) + 100 * r for r in range(world)])
+        errs["all_gather"] = float(np.abs(dg.download() - want).max())
+        errs["all_reduce"] = float(np.abs(dr.download() - want.reshape(world, 8).sum(0)).max())
+        send_counts = [(rank + p) % 3 + 1 for p in range(world)]        # rows of 4 floats
+        recv_counts = [(p + rank) % 3 + 1 for p in range(world)]
+        rows = np.arange(sum(send_counts) * 4, dtype=np.float32).reshape(-1, 4) + 1000 * rank
+        tr = parallel.NcclTransport(comm, gather)
+        got = tr.exchange_rows(DeviceArray.from_host(rows), send_counts, recv_counts)
+        device.synchronize()
+        exp = []
+        for p in range(world):
+            sc = [(p + d) % 3 + 1 for d in range(world)]
+            src_rows = np.arange(sum(sc) * 4, dtype=np.float32).reshape(-1, 4) + 1000 * p
+            off = sum(sc[:rank])
+            exp.append(src_rows[off:off + sc[rank]])
+        errs["all_to_all_v"] = float(np.abs(got.download() - np.concatenate(exp)).max())
+        # --- column-parallel GEMM with fused all-gather
+        rng = np.random.default_rng(5)
+        M, N, K = 384, 1024, 512
+        A = (rng.standard_normal((M, K), dtype=np.float32) / np.sqrt(K)).astype(bfloat16)
+        Wm = rng.standard_normal((K, N), dtype=np.float32).astype(bfloat16)
+        tp = parallel.TensorParallelGemm(M, N, K, world, rank, gather, bfloat16, bfloat16)
+        tp(DeviceArray.from_host(A), DeviceArray.from_host(Wm))
+        device.synchronize()
+        dist.barrier()
+        errs["tp_gemm"] = orc.max_rel_err(tp.Y.download(), orc.gemm(A, Wm))
+        dist.barrier()
+        tp.close()
+        # --- expert-parallel MoE
+        T, H, F, E, k = 256, 128, 256, 8, 2
+        xs = rng.standard_normal((T, H), dtype=np.float32).astype(bfloat16)
+        logits = rng.standard_normal((T, E), dtype=np.float32)
+        wg = (rng.standard_normal((E, H, F), dtype=np.float32) / 11).astype(bfloat16)
+        wu = (rng.standard_normal((E, H, F), dtype=np.float32) / 11).astype(bfloat16)
+        wd = (rng.standard_normal((E, F, H), dtype=np.float32) / 16).astype(bfloat16)
+        Tl, Ep = T // world, E // world
+        sl, es = slice(rank * Tl, (rank + 1) * Tl), slice(rank * Ep, (rank + 1) * Ep)
+        backend = parallel.GpuMoeBackend(*(DeviceArray.from_host(np.ascontiguousarray(w[es])) for w in (wg, wu, wd)))
+        moe = parallel.ExpertParallelMoE(E, k, tr, backend)
+        y = moe.forward(DeviceArray.from_host(xs[sl]), np.ascontiguousarray(logits[sl]))
+        device.synchronize()
+        ref = orc.moe_layer_from_logits(xs, logits, wg, wu, wd, k)[0]
+        errs["ep_moe"] = orc.max_rel_err(y.download(), ref[sl])
+        device.check_device_error("multi-gpu test")
+        dist.barrier()
+        comm.close()
+        dist.destroy_process_group()
+        q.put((rank, errs, None))
+    except Exception as exc:
+        import traceback
+        q.put((rank, None, traceback.format_exc()))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_two_gpu_collectives_tp_gemm_and_ep_moe():
+    from tessera_b200 import device
+    if device.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, errs, exc in results:
+        assert exc is None, f"rank {rank}:\n{exc}"
+        assert errs["all_gather"] == 0 and errs["all_reduce"] == 0 and errs["all_to_all_v"] == 0, errs
+        assert errs["tp_gemm"] < 1e-2 and errs["ep_moe"] < 1e-2, errs

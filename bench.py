@@ -247,8 +247,8 @@ def bench_gemm(ranks, args, peaks, peak_kind, sampler):
     m0 = sampler.mark()
     times = timed_steps(ranks, device, step, args.steps, args.warmup)
     m1 = sampler.mark()
-    probe_marks = clock_probe(device, sampler, step)
     launches = (device.launch_count() - l0) * args.steps // (args.steps + args.warmup)
+    probe_marks = clock_probe(device, sampler, step)
     kernel_times = timed_steps(ranks, device, gemm_only, max(3, args.steps // 2), 1)
     flops = 2.0 * n * n * n
     ms = statistics.mean(times)
@@ -527,6 +527,8 @@ def main():
                "--master-addr", "127.0.0.1", "--master-port", "29541", os.path.abspath(__file__)] + sys.argv[1:]
         sys.exit(subprocess.call(cmd))
 
+    # NCCL writes its version/INFO lines to stdout by default; stdout carries the one JSON line.
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     ranks = Ranks(args.gpus)
     from tessera_b200 import device
     device.set_device(ranks.local_rank)

@@ -43,6 +43,10 @@ long long tessera_sm100_launch_count(void);
  * (tessera_nvidia_gemm.cpp:617-697). */
 int tessera_sm100_device_alloc(void** out, size_t bytes);
 int tessera_sm100_device_free(void* ptr);
+/* Caching device allocator (blocks are recycled without cudaFree; stream-ordered reuse). */
+int tessera_sm100_pool_alloc(void** out, size_t bytes);
+int tessera_sm100_pool_free(void* ptr);
+int tessera_sm100_pool_release(void);
 int tessera_sm100_device_memset(void* ptr, int value, size_t bytes, void* stream);
 int tessera_sm100_device_upload(void* dst, const void* src, size_t bytes, void* stream);
 int tessera_sm100_device_download(void* dst, const void* src, size_t bytes, void* stream);

@@ -61,6 +61,24 @@ int tessera_sm100_device_free(void* ptr) {
   TSB_CUDA_OK(cudaFree(ptr));
   return kOk;
 }
+// Caching allocator shared with the host-pointer entry points: freed blocks are kept and handed
+// out again, so steady-state loops make no cudaMalloc/cudaFree calls (each of which synchronises
+// the device). A block may be reused as soon as it is freed: free it only after the work that
+// uses it has been enqueued, and use one stream per pool block chain.
+int tessera_sm100_pool_alloc(void** out, size_t bytes) {
+  if (!out) return kBadArg;
+  if (int rc = ensure_device()) return rc;
+  *out = pool_alloc(bytes);
+  return *out ? kOk : kDeviceFailed;
+}
+int tessera_sm100_pool_free(void* ptr) {
+  pool_free(ptr);
+  return kOk;
+}
+int tessera_sm100_pool_release(void) {
+  pool_release_all();
+  return kOk;
+}
 int tessera_sm100_device_memset(void* ptr, int value, size_t bytes, void* stream) {
   if (!ptr) return kBadArg;
   TSB_CUDA_OK(cudaMemsetAsync(ptr, value, bytes, static_cast<cudaStream_t>(stream)));

@@ -113,14 +113,17 @@ class Event:
 class DeviceArray:
     """A dense row-major array in device memory (shape + dtype + pointer)."""
 
-    def __init__(self, shape: Sequence[int], dtype, ptr: Optional[int] = None, owner=None):
+    def __init__(self, shape: Sequence[int], dtype, ptr: Optional[int] = None, owner=None,
+                 pooled: bool = False):
         self.shape = tuple(int(s) for s in shape)
         self.dtype = np.dtype(dtype)
         self.nbytes = int(np.prod(self.shape, dtype=np.int64)) * self.dtype.itemsize
         self._owner = owner
+        self._pooled = bool(pooled) and ptr is None
         if ptr is None:
             h = ctypes.c_void_p()
-            _lib.call("tessera_sm100_device_alloc", ctypes.byref(h), max(self.nbytes, 1))
+            _lib.call("tessera_sm100_pool_alloc" if self._pooled else "tessera_sm100_device_alloc",
+                      ctypes.byref(h), max(self.nbytes, 1))
             self.ptr = int(h.value)
             self._owns = True
         else:
@@ -136,9 +139,9 @@ class DeviceArray:
         return len(self.shape)
 
     @classmethod
-    def from_host(cls, arr: np.ndarray, stream=None) -> "DeviceArray":
+    def from_host(cls, arr: np.ndarray, stream=None, pooled: bool = False) -> "DeviceArray":
         arr = np.ascontiguousarray(arr)
-        out = cls(arr.shape, arr.dtype)
+        out = cls(arr.shape, arr.dtype, pooled=pooled)
         out.upload(arr, stream)
         return out
 
@@ -175,7 +178,7 @@ class DeviceArray:
 
     def free(self) -> None:
         if self._owns and self.ptr:
-            _lib.call("tessera_sm100_device_free", self.ptr)
+            _lib.call("tessera_sm100_pool_free" if self._pooled else "tessera_sm100_device_free", self.ptr)
             self.ptr = 0
             self._owns = False
 

@@ -197,13 +197,19 @@ class NcclTransport:
         self.stream = stream
 
     def all_gather_small(self, arr: np.ndarray) -> np.ndarray:
-        return np.stack(self._gather_host(np.asarray(arr)))
+        """Small integer metadata over NCCL (one upload, one all-gather, one download)."""
+        from .device import DeviceArray
+        a = np.ascontiguousarray(arr, np.int32)
+        send = DeviceArray.from_host(a, pooled=True)
+        recv = DeviceArray((self.world,) + a.shape, np.int32, pooled=True)
+        self.comm.all_gather(send, recv, self.stream)
+        return recv.download(stream=self.stream).astype(np.int64)
 
     def exchange_rows(self, rows, send_counts, recv_counts):
         from .device import DeviceArray
         width = rows.shape[1]
         row_bytes = width * rows.dtype.itemsize
-        out = DeviceArray((int(np.sum(recv_counts)), width), rows.dtype)
+        out = DeviceArray((int(np.sum(recv_counts)), width), rows.dtype, pooled=True)
         self.comm.all_to_all_v(rows.ptr, [int(c) * row_bytes for c in send_counts], out.ptr,
                                [int(c) * row_bytes for c in recv_counts], self.stream)
         return out
@@ -223,8 +229,8 @@ class GpuMoeBackend:
         from .device import DeviceArray, _stream_handle
         logits = np.ascontiguousarray(logits, np.float32)
         T, E = logits.shape
-        dl = DeviceArray.from_host(logits)
-        da, dw = DeviceArray((T, top_k), np.int32), DeviceArray((T, top_k), np.float32)
+        dl = DeviceArray.from_host(logits, pooled=True)
+        da, dw = DeviceArray((T, top_k), np.int32, pooled=True), DeviceArray((T, top_k), np.float32, pooled=True)
         _lib.call("tessera_sm100_moe_route_device", dl.ptr, T, E, top_k, int(normalize), da.ptr, dw.ptr,
                   _stream_handle(self.stream))
         return da.download(), dw.download()
@@ -234,9 +240,9 @@ class GpuMoeBackend:
         from .device import DeviceArray, _stream_handle
         index = np.ascontiguousarray(index, np.int32)
         S, H = int(index.shape[0]), rows.shape[1]
-        out = DeviceArray((S, H), rows.dtype)
+        out = DeviceArray((S, H), rows.dtype, pooled=True)
         if S:
-            didx = DeviceArray.from_host(index)
+            didx = DeviceArray.from_host(index, pooled=True)
             _lib.call("tessera_sm100_moe_dispatch_device", rows.ptr, didx.ptr, out.ptr, rows.shape[0], S,
                       H, self._code, _stream_handle(self.stream))
         return out
@@ -246,9 +252,9 @@ class GpuMoeBackend:
         from .device import DeviceArray, _stream_handle
         S, H = rows.shape
         Ep, _, F = self.wg.shape
-        doff = DeviceArray.from_host(np.ascontiguousarray(group_offsets, np.int32))
-        hidden = DeviceArray((max(S, 1), F), rows.dtype)
-        out = DeviceArray((S, self.wd.shape[2]), rows.dtype)
+        doff = DeviceArray.from_host(np.ascontiguousarray(group_offsets, np.int32), pooled=True)
+        hidden = DeviceArray((max(S, 1), F), rows.dtype, pooled=True)
+        out = DeviceArray((S, self.wd.shape[2]), rows.dtype, pooled=True)
         if S:
             sh = _stream_handle(self.stream)
             _lib.call("tessera_sm100_grouped_swiglu_device", rows.ptr, self.wg.ptr, self.wu.ptr, doff.ptr,
@@ -262,9 +268,9 @@ class GpuMoeBackend:
         from .device import DeviceArray, _stream_handle
         k = slot_of.shape[1]
         H = rows.shape[1]
-        dso = DeviceArray.from_host(np.ascontiguousarray(slot_of, np.int32))
-        dw = DeviceArray.from_host(np.ascontiguousarray(weights, np.float32))
-        out = DeviceArray((num_tokens, H), rows.dtype)
+        dso = DeviceArray.from_host(np.ascontiguousarray(slot_of, np.int32), pooled=True)
+        dw = DeviceArray.from_host(np.ascontiguousarray(weights, np.float32), pooled=True)
+        out = DeviceArray((num_tokens, H), rows.dtype, pooled=True)
         _lib.call("tessera_sm100_moe_combine_device", rows.ptr, dso.ptr, dw.ptr, out.ptr, num_tokens, k, H,
                   self._code, self._code, _stream_handle(self.stream))
         return out

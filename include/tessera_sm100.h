@@ -174,6 +174,27 @@ size_t tessera_sm100_attn_decode_scratch_bytes(int B, int Hq, int splits);
 int tessera_sm100_attn_decode_device(const void* Q, const void* K, const void* V, void* O, int B,
                                      int Hq, int Hkv, int Sk, int D, float scale, int splits,
                                      void* scratch, void* stream);
+/* Decode attention for callers that must not allocate (this entry point has no counterpart in the
+ * reference). Same arguments and result as tessera_sm100_attn_decode_device, but the split-KV
+ * partials live in a static device array inside the library (8 MiB per GPU, held from library
+ * load to process exit) and neither the first call nor any later one calls cudaMalloc, cudaFree
+ * or an allocating library routine. It is meant for serving loops whose device-memory budget is
+ * fixed at start-up, and for latency-critical decode steps that cannot afford the device-wide
+ * synchronisation an allocation implies.
+ *  - Limit: B * Hq * splits * 130 * 4 bytes <= 8 MiB when splits > 1 (the benchmark shape, batch 64
+ *    x 32 heads x 3 splits, needs 3.05 MiB). splits <= 0 picks the library's split count, lowered
+ *    until the partials fit; an explicit split count that does not fit returns 1 with an error
+ *    text naming the required and the available bytes.
+ *  - The first call on each device resolves the array's device address (with that device
+ *    current); issue that first call outside any stream capture.
+ *  - All calls share the one array. Calls ordered on a stream are safe; calls that overlap on the
+ *    GPU (different streams without ordering) race on it. Nothing in it needs clearing between
+ *    calls: every partial a launch reads it has written itself.
+ *  - check_previous != 0 first synchronises `stream` and returns 3 if an earlier launch of this
+ *    entry point gave up a bounded wait (the error word is static too), clearing the record. */
+int tessera_sm100_attn_decode_static_device(const void* Q, const void* K, const void* V, void* O,
+                                            int B, int Hq, int Hkv, int Sk, int D, float scale,
+                                            int splits, int check_previous, void* stream);
 
 /* ---- flash-attention forward (prefill) ----------------------------------------------------
  * O = softmax(scale * Q K^T [+ bottom-right causal mask]) V with fp32 statistics:

@@ -22,6 +22,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <mutex>
 
 #include "../../include/tessera_sm100.h"
 #include "device_ctx.h"
@@ -385,6 +386,141 @@ int launch(const void* Q, const void* K, const void* V, void* O, int B, int Hq, 
   return kOk;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Decode attention without any allocation.
+//
+// Some callers must not allocate device memory while they run: a serving loop whose memory
+// budget was fixed at start-up (another component owns every remaining byte, so a cudaMalloc from
+// inside this library could fail or evict it), or a latency-critical decode step where the
+// implicit device-wide synchronisation of cudaMalloc/cudaFree would stall the other streams. For
+// them the split-KV partials and the error word live in the two file-scope arrays below, which
+// every GPU that loads the library holds until the process exits (8 MiB + 16 bytes per GPU).
+constexpr size_t kStaticScratchBytes = 8u << 20;
+static __device__ __align__(256) float g_static_partials[kStaticScratchBytes / sizeof(float)];
+static __device__ __align__(256) int g_static_err[4];
+
+constexpr int kMaxDevices = 64;
+struct StaticSlots {
+  float* partials = nullptr;  // DEVICE address of g_static_partials on that device
+  int* err = nullptr;         // DEVICE address of g_static_err on that device
+};
+StaticSlots g_static_slots[kMaxDevices];
+std::mutex g_static_mu;
+
+// In host code the array names above are host-side stand-ins, not device addresses. The device
+// address is looked up once per device, with that device current, and cached.
+int static_slots_for_current_device(StaticSlots* out) {
+  const int dev = current_device();
+  if (dev < 0 || dev >= kMaxDevices) {
+    set_last_error("attn_decode_static: device ordinal %d is outside [0, %d)", dev, kMaxDevices);
+    return kBadArg;
+  }
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  StaticSlots& s = g_static_slots[dev];
+  if (!s.partials) {
+    float* pp = nullptr;
+    int* pe = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&pp), g_static_partials);
+    if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void**>(&pe), g_static_err);
+    if (e != cudaSuccess || !pp || !pe) {
+      cudaGetLastError();
+      set_last_error("attn_decode_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return kDeviceFailed;
+    }
+    s.partials = pp;
+    s.err = pe;
+  }
+  *out = s;
+  return kOk;
+}
+
+int launch_static(const void* Q, const void* K, const void* V, void* O, int B, int Hq, int Hkv,
+                  int Sk, int Dh, float scale, int splits, int check_previous, cudaStream_t st) {
+  if (!Q || !K || !V || !O || B <= 0 || Hq <= 0 || Hkv <= 0 || Sk <= 0) {
+    set_last_error("attn_decode_static: null pointer or non-positive size");
+    return kBadArg;
+  }
+  if (Dh != D) {
+    set_last_error("attn_decode_static: head dimension must be %d (got %d)", D, Dh);
+    return kBadArg;
+  }
+  if (Hq % Hkv) {
+    set_last_error("attn_decode_static: Hq (%d) must be divisible by Hkv (%d)", Hq, Hkv);
+    return kBadArg;
+  }
+  if ((reinterpret_cast<uintptr_t>(K) & 15) || (reinterpret_cast<uintptr_t>(V) & 15) ||
+      (reinterpret_cast<uintptr_t>(Q) & 3)) {
+    set_last_error("attn_decode_static: K and V must be 16-byte aligned");
+    return kBadArg;
+  }
+  if (int rc = ensure_device()) return rc;
+  StaticSlots slots;
+  if (int rc = static_slots_for_current_device(&slots)) return rc;
+  if (check_previous) {
+    // Report (and clear) a bounded-wait expiry of an earlier launch of this entry point.
+    int w[4] = {0, 0, 0, 0};
+    TSB_CUDA_OK(cudaStreamSynchronize(st));
+    TSB_CUDA_OK(cudaMemcpy(w, slots.err, sizeof(w), cudaMemcpyDeviceToHost));
+    if (w[0] != 0) {
+      TSB_CUDA_OK(cudaMemset(slots.err, 0, sizeof(w)));
+      set_last_error("attn_decode_static: an earlier launch gave up a wait (code %d, block %d, "
+                     "detail %d)", w[0], w[1], w[2]);
+      return kDeviceFailed;
+    }
+  }
+  Params p{};
+  p.Q = static_cast<const __nv_bfloat16*>(Q);
+  p.O = static_cast<__nv_bfloat16*>(O);
+  p.B = B;
+  p.Hq = Hq;
+  p.Hkv = Hkv;
+  p.Sk = Sk;
+  p.G = Hq / Hkv;
+  p.groups_per_kv = (p.G + 7) / 8;
+  p.tiles_total = (Sk + TILE - 1) / TILE;
+  const bool automatic = splits <= 0;
+  if (automatic) splits = choose_splits(B, Hkv, p.groups_per_kv, p.tiles_total);
+  splits = std::min(splits, std::min(p.tiles_total, MAX_SPLITS));
+  if (automatic)  // take the largest split count whose partials fit the static array
+    while (splits > 1 && scratch_bytes(B, Hq, splits) > kStaticScratchBytes) --splits;
+  p.tiles_per_split = (p.tiles_total + splits - 1) / splits;
+  splits = (p.tiles_total + p.tiles_per_split - 1) / p.tiles_per_split;
+  if (splits > 1 && scratch_bytes(B, Hq, splits) > kStaticScratchBytes) {
+    set_last_error("attn_decode_static: B=%d Hq=%d splits=%d needs %zu bytes of partials; the static "
+                   "scratch holds %zu (use fewer splits, or tessera_sm100_attn_decode_device with "
+                   "caller scratch)", B, Hq, splits, scratch_bytes(B, Hq, splits), kStaticScratchBytes);
+    return kBadArg;
+  }
+  p.splits = splits;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.err = slots.err;
+  if (splits > 1) {
+    p.part_o = slots.partials;
+    p.part_ml = p.part_o + (size_t)B * Hq * splits * D;
+  }
+  CUtensorMap tK, tV;
+  uint64_t dims[4] = {(uint64_t)D, (uint64_t)Sk, (uint64_t)Hkv, (uint64_t)B};
+  uint64_t str[3] = {(uint64_t)D * 2, (uint64_t)Sk * D * 2, (uint64_t)Hkv * Sk * D * 2};
+  uint32_t box[4] = {64, TILE, 1, 1};
+  if (!encode_tmap(&tK, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, K, dims, str, box,
+                   CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !encode_tmap(&tV, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, V, dims, str, box,
+                   CU_TENSOR_MAP_SWIZZLE_128B))
+    return kBadArg;
+  TSB_CUDA_OK(cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   SMEM_ALLOC));
+  dim3 grid(splits, Hkv * p.groups_per_kv, B);
+  decode_kernel<<<grid, THREADS, SMEM_ALLOC, st>>>(tK, tV, p);
+  TSB_CUDA_OK(cudaGetLastError());
+  note_launch();
+  if (splits > 1) {
+    merge_kernel<<<B * Hq, D, 0, st>>>(p.part_o, p.part_ml, p.O, splits);
+    TSB_CUDA_OK(cudaGetLastError());
+    note_launch();
+  }
+  return kOk;
+}
+
 }  // namespace attn_decode
 }  // namespace tsb
 
@@ -412,6 +548,17 @@ int tessera_sm100_attn_decode_device(const void* Q, const void* K, const void* V
                                      void* scratch, void* stream) {
   return attn_decode::launch(Q, K, V, O, B, Hq, Hkv, Sk, D, scale, splits, scratch,
                              static_cast<cudaStream_t>(stream));
+}
+
+// Decode attention that allocates nothing (no cudaMalloc, cudaFree or allocating library call, on
+// the first call or any later one): the split-KV partials go to a static device array of 8 MiB.
+// The first call on each device looks up that array's device address (cudaGetSymbolAddress, with
+// the device current); make that first call before any stream capture.
+int tessera_sm100_attn_decode_static_device(const void* Q, const void* K, const void* V, void* O,
+                                            int B, int Hq, int Hkv, int Sk, int D, float scale,
+                                            int splits, int check_previous, void* stream) {
+  return attn_decode::launch_static(Q, K, V, O, B, Hq, Hkv, Sk, D, scale, splits, check_previous,
+                                    static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

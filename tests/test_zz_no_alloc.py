@@ -1,0 +1,80 @@
+"""Decode attention through the entry point that allocates nothing.
+
+``tessera_sm100_attn_decode_static_device`` is for callers that must not allocate device memory
+while they run (a serving loop with a memory budget fixed at start-up, a latency-critical decode
+step that cannot take the device-wide synchronisation of an allocation): it keeps the split-KV
+partials in a static 8 MiB device array instead of caller- or pool-provided scratch. This test
+calls it through the C ABI twice in a row and checks both results against the regular entry
+point (``tessera_sm100_attn_decode_device`` with caller scratch), and checks that an over-sized
+request is rejected with a clear message. It is collected last so that a failure here cannot
+hide the other tests from a run that stops at the first failure.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-2  # max|y - ref| / max|ref| in fp32, the tolerance of the other parity tests
+
+
+def _rel(a, b):
+    a, b = a.astype(np.float32), b.astype(np.float32)
+    return float(np.abs(a - b).max() / max(float(np.abs(b).max()), 1e-30))
+
+
+def test_static_scratch_decode_matches_regular_entry_point_twice():
+    from tessera_b200 import _lib, device
+    from tessera_b200.device import DeviceArray, bfloat16
+    lib = _lib.load()
+    device.set_device(0)
+    rng = np.random.default_rng(2024)
+    B, Hq, Hkv, Sk, D = 8, 32, 8, 2048, 128
+    scale = ctypes.c_float(1.0 / np.sqrt(D))
+    k = rng.standard_normal((B, Hkv, Sk, D), dtype=np.float32).astype(bfloat16)
+    v = rng.standard_normal((B, Hkv, Sk, D), dtype=np.float32).astype(bfloat16)
+    dk, dv = DeviceArray.from_host(k), DeviceArray.from_host(v)
+    splits = lib.tessera_sm100_attn_decode_splits(B, Hq, Hkv, Sk)
+    assert splits > 1, "the case must exercise the scratch"
+    scratch = DeviceArray((lib.tessera_sm100_attn_decode_scratch_bytes(B, Hq, splits),), np.uint8)
+    for call in range(2):  # two calls in a row share the static array; fresh queries each time
+        q = rng.standard_normal((B, Hq, 1, D), dtype=np.float32).astype(bfloat16)
+        dq = DeviceArray.from_host(q)
+        want, got = DeviceArray.zeros(q.shape, bfloat16), DeviceArray.zeros(q.shape, bfloat16)
+        _lib.call("tessera_sm100_attn_decode_device", dq.ptr, dk.ptr, dv.ptr, want.ptr, B, Hq, Hkv, Sk, D,
+                  scale, splits, scratch.ptr, None)
+        _lib.call("tessera_sm100_attn_decode_static_device", dq.ptr, dk.ptr, dv.ptr, got.ptr, B, Hq, Hkv,
+                  Sk, D, scale, splits, 1, None)
+        device.synchronize()
+        a, b = got.download(), want.download()
+        assert not np.isnan(a.astype(np.float32)).any()
+        assert _rel(a, b) < TOL, f"call {call}: static-scratch result differs from the regular entry point"
+    # automatic split choice and a last check of the static error word
+    _lib.call("tessera_sm100_attn_decode_static_device", dq.ptr, dk.ptr, dv.ptr, got.ptr, B, Hq, Hkv, Sk, D,
+              scale, 0, 1, None)
+    device.synchronize()
+    assert _rel(got.download(), want.download()) < TOL
+    code, _, _ = device.consume_device_error()
+    assert code == 0
+
+
+def test_static_scratch_rejects_sizes_beyond_its_maximum():
+    from tessera_b200 import _lib, device
+    from tessera_b200.device import DeviceArray, bfloat16
+    lib = _lib.load()
+    device.set_device(0)
+    # 64 x 32 heads x 16 splits x 130 floats = 17 MiB of partials: over the 8 MiB static array.
+    B, Hq, Hkv, Sk, D = 64, 32, 8, 1024, 128
+    q = DeviceArray.zeros((B, Hq, 1, D), bfloat16)
+    kv = DeviceArray.zeros((B, Hkv, Sk, D), bfloat16)
+    out = DeviceArray.zeros((B, Hq, 1, D), bfloat16)
+    rc = lib.tessera_sm100_attn_decode_static_device(q.ptr, kv.ptr, kv.ptr, out.ptr, B, Hq, Hkv, Sk, D,
+                                                     ctypes.c_float(0.1), 16, 0, None)
+    assert rc == 1
+    msg = lib.tessera_sm100_last_error().decode()
+    assert "static" in msg and "bytes" in msg
+    # the automatic choice lowers the split count until it fits instead of failing
+    _lib.call("tessera_sm100_attn_decode_static_device", q.ptr, kv.ptr, kv.ptr, out.ptr, B, Hq, Hkv, Sk, D,
+              ctypes.c_float(0.1), 0, 0, None)
+    device.synchronize()

@@ -368,6 +368,7 @@ def bench_moe(ranks, args, peaks, peak_kind):
     wd = tiled_normal(rngw, (Ep, F, H), 1, 1 / np.sqrt(F), bfloat16)
     dwg, dwu, dwd = (DeviceArray.from_host(t) for t in (wg, wu, wd))
     flops = 3 * 2.0 * T * k * H * F
+    ep_mode = "single"
     if W == 1:
         dx, dl = DeviceArray.from_host(x), DeviceArray.from_host(logits)
         out = DeviceArray.zeros((T, H), bfloat16)
@@ -382,9 +383,20 @@ def bench_moe(ranks, args, peaks, peak_kind):
         sl = slice(ranks.rank * Tl, (ranks.rank + 1) * Tl)
         dxl = DeviceArray.from_host(x[sl])
         ll = np.ascontiguousarray(logits[sl])
-        moe = parallel.ExpertParallelMoE(E, k, parallel.NcclTransport(comm, ranks.gather),
-                                         parallel.GpuMoeBackend(dwg, dwu, dwd))
-        fn = lambda: moe.forward(dxl, ll)
+        ep_mode = "device"
+        try:
+            moe = parallel.DeviceExpertParallelMoE(comm, ranks.gather, dwg, dwu, dwd, Tl, k, E)
+            dll = DeviceArray.from_host(ll)
+            out_l = DeviceArray.zeros((Tl, H), bfloat16)
+            fn = lambda: moe.forward(dxl, dll, out=out_l)
+        except Exception as exc:
+            ep_mode = f"nccl all-to-all (device exchange set-up failed: {exc})"
+        modes = ranks.gather(ep_mode)
+        if any(m != "device" for m in modes):
+            ep_mode = next(m for m in modes if m != "device")
+            moe = parallel.ExpertParallelMoE(E, k, parallel.NcclTransport(comm, ranks.gather),
+                                             parallel.GpuMoeBackend(dwg, dwu, dwd))
+            fn = lambda: moe.forward(dxl, ll)
     times = timed_steps(ranks, device, fn, max(2, args.steps // 2), min(args.warmup, 3))
     if comm:
         comm.close()
@@ -392,7 +404,7 @@ def bench_moe(ranks, args, peaks, peak_kind):
     ach = flops / W / ms / 1e9
     return {"metric": "MoE FFN layer TFLOP/s (routed slots, unpadded)", "value": flops / ms / 1e9,
             "unit": "TFLOP/s", "ms_per_step": ms,
-            "config": f"T={T} H={H} F={F} E={E} top-{k} bf16, " + ("single GPU" if W == 1 else f"expert-parallel /{W}, ragged all-to-all"),
+            "config": f"T={T} H={H} F={F} E={E} top-{k} bf16, " + ("single GPU" if W == 1 else f"expert-parallel /{W}, exchange: {ep_mode}"),
             "roofline": {"bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops_sustained"],
                          "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops_sustained"],
                          "traffic": NCU_TRAFFIC_BYTES["moe"],

@@ -163,6 +163,33 @@ int tessera_sm100_moe_workspace_views(void* workspace, int T, int H, int F, int 
                                       void** group_sizes, void** group_offsets,
                                       void** slot_of_assignment);
 
+/* ---- expert-parallel MoE exchange over peer memory ---------------------------------------------
+ * Device-side dispatch and combine for the expert-parallel forward of
+ * python/tessera/distributed/moe.py:358-483 (rank r owns experts [r*E/world, (r+1)*E/world)),
+ * with no host round trip and no capacity padding. Per rank: sort the local slots by GLOBAL expert
+ * with tessera_sm100_moe_permute_device, all-gather its group_sizes[E] into all_counts[world][E],
+ * then
+ *   ep_plan      -> group_offsets_local[E/world + 1] of the rows this rank will receive
+ *                   (expert-major, source-major inside an expert) and dst_base[E]: the first row,
+ *                   in the owner's receive buffer, of this rank's block for each expert;
+ *   ep_dispatch  -> stores every kept token row into its owner's receive buffer (recv_bufs[i] is
+ *                   rank i's buffer, a CUDA-IPC peer pointer for i != rank);
+ *   (all ranks run the grouped GEMMs on their receive buffer into y_bufs[rank]);
+ *   ep_combine   -> out[t] = sum_j w[t,j] * y_bufs[owner][row of slot (t,j)], j ascending.
+ * Ranks must be ordered between the phases (dispatch -> expert GEMMs -> combine -> next dispatch),
+ * e.g. by a small stream-ordered NCCL all-reduce. capacity_rows bounds the rows of each buffer. */
+int tessera_sm100_ep_plan_device(const int* all_counts, int world, int rank, int E,
+                                 int* group_offsets_local, int* dst_base, void* stream);
+int tessera_sm100_ep_dispatch_device(const void* x, const int* token_of_slot,
+                                     const int* expert_of_slot, const int* my_offsets,
+                                     const int* dst_base, void* const* recv_bufs, int world, int E,
+                                     int max_slots, int capacity_rows, int H, int dtype, void* stream);
+int tessera_sm100_ep_combine_device(void* const* y_bufs, const int* assignment,
+                                    const int* slot_of_assignment, const float* weights,
+                                    const int* my_offsets, const int* dst_base, void* out, int T,
+                                    int top_k, int world, int E, int capacity_rows, int H, int dtype,
+                                    void* stream);
+
 /* ---- decode attention --------------------------------------------------------------------
  * One query token per sequence against a KV cache: Q,O [B,Hq,1,D], K,V [B,Hkv,Sk,D] bf16,
  * D = 128, query head hq reads KV head hq / (Hq/Hkv) (python/tessera/nn/functional.py:349-356;

@@ -92,6 +92,11 @@ _SIGNATURES = {
                                                c_int, c_int, c_int, c_int, c_int, c_int, _VP, _VP]),
     "tessera_sm100_moe_workspace_views": (c_int, [_VP, c_int, c_int, c_int, c_int, c_int]
                                           + [POINTER(_VP)] * 8),
+    "tessera_sm100_ep_plan_device": (c_int, [_VP, c_int, c_int, c_int, _VP, _VP, _VP]),
+    "tessera_sm100_ep_dispatch_device": (c_int, [_VP, _VP, _VP, _VP, _VP, POINTER(_VP), c_int, c_int,
+                                                 c_int, c_int, c_int, c_int, _VP]),
+    "tessera_sm100_ep_combine_device": (c_int, [POINTER(_VP), _VP, _VP, _VP, _VP, _VP, _VP, c_int, c_int,
+                                                c_int, c_int, c_int, c_int, c_int, _VP]),
     "tessera_sm100_attn_decode_splits": (c_int, [c_int, c_int, c_int, c_int]),
     "tessera_sm100_attn_decode_scratch_bytes": (c_size_t, [c_int, c_int, c_int]),
     "tessera_sm100_attn_decode_device": (c_int, [_VP, _VP, _VP, _VP, c_int, c_int, c_int, c_int,

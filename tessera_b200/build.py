@@ -77,12 +77,14 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         objs = list(pool.map(lambda s: _compile(s, force, verbose), sources))
     newest = max(o.stat().st_mtime for o in objs)
     if force or not LIB_PATH.exists() or LIB_PATH.stat().st_mtime < newest:
-        cmd = [_nvcc(), "-shared", "-o", str(LIB_PATH), *map(str, objs),
+        tmp = LIB_PATH.with_suffix(".so.tmp")
+        cmd = [_nvcc(), "-shared", "-o", str(tmp), *map(str, objs),
                "-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "static", "-ldl",
                "-lpthread"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+        os.replace(tmp, LIB_PATH)  # atomic: a reader never sees a half-written library
     return LIB_PATH
 
 

@@ -242,22 +242,40 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       const int kv0 = j * BKV;
       const bool need_mask = (kv0 + BKV - 1 > qi0 + shift && p.causal) || (kv0 + BKV > p.Sk);
       const uint32_t t_s = tS(i) + lane_base;
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(t_s + c * 32, v);
-        tmem_ld_wait();
-        if (need_mask) {
+      // One pass over TMEM: the whole 128-column row of S goes to registers (four loads in
+      // flight, one wait); maxima and sums run as independent chains.
+      uint32_t s0[32], s1[32], s2[32], s3[32];
+      tmem_ld_32x32b_x32(t_s, s0);
+      tmem_ld_32x32b_x32(t_s + 32, s1);
+      tmem_ld_32x32b_x32(t_s + 64, s2);
+      tmem_ld_32x32b_x32(t_s + 96, s3);
+      tmem_ld_wait();
+      if (need_mask) {
+        constexpr uint32_t kNegInf = 0xff800000u;
 #pragma unroll
-          for (int k = 0; k < 32; ++k)
-            mx = fmaxf(mx, (kv0 + c * 32 + k <= kv_limit) ? __uint_as_float(v[k]) : -INFINITY);
-        } else {
-#pragma unroll
-          for (int k = 0; k < 32; ++k) mx = fmaxf(mx, __uint_as_float(v[k]));
+        for (int k = 0; k < 32; ++k) {
+          if (kv0 + k > kv_limit) s0[k] = kNegInf;
+          if (kv0 + 32 + k > kv_limit) s1[k] = kNegInf;
+          if (kv0 + 64 + k > kv_limit) s2[k] = kNegInf;
+          if (kv0 + 96 + k > kv_limit) s3[k] = kNegInf;
         }
       }
+      float mxa[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) mxa[c] = -INFINITY;
+#pragma unroll
+      for (int k = 0; k < 32; k += 2) {
+        mxa[0] = fmaxf(mxa[0], __uint_as_float(s0[k]));
+        mxa[1] = fmaxf(mxa[1], __uint_as_float(s0[k + 1]));
+        mxa[2] = fmaxf(mxa[2], __uint_as_float(s1[k]));
+        mxa[3] = fmaxf(mxa[3], __uint_as_float(s1[k + 1]));
+        mxa[4] = fmaxf(mxa[4], __uint_as_float(s2[k]));
+        mxa[5] = fmaxf(mxa[5], __uint_as_float(s2[k + 1]));
+        mxa[6] = fmaxf(mxa[6], __uint_as_float(s3[k]));
+        mxa[7] = fmaxf(mxa[7], __uint_as_float(s3[k + 1]));
+      }
+      const float mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])),
+                             fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
       const bool need = m_new > m_used + kRescaleThreshold;
       if (j == 0) {
@@ -280,31 +298,45 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         tmem_st_wait();
       }
-      // pass 2: P = exp2(S * scale - m), row sum, bf16 P back into the first 64 columns of S
+      // P = exp2(S * scale - m) from registers, row sum, bf16 P into the first 64 columns of S
+      // (masked entries are -inf and give exactly 0).
       const float neg_m = -m_used;
-#pragma unroll 1
-      for (int hh = 0; hh < 2; ++hh) {
+      float la[4] = {0.f, 0.f, 0.f, 0.f};
+      {
         uint32_t pk[32];
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          uint32_t v[32];
-          tmem_ld_32x32b_x32(t_s + hh * 64 + q * 32, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int k = 0; k < 32; k += 2) {
-            float e0 = ex2(fmaf(__uint_as_float(v[k]), p.scale_log2, neg_m));
-            float e1 = ex2(fmaf(__uint_as_float(v[k + 1]), p.scale_log2, neg_m));
-            if (need_mask) {
-              const int kv = kv0 + hh * 64 + q * 32 + k;
-              if (kv > kv_limit) e0 = 0.f;
-              if (kv + 1 > kv_limit) e1 = 0.f;
-            }
-            l += e0 + e1;
-            pk[q * 16 + (k >> 1)] = pack_bf16(e0, e1);
-          }
+        for (int k = 0; k < 32; k += 2) {
+          const float a0 = ex2(fmaf(__uint_as_float(s0[k]), p.scale_log2, neg_m));
+          const float a1 = ex2(fmaf(__uint_as_float(s0[k + 1]), p.scale_log2, neg_m));
+          const float b0 = ex2(fmaf(__uint_as_float(s1[k]), p.scale_log2, neg_m));
+          const float b1 = ex2(fmaf(__uint_as_float(s1[k + 1]), p.scale_log2, neg_m));
+          la[0] += a0;
+          la[1] += a1;
+          la[2] += b0;
+          la[3] += b1;
+          pk[k >> 1] = pack_bf16(a0, a1);
+          pk[16 + (k >> 1)] = pack_bf16(b0, b1);
         }
-        tmem_st_32x32b_x32(t_s + hh * 32, pk);
+        tmem_st_32x32b_x32(t_s, pk);
       }
+      {
+        uint32_t pk[32];
+#pragma unroll
+        for (int k = 0; k < 32; k += 2) {
+          const float a0 = ex2(fmaf(__uint_as_float(s2[k]), p.scale_log2, neg_m));
+          const float a1 = ex2(fmaf(__uint_as_float(s2[k + 1]), p.scale_log2, neg_m));
+          const float b0 = ex2(fmaf(__uint_as_float(s3[k]), p.scale_log2, neg_m));
+          const float b1 = ex2(fmaf(__uint_as_float(s3[k + 1]), p.scale_log2, neg_m));
+          la[0] += a0;
+          la[1] += a1;
+          la[2] += b0;
+          la[3] += b1;
+          pk[k >> 1] = pack_bf16(a0, a1);
+          pk[16 + (k >> 1)] = pack_bf16(b0, b1);
+        }
+        tmem_st_32x32b_x32(t_s + 32, pk);
+      }
+      l += (la[0] + la[1]) + (la[2] + la[3]);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(p_full(i));

@@ -222,6 +222,99 @@ __global__ void combine_scatter_kernel(const float* __restrict__ x, const int* _
   }
 }
 
+
+// ------------------------------------------------------------------------- expert parallel
+// Device-side expert-parallel exchange over peer memory (no host round trip, no padding):
+//   * every rank sorts its slots by GLOBAL expert (permute_kernel) and all-gathers its per-expert
+//     counts, so each rank knows cnt[src][e] for all sources;
+//   * ep_plan_kernel turns that table into (a) the group offsets of this rank's local experts
+//     (rows arrive expert-major, source-major inside an expert: the stable expert sort of the
+//     single-device layer) and (b) for every global expert e the first row, inside the owner's
+//     receive buffer, of the block this rank contributes;
+//   * ep_dispatch_kernel stores each token row straight into its owner's receive buffer
+//     (plain 16-byte stores to a peer pointer), already in grouped order;
+//   * ep_combine_kernel reads each slot's result row back from the owner's output buffer (plain
+//     peer loads) and forms the weighted sum per token in slot order.
+// Partitioning follows megamoe_forward (python/tessera/distributed/moe.py:358-483).
+struct PeerPtrs {
+  void* p[8];
+};
+
+__global__ void ep_plan_kernel(const int* __restrict__ cnt, int world, int rank, int E,
+                               int* __restrict__ group_offsets_local, int* __restrict__ dst_base) {
+  const int Ep = E / world;
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    int acc = 0;
+    for (int el = 0; el < Ep; ++el) {
+      group_offsets_local[el] = acc;
+      for (int s = 0; s < world; ++s) acc += cnt[s * E + rank * Ep + el];
+    }
+    group_offsets_local[Ep] = acc;
+  }
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int d = e / Ep;
+    int base = 0;
+    for (int e2 = d * Ep; e2 < e; ++e2)
+      for (int s = 0; s < world; ++s) base += cnt[s * E + e2];
+    for (int s = 0; s < rank; ++s) base += cnt[s * E + e];
+    dst_base[e] = base;
+  }
+}
+
+__global__ void ep_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ token_of_slot,
+                                   const int* __restrict__ expert_of_slot,
+                                   const int* __restrict__ my_offsets, const int* __restrict__ dst_base,
+                                   PeerPtrs recv, int E, int Ep, int capacity_rows, int vec_per_row) {
+  const int S = my_offsets[E];  // kept slots of this rank
+  const long long total = (long long)S * vec_per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int s = (int)(i / vec_per_row);
+    const int c = (int)(i - (long long)s * vec_per_row);
+    const int e = expert_of_slot[s];
+    const int row = dst_base[e] + (s - my_offsets[e]);
+    if (row < capacity_rows) {
+      uint4* dst = static_cast<uint4*>(recv.p[e / Ep]);
+      dst[(long long)row * vec_per_row + c] = x[(long long)token_of_slot[s] * vec_per_row + c];
+    }
+  }
+}
+
+template <typename YT, typename OT>
+__global__ void ep_combine_kernel(PeerPtrs ybufs, const int* __restrict__ assignment,
+                                  const int* __restrict__ slot_of, const float* __restrict__ w,
+                                  const int* __restrict__ my_offsets, const int* __restrict__ dst_base,
+                                  OT* __restrict__ out, int T, int top_k, int Ep, int capacity_rows,
+                                  int H) {
+  const int t = blockIdx.x;
+  if (t >= T) return;
+  for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
+    float acc[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) acc[q] = 0.f;
+    for (int j = 0; j < top_k; ++j) {
+      const int s = slot_of[(long long)t * top_k + j];
+      if (s < 0) continue;
+      const int e = assignment[(long long)t * top_k + j];
+      const int row = dst_base[e] + (s - my_offsets[e]);
+      if (row >= capacity_rows) continue;
+      const float wj = w[(long long)t * top_k + j];
+      const YT* src = static_cast<const YT*>(ybufs.p[e / Ep]) + (long long)row * H + c;
+      if constexpr (sizeof(YT) == 2) {
+        const uint4 v = *reinterpret_cast<const uint4*>(src);   // 8 x 16-bit, H % 8 == 0
+        const YT* h = reinterpret_cast<const YT*>(&v);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[q] += wj * to_f32<YT>(h[q]);
+      } else {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[q] += wj * to_f32<YT>(src[q]);
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < 8; ++q) out[(long long)t * H + c + q] = from_f32<OT>(acc[q]);
+  }
+}
+
 size_t dtype_size(int dt) { return dt == TESSERA_SM100_F32 ? 4 : 2; }
 
 int route(const float* logits, int T, int E, int top_k, int normalize, int* assignment,
@@ -474,6 +567,90 @@ int tessera_sm100_moe_workspace_views(void* workspace, int T, int H, int F, int 
   if (group_sizes) *group_sizes = ws + w.group_sizes;
   if (group_offsets) *group_offsets = ws + w.group_offsets;
   if (slot_of_assignment) *slot_of_assignment = ws + w.slot_of;
+  return kOk;
+}
+
+// ---- expert-parallel exchange over peer memory -------------------------------------------------
+int tessera_sm100_ep_plan_device(const int* all_counts, int world, int rank, int E,
+                                 int* group_offsets_local, int* dst_base, void* stream) {
+  if (!all_counts || !group_offsets_local || !dst_base || world <= 0 || world > 8 || rank < 0 ||
+      rank >= world || E <= 0 || E % world) {
+    set_last_error("ep_plan: bad arguments (world %d rank %d E %d; world <= 8, E %% world == 0)", world,
+                   rank, E);
+    return kBadArg;
+  }
+  moe::ep_plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(all_counts, world, rank, E,
+                                                                        group_offsets_local, dst_base);
+  TSB_CUDA_OK(cudaGetLastError());
+  note_launch();
+  return kOk;
+}
+
+int tessera_sm100_ep_dispatch_device(const void* x, const int* token_of_slot,
+                                     const int* expert_of_slot, const int* my_offsets,
+                                     const int* dst_base, void* const* recv_bufs, int world, int E,
+                                     int max_slots, int capacity_rows, int H, int dtype, void* stream) {
+  const size_t row_bytes = (size_t)H * moe::dtype_size(dtype);
+  if (!x || !token_of_slot || !expert_of_slot || !my_offsets || !dst_base || !recv_bufs ||
+      world <= 0 || world > 8 || E % world || (row_bytes % 16) || max_slots < 0) {
+    set_last_error("ep_dispatch: bad arguments (rows must be 16-byte multiples, world <= 8)");
+    return kBadArg;
+  }
+  if (max_slots == 0) return kOk;
+  moe::PeerPtrs pp{};
+  for (int i = 0; i < world; ++i) {
+    if (!recv_bufs[i]) {
+      set_last_error("ep_dispatch: receive buffer %d is null", i);
+      return kBadArg;
+    }
+    pp.p[i] = recv_bufs[i];
+  }
+  const int vec = (int)(row_bytes / 16);
+  const long long total = (long long)max_slots * vec;
+  const int grid = (int)std::min<long long>((total + 255) / 256, 148 * 16);
+  moe::ep_dispatch_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), token_of_slot, expert_of_slot, my_offsets, dst_base, pp, E,
+      E / world, capacity_rows, vec);
+  TSB_CUDA_OK(cudaGetLastError());
+  note_launch();
+  return kOk;
+}
+
+int tessera_sm100_ep_combine_device(void* const* y_bufs, const int* assignment,
+                                    const int* slot_of_assignment, const float* weights,
+                                    const int* my_offsets, const int* dst_base, void* out, int T,
+                                    int top_k, int world, int E, int capacity_rows, int H, int dtype,
+                                    void* stream) {
+  if (!y_bufs || !assignment || !slot_of_assignment || !weights || !my_offsets || !dst_base || !out ||
+      world <= 0 || world > 8 || E % world || (H % 8) || T < 0) {
+    set_last_error("ep_combine: bad arguments (H must be a multiple of 8, world <= 8)");
+    return kBadArg;
+  }
+  if (T == 0) return kOk;
+  moe::PeerPtrs pp{};
+  for (int i = 0; i < world; ++i) {
+    if (!y_bufs[i]) {
+      set_last_error("ep_combine: output buffer %d is null", i);
+      return kBadArg;
+    }
+    pp.p[i] = y_bufs[i];
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int Ep = E / world;
+  if (dtype == TESSERA_SM100_BF16)
+    moe::ep_combine_kernel<__nv_bfloat16, __nv_bfloat16><<<T, 128, 0, st>>>(
+        pp, assignment, slot_of_assignment, weights, my_offsets, dst_base,
+        static_cast<__nv_bfloat16*>(out), T, top_k, Ep, capacity_rows, H);
+  else if (dtype == TESSERA_SM100_F16)
+    moe::ep_combine_kernel<__half, __half><<<T, 128, 0, st>>>(
+        pp, assignment, slot_of_assignment, weights, my_offsets, dst_base, static_cast<__half*>(out),
+        T, top_k, Ep, capacity_rows, H);
+  else {
+    set_last_error("ep_combine: dtype must be bf16 or f16");
+    return kBadArg;
+  }
+  TSB_CUDA_OK(cudaGetLastError());
+  note_launch();
   return kOk;
 }
 

@@ -274,3 +274,109 @@ class GpuMoeBackend:
         _lib.call("tessera_sm100_moe_combine_device", rows.ptr, dso.ptr, dw.ptr, out.ptr, num_tokens, k, H,
                   self._code, self._code, _stream_handle(self.stream))
         return out
+
+
+class DeviceExpertParallelMoE:
+    """Expert-parallel MoE forward with the exchange done by the kernels themselves: token rows are
+    stored straight into the owning rank's receive buffer over NVLink, results are read back from
+    the owner's output buffer, and the only NCCL traffic is an all-gather of E int32 counts plus
+    small all-reduces that order the phases. Nothing returns to the host between route and
+    combine. Buffers are sized for the worst case (every slot of every rank on one rank).
+
+    ``gather_host`` exchanges CUDA IPC handles once at construction."""
+
+    def __init__(self, comm, gather_host, w_gate, w_up, w_down, tokens_per_rank: int, top_k: int,
+                 num_experts: int, normalize_weights: bool = True, stream=None) -> None:
+        import ctypes
+        from . import _lib, device
+        from .device import DeviceArray
+        self.comm, self.world, self.rank = comm, comm.world, comm.rank
+        if num_experts % self.world:
+            raise ValueError("num_experts must be divisible by the number of ranks")
+        self.E, self.k, self.Tl = num_experts, top_k, tokens_per_rank
+        self.Ep = num_experts // self.world
+        self.wg, self.wu, self.wd = w_gate, w_up, w_down
+        self.H, self.F = w_gate.shape[1], w_gate.shape[2]
+        self.normalize = normalize_weights
+        self.stream = stream
+        self.dtype = w_gate.dtype
+        self._code = device.dtype_code(self.dtype)
+        self.capacity = self.Tl * self.k * self.world
+        S = self.Tl * self.k
+        i32, f32 = np.int32, np.float32
+        self.assignment = DeviceArray((self.Tl, self.k), i32)
+        self.weights = DeviceArray((self.Tl, self.k), f32)
+        self.token_of_slot, self.expert_of_slot = DeviceArray((S,), i32), DeviceArray((S,), i32)
+        self.weight_of_slot = DeviceArray((S,), f32)
+        self.group_sizes, self.my_offsets = DeviceArray((self.E,), i32), DeviceArray((self.E + 1,), i32)
+        self.slot_of = DeviceArray((S,), i32)
+        self.all_counts = DeviceArray((self.world, self.E), i32)
+        self.local_offsets, self.dst_base = DeviceArray((self.Ep + 1,), i32), DeviceArray((self.E,), i32)
+        self.flag = DeviceArray.zeros((4,), i32)
+        self.flag_out = DeviceArray.zeros((4,), i32)
+        self.recv = DeviceArray.zeros((self.capacity, self.H), self.dtype)      # peers store here
+        self.hidden = DeviceArray((self.capacity, self.F), self.dtype)
+        self.y = DeviceArray.zeros((self.capacity, self.H), self.dtype)         # peers read here
+        device.synchronize()
+        self._opened = []
+
+        def exchange(buf):
+            h = ctypes.create_string_buffer(64)
+            _lib.call("tessera_sm100_ipc_get_handle", buf.ptr, h)
+            handles = gather_host(h.raw)
+            ptrs = []
+            for r in range(self.world):
+                if r == self.rank:
+                    ptrs.append(buf.ptr)
+                else:
+                    p = ctypes.c_void_p()
+                    _lib.call("tessera_sm100_ipc_open_handle", ctypes.c_char_p(handles[r]), ctypes.byref(p))
+                    self._opened.append(p.value)
+                    ptrs.append(p.value)
+            return (ctypes.c_void_p * self.world)(*ptrs)
+
+        self._recv_ptrs = exchange(self.recv)
+        self._y_ptrs = exchange(self.y)
+
+    def _barrier(self, sh) -> None:
+        """Stream-ordered rendezvous of all ranks (a 4-int all-reduce)."""
+        self.comm.all_reduce(self.flag, self.flag_out, "sum", self.stream)
+
+    def forward(self, x_local, logits_local, out=None):
+        """``x_local`` (Tl, H) and ``logits_local`` (Tl, E) fp32 DeviceArrays; returns a (Tl, H)
+        DeviceArray. Everything is enqueued on one stream; the caller synchronises."""
+        from . import _lib, device
+        from .device import DeviceArray
+        sh = device._stream_handle(self.stream)
+        Tl, k, E, H, F = self.Tl, self.k, self.E, self.H, self.F
+        if out is None:
+            out = DeviceArray((Tl, H), self.dtype, pooled=True)
+        self._barrier(sh)   # peers are done with the previous call's buffers
+        _lib.call("tessera_sm100_moe_route_device", logits_local.ptr, Tl, E, k, int(self.normalize),
+                  self.assignment.ptr, self.weights.ptr, sh)
+        _lib.call("tessera_sm100_moe_permute_device", self.assignment.ptr, self.weights.ptr, Tl, k, E, -1,
+                  self.token_of_slot.ptr, self.expert_of_slot.ptr, self.weight_of_slot.ptr,
+                  self.group_sizes.ptr, self.my_offsets.ptr, self.slot_of.ptr, sh)
+        self.comm.all_gather(self.group_sizes, self.all_counts, self.stream)
+        _lib.call("tessera_sm100_ep_plan_device", self.all_counts.ptr, self.world, self.rank, E,
+                  self.local_offsets.ptr, self.dst_base.ptr, sh)
+        _lib.call("tessera_sm100_ep_dispatch_device", x_local.ptr, self.token_of_slot.ptr,
+                  self.expert_of_slot.ptr, self.my_offsets.ptr, self.dst_base.ptr, self._recv_ptrs,
+                  self.world, E, Tl * k, self.capacity, H, self._code, sh)
+        self._barrier(sh)   # every rank's rows have landed
+        _lib.call("tessera_sm100_grouped_swiglu_device", self.recv.ptr, self.wg.ptr, self.wu.ptr,
+                  self.local_offsets.ptr, self.hidden.ptr, self.capacity, H, F, self.Ep, self._code,
+                  self._code, sh)
+        _lib.call("tessera_sm100_grouped_gemm_device", self.hidden.ptr, self.wd.ptr, self.local_offsets.ptr,
+                  self.y.ptr, self.capacity, F, H, self.Ep, self._code, self._code, sh)
+        self._barrier(sh)   # every rank's expert outputs are complete
+        _lib.call("tessera_sm100_ep_combine_device", self._y_ptrs, self.assignment.ptr, self.slot_of.ptr,
+                  self.weights.ptr, self.my_offsets.ptr, self.dst_base.ptr, out.ptr, Tl, k, self.world, E,
+                  self.capacity, H, self._code, sh)
+        return out
+
+    def close(self) -> None:
+        from . import _lib
+        for p in self._opened:
+            _lib.call("tessera_sm100_ipc_close_handle", p)
+        self._opened = []

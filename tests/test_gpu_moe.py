@@ -172,3 +172,28 @@ def test_config5_full_size():
             ref[i] += r.weights[t, j] * (h @ wd[e].astype(np.float32))
     assert rel_err(out[toks], ref) < TOL
     assert not np.isnan(out).any()
+
+
+def test_device_side_expert_parallel_exchange_on_one_rank():
+    """The peer-memory dispatch/combine kernels with a world of one (own buffers stand in for the
+    peers'): the result must equal the single-device layer, twice in a row (buffers are reused)."""
+    from tessera_b200 import collectives, parallel
+    rng = np.random.default_rng(31)
+    T, H, F, E, k = 300, 128, 256, 8, 2
+    x = rng.standard_normal((T, H), dtype=np.float32).astype(bfloat16)
+    logits = rng.standard_normal((T, E), dtype=np.float32)
+    wg = (rng.standard_normal((E, H, F), dtype=np.float32) / 11).astype(bfloat16)
+    wu = (rng.standard_normal((E, H, F), dtype=np.float32) / 11).astype(bfloat16)
+    wd = (rng.standard_normal((E, F, H), dtype=np.float32) / 16).astype(bfloat16)
+    comm = collectives.Communicator.from_unique_id(collectives.Communicator.unique_id(), 1, 0)
+    moe = parallel.DeviceExpertParallelMoE(comm, lambda h: [h], DA.from_host(wg), DA.from_host(wu),
+                                           DA.from_host(wd), T, k, E)
+    dx, dl = DA.from_host(x), DA.from_host(logits)
+    ref = orc.moe_layer_from_logits(x, logits, wg, wu, wd, k)[0]
+    for _ in range(2):
+        y = moe.forward(dx, dl)
+        device.synchronize()
+        assert rel_err(y.download(), ref) < TOL
+    no_device_error()
+    moe.close()
+    comm.close()

@@ -79,6 +79,16 @@ def _worker(rank, world, port, q):
         device.synchronize()
         ref = orc.moe_layer_from_logits(xs, logits, wg, wu, wd, k)[0]
         errs["ep_moe"] = orc.max_rel_err(y.download(), ref[sl])
+        # --- the same forward with the exchange done by the kernels over peer memory
+        dmoe = parallel.DeviceExpertParallelMoE(comm, gather, backend.wg, backend.wu, backend.wd, Tl, k, E)
+        dx, dlog = DeviceArray.from_host(xs[sl]), DeviceArray.from_host(np.ascontiguousarray(logits[sl]))
+        for _ in range(2):     # twice: buffers are reused across calls
+            yd = dmoe.forward(dx, dlog)
+        device.synchronize()
+        dist.barrier()
+        errs["ep_moe_device"] = orc.max_rel_err(yd.download(), ref[sl])
+        dist.barrier()
+        dmoe.close()
         device.check_device_error("multi-gpu test")
         dist.barrier()
         comm.close()
@@ -112,4 +122,4 @@ def test_two_gpu_collectives_tp_gemm_and_ep_moe():
     for rank, errs, exc in results:
         assert exc is None, f"rank {rank}:\n{exc}"
         assert errs["all_gather"] == 0 and errs["all_reduce"] == 0 and errs["all_to_all_v"] == 0, errs
-        assert errs["tp_gemm"] < 1e-2 and errs["ep_moe"] < 1e-2, errs
+        assert errs["tp_gemm"] < 1e-2 and errs["ep_moe"] < 1e-2 and errs["ep_moe_device"] < 1e-2, errs

@@ -56,6 +56,32 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Packed two-wide fp32 arithmetic and the three-input maximum of sm_100.
+__device__ __forceinline__ uint64_t pack_u32x2(uint32_t lo, uint32_t hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  return pack_u32x2(__float_as_uint(lo), __float_as_uint(hi));
+}
+__device__ __forceinline__ float lo_f32(uint64_t v) { return __uint_as_float(static_cast<uint32_t>(v)); }
+__device__ __forceinline__ float hi_f32(uint64_t v) { return __uint_as_float(static_cast<uint32_t>(v >> 32)); }
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
@@ -117,7 +143,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       mbar_init(v_full(i), 1);
       mbar_init(v_empty(i), 1);
       mbar_init(s_full(i), 1);
-      mbar_init(p_full(i), 128);
+      mbar_init(p_full(i), 4);  // one arrival per softmax warp
       mbar_init(o_full(i), 1);
     }
     fence_mbar_init();
@@ -164,25 +190,33 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc_f16(true, false, false, BQ, BKV);  // Q K^T, both K-major
       const uint32_t idesc_pv = make_idesc_f16(true, false, true, BQ, D);    // P (TMEM) V (N-major)
+      // Descriptor words kept in registers: one low word per operand buffer, one shared high
+      // word (SBO 1024, 128-byte swizzle). Per MMA only a constant is added to a low word.
+      const uint32_t desc_hi = smem_desc_hi(1024);
+      const uint32_t q_lo[2] = {smem_desc_lo(sQ, 16), smem_desc_lo(sQ + TILE_BYTES, 16)};
+      const uint32_t k_lo[2] = {smem_desc_lo(sK, 16), smem_desc_lo(sK + TILE_BYTES, 16)};
+      const uint32_t v_lo[2] = {smem_desc_lo(sV, HALF_BYTES), smem_desc_lo(sV + TILE_BYTES, HALF_BYTES)};
+      const uint32_t t_s[2] = {tS(0), tS(1)};
+      const uint32_t t_o[2] = {tO(0), tO(1)};
+      const uint32_t bar_s[2] = {s_full(0), s_full(1)};
       auto issue_s = [&](int i, int kst) {
-        const uint32_t a_base = sQ + i * TILE_BYTES;
-        const uint32_t b_base = sK + kst * TILE_BYTES;
+        const uint32_t a_lo = q_lo[i], b_lo = k_lo[kst], d = t_s[i];
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
-          umma_f16_ss(tS(i), make_smem_desc(a_base + off, 16, 1024),
-                      make_smem_desc(b_base + off, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+          // 16 elements of d per step: 32 B inside a 128-byte row, next 64-wide block after 4.
+          const uint32_t off = ((ks >> 2) * HALF_BYTES + (ks & 3) * 32) >> 4;
+          umma_f16_ss_parts(d, a_lo + off, desc_hi, b_lo + off, desc_hi, idesc_s, ks > 0 ? 1u : 0u);
         }
-        umma_commit(s_full(i));
+        umma_commit(bar_s[i]);
       };
       auto issue_pv = [&](int i, int vst, bool accumulate) {
-        const uint32_t b_base = sV + vst * TILE_BYTES;
+        const uint32_t b_lo = v_lo[vst], d = t_o[i], a = t_s[i];
 #pragma unroll
         for (int ks = 0; ks < BKV / 16; ++ks) {
           // A: P rows in TMEM lanes, 16 bf16 of K per 8 columns. B: V[kv][d], 16 kv rows = 2048 B;
-          // the two 64-wide d blocks are HALF_BYTES apart.
-          umma_f16_ts(tO(i), tS(i) + 8u * ks, make_smem_desc(b_base + ks * 2048, HALF_BYTES, 1024),
-                      idesc_pv, (accumulate || ks > 0) ? 1u : 0u);
+          // the two 64-wide d blocks are HALF_BYTES apart (the LBO field).
+          umma_f16_ts_parts(d, a + 8u * ks, b_lo + ((ks * 2048) >> 4), desc_hi, idesc_pv,
+                            (accumulate || ks > 0) ? 1u : 0u);
         }
       };
       bool ok = true;
@@ -260,22 +294,22 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           if (kv0 + 96 + k > kv_limit) s3[k] = kNegInf;
         }
       }
+      // Row maximum: 3-input max, eight independent chains.
       float mxa[8];
 #pragma unroll
       for (int c = 0; c < 8; ++c) mxa[c] = -INFINITY;
 #pragma unroll
-      for (int k = 0; k < 32; k += 2) {
-        mxa[0] = fmaxf(mxa[0], __uint_as_float(s0[k]));
-        mxa[1] = fmaxf(mxa[1], __uint_as_float(s0[k + 1]));
-        mxa[2] = fmaxf(mxa[2], __uint_as_float(s1[k]));
-        mxa[3] = fmaxf(mxa[3], __uint_as_float(s1[k + 1]));
-        mxa[4] = fmaxf(mxa[4], __uint_as_float(s2[k]));
-        mxa[5] = fmaxf(mxa[5], __uint_as_float(s2[k + 1]));
-        mxa[6] = fmaxf(mxa[6], __uint_as_float(s3[k]));
-        mxa[7] = fmaxf(mxa[7], __uint_as_float(s3[k + 1]));
+      for (int k = 0; k < 32; k += 4) {
+        mxa[0] = fmax3(mxa[0], __uint_as_float(s0[k]), __uint_as_float(s0[k + 1]));
+        mxa[1] = fmax3(mxa[1], __uint_as_float(s0[k + 2]), __uint_as_float(s0[k + 3]));
+        mxa[2] = fmax3(mxa[2], __uint_as_float(s1[k]), __uint_as_float(s1[k + 1]));
+        mxa[3] = fmax3(mxa[3], __uint_as_float(s1[k + 2]), __uint_as_float(s1[k + 3]));
+        mxa[4] = fmax3(mxa[4], __uint_as_float(s2[k]), __uint_as_float(s2[k + 1]));
+        mxa[5] = fmax3(mxa[5], __uint_as_float(s2[k + 2]), __uint_as_float(s2[k + 3]));
+        mxa[6] = fmax3(mxa[6], __uint_as_float(s3[k]), __uint_as_float(s3[k + 1]));
+        mxa[7] = fmax3(mxa[7], __uint_as_float(s3[k + 2]), __uint_as_float(s3[k + 3]));
       }
-      const float mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])),
-                             fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
+      const float mx = fmaxf(fmax3(mxa[0], mxa[1], mxa[2]), fmax3(fmax3(mxa[3], mxa[4], mxa[5]), mxa[6], mxa[7]));
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
       const bool need = m_new > m_used + kRescaleThreshold;
       if (j == 0) {
@@ -298,48 +332,51 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         tmem_st_wait();
       }
-      // P = exp2(S * scale - m) from registers, row sum, bf16 P into the first 64 columns of S
-      // (masked entries are -inf and give exactly 0).
-      const float neg_m = -m_used;
-      float la[4] = {0.f, 0.f, 0.f, 0.f};
+      // P = exp2(S * scale - m) from registers (masked entries are -inf and give exactly 0), row
+      // sum, bf16 P into the first 64 columns of S. The scale-and-shift and the sums use the packed
+      // two-wide fp32 instructions; each batch of 32 columns is laid out as independent work
+      // (16 packed FMAs, 32 exponentials, 16 packed adds, 16 packs) so that the single warp a tile
+      // has on each scheduler can issue back to back.
+      const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
+      const uint64_t negm2 = pack_f32x2(-m_used, -m_used);
+      uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};
+      auto exp_batch = [&](const uint32_t (&sv)[32], uint32_t* pk) {
+        uint64_t x[16];
+#pragma unroll
+        for (int q = 0; q < 16; ++q) x[q] = ffma2(pack_u32x2(sv[2 * q], sv[2 * q + 1]), scale2, negm2);
+        float e[32];
+#pragma unroll
+        for (int q = 0; q < 16; ++q) {
+          e[2 * q] = ex2(lo_f32(x[q]));
+          e[2 * q + 1] = ex2(hi_f32(x[q]));
+        }
+#pragma unroll
+        for (int q = 0; q < 16; ++q) {
+          sum2[q & 3] = fadd2(sum2[q & 3], pack_f32x2(e[2 * q], e[2 * q + 1]));
+          pk[q] = pack_bf16(e[2 * q], e[2 * q + 1]);
+        }
+      };
       {
         uint32_t pk[32];
-#pragma unroll
-        for (int k = 0; k < 32; k += 2) {
-          const float a0 = ex2(fmaf(__uint_as_float(s0[k]), p.scale_log2, neg_m));
-          const float a1 = ex2(fmaf(__uint_as_float(s0[k + 1]), p.scale_log2, neg_m));
-          const float b0 = ex2(fmaf(__uint_as_float(s1[k]), p.scale_log2, neg_m));
-          const float b1 = ex2(fmaf(__uint_as_float(s1[k + 1]), p.scale_log2, neg_m));
-          la[0] += a0;
-          la[1] += a1;
-          la[2] += b0;
-          la[3] += b1;
-          pk[k >> 1] = pack_bf16(a0, a1);
-          pk[16 + (k >> 1)] = pack_bf16(b0, b1);
-        }
+        exp_batch(s0, pk);
+        exp_batch(s1, pk + 16);
         tmem_st_32x32b_x32(t_s, pk);
       }
       {
         uint32_t pk[32];
-#pragma unroll
-        for (int k = 0; k < 32; k += 2) {
-          const float a0 = ex2(fmaf(__uint_as_float(s2[k]), p.scale_log2, neg_m));
-          const float a1 = ex2(fmaf(__uint_as_float(s2[k + 1]), p.scale_log2, neg_m));
-          const float b0 = ex2(fmaf(__uint_as_float(s3[k]), p.scale_log2, neg_m));
-          const float b1 = ex2(fmaf(__uint_as_float(s3[k + 1]), p.scale_log2, neg_m));
-          la[0] += a0;
-          la[1] += a1;
-          la[2] += b0;
-          la[3] += b1;
-          pk[k >> 1] = pack_bf16(a0, a1);
-          pk[16 + (k >> 1)] = pack_bf16(b0, b1);
-        }
+        exp_batch(s2, pk);
+        exp_batch(s3, pk + 16);
         tmem_st_32x32b_x32(t_s + 32, pk);
       }
-      l += (la[0] + la[1]) + (la[2] + la[3]);
+      {
+        const uint64_t t2 = fadd2(fadd2(sum2[0], sum2[1]), fadd2(sum2[2], sum2[3]));
+        l += lo_f32(t2) + hi_f32(t2);
+      }
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(p_full(i));
+      // One arrival per warp: 128 arrivals on a single shared-memory word would serialise.
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full(i));
     }
     // ---- epilogue: O / l -> bf16 -> swizzled smem (the Q tile's buffer) -> TMA store
     if (ok && nblk[i] > 0) ok = mbar_wait(o_full(i), 0, abort_flag, p.err, kErrWaitTmemFull, 9000);

@@ -117,14 +117,16 @@ int launch_plain(const void* A, const void* B, void* D, int batch, int M, int N,
     }
     uint64_t dims[3] = {(uint64_t)N, (uint64_t)M, (uint64_t)batch};
     uint64_t str[2] = {(uint64_t)ldd * osz, (uint64_t)sD * osz};
-    uint32_t box[3] = {(uint32_t)(128 / osz), 32, 1};
+    // 16-bit outputs take the wide epilogue: 128-column (256-byte) rows, unswizzled staging.
+    const bool wide = (osz == 2);
+    uint32_t box[3] = {wide ? 128u : (uint32_t)(128 / osz), 32, 1};
     for (int i = 0; i < num_peers; ++i) {
       if (!peer_D[i] || !aligned16(peer_D[i])) {
         set_last_error("gemm: output copy %d is null or not 16-byte aligned", i);
         return kBadArg;
       }
       if (!encode_tmap(&peer_maps.m[i], tm_dtype(out_dtype), 3, peer_D[i], dims, str, box,
-                       CU_TENSOR_MAP_SWIZZLE_128B))
+                       wide ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B))
         return kBadArg;
     }
     for (int i = num_peers; i < MAX_PEERS; ++i) peer_maps.m[i] = peer_maps.m[0];

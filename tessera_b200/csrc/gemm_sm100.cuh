@@ -320,8 +320,61 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const bool warp_has_rows = (kMode == kPlain) ? (row0 < p.M) : (rows_w > 0);
       const uint32_t t_acc = tmem_base + static_cast<uint32_t>(acc * BN) + lane_base;
       constexpr int kChunks = kOutW / kChunk;
+      bool wide_done = false;
+      if constexpr (kMode == kPlain && sizeof(OutT) == 2) {
+        if (p.num_peers > 0) {
+          // Fused all-gather: 128 output columns (256-byte rows) per store, unswizzled staging
+          // (the warp's two 4 KB buffers used as one 8 KB buffer), one TMA store per rank.
+          // Wider rows make better NVLink packets; the bank conflicts of the unswizzled writes
+          // cost a few hundred cycles per tile against a main loop of tens of thousands.
+          wide_done = true;
+          const uint32_t buf = sEpi + static_cast<uint32_t>(warp * 2 * EPI_BUF_BYTES);
 #pragma unroll 1
-      for (int c = 0; c < kChunks; ++c) {
+          for (int c = 0; c < 2; ++c) {
+            const int col0 = tile.n0 + c * 128;
+            if (col0 >= p.N || !warp_has_rows) break;
+            if (lane == 0) tma_store_wait_read<0>();
+            __syncwarp();
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              uint32_t r[32];
+              tmem_ld_32x32b_x32(t_acc + c * 128 + h * 32, r);
+              tmem_ld_wait();
+              uint32_t w[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if constexpr (std::is_same<OutT, __nv_bfloat16>::value) {
+                  __nv_bfloat162 v2 = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                  w[j] = *reinterpret_cast<uint32_t*>(&v2);
+                } else {
+                  __half2 v2 = __floats2half2_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                  w[j] = *reinterpret_cast<uint32_t*>(&v2);
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const uint32_t addr = buf + lane * 256u + static_cast<uint32_t>(h * 4 + j) * 16u;
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * j]),
+                             "r"(w[4 * j + 1]), "r"(w[4 * j + 2]), "r"(w[4 * j + 3])
+                             : "memory");
+              }
+            }
+            if (c == 1 || col0 + 128 >= p.N) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(tempty_bar(acc));
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              for (int i = 0; i < p.num_peers; ++i) tma_store_3d(&peers.m[i], buf, col0, row0, tile.b);
+              tma_store_commit();
+            }
+          }
+        }
+      }
+#pragma unroll 1
+      for (int c = 0; c < kChunks && !wide_done; ++c) {
         const int col0 = tile.n0 + c * kChunk;
         if (col0 >= p.N || !warp_has_rows) break;
         const uint32_t buf = sEpi + static_cast<uint32_t>((warp * 2 + sbuf) * EPI_BUF_BYTES);

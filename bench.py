@@ -248,8 +248,10 @@ def bench_gemm(ranks, args, peaks, peak_kind, sampler):
     times = timed_steps(ranks, device, step, args.steps, args.warmup)
     m1 = sampler.mark()
     launches = (device.launch_count() - l0) * args.steps // (args.steps + args.warmup)
+    # kernel-only time for the roofline entry: at one GPU the step is the kernel; with several,
+    # the GEMM without the exchange, timed the same way (before the clock probe heats the GPU)
+    kernel_times = times if W == 1 else timed_steps(ranks, device, gemm_only, args.steps, args.warmup)
     probe_marks = clock_probe(device, sampler, step)
-    kernel_times = timed_steps(ranks, device, gemm_only, max(3, args.steps // 2), 1)
     flops = 2.0 * n * n * n
     ms = statistics.mean(times)
     k_ms = statistics.mean(kernel_times)

@@ -262,6 +262,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+      const uint32_t desc_hi = smem_desc_hi(1024);
+      const uint32_t a_lo0 = smem_desc_lo(sA, 16);
+      const uint32_t b_lo0 = smem_desc_lo(sB, B_BLOCK_BYTES);
       while (ok && walk.next(p, tile)) {
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.err, kErrWaitTmemEmpty)) {
           ok = false;
@@ -275,16 +278,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             break;
           }
           tc_fence_after();
-          const uint32_t a_base = sA + stage * A_STAGE_BYTES;
-          const uint32_t b_base = sB + stage * B_STAGE_BYTES;
+          // Descriptor low words of this stage; per MMA only a constant is added to the start
+          // address field (16-byte units). A: K-major, 16 elements = 32 B inside the 128-byte
+          // swizzle row. B: N-major, 16 k-rows = 2048 B; 64-column blocks are 8 KB apart (LBO).
+          const uint32_t a_lo = a_lo0 + stage * (A_STAGE_BYTES >> 4);
+          const uint32_t b_lo = b_lo0 + stage * (B_STAGE_BYTES >> 4);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            // A: K-major, advance 16 elements = 32 B inside the 128-byte swizzle row.
-            const uint64_t adesc = make_smem_desc(a_base + k * 32, 16, 1024);
-            // B: N-major, advance 16 k-rows = 2048 B; 64-column blocks are 8 KB apart.
-            const uint64_t bdesc = make_smem_desc(b_base + k * 2048, B_BLOCK_BYTES, 1024);
-            umma_f16_ss(d_tmem, adesc, bdesc, p.idesc, (kb > 0 || k > 0) ? 1u : 0u);
-          }
+          for (int k = 0; k < BK / 16; ++k)
+            umma_f16_ss_parts(d_tmem, a_lo + k * 2, desc_hi, b_lo + k * 128, desc_hi, p.idesc,
+                              (kb > 0 || k > 0) ? 1u : 0u);
           umma_commit(empty_bar(stage));
           if (++stage == STAGES) {
             stage = 0;

@@ -92,6 +92,15 @@ int tessera_sm100_gemm_strided_device(const void* A, const void* B, void* D, int
                                       int N, int K, long long lda, long long ldb, long long ldd,
                                       long long strideA, long long strideB, long long strideD,
                                       int in_dtype, int out_dtype, void* stream);
+/* D[M,N] = act(A*B + bias[col] + residual[row,col]) with the bias / residual / activation applied in
+ * the kernel epilogue: tessera.ops.gemm(A, B, epilogue={...}) -> fused_epilogue
+ * (python/tessera/__init__.py:239-248, 2658-2675; the reference's GPU lane for it is the emitted
+ * tessera_nvidia_mma_fused kernel, python/tessera/compiler/emit/nvidia_cuda.py:3446-3548).
+ * bias: fp32 [N] or NULL. residual: [M,N] in the output dtype or NULL. activation: 0 none, 1 relu,
+ * 2 gelu (tanh form), 3 silu. K and N multiples of 8. */
+int tessera_sm100_gemm_epilogue_device(const void* A, const void* B, void* D, int M, int N, int K,
+                                       int in_dtype, int out_dtype, const float* bias,
+                                       const void* residual, int activation, void* stream);
 /* Column-parallel GEMM with the all-gather of Y fused into the epilogue
  * (Y = all_gather(A @ W_r, axis=1), python/tessera/compiler/tensor_parallel.py:118-123): rank r
  * multiplies columns [r*N/world, (r+1)*N/world) of the full B[K,N] and TMA-stores every output

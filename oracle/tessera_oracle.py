@@ -66,6 +66,24 @@ def gemm(A, B) -> np.ndarray:
     return np.matmul(_f32(A), _f32(B)).astype(np.float32)
 
 
+def fused_epilogue(x, bias=None, activation="linear", residual=None) -> np.ndarray:
+    """bias, residual, then activation (python/tessera/__init__.py:2658-2675; gelu is the tanh
+    form of :487-497, silu :554-557, relu :549-552), in f32."""
+    x = np.asarray(x, np.float32)
+    if bias is not None:
+        x = x + np.asarray(bias, np.float32)
+    if residual is not None:
+        x = x + _f32(residual)
+    if activation == "gelu":
+        k = float(np.sqrt(2.0 / np.pi))
+        x = x * 0.5 * (1.0 + np.tanh(k * (x + 0.044715 * x ** 3)))
+    elif activation == "relu":
+        x = np.maximum(0, x)
+    elif activation == "silu":
+        x = x / (1.0 + np.exp(-x))
+    return x.astype(np.float32)
+
+
 # ----------------------------------------------------------------------------- attention
 def softmax(x, axis: int = -1) -> np.ndarray:
     """python/tessera/__init__.py:450-454."""

@@ -73,6 +73,8 @@ _SIGNATURES = {
     "tessera_sm100_gemm_strided_device": (c_int, [_VP, _VP, _VP, c_int, c_int, c_int, c_int,
                                                   c_longlong, c_longlong, c_longlong, c_longlong,
                                                   c_longlong, c_longlong, c_int, c_int, _VP]),
+    "tessera_sm100_gemm_epilogue_device": (c_int, [_VP, _VP, _VP, c_int, c_int, c_int, c_int, c_int, _VP,
+                                                   _VP, c_int, _VP]),
     "tessera_sm100_gemm_allgather_device": (c_int, [_VP, _VP, POINTER(_VP), c_int, c_int, c_int, c_int,
                                                     c_int, c_int, c_int, _VP]),
     "tessera_sm100_grouped_gemm_device": (c_int, [_VP, _VP, _VP, _VP, c_int, c_int, c_int, c_int,

@@ -64,7 +64,8 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 int launch_plain(const void* A, const void* B, void* D, int batch, int M, int N, int K,
                  long long lda, long long ldb, long long ldd, long long sA, long long sB,
                  long long sD, int in_dtype, int out_dtype, cudaStream_t stream,
-                 void* const* peer_D = nullptr, int num_peers = 0) {
+                 void* const* peer_D = nullptr, int num_peers = 0, const float* bias = nullptr,
+                 const void* residual = nullptr, long long ldr = 0, int activation = 0) {
   if (!A || !B || !D || batch <= 0 || M <= 0 || N <= 0 || K <= 0) {
     set_last_error("gemm: null pointer or non-positive size (batch %d M %d N %d K %d)", batch, M,
                    N, K);
@@ -138,6 +139,10 @@ int launch_plain(const void* A, const void* B, void* D, int batch, int M, int N,
   p.K = K;
   p.batch = batch;
   p.num_peers = num_peers;
+  p.bias = bias;
+  p.residual = residual;
+  p.ldr = ldr;
+  p.activation = activation;
   p.m_tiles = (M + BM - 1) / BM;
   p.n_tiles = (N + BN - 1) / BN;
   p.idesc = make_idesc_f16(in_dtype == TESSERA_SM100_BF16, false, true, BM, BN);
@@ -409,6 +414,28 @@ int tessera_sm100_gemm_allgather_device(const void* A, const void* B, void* cons
   const char* Bblk = static_cast<const char*>(B) + (size_t)rank * nb * 2;
   return gemm::launch_plain(A, Bblk, outs[rank], 1, M, nb, K, K, N_total, N_total, 0, 0, 0, in_dtype,
                             out_dtype, static_cast<cudaStream_t>(stream), outs, world);
+}
+// D = act(A*B + bias + residual): the GEMM with the reference's fused_epilogue applied in the
+// kernel epilogue. bias is fp32 [N] or null; residual is [M,N] in the output dtype or null;
+// activation 0 none, 1 relu, 2 gelu (tanh form), 3 silu. K and N must be multiples of 8.
+int tessera_sm100_gemm_epilogue_device(const void* A, const void* B, void* D, int M, int N, int K,
+                                       int in_dtype, int out_dtype, const float* bias,
+                                       const void* residual, int activation, void* stream) {
+  if ((K % 8) || (N % 8)) {
+    set_last_error("gemm_epilogue: K (%d) and N (%d) must be multiples of 8", K, N);
+    return kBadArg;
+  }
+  if (activation < 0 || activation > 3) {
+    set_last_error("gemm_epilogue: activation must be 0 (none), 1 (relu), 2 (gelu) or 3 (silu)");
+    return kBadArg;
+  }
+  if (out_dtype == TESSERA_SM100_F32 && residual && (reinterpret_cast<uintptr_t>(residual) & 3)) {
+    set_last_error("gemm_epilogue: residual is misaligned");
+    return kBadArg;
+  }
+  return gemm::launch_plain(A, B, D, 1, M, N, K, K, N, N, 0, 0, 0, in_dtype, out_dtype,
+                            static_cast<cudaStream_t>(stream), nullptr, 0, bias, residual, N,
+                            activation);
 }
 int tessera_sm100_grouped_gemm_device(const void* x, const void* w, const int* offsets, void* out,
                                       int T, int K, int N, int E, int in_dtype, int out_dtype,

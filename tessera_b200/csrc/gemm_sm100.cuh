@@ -57,6 +57,11 @@ struct Params {
   void* D;                   // grouped modes: output base for masked stores
   long long ldd;             // grouped modes: output leading dimension (elements)
   int num_peers;             // plain mode: > 0 = store each tile through peers.m[0..num_peers)
+  // plain mode, optional fused epilogue: D = act(A*B + bias[col] + residual[row, col])
+  const float* bias;         // [N] fp32 or null
+  const void* residual;      // [M, N] in the output dtype, leading dimension ldr, or null
+  long long ldr;
+  int activation;            // 0 none, 1 relu, 2 gelu (tanh form), 3 silu
   int* err;
 };
 
@@ -148,6 +153,33 @@ __device__ __forceinline__ void stage_row32(uint32_t buf, uint32_t row, uint32_t
       asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * j]),
                    "r"(w[4 * j + 1]), "r"(w[4 * j + 2]), "r"(w[4 * j + 3])
                    : "memory");
+    }
+  }
+}
+
+// bias + residual + activation on 32 consecutive columns of one output row, in the order of the
+// reference's fused_epilogue (python/tessera/__init__.py:2658-2675): bias, residual, activation.
+template <typename OutT>
+__device__ __forceinline__ void apply_epilogue(float (&v)[32], const Params& p, int row, int col0) {
+  if (row >= p.M) return;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    const int col = col0 + j;
+    if (col < p.N) {
+      float x = v[j];
+      if (p.bias) x += __ldg(p.bias + col);
+      if (p.residual) {
+        const OutT* r = static_cast<const OutT*>(p.residual) + static_cast<long long>(row) * p.ldr + col;
+        x += static_cast<float>(*r);
+      }
+      if (p.activation == 1) {
+        x = fmaxf(x, 0.f);
+      } else if (p.activation == 2) {
+        x = 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+      } else if (p.activation == 3) {
+        x = x / (1.0f + __expf(-x));
+      }
+      v[j] = x;
     }
   }
 }
@@ -405,6 +437,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             float v[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            if constexpr (kMode == kPlain) {
+              if (p.bias || p.residual || p.activation)
+                apply_epilogue<OutT>(v, p, row0 + lane, col0 + h * 32);
+            }
             stage_row32<OutT>(buf, lane, h * 32 * sizeof(OutT), v);
           }
         }

@@ -85,7 +85,7 @@ def gemm(A, B, epilogue=None, *, out_dtype=None, compute_dtype: Optional[str] = 
     """Matrix multiply ``A @ B``; leading dimensions are a batch (python/tessera/__init__.py:239-248).
     ``out`` (host operands only) is an optional preallocated result array, e.g. pinned memory."""
     if epilogue:
-        raise NotImplementedError("gemm: fused epilogues are not part of the sm_100a backend yet")
+        return _gemm_fused(A, B, dict(epilogue), out_dtype, compute_dtype, stream)
     A, B = _unwrap(A), _unwrap(B)
     if A.ndim < 2 or B.ndim < 2:
         raise ValueError(f"gemm: operands must be at least 2-D, got {A.shape} @ {B.shape}")
@@ -124,6 +124,53 @@ def gemm(A, B, epilogue=None, *, out_dtype=None, compute_dtype: Optional[str] = 
     _lib.call("tessera_sm100_gemm", a.ctypes.data, b.ctypes.data, out.ctypes.data, batch, M, N, K,
               in_code, out_code)
     return out
+
+
+_ACTIVATIONS = {"linear": 0, "none": 0, None: 0, "relu": 1, "gelu": 2, "silu": 3}
+
+
+def _gemm_fused(A, B, epilogue: dict, out_dtype, compute_dtype, stream):
+    """``fused_epilogue(A @ B, **epilogue)`` (python/tessera/__init__.py:2658-2675) with bias,
+    residual and activation applied inside the GEMM kernel's epilogue."""
+    bias = epilogue.pop("bias", None)
+    activation = epilogue.pop("activation", "linear")
+    residual = epilogue.pop("residual", None)
+    dropout_p = epilogue.pop("dropout_p", 0.0)
+    cast_dtype = epilogue.pop("cast_dtype", None)
+    if dropout_p:
+        raise NotImplementedError("gemm: dropout in the fused epilogue is not part of this backend")
+    if epilogue:
+        raise TypeError(f"gemm: unknown epilogue key(s) {sorted(epilogue)}")
+    if activation not in _ACTIVATIONS:
+        raise ValueError(f"gemm: activation must be one of linear/relu/gelu/silu, got {activation!r}")
+    A, B = _unwrap(A), _unwrap(B)
+    if A.ndim != 2 or B.ndim != 2:
+        raise ValueError("gemm: the fused epilogue takes 2-D operands")
+    if A.shape[1] != B.shape[0]:
+        raise ValueError(f"gemm: K mismatch — {A.shape} @ {B.shape}")
+    M, K, N = A.shape[0], A.shape[1], B.shape[1]
+    dt = _storage_dtype((A, B), compute_dtype, "gemm")
+    out_code = _out_code(cast_dtype if cast_dtype is not None else out_dtype, _lib.F32)
+    out_dt = device.code_dtype(out_code)
+    on_device = _any_device(A, B)
+    dA, dB = _to_device(A, dt), _to_device(B, dt)
+    dbias = dres = None
+    if bias is not None:
+        b = np.ascontiguousarray(np.broadcast_to(np.asarray(_unwrap(bias), np.float32), (N,)))
+        dbias = DeviceArray.from_host(b)
+    if residual is not None:
+        r = _unwrap(residual)
+        if isinstance(r, DeviceArray):
+            if r.shape != (M, N) or r.dtype != out_dt:
+                raise ValueError(f"gemm: device residual must be {(M, N)} {out_dt}")
+            dres = r
+        else:
+            dres = DeviceArray.from_host(np.ascontiguousarray(np.broadcast_to(np.asarray(r), (M, N))).astype(out_dt))
+    out = DeviceArray((M, N), out_dt)
+    _lib.call("tessera_sm100_gemm_epilogue_device", dA.ptr, dB.ptr, out.ptr, M, N, K, device.dtype_code(dt),
+              out_code, dbias.ptr if dbias else None, dres.ptr if dres else None, _ACTIVATIONS[activation],
+              device._stream_handle(stream))
+    return out if on_device else _finish(out)
 
 
 def matmul(A, B, epilogue=None, **kw):

@@ -7,7 +7,7 @@ Run it where the reference checkout is available (it cannot run on a machine wit
 It imports the reference's own ``tessera`` package (pure Python + numpy) and records inputs and
 outputs of the hot-path functions at small sizes:
 
-  gemm.npz        tessera.ops.gemm / MatmulRegion.reference       (python/tessera/__init__.py:239-254,
+  gemm.npz        tessera.ops.gemm (plain and with epilogue=) / MatmulRegion.reference  (python/tessera/__init__.py:239-254, 2658-2675,
                                                                    python/tessera/compiler/fusion_core.py:398-405)
   attention.npz   tessera.ops.flash_attn, nn.functional.gqa_attention, softmax_merge/finalize
                                                                   (python/tessera/__init__.py:1304-1356,
@@ -61,6 +61,15 @@ def gemm():
         out[f"A{i}"], out[f"B{i}"], out[f"Y{i}"], out[f"Yregion{i}"] = A, B, Y, Yr
         out[f"dtype{i}"] = np.array(dt)
     out["n"] = np.array(4)
+    # fused epilogue: ops.gemm(A, B, epilogue={...}) -> fused_epilogue (python/tessera/__init__.py:2658-2675)
+    A = rt(rng.standard_normal((40, 64)) / 8, bf16)
+    B = rt(rng.standard_normal((64, 72)), bf16)
+    bias = rng.standard_normal(72).astype(np.float32)
+    res = rt(rng.standard_normal((40, 72)), bf16)
+    out.update(epiA=A, epiB=B, epi_bias=bias, epi_res=res)
+    for act in ("linear", "relu", "gelu", "silu"):
+        out[f"epi_{act}"] = np.asarray(
+            tessera.ops.gemm(A, B, epilogue=dict(bias=bias, activation=act, residual=res)), np.float32)
     np.savez_compressed(os.path.join(HERE, "gemm.npz"), **out)
 
 

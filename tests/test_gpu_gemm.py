@@ -108,3 +108,26 @@ def test_strided_column_block_output(lib):
                   1, M, nb, K, K, N, N, 0, 0, 0, _lib.BF16, _lib.BF16, None)
     assert rel_err(dY.download(), orc.gemm(A, W)) < TOL
     no_device_error()
+
+
+@pytest.mark.parametrize("act", ["linear", "relu", "gelu", "silu"])
+def test_fused_epilogue(golden_dir, act):
+    """ops.gemm(A, B, epilogue={bias, residual, activation}) against the reference-made fixture and
+    the oracle at a multi-tile size, fp32 and bf16 outputs."""
+    import tessera_b200 as tessera
+    g = np.load(os.path.join(golden_dir, "gemm.npz"))
+    A, B = g["epiA"].astype(bfloat16), g["epiB"].astype(bfloat16)
+    got = tessera.ops.gemm(A, B, epilogue=dict(bias=g["epi_bias"], activation=act, residual=g["epi_res"]))
+    assert rel_err(got, g[f"epi_{act}"]) < 1e-4
+    rng = np.random.default_rng(17)
+    M, N, K = 300, 520, 264
+    A = (rng.standard_normal((M, K), dtype=np.float32) / 16).astype(bfloat16)
+    B = rng.standard_normal((K, N), dtype=np.float32).astype(bfloat16)
+    bias = rng.standard_normal(N, dtype=np.float32)
+    res = rng.standard_normal((M, N), dtype=np.float32).astype(bfloat16)
+    ref = orc.fused_epilogue(orc.gemm(A, B), bias=bias, activation=act, residual=res)
+    got = tessera.ops.gemm(A, B, epilogue=dict(bias=bias, activation=act, residual=res), out_dtype=bfloat16)
+    assert got.dtype == bfloat16 and rel_err(got, ref) < TOL
+    got32 = tessera.ops.gemm(A, B, epilogue=dict(bias=bias, activation=act))
+    assert rel_err(got32, orc.fused_epilogue(orc.gemm(A, B), bias=bias, activation=act)) < 1e-4
+    no_device_error()

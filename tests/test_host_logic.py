@@ -168,3 +168,9 @@ def test_op_argument_validation_happens_before_any_device_work():
         ops.flash_attn(np.zeros((1, 2, 4, 128)), np.zeros((1, 2, 4, 128)), np.zeros((1, 2, 4, 128)),
                        dropout_p=1.5)
     assert ops.gemm(np.zeros((0, 8), np.float16), np.zeros((8, 4), np.float16)).shape == (0, 4)
+    with pytest.raises(ValueError):
+        ops.gemm(a16, np.zeros((8, 8), np.float16), epilogue={"activation": "swish"})
+    with pytest.raises(NotImplementedError):
+        ops.gemm(a16, np.zeros((8, 8), np.float16), epilogue={"dropout_p": 0.1})
+    with pytest.raises(TypeError):
+        ops.gemm(a16, np.zeros((8, 8), np.float16), epilogue={"bogus": 1})

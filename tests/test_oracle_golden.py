@@ -23,6 +23,14 @@ def test_gemm_matches_reference(golden_dir):
         np.testing.assert_array_equal(orc.round_to_storage(g[f"A{i}"], dt), g[f"A{i}"])
 
 
+def test_fused_epilogue_matches_reference(golden_dir):
+    g = _load(golden_dir, "gemm.npz")
+    y = orc.gemm(g["epiA"], g["epiB"])
+    for act in ("linear", "relu", "gelu", "silu"):
+        got = orc.fused_epilogue(y, bias=g["epi_bias"], activation=act, residual=g["epi_res"])
+        np.testing.assert_allclose(got, g[f"epi_{act}"], rtol=1e-6, atol=1e-6)
+
+
 def test_attention_matches_reference(golden_dir):
     g = _load(golden_dir, "attention.npz")
     for i in range(int(g["n"])):

@@ -54,7 +54,13 @@ struct Params {
   int splits, tiles_total, tiles_per_split;
   float scale_log2;        // scale * log2(e)
   int* err;
+  // Paged mode only: K/V live in pages [P, page_size, Hkv, D]; sequence b reads logical page lp
+  // from physical page page_table[b * max_pages + lp] and holds seq_lens[b] positions.
+  const int* page_table;
+  const int* seq_lens;
+  int max_pages, num_pages, page_size, page_shift;
 };
+
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -87,6 +93,11 @@ __device__ __forceinline__ void consumer_bar() {
   asm volatile("bar.sync 1, %0;" ::"n"(CONSUMERS * 32) : "memory");
 }
 
+// kPaged = false: K, V are dense [B, Hkv, Sk, D] (tensor maps over (d, pos, head, batch)).
+// kPaged = true : K, V are pages [P, page_size, Hkv, D] (tensor maps over (d, head, offset, page));
+//                 the producer walks the sequence's page table and the length comes from
+//                 seq_lens[b]. Everything after the TMA loads is shared.
+template <bool kPaged>
 __global__ void __launch_bounds__(THREADS, 2)
 decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
               const Params p) {
@@ -106,8 +117,14 @@ decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ C
   const int b = blockIdx.z;
   const int head0 = kvh * p.G + hgroup * 8;             // first query head of this CTA
   const int nheads = min(8, p.G - hgroup * 8);          // valid heads in the N dimension
+  int Sk = p.Sk;
+  int tiles_total = p.tiles_total;
+  if constexpr (kPaged) {
+    Sk = max(0, min(p.seq_lens[b], p.Sk));
+    tiles_total = (Sk + TILE - 1) / TILE;
+  }
   const int tile_begin = split * p.tiles_per_split;
-  const int tile_end = min(p.tiles_total, tile_begin + p.tiles_per_split);
+  const int tile_end = min(tiles_total, tile_begin + p.tiles_per_split);
   const int ntiles = max(0, tile_end - tile_begin);
 
   if (threadIdx.x == 0) {
@@ -132,10 +149,41 @@ decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ C
         mbar_arrive_expect_tx(full_bar(stage), STAGE_BYTES);
         const int pos0 = (tile_begin + i) * TILE;
         const uint32_t dst = smem_base + stage * STAGE_BYTES;
-        tma_load_4d(dst, &tmK, full_bar(stage), 0, pos0, kvh, b);
-        tma_load_4d(dst + HALF_BYTES, &tmK, full_bar(stage), 64, pos0, kvh, b);
-        tma_load_4d(dst + KV_BYTES, &tmV, full_bar(stage), 0, pos0, kvh, b);
-        tma_load_4d(dst + KV_BYTES + HALF_BYTES, &tmV, full_bar(stage), 64, pos0, kvh, b);
+        if constexpr (!kPaged) {
+          tma_load_4d(dst, &tmK, full_bar(stage), 0, pos0, kvh, b);
+          tma_load_4d(dst + HALF_BYTES, &tmK, full_bar(stage), 64, pos0, kvh, b);
+          tma_load_4d(dst + KV_BYTES, &tmV, full_bar(stage), 0, pos0, kvh, b);
+          tma_load_4d(dst + KV_BYTES + HALF_BYTES, &tmV, full_bar(stage), 64, pos0, kvh, b);
+        } else {
+          // One box per page piece: min(page_size, 64) positions. Pieces past the end of the
+          // sequence (or with a bad table entry) are fetched at page index num_pages, which is
+          // outside the tensor and therefore arrives as zeros with the full byte count.
+          const int rows = min(p.page_size, TILE);
+          const int pieces = TILE / rows;
+          const int* table = p.page_table + static_cast<long long>(b) * p.max_pages;
+          for (int s = 0; s < pieces; ++s) {
+            const int pos = pos0 + s * rows;
+            const int lp = pos >> p.page_shift;
+            int phys = p.num_pages;
+            if (pos < Sk && lp < p.max_pages) {
+              phys = table[lp];
+              if (phys < 0 || phys >= p.num_pages) {
+                if (atomicCAS(p.err, 0, kErrBadPage) == 0) {
+                  p.err[1] = b;
+                  p.err[2] = lp;
+                  p.err[3] = phys;
+                }
+                phys = p.num_pages;
+              }
+            }
+            const int off = pos & (p.page_size - 1);
+            const uint32_t d2 = dst + s * rows * 128;
+            tma_load_4d(d2, &tmK, full_bar(stage), 0, kvh, off, phys);
+            tma_load_4d(d2 + HALF_BYTES, &tmK, full_bar(stage), 64, kvh, off, phys);
+            tma_load_4d(d2 + KV_BYTES, &tmV, full_bar(stage), 0, kvh, off, phys);
+            tma_load_4d(d2 + KV_BYTES + HALF_BYTES, &tmV, full_bar(stage), 64, kvh, off, phys);
+          }
+        }
         if (++stage == STAGES) {
           stage = 0;
           phase ^= 1u;
@@ -178,6 +226,22 @@ decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ C
     }
     const uint32_t kbase = smem_base + stage * STAGE_BYTES;
     const uint32_t vbase = kbase + KV_BYTES;
+    if constexpr (kPaged) {
+      // The tail of the last page may hold anything (stale tokens, never-written memory); a
+      // probability of zero times a NaN would still poison O, so this warp clears the V rows it
+      // owns beyond the sequence end. K needs nothing: those scores are replaced by -inf below.
+      const int first_dead = Sk - ((tile_begin + i) * TILE + 16 * warp);  // rows >= this are dead
+      if (first_dead < 16) {
+        uint8_t* vgen = smem_gen + stage * STAGE_BYTES + KV_BYTES;
+        for (int c = lane; c < 16 * 16; c += 32) {
+          const int r = c >> 4, chunk = c & 15;
+          if (r >= first_dead)
+            *reinterpret_cast<uint4*>(vgen + (chunk >> 3) * HALF_BYTES + (16 * warp + r) * 128 +
+                                      (chunk & 7) * 16) = make_uint4(0, 0, 0, 0);
+        }
+        __syncwarp();
+      }
+    }
     // S^T = K . Q^T for this warp's 16 positions
     float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -189,7 +253,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ C
       mma_bf16_16816(c, a, qb[ks][0], qb[ks][1]);
     }
     const int pos_a = (tile_begin + i) * TILE + 16 * warp + g;  // rows g and g + 8
-    const bool va = pos_a < p.Sk, vb = (pos_a + 8) < p.Sk;
+    const bool va = pos_a < Sk, vb = (pos_a + 8) < Sk;
     float s0 = va ? c[0] * p.scale_log2 : -INFINITY;
     float s1 = va ? c[1] * p.scale_log2 : -INFINITY;
     float s2 = vb ? c[2] * p.scale_log2 : -INFINITY;
@@ -372,10 +436,10 @@ int launch(const void* Q, const void* K, const void* V, void* O, int B, int Hq, 
       !encode_tmap(&tV, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, V, dims, str, box,
                    CU_TENSOR_MAP_SWIZZLE_128B))
     return kBadArg;
-  TSB_CUDA_OK(cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  TSB_CUDA_OK(cudaFuncSetAttribute(decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    SMEM_ALLOC));
   dim3 grid(splits, Hkv * p.groups_per_kv, B);
-  decode_kernel<<<grid, THREADS, SMEM_ALLOC, st>>>(tK, tV, p);
+  decode_kernel<false><<<grid, THREADS, SMEM_ALLOC, st>>>(tK, tV, p);
   TSB_CUDA_OK(cudaGetLastError());
   note_launch();
   if (splits > 1) {
@@ -384,6 +448,158 @@ int launch(const void* Q, const void* K, const void* V, void* O, int B, int Hq, 
     note_launch();
   }
   return kOk;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Paged KV (python/tessera/cache/paged_kv.py:91-140: pages are [physical_page, page_offset, head,
+// dim] and page_table[logical_page] names the physical page). Storage here is bf16 and the table
+// is per sequence: page_table[B, max_pages], seq_lens[B].
+int launch_paged(const void* Q, const void* k_pages, const void* v_pages, const int* page_table,
+                 const int* seq_lens, void* O, int B, int Hq, int Hkv, int Dh, int page_size,
+                 int num_pages, int max_pages, int max_seq_len, float scale, int splits,
+                 void* scratch, cudaStream_t st) {
+  if (!Q || !k_pages || !v_pages || !page_table || !seq_lens || !O || B <= 0 || Hq <= 0 ||
+      Hkv <= 0 || num_pages <= 0 || max_pages <= 0 || max_seq_len <= 0) {
+    set_last_error("paged_attn_decode: null pointer or non-positive size");
+    return kBadArg;
+  }
+  if (Dh != D) {
+    set_last_error("paged_attn_decode: head dimension must be %d (got %d)", D, Dh);
+    return kBadArg;
+  }
+  if (Hq % Hkv) {
+    set_last_error("paged_attn_decode: Hq (%d) must be divisible by Hkv (%d)", Hq, Hkv);
+    return kBadArg;
+  }
+  if (page_size < 8 || page_size > 1024 || (page_size & (page_size - 1))) {
+    set_last_error("paged_attn_decode: page_size must be a power of two in [8, 1024] (got %d)",
+                   page_size);
+    return kBadArg;
+  }
+  if ((long long)max_pages * page_size < max_seq_len) {
+    set_last_error("paged_attn_decode: max_seq_len %d exceeds the table capacity %d x %d",
+                   max_seq_len, max_pages, page_size);
+    return kBadArg;
+  }
+  if ((reinterpret_cast<uintptr_t>(k_pages) & 15) || (reinterpret_cast<uintptr_t>(v_pages) & 15) ||
+      (reinterpret_cast<uintptr_t>(Q) & 3)) {
+    set_last_error("paged_attn_decode: pages must be 16-byte aligned");
+    return kBadArg;
+  }
+  Params p{};
+  p.Q = static_cast<const __nv_bfloat16*>(Q);
+  p.O = static_cast<__nv_bfloat16*>(O);
+  p.B = B;
+  p.Hq = Hq;
+  p.Hkv = Hkv;
+  p.Sk = max_seq_len;
+  p.G = Hq / Hkv;
+  p.groups_per_kv = (p.G + 7) / 8;
+  p.tiles_total = (max_seq_len + TILE - 1) / TILE;
+  p.page_table = page_table;
+  p.seq_lens = seq_lens;
+  p.max_pages = max_pages;
+  p.num_pages = num_pages;
+  p.page_size = page_size;
+  p.page_shift = 0;
+  while ((1 << p.page_shift) < page_size) ++p.page_shift;
+  if (splits <= 0) splits = choose_splits(B, Hkv, p.groups_per_kv, p.tiles_total);
+  splits = std::min(splits, std::min(p.tiles_total, MAX_SPLITS));
+  p.tiles_per_split = (p.tiles_total + splits - 1) / splits;
+  splits = (p.tiles_total + p.tiles_per_split - 1) / p.tiles_per_split;
+  p.splits = splits;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.err = device_err_word();
+  if (!p.err) return kDeviceFailed;
+  if (splits > 1) {
+    if (!scratch) {
+      set_last_error("paged_attn_decode: %d splits need a scratch buffer", splits);
+      return kBadArg;
+    }
+    p.part_o = static_cast<float*>(scratch);
+    p.part_ml = p.part_o + (size_t)B * Hq * splits * D;
+  }
+  CUtensorMap tK, tV;
+  uint64_t dims[4] = {(uint64_t)D, (uint64_t)Hkv, (uint64_t)page_size, (uint64_t)num_pages};
+  uint64_t str[3] = {(uint64_t)D * 2, (uint64_t)Hkv * D * 2, (uint64_t)page_size * Hkv * D * 2};
+  uint32_t box[4] = {64, 1, (uint32_t)std::min(page_size, TILE), 1};
+  if (!encode_tmap(&tK, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, k_pages, dims, str, box,
+                   CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !encode_tmap(&tV, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, v_pages, dims, str, box,
+                   CU_TENSOR_MAP_SWIZZLE_128B))
+    return kBadArg;
+  TSB_CUDA_OK(cudaFuncSetAttribute(decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   SMEM_ALLOC));
+  dim3 grid(splits, Hkv * p.groups_per_kv, B);
+  decode_kernel<true><<<grid, THREADS, SMEM_ALLOC, st>>>(tK, tV, p);
+  TSB_CUDA_OK(cudaGetLastError());
+  note_launch();
+  if (splits > 1) {
+    merge_kernel<<<B * Hq, D, 0, st>>>(p.part_o, p.part_ml, p.O, splits);
+    TSB_CUDA_OK(cudaGetLastError());
+    note_launch();
+  }
+  return kOk;
+}
+
+// Appends one token per sequence: K/V rows [B, Hkv, D] go to position seq_lens[b] of sequence b
+// (page page_table[b, pos / page_size], offset pos % page_size) and seq_lens[b] grows by one.
+// One CTA per sequence; 16-byte stores. A sequence whose table is full, or whose table entry is
+// outside [0, num_pages), is left unchanged and reported through the error word.
+__global__ void paged_append_kernel(const uint4* __restrict__ k_new, const uint4* __restrict__ v_new,
+                                    uint4* __restrict__ k_pages, uint4* __restrict__ v_pages,
+                                    const int* __restrict__ page_table, int* __restrict__ seq_lens,
+                                    int row_vecs, int page_size, int num_pages, int max_pages,
+                                    int* err) {
+  const int b = blockIdx.x;
+  const int pos = seq_lens[b];
+  const int lp = pos / page_size;
+  int phys = -1;
+  if (pos >= 0 && lp < max_pages) phys = page_table[static_cast<long long>(b) * max_pages + lp];
+  __syncthreads();  // every thread has read seq_lens[b] before thread 0 bumps it
+  if (phys < 0 || phys >= num_pages) {
+    if (threadIdx.x == 0 && atomicCAS(err, 0, kErrBadPage) == 0) {
+      err[1] = b;
+      err[2] = lp;
+      err[3] = phys;
+    }
+    return;
+  }
+  const long long dst = (static_cast<long long>(phys) * page_size + (pos - lp * page_size)) * row_vecs;
+  const long long src = static_cast<long long>(b) * row_vecs;
+  for (int i = threadIdx.x; i < row_vecs; i += blockDim.x) {
+    k_pages[dst + i] = k_new[src + i];
+    v_pages[dst + i] = v_new[src + i];
+  }
+  if (threadIdx.x == 0) seq_lens[b] = pos + 1;
+}
+
+// Gathers tokens of one sequence out of the pages, in caller order (the staged read of
+// python/tessera/compiler/emit/nvidia_cuda.py:2521, 2532): out[x, h, :] = pages[table[idx[x] /
+// L], idx[x] % L, h, :]. One 16-byte vector per thread. Indices outside [0, table capacity) or
+// bad table entries produce zeros and set the error word.
+__global__ void paged_gather_kernel(const uint4* __restrict__ pages, const int* __restrict__ table,
+                                    const long long* __restrict__ idx, uint4* __restrict__ out,
+                                    long long T, int row_vecs, int page_size, int num_pages,
+                                    int max_pages, int* err) {
+  const long long z = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (z >= T * row_vecs) return;
+  const long long x = z / row_vecs;
+  const int i = static_cast<int>(z - x * row_vecs);
+  const long long tok = idx[x];
+  const long long lp = tok / page_size;
+  int phys = -1;
+  if (tok >= 0 && lp < max_pages) phys = table[lp];
+  if (phys < 0 || phys >= num_pages) {
+    if (atomicCAS(err, 0, kErrBadPage) == 0) {
+      err[1] = static_cast<int>(x);
+      err[2] = static_cast<int>(lp);
+      err[3] = phys;
+    }
+    out[z] = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  out[z] = pages[(static_cast<long long>(phys) * page_size + (tok - lp * page_size)) * row_vecs + i];
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -507,10 +723,10 @@ int launch_static(const void* Q, const void* K, const void* V, void* O, int B, i
       !encode_tmap(&tV, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, V, dims, str, box,
                    CU_TENSOR_MAP_SWIZZLE_128B))
     return kBadArg;
-  TSB_CUDA_OK(cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  TSB_CUDA_OK(cudaFuncSetAttribute(decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    SMEM_ALLOC));
   dim3 grid(splits, Hkv * p.groups_per_kv, B);
-  decode_kernel<<<grid, THREADS, SMEM_ALLOC, st>>>(tK, tV, p);
+  decode_kernel<false><<<grid, THREADS, SMEM_ALLOC, st>>>(tK, tV, p);
   TSB_CUDA_OK(cudaGetLastError());
   note_launch();
   if (splits > 1) {
@@ -548,6 +764,76 @@ int tessera_sm100_attn_decode_device(const void* Q, const void* K, const void* V
                                      void* scratch, void* stream) {
   return attn_decode::launch(Q, K, V, O, B, Hq, Hkv, Sk, D, scale, splits, scratch,
                              static_cast<cudaStream_t>(stream));
+}
+
+// Paged decode: Q, O [B, Hq, D] bf16; pages [num_pages, page_size, Hkv, D] bf16; page_table
+// [B, max_pages] int32; seq_lens [B] int32 (each in [1, max_seq_len]). `scratch` as for
+// tessera_sm100_attn_decode_device, sized with the split count of (B, Hq, Hkv, max_seq_len).
+int tessera_sm100_paged_attn_decode_device(const void* Q, const void* k_pages, const void* v_pages,
+                                           const int* page_table, const int* seq_lens, void* O,
+                                           int B, int Hq, int Hkv, int D, int page_size,
+                                           int num_pages, int max_pages, int max_seq_len,
+                                           float scale, int splits, void* scratch, void* stream) {
+  return attn_decode::launch_paged(Q, k_pages, v_pages, page_table, seq_lens, O, B, Hq, Hkv, D,
+                                   page_size, num_pages, max_pages, max_seq_len, scale, splits,
+                                   scratch, static_cast<cudaStream_t>(stream));
+}
+
+int tessera_sm100_paged_kv_append_device(const void* k_new, const void* v_new, void* k_pages,
+                                         void* v_pages, const int* page_table, int* seq_lens, int B,
+                                         int Hkv, int D, int page_size, int num_pages,
+                                         int max_pages, void* stream) {
+  if (!k_new || !v_new || !k_pages || !v_pages || !page_table || !seq_lens || B <= 0 || Hkv <= 0 ||
+      D <= 0 || page_size <= 0 || num_pages <= 0 || max_pages <= 0) {
+    set_last_error("paged_kv_append: null pointer or non-positive size");
+    return kBadArg;
+  }
+  if ((Hkv * D) % 8) {
+    set_last_error("paged_kv_append: Hkv * D must be a multiple of 8 (16-byte rows)");
+    return kBadArg;
+  }
+  if (int rc = ensure_device()) return rc;
+  int* err = device_err_word();
+  if (!err) return kDeviceFailed;
+  const int row_vecs = Hkv * D / 8;
+  attn_decode::paged_append_kernel<<<B, std::min(256, std::max(32, row_vecs)), 0,
+                                     static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(k_new), static_cast<const uint4*>(v_new),
+      static_cast<uint4*>(k_pages), static_cast<uint4*>(v_pages), page_table, seq_lens, row_vecs,
+      page_size, num_pages, max_pages, err);
+  TSB_CUDA_OK(cudaGetLastError());
+  note_launch();
+  return kOk;
+}
+
+// pages [num_pages, page_size, H, D] bf16 -> out [T, H, D] bf16 for the logical token indices
+// idx[T] (int64) of the sequence whose table is page_table[max_pages].
+int tessera_sm100_paged_kv_gather_device(const void* pages, const int* page_table,
+                                         const long long* idx, void* out, long long T, int H, int D,
+                                         int page_size, int num_pages, int max_pages,
+                                         void* stream) {
+  if (!pages || !page_table || !idx || !out || T < 0 || H <= 0 || D <= 0 || page_size <= 0 ||
+      num_pages <= 0 || max_pages <= 0) {
+    set_last_error("paged_kv_gather: null pointer or non-positive size");
+    return kBadArg;
+  }
+  if ((H * D) % 8) {
+    set_last_error("paged_kv_gather: H * D must be a multiple of 8 (16-byte rows)");
+    return kBadArg;
+  }
+  if (T == 0) return kOk;
+  if (int rc = ensure_device()) return rc;
+  int* err = device_err_word();
+  if (!err) return kDeviceFailed;
+  const int row_vecs = H * D / 8;
+  const long long n = T * row_vecs;
+  attn_decode::paged_gather_kernel<<<(unsigned)((n + 255) / 256), 256, 0,
+                                     static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(pages), page_table, idx, static_cast<uint4*>(out), T, row_vecs,
+      page_size, num_pages, max_pages, err);
+  TSB_CUDA_OK(cudaGetLastError());
+  note_launch();
+  return kOk;
 }
 
 // Decode attention that allocates nothing (no cudaMalloc, cudaFree or allocating library call, on

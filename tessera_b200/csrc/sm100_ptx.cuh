@@ -23,6 +23,7 @@ enum DeviceErr : int {
   kErrWaitTmemFull = 3,   // epilogue gave up waiting for an accumulator
   kErrWaitTmemEmpty = 4,  // MMA warp gave up waiting for a free accumulator
   kErrWaitOther = 5,
+  kErrBadPage = 6,        // paged KV: a page-table entry outside [0, num_pages)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

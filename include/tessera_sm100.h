@@ -232,6 +232,46 @@ int tessera_sm100_attn_decode_static_device(const void* Q, const void* K, const 
                                             int B, int Hq, int Hkv, int Sk, int D, float scale,
                                             int splits, int check_previous, void* stream);
 
+/* ---- paged KV cache ------------------------------------------------------------------------
+ * The page ABI of python/tessera/cache/paged_kv.py:91-140 (PagedKVBufferABI): K and V pages are
+ * [physical_page, page_offset, head, dim] and page_table[logical_page] names the physical page;
+ * attention never infers placement from a logical token index. Storage here is bf16 (the
+ * reference's version 1 is f32), head_dim 128, page_size a power of two in [8, 1024], and the
+ * table is per sequence so a whole decode batch is one launch: page_table [B, max_pages] int32,
+ * seq_lens [B] int32.
+ *
+ * tessera_sm100_paged_attn_decode_device: one query token per sequence against its pages; replaces
+ * ops.paged_attention / cache.paged_kv.paged_attention(backend="nvidia")
+ * (python/tessera/__init__.py:1291-1302, python/tessera/cache/paged_kv.py:480-559, 772-788) and
+ * the reference's tessera_nvidia_resident_paged_attention
+ * (python/tessera/compiler/emit/nvidia_cuda.py:2522, 2533). Q, O [B, Hq, 128] bf16. Every
+ * seq_lens[b] must be in [1, max_seq_len]; max_seq_len <= max_pages * page_size sizes the grid.
+ * splits / scratch as for tessera_sm100_attn_decode_device (use tessera_sm100_attn_decode_splits
+ * with Sk = max_seq_len). A table entry outside [0, num_pages) is read as zeros and recorded in
+ * the device error word (tessera_sm100_consume_device_error), never dereferenced. */
+int tessera_sm100_paged_attn_decode_device(const void* Q, const void* k_pages, const void* v_pages,
+                                           const int* page_table, const int* seq_lens, void* O,
+                                           int B, int Hq, int Hkv, int D, int page_size,
+                                           int num_pages, int max_pages, int max_seq_len,
+                                           float scale, int splits, void* scratch, void* stream);
+
+/* Appends one token per sequence (k_new, v_new [B, Hkv, D] bf16) at position seq_lens[b] and adds
+ * one to seq_lens[b] on the device: KVCacheHandle.append for a decode step
+ * (python/tessera/cache/handle.py:156-215) against paged storage. A sequence whose table is full
+ * is left unchanged and recorded in the device error word. */
+int tessera_sm100_paged_kv_append_device(const void* k_new, const void* v_new, void* k_pages,
+                                         void* v_pages, const int* page_table, int* seq_lens, int B,
+                                         int Hkv, int D, int page_size, int num_pages,
+                                         int max_pages, void* stream);
+
+/* out[x, h, :] = pages[page_table[idx[x] / page_size], idx[x] % page_size, h, :] for idx[T] int64,
+ * in caller order: PagedKVBufferABI.gather (python/tessera/cache/paged_kv.py:130-140), the
+ * reference's tessera_nvidia_resident_paged / tessera_nvidia_paged_kv_read_f32
+ * (python/tessera/compiler/emit/nvidia_cuda.py:1883, 2521, 2532). bf16, H * D a multiple of 8. */
+int tessera_sm100_paged_kv_gather_device(const void* pages, const int* page_table,
+                                         const long long* idx, void* out, long long T, int H, int D,
+                                         int page_size, int num_pages, int max_pages, void* stream);
+
 /* ---- flash-attention forward (prefill) ----------------------------------------------------
  * O = softmax(scale * Q K^T [+ bottom-right causal mask]) V with fp32 statistics:
  * tessera.ops.flash_attn (python/tessera/__init__.py:1304-1356). Q,O [B,Hq,Sq,D], K,V [B,Hkv,Sk,D]

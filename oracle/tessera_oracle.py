@@ -147,6 +147,59 @@ def softmax_finalize(o, l) -> np.ndarray:
     return np.asarray(o / l[..., None], dtype=np.float32)
 
 
+# ----------------------------------------------------------------------------- paged KV
+def paged_pack(k, v, page_size: int):
+    """Tokens ``[n, H, D]`` -> identity-mapped pages ``[P, L, H, D]`` + table
+    (``materialize_paged_kv_abi``, python/tessera/cache/paged_kv.py:421-454)."""
+    k, v = _f32(k), _f32(v)
+    n, H, D = k.shape
+    pages = max(1, (n + page_size - 1) // page_size)
+    kp = np.zeros((pages, page_size, H, D), np.float32)
+    vp = np.zeros((pages, page_size, H, D), np.float32)
+    kp.reshape(-1, H, D)[:n] = k
+    vp.reshape(-1, H, D)[:n] = v
+    return kp, vp, np.arange(pages, dtype=np.int32)
+
+
+def paged_gather(k_pages, v_pages, page_table, logical_length: int, token_indices):
+    """``PagedKVBufferABI.gather`` (python/tessera/cache/paged_kv.py:130-140): caller order,
+    logical page -> physical page through the table."""
+    idx = np.asarray(token_indices, np.int64).reshape(-1)
+    if idx.size and (idx.min() < 0 or idx.max() >= logical_length):
+        raise IndexError(f"paged KV token index outside [0, {logical_length})")
+    L = np.asarray(k_pages).shape[1]
+    lp, off = np.divmod(idx, L)
+    pp = np.asarray(page_table)[lp]
+    return _f32(np.asarray(k_pages)[pp, off]), _f32(np.asarray(v_pages)[pp, off])
+
+
+def paged_attention(Q, k_pages, v_pages, page_table, logical_length: int, scale=None,
+                    causal: bool = False, token_indices=None) -> np.ndarray:
+    """``paged_attention`` (python/tessera/cache/paged_kv.py:480-559) over the page ABI: gather
+    the requested tokens (all of ``[0, logical_length)`` by default), repeat KV heads for
+    grouped queries and run ``_reference_attention`` (:457-477). Q ``(Hq, q_len, D)``."""
+    Q = _f32(Q)
+    idx = np.arange(logical_length) if token_indices is None else np.asarray(token_indices, np.int64)
+    gk, gv = paged_gather(k_pages, v_pages, page_table, logical_length, idx)
+    K, V = np.transpose(gk, (1, 0, 2)), np.transpose(gv, (1, 0, 2))
+    if K.shape[0] != Q.shape[0]:
+        if K.shape[0] < 1 or Q.shape[0] % K.shape[0]:
+            raise ValueError("attention query heads must be divisible by KV heads")
+        rep = Q.shape[0] // K.shape[0]
+        K, V = np.repeat(K, rep, axis=0), np.repeat(V, rep, axis=0)
+    if scale is None:
+        scale = 1.0 / np.sqrt(Q.shape[-1])
+    scores = np.matmul(Q, K.swapaxes(-1, -2)) * scale
+    if causal:
+        q_len, k_len = scores.shape[-2], scores.shape[-1]
+        mask = np.triu(np.ones((q_len, k_len), dtype=bool), k=1 + max(k_len - q_len, 0))
+        scores = np.where(mask, -np.inf, scores)
+    scores = scores - scores.max(axis=-1, keepdims=True)
+    w = np.exp(scores)
+    w = w / w.sum(axis=-1, keepdims=True)
+    return np.matmul(w, V).astype(np.float32)
+
+
 # ----------------------------------------------------------------------------- MoE
 class Routing(NamedTuple):
     assignment: np.ndarray  # (T, k) int64, -1 = dropped

@@ -53,11 +53,15 @@ def consume_device_error() -> tuple[int, int, int]:
 
 
 def check_device_error(where: str = "") -> None:
-    code, block, detail = consume_device_error()
+    code, a, b = consume_device_error()
+    if code == 6:
+        raise _lib.BackendError(where or "kernel", 3,
+                                f"a paged-KV page-table entry is outside the page pool (sequence or row {a}, "
+                                f"logical page {b}); it was read as zeros")
     if code:
         raise _lib.BackendError(where or "kernel", 3,
-                                f"a bounded wait expired on the device (code {code}, block {block}, "
-                                f"detail {detail})")
+                                f"a bounded wait expired on the device (code {code}, block {a}, "
+                                f"detail {b})")
 
 
 def launch_count() -> int:

@@ -187,8 +187,10 @@ def flash_attn(Q, K=None, V=None, scale=None, causal: bool = False, cache=None,
                kv_state=None, *, stream=None):
     """``softmax(scale * Q K^T, causal) V`` (python/tessera/__init__.py:1304-1356). Q [B,Hq,Sq,D],
     K/V [B,Hkv,Sk,D] bfloat16, D = 128; Hkv may divide Hq (grouped-query attention)."""
-    if kv_state is not None or cache is not None:
-        raise NotImplementedError("flash_attn: paged / cached KV state is not part of this backend")
+    if kv_state is not None:  # python/tessera/__init__.py:1318-1321
+        return paged_attention(Q, kv_state, scale=scale, causal=causal)
+    if cache is not None:
+        raise NotImplementedError("flash_attn: cache= is not part of this backend; pass kv_state=")
     if not 0.0 <= dropout_p < 1.0:
         raise ValueError("dropout_p must be in [0.0, 1.0)")
     if dropout_p > 0.0 or attn_bias is not None:
@@ -229,6 +231,13 @@ def flash_attn(Q, K=None, V=None, scale=None, causal: bool = False, cache=None,
     for _ in range(squeeze):
         out = out[0]
     return out
+
+
+def paged_attention(Q, kv_state, *, scale=None, causal: bool = False, token_indices=None):
+    """Attention over a paged KV state (python/tessera/__init__.py:1291-1302): ``Q`` is
+    ``(num_heads, q_len, 128)``; the pages are read in place by the paged decode kernel."""
+    from .cache import paged_attention as _pa
+    return _pa(_unwrap(Q), kv_state, scale=scale, causal=causal, token_indices=token_indices)
 
 
 def gqa_attention(Q, K, V, num_query_heads: int, num_kv_heads: int, **kwargs):

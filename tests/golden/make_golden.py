@@ -13,6 +13,8 @@ outputs of the hot-path functions at small sizes:
                                                                   (python/tessera/__init__.py:1304-1356,
                                                                    python/tessera/nn/functional.py:349-356,
                                                                    python/tessera/_block_attnres_ops.py:104-146)
+  paged.npz       cache.paged_attention over KVCacheHandle, materialize_paged_kv_abi,
+                  PagedKVBufferABI.gather                         (python/tessera/cache/paged_kv.py:91-140, 421-559)
   moe.npz         distributed.moe.route_tokens, stdlib.moe.plan_dispatch +
                   compiler.moe_transport.descriptor_from_dispatch_plan, ops.grouped_gemm,
                   ops.moe_swiglu_block, nn.functional.moe_layer, distributed.moe.megamoe_layer
@@ -143,8 +145,68 @@ def moe():
     np.savez_compressed(os.path.join(HERE, "moe.npz"), **out)
 
 
+def paged():
+    """cache.paged_attention over a KVCacheHandle, and the page ABI it is materialised into
+    (python/tessera/cache/paged_kv.py:421-559)."""
+    from tessera.cache import KVCacheHandle, paged_attention
+    from tessera.cache.paged_kv import PagedKVBufferABI, materialize_paged_kv_abi
+    rng = np.random.default_rng(404)
+    out = {}
+    cases = [  # Hq, Hkv, q_len, n, page_size, causal, token_indices
+        (4, 4, 1, 200, 16, False, None),
+        (8, 2, 3, 150, 8, True, None),
+        (8, 2, 2, 97, 32, False, None),
+        (16, 2, 1, 333, 64, False, None),
+        (4, 2, 4, 130, 16, True, "subset"),
+        (4, 4, 5, 3, 8, True, None),
+    ]
+    for i, (Hq, Hkv, q_len, n, L, causal, ti) in enumerate(cases):
+        h = KVCacheHandle(num_heads=Hkv, head_dim=128, max_seq=n + 8, page_size=L)
+        k = rt(rng.standard_normal((n, Hkv, 128)), bf16)
+        v = rt(rng.standard_normal((n, Hkv, 128)), bf16)
+        h.append(k, v)
+        Q = rt(rng.standard_normal((Hq, q_len, 128)), bf16)
+        idx = None
+        if ti == "subset":
+            idx = rng.permutation(n)[: n // 2].astype(np.int64)
+        o = paged_attention(Q, h, causal=causal, token_indices=None if idx is None else idx.tolist())
+        abi = materialize_paged_kv_abi(h)
+        out.update({f"Q{i}": Q, f"k{i}": k, f"v{i}": v, f"O{i}": np.asarray(o, np.float32),
+                    f"meta{i}": np.array([Hq, Hkv, q_len, n, L, int(causal)]),
+                    f"kpages{i}": abi.k_pages, f"table{i}": abi.page_table})
+        if idx is not None:
+            out[f"idx{i}"] = idx
+    # a scattered table: the same tokens behind a permuted physical placement
+    n, Hkv, L = 75, 2, 16
+    k = rt(rng.standard_normal((n, Hkv, 128)), bf16)
+    v = rt(rng.standard_normal((n, Hkv, 128)), bf16)
+    pages = (n + L - 1) // L
+    table = rng.permutation(pages + 3)[:pages].astype(np.int32)
+    kp = np.zeros((pages + 3, L, Hkv, 128), np.float32)
+    vp = np.zeros_like(kp)
+    for t in range(n):
+        kp[table[t // L], t % L] = k[t]
+        vp[table[t // L], t % L] = v[t]
+    abi = PagedKVBufferABI(kp, vp, table, n)
+
+    class _State:  # a backend-native state: exposes only its own page ABI
+        def paged_kv_abi(self):
+            return abi
+    gidx = rng.integers(0, n, 40)
+    gk, gv = abi.gather(gidx)
+    out.update(sk_pages=kp, sv_pages=vp, stable=table, sn=np.array(n), sgidx=gidx, sgk=gk, sgv=gv)
+    Q = rt(rng.standard_normal((4, 2, 128)), bf16)
+    kk, vv = abi.gather(np.arange(n))
+    from tessera.cache.paged_kv import _reference_attention
+    out.update(sQ=Q, sO=_reference_attention(Q, np.transpose(kk, (1, 0, 2)), np.transpose(vv, (1, 0, 2)),
+                                             1.0 / np.sqrt(128.0), False).astype(np.float32))
+    out["n"] = np.array(len(cases))
+    np.savez_compressed(os.path.join(HERE, "paged.npz"), **out)
+
+
 if __name__ == "__main__":
     gemm()
     attention()
     moe()
+    paged()
     print("wrote", sorted(f for f in os.listdir(HERE) if f.endswith(".npz")))

@@ -174,3 +174,55 @@ def test_op_argument_validation_happens_before_any_device_work():
         ops.gemm(a16, np.zeros((8, 8), np.float16), epilogue={"dropout_p": 0.1})
     with pytest.raises(TypeError):
         ops.gemm(a16, np.zeros((8, 8), np.float16), epilogue={"bogus": 1})
+
+
+def test_paged_kv_descriptors(golden_dir):
+    """Page-ABI descriptors (python/tessera/cache/paged_kv.py:91-140, 421-454): validation, the
+    host gather and materialisation through the protocol — no GPU involved."""
+    import os
+    from tessera_b200 import cache as pk
+    g = np.load(os.path.join(golden_dir, "paged.npz"))
+    n = int(g["sn"])
+    abi = pk.PagedKVBufferABI(g["sk_pages"], g["sv_pages"], g["stable"], n)
+    assert abi.page_size == 16
+    gk, gv = abi.gather(g["sgidx"])
+    np.testing.assert_array_equal(gk, g["sgk"])
+    np.testing.assert_array_equal(gv, g["sgv"])
+    with pytest.raises(IndexError):
+        abi.gather([n])
+    with pytest.raises(ValueError):
+        pk.PagedKVBufferABI(g["sk_pages"], g["sv_pages"], g["stable"].astype(np.int64), n)
+    with pytest.raises(ValueError):
+        pk.PagedKVBufferABI(g["sk_pages"], g["sv_pages"], np.array([99], np.int32), 1)
+    with pytest.raises(ValueError):
+        pk.PagedKVBufferABI(g["sk_pages"], g["sv_pages"], g["stable"], 10 ** 6)
+    with pytest.raises(ValueError):
+        pk.PagedKVBufferABI(g["sk_pages"], g["sv_pages"][:1], g["stable"], n)
+
+    class Handle:  # the protocol a contiguous cache satisfies
+        def __init__(self, k, v, L):
+            self.k, self.v, self.L = k, v, L
+
+        def kv_geometry(self):
+            return pk.KVGeometry(self.k.shape[1], self.k.shape[2], 4096, self.L)
+
+        def seq_len(self):
+            return self.k.shape[0]
+
+        def gather(self, idx):
+            idx = np.asarray(list(idx), np.int64)
+            return self.k[idx], self.v[idx]
+
+    m = pk.materialize_paged_kv_abi(Handle(g["k0"], g["v0"], 16))
+    np.testing.assert_array_equal(m.k_pages, g["kpages0"])
+    np.testing.assert_array_equal(m.page_table, g["table0"])
+    assert m.logical_length == g["k0"].shape[0]
+    with pytest.raises(TypeError):
+        pk.materialize_paged_kv_abi(object())
+    for bad in (0, 4, 24, 2048):
+        with pytest.raises(ValueError):
+            pk._check_page_size(bad)
+    with pytest.raises(ValueError):
+        pk.paged_attention(np.zeros((2, 1, 64), np.float32), abi)          # head_dim
+    with pytest.raises(ValueError):
+        pk.paged_attention(np.zeros((2, 1, 128), np.float32), abi, backend="rocm")

@@ -110,3 +110,22 @@ def test_seeded_moe_routing_known_answer():
     assert r.load.tolist() == [1994, 2066, 2065, 2092, 2074, 2036, 1965, 2092]
     srt = np.sort(logits, axis=1)
     assert (srt[:, -2] - srt[:, -3]).min() > 1e-5  # no near-ties: the top-2 choice is well-posed
+
+
+def test_paged_attention_matches_reference(golden_dir):
+    g = _load(golden_dir, "paged.npz")
+    for i in range(int(g["n"])):
+        Hq, Hkv, q_len, n, L, causal = (int(x) for x in g[f"meta{i}"])
+        kp, vp, table = orc.paged_pack(g[f"k{i}"], g[f"v{i}"], L)
+        np.testing.assert_array_equal(kp, g[f"kpages{i}"])
+        np.testing.assert_array_equal(table, g[f"table{i}"])
+        idx = g[f"idx{i}"] if f"idx{i}" in g else None
+        o = orc.paged_attention(g[f"Q{i}"], kp, vp, table, n, causal=bool(causal), token_indices=idx)
+        np.testing.assert_allclose(o, g[f"O{i}"], rtol=1e-6, atol=1e-6)
+    # scattered physical placement
+    n = int(g["sn"])
+    gk, gv = orc.paged_gather(g["sk_pages"], g["sv_pages"], g["stable"], n, g["sgidx"])
+    np.testing.assert_array_equal(gk, g["sgk"])
+    np.testing.assert_array_equal(gv, g["sgv"])
+    o = orc.paged_attention(g["sQ"], g["sk_pages"], g["sv_pages"], g["stable"], n)
+    np.testing.assert_allclose(o, g["sO"], rtol=1e-6, atol=1e-6)

@@ -355,6 +355,46 @@ def bench_attn_decode(ranks, args, peaks, peak_kind):
                          "peak_kind": f"copy bandwidth, of {peak_kind}"}}
 
 
+def bench_attn_decode_paged(ranks, args, peaks, peak_kind):
+    """The decode workload with K/V behind a page table: pages [P, 64, Hkv, D] placed by a random
+    permutation, one table row per sequence."""
+    import ctypes
+    from tessera_b200 import _lib, device
+    from tessera_b200.device import DeviceArray, bfloat16
+    B, Hq, Hkv, S, D, L = 64, 32, 8, 8192, 128, 64
+    W = ranks.world
+    Bl = B // W
+    rng = np.random.default_rng(1006 + ranks.rank)
+    per_seq = S // L
+    P = Bl * per_seq
+    q = rng.standard_normal((Bl, Hq, D), dtype=np.float32).astype(bfloat16)
+    kp = tiled_normal(rng, (P, L, Hkv, D), 64, 1.0, bfloat16)
+    vp = tiled_normal(rng, (P, L, Hkv, D), 64, 1.0, bfloat16)
+    table = rng.permutation(P).astype(np.int32).reshape(Bl, per_seq)
+    lens = np.full(Bl, S, np.int32)
+    dq, dk, dv, dt, dl = (DeviceArray.from_host(t) for t in (q, kp, vp, table, lens))
+    do = DeviceArray.zeros((Bl, Hq, D), bfloat16)
+    lib = _lib.load()
+    ns = lib.tessera_sm100_attn_decode_splits(Bl, Hq, Hkv, S)
+    scr = DeviceArray((max(1, lib.tessera_sm100_attn_decode_scratch_bytes(Bl, Hq, ns)),), np.uint8)
+    scale = ctypes.c_float(1.0 / np.sqrt(D))
+    fn = lambda: _lib.call("tessera_sm100_paged_attn_decode_device", dq.ptr, dk.ptr, dv.ptr, dt.ptr, dl.ptr,
+                           do.ptr, Bl, Hq, Hkv, D, L, P, per_seq, S, scale, ns, scr.ptr, None)
+    times = timed_steps(ranks, device, fn, args.steps, args.warmup)
+    ms = statistics.mean(times)
+    code = device.consume_device_error()[0]
+    nbytes = 2.0 * B * Hkv * S * D * 2
+    ach = nbytes / W / ms / 1e6
+    return {"metric": "paged GQA decode attention GB/s (K+V bytes)", "value": nbytes / ms / 1e6, "unit": "GB/s",
+            "ms_per_step": ms, "device_error": code,
+            "config": f"batch={B} Hq={Hq} Hkv={Hkv} KV={S} D={D} bf16, pages of {L} tokens [P,L,Hkv,D] in "
+                      f"random physical order, batch sharded /{W}",
+            "splits": ns,
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": ach / peaks["hbm_gbs"], "traffic": None,
+                         "peak_kind": f"copy bandwidth, of {peak_kind}"}}
+
+
 def bench_moe(ranks, args, peaks, peak_kind):
     from tessera_b200 import _lib, collectives, device, parallel
     from tessera_b200.device import DeviceArray, bfloat16
@@ -520,7 +560,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="all", choices=["all", "gemm", "attn_prefill", "attn_decode", "moe"])
+    ap.add_argument("--workload", default="all", choices=["all", "gemm", "attn_prefill", "attn_decode", "attn_decode_paged", "moe"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tp-mode", default="fused", choices=["fused", "nccl"],
                     help="N>1 GEMM: all-gather fused into the epilogue (peer TMA stores) or NCCL after it")
@@ -554,9 +594,9 @@ def main():
 
     g = bench_gemm(ranks, args, peaks, peak_kind, sampler)
     extras = {}
-    if args.workload in ("all", "attn_prefill", "attn_decode", "moe"):
+    if args.workload in ("all", "attn_prefill", "attn_decode", "attn_decode_paged", "moe"):
         for name, fn in (("attn_prefill", bench_attn_prefill), ("attn_decode", bench_attn_decode),
-                         ("moe", bench_moe)):
+                         ("attn_decode_paged", bench_attn_decode_paged), ("moe", bench_moe)):
             if args.workload not in ("all", name):
                 continue
             try:

@@ -51,6 +51,21 @@ struct Params {
   int* err;
 };
 
+// Optional timeline of one CTA (compile with -DTESSERA_PREFILL_TRACE): clock64 stamps of the
+// hand-offs between the softmax groups and the MMA warp, read back with
+// tessera_sm100_prefill_trace_read. Not part of the normal build.
+#ifdef TESSERA_PREFILL_TRACE
+__device__ long long g_trace[3 * 4096];
+#define PF_TRACE(role, idx)                                                        \
+  do {                                                                             \
+    if (trace_on && (idx) < 4096) g_trace[(role) * 4096 + (idx)] = clock64();      \
+  } while (0)
+#else
+#define PF_TRACE(role, idx) \
+  do {                      \
+  } while (0)
+#endif
+
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -75,6 +90,32 @@ __device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
 __device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
   uint64_t d;
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// Volatile forms: the compiler keeps volatile asm statements in program order, which is how the
+// softmax loop pins its interleaving.
+__device__ __forceinline__ uint64_t ffma2_v(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm volatile("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t fadd2_v(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm volatile("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float ex2_v(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// {hi, lo} -> packed bf16x2 (hi in the upper half). cvt.rn.bf16x2.f32 issues to the same pipe as
+// ex2 (8 cycles per warp instruction each, measured), so the conversion is a third of the
+// exponent phase's MUFU time; packing with integer adds and a byte permute instead was faster in
+// an isolated loop but 4 % slower in this kernel, so the convert stays.
+__device__ __forceinline__ uint32_t cvt_bf16x2_v(float hi, float lo) {
+  uint32_t d;
+  asm volatile("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
   return d;
 }
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
@@ -107,8 +148,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   auto s_full = [&](int i) { return bars + 8u * (10 + i); };
   auto p_full = [&](int i) { return bars + 8u * (12 + i); };
   auto o_full = [&](int i) { return bars + 8u * (14 + i); };
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + SMEM_BAR_OFF + 128);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + SMEM_BAR_OFF + 132);
+  auto p_half = [&](int i) { return bars + 8u * (16 + i); };  // first 64 kv columns of P written
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + SMEM_BAR_OFF + 160);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + SMEM_BAR_OFF + 164);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -133,6 +175,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
   }
   const int n_iter = max(nblk[0], nblk[1]);
+#ifdef TESSERA_PREFILL_TRACE
+  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0;
+#endif
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -144,6 +189,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       mbar_init(v_empty(i), 1);
       mbar_init(s_full(i), 1);
       mbar_init(p_full(i), 4);  // one arrival per softmax warp
+      mbar_init(p_half(i), 4);
       mbar_init(o_full(i), 1);
     }
     fence_mbar_init();
@@ -209,10 +255,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         }
         umma_commit(bar_s[i]);
       };
-      auto issue_pv = [&](int i, int vst, bool accumulate) {
+      // P.V over kv steps [ks0, ks0 + 4): the softmax group releases P in two halves so the first
+      // half of this MMA overlaps the second half of the exponentials.
+      auto issue_pv = [&](int i, int vst, bool accumulate, int ks0) {
         const uint32_t b_lo = v_lo[vst], d = t_o[i], a = t_s[i];
 #pragma unroll
-        for (int ks = 0; ks < BKV / 16; ++ks) {
+        for (int ks = ks0; ks < ks0 + BKV / 32; ++ks) {
           // A: P rows in TMEM lanes, 16 bf16 of K per 8 columns. B: V[kv][d], 16 kv rows = 2048 B;
           // the two 64-wide d blocks are HALF_BYTES apart (the LBO field).
           umma_f16_ts_parts(d, a + 8u * ks, b_lo + ((ks * 2048) >> 4), desc_hi, idesc_pv,
@@ -241,9 +289,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         bool next_k_ready = false;
         for (int i = 0; i < 2 && ok; ++i) {
           if (j >= nblk[i]) continue;
-          if (!(ok = mbar_wait(p_full(i), j & 1, abort_flag, p.err, kErrWaitOther, 4000 + j))) break;
+          PF_TRACE(2, (j * 2 + i) * 4 + 0);
+          if (!(ok = mbar_wait(p_half(i), j & 1, abort_flag, p.err, kErrWaitOther, 6000 + j))) break;
+          PF_TRACE(2, (j * 2 + i) * 4 + 1);
           tc_fence_after();
-          issue_pv(i, st, j > 0);
+          issue_pv(i, st, j > 0, 0);
+          if (!(ok = mbar_wait(p_full(i), j & 1, abort_flag, p.err, kErrWaitOther, 4000 + j))) break;
+          PF_TRACE(2, (j * 2 + i) * 4 + 2);
+          tc_fence_after();
+          issue_pv(i, st, true, BKV / 32);
           if (j == nblk[i] - 1) umma_commit(o_full(i));
           if (j + 1 < nblk[i]) {
             if (!next_k_ready) {
@@ -253,6 +307,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             }
             issue_s(i, nst);
           }
+          PF_TRACE(2, (j * 2 + i) * 4 + 3);
         }
         if (!ok) break;
         umma_commit(v_empty(st));
@@ -271,7 +326,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     float l = 0.f;
     bool ok = true;
     for (int j = 0; j < nblk[i] && ok; ++j) {
+      if ((warp & 3) == 0) PF_TRACE(i, j * 8 + 0);
       if (!(ok = mbar_wait(s_full(i), j & 1, abort_flag, p.err, kErrWaitTmemFull, j))) break;
+      if ((warp & 3) == 0) PF_TRACE(i, j * 8 + 1);
       tc_fence_after();
       const int kv0 = j * BKV;
       const bool need_mask = (kv0 + BKV - 1 > qi0 + shift && p.causal) || (kv0 + BKV > p.Sk);
@@ -284,6 +341,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       tmem_ld_32x32b_x32(t_s + 64, s2);
       tmem_ld_32x32b_x32(t_s + 96, s3);
       tmem_ld_wait();
+      if ((warp & 3) == 0) PF_TRACE(i, j * 8 + 2);
       if (need_mask) {
         constexpr uint32_t kNegInf = 0xff800000u;
 #pragma unroll
@@ -337,37 +395,43 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       // two-wide fp32 instructions; each batch of 32 columns is laid out as independent work
       // (16 packed FMAs, 32 exponentials, 16 packed adds, 16 packs) so that the single warp a tile
       // has on each scheduler can issue back to back.
+      if ((warp & 3) == 0) PF_TRACE(i, j * 8 + 3);
       const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
       const uint64_t negm2 = pack_f32x2(-m_used, -m_used);
       uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};
-      auto exp_batch = [&](const uint32_t (&sv)[32], uint32_t* pk) {
-        uint64_t x[16];
-#pragma unroll
-        for (int q = 0; q < 16; ++q) x[q] = ffma2(pack_u32x2(sv[2 * q], sv[2 * q + 1]), scale2, negm2);
-        float e[32];
-#pragma unroll
-        for (int q = 0; q < 16; ++q) {
-          e[2 * q] = ex2(lo_f32(x[q]));
-          e[2 * q + 1] = ex2(hi_f32(x[q]));
-        }
-#pragma unroll
-        for (int q = 0; q < 16; ++q) {
-          sum2[q & 3] = fadd2(sum2[q & 3], pack_f32x2(e[2 * q], e[2 * q + 1]));
-          pk[q] = pack_bf16(e[2 * q], e[2 * q + 1]);
-        }
+      // The 128 columns are handled as 64 pairs in a software pipeline whose instruction order is
+      // pinned (volatile asm): a warp issues in order, and a run of back-to-back exponentials
+      // would hold it for 8 cycles each with nothing else going out. Per step the scale-and-shift
+      // of pair t+2, the two exponentials of pair t and the sum and bf16 pack of pair t-3 are
+      // interleaved, so the packed FMA / add / convert work sits in the shadow of the MUFU pipe.
+      auto S = [&](int k) -> uint32_t {
+        return k < 32 ? s0[k & 31] : k < 64 ? s1[k & 31] : k < 96 ? s2[k & 31] : s3[k & 31];
       };
-      {
-        uint32_t pk[32];
-        exp_batch(s0, pk);
-        exp_batch(s1, pk + 16);
-        tmem_st_32x32b_x32(t_s, pk);
+      constexpr int kAhead = 2, kLag = 3;
+      uint64_t xs[64];
+      float ev[128];
+      uint32_t pka[32], pkb[32];
+#pragma unroll
+      for (int t = -kAhead; t < 64 + kLag; ++t) {
+        const int ta = t + kAhead, tc = t - kLag;
+        if (ta >= 0 && ta < 64) xs[ta] = ffma2_v(pack_u32x2(S(2 * ta), S(2 * ta + 1)), scale2, negm2);
+        if (t >= 0 && t < 64) ev[2 * t] = ex2_v(lo_f32(xs[t]));
+        if (tc >= 0 && tc < 64)
+          sum2[tc & 3] = fadd2_v(sum2[tc & 3], pack_f32x2(ev[2 * tc], ev[2 * tc + 1]));
+        if (t >= 0 && t < 64) ev[2 * t + 1] = ex2_v(hi_f32(xs[t]));
+        if (tc >= 0 && tc < 32) pka[tc] = cvt_bf16x2_v(ev[2 * tc + 1], ev[2 * tc]);
+        if (tc >= 32 && tc < 64) pkb[tc - 32] = cvt_bf16x2_v(ev[2 * tc + 1], ev[2 * tc]);
+        if (tc == 31) tmem_st_32x32b_x32(t_s, pka);  // kv 0..63 of P
+        if (tc == 47) {
+          // the first half of P has landed: hand it to the MMA warp while the rest is computed
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(p_half(i));
+          if ((warp & 3) == 0) PF_TRACE(i, j * 8 + 4);
+        }
       }
-      {
-        uint32_t pk[32];
-        exp_batch(s2, pk);
-        exp_batch(s3, pk + 16);
-        tmem_st_32x32b_x32(t_s + 32, pk);
-      }
+      tmem_st_32x32b_x32(t_s + 32, pkb);
       {
         const uint64_t t2 = fadd2(fadd2(sum2[0], sum2[1]), fadd2(sum2[2], sum2[3]));
         l += lo_f32(t2) + hi_f32(t2);
@@ -377,6 +441,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       // One arrival per warp: 128 arrivals on a single shared-memory word would serialise.
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full(i));
+      if ((warp & 3) == 0) PF_TRACE(i, j * 8 + 5);
     }
     // ---- epilogue: O / l -> bf16 -> swizzled smem (the Q tile's buffer) -> TMA store
     if (ok && nblk[i] > 0) ok = mbar_wait(o_full(i), 0, abort_flag, p.err, kErrWaitTmemFull, 9000);
@@ -494,6 +559,12 @@ int launch(const void* Q, const void* K, const void* V, void* O, int B, int H, i
 }  // namespace tsb
 
 using namespace tsb;
+
+#ifdef TESSERA_PREFILL_TRACE
+extern "C" int tessera_sm100_prefill_trace_read(long long* out, int n) {
+  return cudaMemcpyFromSymbol(out, tsb::attn_prefill::g_trace, sizeof(long long) * n) == cudaSuccess ? 0 : 3;
+}
+#endif
 
 extern "C" {
 

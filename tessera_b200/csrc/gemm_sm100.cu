@@ -2,6 +2,7 @@
 #include "gemm_sm100.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 
 #include "../../include/tessera_sm100.h"
@@ -299,7 +300,46 @@ int gemm_device(const void* A, const void* B, void* D, int batch, int M, int N, 
   return rc;
 }
 
+// Streams and events of the pipelined host-pointer form, created once per device.
+constexpr int kMaxChunks = 32;
+struct HostPipe {
+  cudaStream_t up = nullptr, comp = nullptr, down = nullptr;
+  cudaEvent_t b_ready = nullptr, up_done[kMaxChunks] = {}, comp_done[kMaxChunks] = {};
+  bool ok = false;
+};
+HostPipe g_pipes[64];
+std::mutex g_pipe_mu;
+
+HostPipe* host_pipe() {
+  const int dev = current_device();
+  if (dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lk(g_pipe_mu);
+  HostPipe& p = g_pipes[dev];
+  if (!p.ok) {
+    bool good = cudaStreamCreateWithFlags(&p.up, cudaStreamNonBlocking) == cudaSuccess &&
+                cudaStreamCreateWithFlags(&p.comp, cudaStreamNonBlocking) == cudaSuccess &&
+                cudaStreamCreateWithFlags(&p.down, cudaStreamNonBlocking) == cudaSuccess &&
+                cudaEventCreateWithFlags(&p.b_ready, cudaEventDisableTiming) == cudaSuccess;
+    for (int i = 0; good && i < kMaxChunks; ++i)
+      good = cudaEventCreateWithFlags(&p.up_done[i], cudaEventDisableTiming) == cudaSuccess &&
+             cudaEventCreateWithFlags(&p.comp_done[i], cudaEventDisableTiming) == cudaSuccess;
+    if (!good) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    p.ok = true;
+  }
+  return &p;
+}
+
 // Host-pointer form: upload (re-pitching rows on the way), run, download.
+//
+// Large problems are cut into chunks that flow through three streams — upload, compute,
+// download — so the transfer of chunk i+1 to the device, the GEMM of chunk i and the transfer of
+// chunk i-1 back to the host overlap (the link is full duplex; with page-locked host buffers the
+// call then costs about the larger of the two transfer directions instead of their sum plus the
+// kernel). A chunk is a block of rows of A and D (one batch entry when batch > 1); B is uploaded
+// first (per entry when batched). Small problems take one chunk.
 int gemm_host(const void* A, const void* B, void* D, int batch, int M, int N, int K, int in_dtype,
               int out_dtype) {
   if (!A || !B || !D || batch <= 0 || M <= 0 || N <= 0 || K <= 0) {
@@ -310,28 +350,110 @@ int gemm_host(const void* A, const void* B, void* D, int batch, int M, int N, in
   if (int rc = ensure_device()) return rc;
   const size_t osz = out_size(out_dtype);
   const long long Kp = round_up8(K), Np = round_up8(N);
+  const size_t bytes = ((size_t)batch * M * K + (size_t)batch * K * N) * 2 + (size_t)batch * M * N * osz;
+  // Chunk plan: rows of one matrix, or whole batch entries.
+  int chunks = 1, rows_per_chunk = M;
+  HostPipe* pipe = nullptr;
+  if (bytes >= (size_t)(32u << 20) && (pipe = host_pipe()) != nullptr) {
+    if (batch > 1) {
+      chunks = std::min(batch, kMaxChunks);
+    } else {
+      chunks = std::max(1, std::min({M / 1024, kMaxChunks, 16}));  // 8 chunks measured best at 8192^3
+      // Tuning override: TESSERA_SM100_HOST_GEMM_CHUNKS=<1..32> fixes the number of row chunks.
+      if (const char* env = std::getenv("TESSERA_SM100_HOST_GEMM_CHUNKS")) {
+        const int v = std::atoi(env);
+        if (v >= 1) chunks = std::min({v, kMaxChunks, std::max(1, M / 128)});
+      }
+      rows_per_chunk = (((M + chunks - 1) / chunks) + 127) / 128 * 128;
+      chunks = (M + rows_per_chunk - 1) / rows_per_chunk;
+    }
+  }
   void* pA = pool_alloc((size_t)batch * M * Kp * 2);
   void* pB = pool_alloc((size_t)batch * K * Np * 2);
   void* pD = pool_alloc((size_t)batch * M * Np * osz);
   int rc = (pA && pB && pD) ? kOk : kDeviceFailed;
-  cudaStream_t st = nullptr;
   auto fail = [&](const char* what) {
     set_last_error("gemm: %s failed: %s", what, cudaGetErrorString(cudaGetLastError()));
     rc = kDeviceFailed;
   };
-  if (rc == kOk && cudaMemcpy2DAsync(pA, Kp * 2, A, (size_t)K * 2, (size_t)K * 2,
-                                     (size_t)batch * M, cudaMemcpyHostToDevice, st) != cudaSuccess)
-    fail("upload of A");
-  if (rc == kOk && cudaMemcpy2DAsync(pB, Np * 2, B, (size_t)N * 2, (size_t)N * 2,
-                                     (size_t)batch * K, cudaMemcpyHostToDevice, st) != cudaSuccess)
-    fail("upload of B");
-  if (rc == kOk)
-    rc = launch_plain(pA, pB, pD, batch, M, N, K, Kp, Np, Np, (long long)M * Kp,
-                      (long long)K * Np, (long long)M * Np, in_dtype, out_dtype, st);
-  if (rc == kOk && cudaMemcpy2DAsync(D, (size_t)N * osz, pD, Np * osz, (size_t)N * osz,
-                                     (size_t)batch * M, cudaMemcpyDeviceToHost, st) != cudaSuccess)
-    fail("download of D");
-  if (cudaStreamSynchronize(st) != cudaSuccess && rc == kOk) fail("synchronise");
+  auto up2d = [&](void* dst, long long dpitch, const void* src, long long cols, long long rows,
+                  cudaStream_t st, const char* what) {
+    if (rc != kOk) return;
+    const cudaError_t e =
+        dpitch == cols  // contiguous on both sides: one linear copy
+            ? cudaMemcpyAsync(dst, src, (size_t)rows * cols * 2, cudaMemcpyHostToDevice, st)
+            : cudaMemcpy2DAsync(dst, dpitch * 2, src, (size_t)cols * 2, (size_t)cols * 2,
+                                (size_t)rows, cudaMemcpyHostToDevice, st);
+    if (e != cudaSuccess) fail(what);
+  };
+  auto down2d = [&](void* dst, const void* src, long long rows, cudaStream_t st) {
+    if (rc != kOk) return;
+    const cudaError_t e =
+        Np == N ? cudaMemcpyAsync(dst, src, (size_t)rows * N * osz, cudaMemcpyDeviceToHost, st)
+                : cudaMemcpy2DAsync(dst, (size_t)N * osz, src, Np * osz, (size_t)N * osz,
+                                    (size_t)rows, cudaMemcpyDeviceToHost, st);
+    if (e != cudaSuccess) fail("download of D");
+  };
+  const char* hA = static_cast<const char*>(A);
+  const char* hB = static_cast<const char*>(B);
+  char* hD = static_cast<char*>(D);
+  char* dA = static_cast<char*>(pA);
+  char* dB = static_cast<char*>(pB);
+  char* dD = static_cast<char*>(pD);
+  if (chunks <= 1) {
+    cudaStream_t st = nullptr;
+    up2d(pA, Kp, A, K, (long long)batch * M, st, "upload of A");
+    up2d(pB, Np, B, N, (long long)batch * K, st, "upload of B");
+    if (rc == kOk)
+      rc = launch_plain(pA, pB, pD, batch, M, N, K, Kp, Np, Np, (long long)M * Kp,
+                        (long long)K * Np, (long long)M * Np, in_dtype, out_dtype, st);
+    down2d(D, pD, (long long)batch * M, st);
+    if (cudaStreamSynchronize(st) != cudaSuccess && rc == kOk) fail("synchronise");
+  } else {
+    // Work queued earlier on the default stream (none by this library's host forms, which all
+    // synchronise before returning) is not waited for: the three streams are non-blocking.
+    if (batch == 1) {
+      up2d(pB, Np, B, N, K, pipe->up, "upload of B");
+      if (rc == kOk && cudaEventRecord(pipe->b_ready, pipe->up) != cudaSuccess) fail("event record");
+      if (rc == kOk && cudaStreamWaitEvent(pipe->comp, pipe->b_ready, 0) != cudaSuccess)
+        fail("stream wait");
+    }
+    for (int c = 0; c < chunks && rc == kOk; ++c) {
+      // chunk c: batch entries [e0, e1) x rows [r0, r1)
+      int e0 = 0, e1 = 1, r0 = 0, r1 = M;
+      if (batch > 1) {
+        e0 = (int)((long long)batch * c / chunks);
+        e1 = (int)((long long)batch * (c + 1) / chunks);
+      } else {
+        r0 = c * rows_per_chunk;
+        r1 = std::min(M, r0 + rows_per_chunk);
+      }
+      const long long a_off = (long long)e0 * M + r0;  // first row of A / D in this chunk
+      const long long rows = batch > 1 ? (long long)(e1 - e0) * M : (r1 - r0);
+      up2d(dA + a_off * Kp * 2, Kp, hA + a_off * K * 2, K, rows, pipe->up, "upload of A");
+      if (batch > 1)
+        up2d(dB + (long long)e0 * K * Np * 2, Np, hB + (long long)e0 * K * N * 2, N,
+             (long long)(e1 - e0) * K, pipe->up, "upload of B");
+      if (rc == kOk && cudaEventRecord(pipe->up_done[c], pipe->up) != cudaSuccess) fail("event record");
+      if (rc == kOk && cudaStreamWaitEvent(pipe->comp, pipe->up_done[c], 0) != cudaSuccess)
+        fail("stream wait");
+      if (rc == kOk)
+        rc = launch_plain(dA + a_off * Kp * 2, dB + (batch > 1 ? (long long)e0 * K * Np * 2 : 0),
+                          dD + a_off * Np * osz, batch > 1 ? e1 - e0 : 1, batch > 1 ? M : r1 - r0, N,
+                          K, Kp, Np, Np, (long long)M * Kp, (long long)K * Np, (long long)M * Np,
+                          in_dtype, out_dtype, pipe->comp);
+      if (rc == kOk && cudaEventRecord(pipe->comp_done[c], pipe->comp) != cudaSuccess)
+        fail("event record");
+      if (rc == kOk && cudaStreamWaitEvent(pipe->down, pipe->comp_done[c], 0) != cudaSuccess)
+        fail("stream wait");
+      down2d(hD + a_off * N * osz, dD + a_off * Np * osz, rows, pipe->down);
+    }
+    // Drain all three streams whatever happened, so the pooled buffers can be reused.
+    const bool s1 = cudaStreamSynchronize(pipe->up) == cudaSuccess;
+    const bool s2 = cudaStreamSynchronize(pipe->comp) == cudaSuccess;
+    const bool s3 = cudaStreamSynchronize(pipe->down) == cudaSuccess;
+    if (!(s1 && s2 && s3) && rc == kOk) fail("synchronise");
+  }
   if (rc == kOk) {
     int e[4];
     if (consume_device_err(e) != 0) {

@@ -131,3 +131,25 @@ def test_fused_epilogue(golden_dir, act):
     got32 = tessera.ops.gemm(A, B, epilogue=dict(bias=bias, activation=act))
     assert rel_err(got32, orc.fused_epilogue(orc.gemm(A, B), bias=bias, activation=act)) < 1e-4
     no_device_error()
+
+
+@pytest.mark.parametrize("batch,M,N,K,out_dt", [(1, 4352, 2048, 2048, np.float32), (3, 1536, 1536, 1536, np.float32),
+                                                (1, 3100, 3080, 3064, bfloat16)])
+def test_host_pointer_form_pipelined_chunks(lib, batch, M, N, K, out_dt):
+    """Host-pointer GEMMs of 32 MB and more run as row (or batch-entry) chunks over three streams;
+    the result must equal the device-pointer form bit for bit (same kernel, same tiles per row
+    block) and the oracle within tolerance. The last case has a ragged last chunk and row pitches
+    that are not multiples of 8 elements."""
+    rng = np.random.default_rng(M + N)
+    shapeA = (batch, M, K) if batch > 1 else (M, K)
+    shapeB = (batch, K, N) if batch > 1 else (K, N)
+    A = _rand(rng, shapeA, bfloat16, 1 / np.sqrt(K))
+    B = _rand(rng, shapeB, bfloat16)
+    D = np.zeros(shapeA[:-1] + (N,), out_dt)
+    rc = lib.tessera_sm100_gemm(A.ctypes.data, B.ctypes.data, D.ctypes.data, batch, M, N, K, 1,
+                                0 if out_dt == np.float32 else 1)
+    assert rc == 0, lib.tessera_sm100_last_error()
+    assert rel_err(D, orc.gemm(A, B)) < (1e-4 if out_dt == np.float32 else TOL)
+    if N % 8 == 0 and K % 8 == 0:
+        np.testing.assert_array_equal(D, gemm_device(A, B, out_dt))
+    no_device_error()

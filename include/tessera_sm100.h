@@ -80,7 +80,8 @@ int tessera_sm100_mma_gemm_bf16_device(const void* A, const void* B, void* D, in
 int tessera_sm100_mma_gemm_f16_device(const void* A, const void* B, void* D, int M, int N, int K,
                                       void* stream);
 /* Batched form with a selectable output dtype: A[batch,M,K], B[batch,K,N], D[batch,M,N].
- * Covers tessera.ops.batched_gemm (python/tessera/__init__.py:252-254).  * Problems of 32 MB and more are cut into row chunks (batch entries when batch > 1) that flow
+ * Covers tessera.ops.batched_gemm (python/tessera/__init__.py:252-254).
+ * Problems of 32 MB and more are cut into row chunks (batch entries when batch > 1) that flow
  * through upload, compute and download streams, so with page-locked host buffers the call costs
  * about the larger transfer direction instead of upload + kernel + download.
  * TESSERA_SM100_HOST_GEMM_CHUNKS=<1..32> in the environment fixes the number of row chunks. */

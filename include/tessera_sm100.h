@@ -236,6 +236,27 @@ int tessera_sm100_attn_decode_static_device(const void* Q, const void* K, const 
                                             int B, int Hq, int Hkv, int Sk, int D, float scale,
                                             int splits, int check_previous, void* stream);
 
+/* Attention forward over strided operands: the same kernels with the layouts described by element
+ * strides, one (batch, head, position) triple per tensor; the head dimension (128) is contiguous
+ * and every stride is a multiple of 8 elements. Serves nn.functional.multi_head_attention
+ * (python/tessera/nn/functional.py:493-548), whose [B, S, H*D] operands the reference reshapes
+ * and transposes to [B, H, S, D] and back: here Q, K, V and O are read and written in place
+ * (strides {S*H*D, D, H*D}), as are the column slices of a fused QKV projection. Sq == 1 runs the
+ * decode kernel, anything else the prefill kernel (tessera_sm100_flash_attn_fwd_strided_device
+ * is the prefill kernel alone). */
+int tessera_sm100_flash_attn_strided_device(const void* Q, const void* K, const void* V, void* O,
+                                            int B, int Hq, int Hkv, int Sq, int Sk, int D,
+                                            const long long* q_strides, const long long* k_strides,
+                                            const long long* v_strides, const long long* o_strides,
+                                            float scale, int causal, void* stream);
+int tessera_sm100_flash_attn_fwd_strided_device(const void* Q, const void* K, const void* V, void* O,
+                                                int B, int Hq, int Hkv, int Sq, int Sk, int D,
+                                                const long long* q_strides,
+                                                const long long* k_strides,
+                                                const long long* v_strides,
+                                                const long long* o_strides, float scale, int causal,
+                                                void* stream);
+
 /* ---- paged KV cache ------------------------------------------------------------------------
  * The page ABI of python/tessera/cache/paged_kv.py:91-140 (PagedKVBufferABI): K and V pages are
  * [physical_page, page_offset, head, dim] and page_table[logical_page] names the physical page;

@@ -132,6 +132,33 @@ def gqa_attention(Q, K, V, num_query_heads: int, num_kv_heads: int, **kwargs) ->
                       **kwargs)
 
 
+def multi_head_attention(Q, K, V, num_heads: int, scale=None, causal: bool = False,
+                         num_kv_heads: Optional[int] = None) -> np.ndarray:
+    """``[B, S, H*D]`` operands: reshape to ``[B, H, S, D]``, ``flash_attn``, transpose back
+    (python/tessera/nn/functional.py:493-548). ``num_kv_heads`` (not in the reference, which takes
+    equal widths) repeats K/V heads as ``gqa_attention`` does."""
+    Q, K, V = _f32(Q), _f32(K), _f32(V)
+    B, Sq, hd = Q.shape
+    D = hd // num_heads
+    Hkv = num_kv_heads or num_heads
+
+    def split(t, h):
+        return t.reshape(B, t.shape[1], h, D).transpose(0, 2, 1, 3)
+
+    q, k, v = split(Q, num_heads), split(K, Hkv), split(V, Hkv)
+    if Hkv != num_heads:
+        out = gqa_attention(q, k, v, num_heads, Hkv, scale=scale, causal=causal)
+    else:
+        out = flash_attn(q, k, v, scale=scale, causal=causal)
+    return np.ascontiguousarray(out.transpose(0, 2, 1, 3)).reshape(B, Sq, hd)
+
+
+def linear(x, W, bias=None) -> np.ndarray:
+    """``x @ W (+ bias)`` (python/tessera/nn/functional.py:33-44)."""
+    y = np.matmul(_f32(x), _f32(W))
+    return (y + np.asarray(bias, np.float32)).astype(np.float32) if bias is not None else y.astype(np.float32)
+
+
 def softmax_merge(oa, ma, la, ob, mb, lb):
     """Associative merge of two max-shifted partial attention states
     (python/tessera/_block_attnres_ops.py:104-131)."""

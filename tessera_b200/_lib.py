@@ -103,6 +103,11 @@ _SIGNATURES = {
     "tessera_sm100_attn_decode_scratch_bytes": (c_size_t, [c_int, c_int, c_int]),
     "tessera_sm100_attn_decode_device": (c_int, [_VP, _VP, _VP, _VP, c_int, c_int, c_int, c_int,
                                                  c_int, c_float, c_int, _VP, _VP]),
+    "tessera_sm100_flash_attn_strided_device": (c_int, [_VP, _VP, _VP, _VP, c_int, c_int, c_int, c_int, c_int,
+                                                        c_int, _VP, _VP, _VP, _VP, c_float, c_int, _VP]),
+    "tessera_sm100_flash_attn_fwd_strided_device": (c_int, [_VP, _VP, _VP, _VP, c_int, c_int, c_int, c_int,
+                                                            c_int, c_int, _VP, _VP, _VP, _VP, c_float, c_int,
+                                                            _VP]),
     "tessera_sm100_paged_attn_decode_device": (c_int, [_VP, _VP, _VP, _VP, _VP, _VP, c_int, c_int, c_int,
                                                        c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                                                        _VP, _VP]),

@@ -56,6 +56,7 @@ struct Params {
   int* err;
   // Paged mode only: K/V live in pages [P, page_size, Hkv, D]; sequence b reads logical page lp
   // from physical page page_table[b * max_pages + lp] and holds seq_lens[b] positions.
+  long long q_sb, q_sh, o_sb, o_sh;  // element strides of Q and O over (batch, head)
   const int* page_table;
   const int* seq_lens;
   int max_pages, num_pages, page_size, page_shift;
@@ -201,7 +202,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ C
   {
     const bool live = g < nheads;
     const uint32_t* qrow = reinterpret_cast<const uint32_t*>(
-        p.Q + (static_cast<long long>(b) * p.Hq + head0 + (live ? g : 0)) * D);
+        p.Q + static_cast<long long>(b) * p.q_sb + (head0 + (live ? g : 0)) * p.q_sh);
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
       qb[ks][0] = live ? qrow[(16 * ks + 2 * t) >> 1] : 0u;
@@ -338,7 +339,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ C
     }
     const long long row = static_cast<long long>(b) * p.Hq + head0 + h;
     if (p.splits == 1) {
-      p.O[row * D + d] = __float2bfloat16_rn(acc / l);
+      p.O[static_cast<long long>(b) * p.o_sb + (head0 + h) * p.o_sh + d] = __float2bfloat16_rn(acc / l);
     } else {
       p.part_o[(row * p.splits + split) * D + d] = acc;
       if (d == 0) {
@@ -351,7 +352,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ C
 
 // One CTA per (b, hq): merges the split partials and writes bf16.
 __global__ void merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                             __nv_bfloat16* __restrict__ O, int splits) {
+                             __nv_bfloat16* __restrict__ O, int splits, int Hq, long long o_sb,
+                             long long o_sh) {
   const long long row = blockIdx.x;
   const int d = threadIdx.x;
   float m = -INFINITY;
@@ -363,7 +365,7 @@ __global__ void merge_kernel(const float* __restrict__ part_o, const float* __re
     acc += f * part_o[(row * splits + s) * D + d];
     l += f * part_ml[(row * splits + s) * 2 + 1];
   }
-  O[row * D + d] = __float2bfloat16_rn(acc / l);
+  O[(row / Hq) * o_sb + (row % Hq) * o_sh + d] = __float2bfloat16_rn(acc / l);
 }
 
 int choose_splits(int B, int Hkv, int groups_per_kv, int tiles_total) {
@@ -382,8 +384,13 @@ size_t scratch_bytes(int B, int Hq, int splits) {
 
 // K, V: [B, Hkv, Sk, D] bf16 device pointers; Q, O: [B, Hq, 1, D]. `scratch` must hold
 // scratch_bytes(B, Hq, splits) bytes when splits > 1.
+// Optional strides (elements, triples over (batch, head, position); the position stride of Q and O
+// is unused): any layout with a contiguous head dimension, e.g. [B, S, H, D] or slices of a fused
+// QKV buffer. Null means the dense layouts above.
 int launch(const void* Q, const void* K, const void* V, void* O, int B, int Hq, int Hkv, int Sk,
-           int Dh, float scale, int splits, void* scratch, cudaStream_t st) {
+           int Dh, float scale, int splits, void* scratch, cudaStream_t st,
+           const long long* qs = nullptr, const long long* ks = nullptr,
+           const long long* vs = nullptr, const long long* os = nullptr) {
   if (!Q || !K || !V || !O || B <= 0 || Hq <= 0 || Hkv <= 0 || Sk <= 0) {
     set_last_error("attn_decode: null pointer or non-positive size");
     return kBadArg;
@@ -409,6 +416,8 @@ int launch(const void* Q, const void* K, const void* V, void* O, int B, int Hq, 
   p.Hkv = Hkv;
   p.Sk = Sk;
   p.G = Hq / Hkv;
+  p.q_sb = p.o_sb = (long long)Hq * D;
+  p.q_sh = p.o_sh = D;
   p.groups_per_kv = (p.G + 7) / 8;
   p.tiles_total = (Sk + TILE - 1) / TILE;
   if (splits <= 0) splits = choose_splits(B, Hkv, p.groups_per_kv, p.tiles_total);
@@ -427,13 +436,34 @@ int launch(const void* Q, const void* K, const void* V, void* O, int B, int Hq, 
     p.part_o = static_cast<float*>(scratch);
     p.part_ml = p.part_o + (size_t)B * Hq * splits * D;
   }
+  for (const long long* t : {qs, ks, vs, os})
+    if (t)
+      for (int i = 0; i < 3; ++i)
+        if (t[i] <= 0 || (t[i] & 7)) {
+          set_last_error("attn_decode: strides must be positive multiples of 8 elements (got %lld)",
+                         t[i]);
+          return kBadArg;
+        }
+  if (qs) {
+    p.q_sb = qs[0];
+    p.q_sh = qs[1];
+  }
+  if (os) {
+    p.o_sb = os[0];
+    p.o_sh = os[1];
+  }
   CUtensorMap tK, tV;
   uint64_t dims[4] = {(uint64_t)D, (uint64_t)Sk, (uint64_t)Hkv, (uint64_t)B};
   uint64_t str[3] = {(uint64_t)D * 2, (uint64_t)Sk * D * 2, (uint64_t)Hkv * Sk * D * 2};
+  uint64_t strk[3], strv[3];
+  for (int i = 0; i < 3; ++i) {
+    strk[i] = ks ? (uint64_t)ks[2 - i] * 2 : str[i];
+    strv[i] = vs ? (uint64_t)vs[2 - i] * 2 : str[i];
+  }
   uint32_t box[4] = {64, TILE, 1, 1};
-  if (!encode_tmap(&tK, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, K, dims, str, box,
+  if (!encode_tmap(&tK, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, K, dims, strk, box,
                    CU_TENSOR_MAP_SWIZZLE_128B) ||
-      !encode_tmap(&tV, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, V, dims, str, box,
+      !encode_tmap(&tV, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, V, dims, strv, box,
                    CU_TENSOR_MAP_SWIZZLE_128B))
     return kBadArg;
   TSB_CUDA_OK(cudaFuncSetAttribute(decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -443,7 +473,7 @@ int launch(const void* Q, const void* K, const void* V, void* O, int B, int Hq, 
   TSB_CUDA_OK(cudaGetLastError());
   note_launch();
   if (splits > 1) {
-    merge_kernel<<<B * Hq, D, 0, st>>>(p.part_o, p.part_ml, p.O, splits);
+    merge_kernel<<<B * Hq, D, 0, st>>>(p.part_o, p.part_ml, p.O, splits, Hq, p.o_sb, p.o_sh);
     TSB_CUDA_OK(cudaGetLastError());
     note_launch();
   }
@@ -494,6 +524,8 @@ int launch_paged(const void* Q, const void* k_pages, const void* v_pages, const 
   p.Hkv = Hkv;
   p.Sk = max_seq_len;
   p.G = Hq / Hkv;
+  p.q_sb = p.o_sb = (long long)Hq * D;
+  p.q_sh = p.o_sh = D;
   p.groups_per_kv = (p.G + 7) / 8;
   p.tiles_total = (max_seq_len + TILE - 1) / TILE;
   p.page_table = page_table;
@@ -535,7 +567,7 @@ int launch_paged(const void* Q, const void* k_pages, const void* v_pages, const 
   TSB_CUDA_OK(cudaGetLastError());
   note_launch();
   if (splits > 1) {
-    merge_kernel<<<B * Hq, D, 0, st>>>(p.part_o, p.part_ml, p.O, splits);
+    merge_kernel<<<B * Hq, D, 0, st>>>(p.part_o, p.part_ml, p.O, splits, Hq, p.o_sb, p.o_sh);
     TSB_CUDA_OK(cudaGetLastError());
     note_launch();
   }
@@ -692,6 +724,8 @@ int launch_static(const void* Q, const void* K, const void* V, void* O, int B, i
   p.Hkv = Hkv;
   p.Sk = Sk;
   p.G = Hq / Hkv;
+  p.q_sb = p.o_sb = (long long)Hq * D;
+  p.q_sh = p.o_sh = D;
   p.groups_per_kv = (p.G + 7) / 8;
   p.tiles_total = (Sk + TILE - 1) / TILE;
   const bool automatic = splits <= 0;
@@ -730,7 +764,7 @@ int launch_static(const void* Q, const void* K, const void* V, void* O, int B, i
   TSB_CUDA_OK(cudaGetLastError());
   note_launch();
   if (splits > 1) {
-    merge_kernel<<<B * Hq, D, 0, st>>>(p.part_o, p.part_ml, p.O, splits);
+    merge_kernel<<<B * Hq, D, 0, st>>>(p.part_o, p.part_ml, p.O, splits, Hq, p.o_sb, p.o_sh);
     TSB_CUDA_OK(cudaGetLastError());
     note_launch();
   }
@@ -764,6 +798,36 @@ int tessera_sm100_attn_decode_device(const void* Q, const void* K, const void* V
                                      void* scratch, void* stream) {
   return attn_decode::launch(Q, K, V, O, B, Hq, Hkv, Sk, D, scale, splits, scratch,
                              static_cast<cudaStream_t>(stream));
+}
+
+// Attention forward over strided operands (contiguous head dimension; element strides as triples
+// over (batch, head, position) per tensor): one query position goes to the decode kernel, anything
+// else to the prefill kernel. Nothing is copied or transposed.
+int tessera_sm100_flash_attn_strided_device(const void* Q, const void* K, const void* V, void* O,
+                                            int B, int Hq, int Hkv, int Sq, int Sk, int D,
+                                            const long long* q_strides, const long long* k_strides,
+                                            const long long* v_strides, const long long* o_strides,
+                                            float scale, int causal, void* stream) {
+  if (!q_strides || !k_strides || !v_strides || !o_strides) {
+    set_last_error("flash_attn_strided: null stride array");
+    return kBadArg;
+  }
+  if (Sq != 1)
+    return tessera_sm100_flash_attn_fwd_strided_device(Q, K, V, O, B, Hq, Hkv, Sq, Sk, D, q_strides,
+                                                       k_strides, v_strides, o_strides, scale,
+                                                       causal, stream);
+  if (int rc = ensure_device()) return rc;
+  const int splits = tessera_sm100_attn_decode_splits(B, Hq, Hkv, Sk);
+  void* scratch = nullptr;
+  if (splits > 1) {
+    scratch = pool_alloc(attn_decode::scratch_bytes(B, Hq, splits));
+    if (!scratch) return kDeviceFailed;
+  }
+  const int rc = attn_decode::launch(Q, K, V, O, B, Hq, Hkv, Sk, D, scale, std::max(splits, 1),
+                                     scratch, static_cast<cudaStream_t>(stream), q_strides,
+                                     k_strides, v_strides, o_strides);
+  if (scratch) pool_free(scratch);  // recycled in stream order, like the dense dispatcher's
+  return rc;
 }
 
 // Paged decode: Q, O [B, Hq, D] bf16; pages [num_pages, page_size, Hkv, D] bf16; page_table

@@ -493,8 +493,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
   }
 }
 
-int launch(const void* Q, const void* K, const void* V, void* O, int B, int H, int Hkv, int Sq,
-           int Sk, int Dh, float scale, int causal, cudaStream_t st) {
+// Strides are in elements, one triple (batch, head, position) per tensor; the head dimension is
+// contiguous. Any layout TMA can describe works: [B,H,S,D], [B,S,H,D], or column slices of a fused
+// QKV projection output. Every stride must be a multiple of 8 elements (16 bytes).
+int launch_strided(const void* Q, const void* K, const void* V, void* O, int B, int H, int Hkv,
+                   int Sq, int Sk, int Dh, const long long* qs, const long long* ks,
+                   const long long* vs, const long long* os, float scale, int causal,
+                   cudaStream_t st) {
   if (!Q || !K || !V || !O || B <= 0 || H <= 0 || Hkv <= 0 || Sq <= 0 || Sk <= 0) {
     set_last_error("attn_prefill: null pointer or non-positive size");
     return kBadArg;
@@ -516,26 +521,24 @@ int launch(const void* Q, const void* K, const void* V, void* O, int B, int H, i
       set_last_error("attn_prefill: pointers must be 16-byte aligned");
       return kBadArg;
     }
+  for (const long long* t : {qs, ks, vs, os})
+    for (int i = 0; i < 3; ++i)
+      if (t[i] <= 0 || (t[i] & 7)) {
+        set_last_error("attn_prefill: strides must be positive multiples of 8 elements (got %lld)",
+                       t[i]);
+        return kBadArg;
+      }
   CUtensorMap tQ, tK, tV, tO;
   uint32_t box[4] = {64, 128, 1, 1};
-  {
-    uint64_t dims[4] = {(uint64_t)D, (uint64_t)Sq, (uint64_t)H, (uint64_t)B};
-    uint64_t str[3] = {(uint64_t)D * 2, (uint64_t)Sq * D * 2, (uint64_t)H * Sq * D * 2};
-    if (!encode_tmap(&tQ, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, Q, dims, str, box,
-                     CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !encode_tmap(&tO, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, O, dims, str, box,
-                     CU_TENSOR_MAP_SWIZZLE_128B))
-      return kBadArg;
-  }
-  {
-    uint64_t dims[4] = {(uint64_t)D, (uint64_t)Sk, (uint64_t)Hkv, (uint64_t)B};
-    uint64_t str[3] = {(uint64_t)D * 2, (uint64_t)Sk * D * 2, (uint64_t)Hkv * Sk * D * 2};
-    if (!encode_tmap(&tK, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, K, dims, str, box,
-                     CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !encode_tmap(&tV, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, V, dims, str, box,
-                     CU_TENSOR_MAP_SWIZZLE_128B))
-      return kBadArg;
-  }
+  auto encode = [&](CUtensorMap* m, const void* base, int S, int heads, const long long* t) {
+    uint64_t dims[4] = {(uint64_t)D, (uint64_t)S, (uint64_t)heads, (uint64_t)B};
+    uint64_t str[3] = {(uint64_t)t[2] * 2, (uint64_t)t[1] * 2, (uint64_t)t[0] * 2};
+    return encode_tmap(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, base, dims, str, box,
+                       CU_TENSOR_MAP_SWIZZLE_128B);
+  };
+  if (!encode(&tQ, Q, Sq, H, qs) || !encode(&tO, O, Sq, H, os) || !encode(&tK, K, Sk, Hkv, ks) ||
+      !encode(&tV, V, Sk, Hkv, vs))
+    return kBadArg;
   Params p{};
   p.B = B;
   p.H = H;
@@ -555,6 +558,13 @@ int launch(const void* Q, const void* K, const void* V, void* O, int B, int H, i
   return kOk;
 }
 
+int launch(const void* Q, const void* K, const void* V, void* O, int B, int H, int Hkv, int Sq,
+           int Sk, int Dh, float scale, int causal, cudaStream_t st) {
+  const long long qs[3] = {(long long)H * Sq * D, (long long)Sq * D, D};
+  const long long ks[3] = {(long long)Hkv * Sk * D, (long long)Sk * D, D};
+  return launch_strided(Q, K, V, O, B, H, Hkv, Sq, Sk, Dh, qs, ks, ks, qs, scale, causal, st);
+}
+
 }  // namespace attn_prefill
 }  // namespace tsb
 
@@ -565,6 +575,20 @@ extern "C" int tessera_sm100_prefill_trace_read(long long* out, int n) {
   return cudaMemcpyFromSymbol(out, tsb::attn_prefill::g_trace, sizeof(long long) * n) == cudaSuccess ? 0 : 3;
 }
 #endif
+
+extern "C" int tessera_sm100_flash_attn_fwd_strided_device(
+    const void* Q, const void* K, const void* V, void* O, int B, int Hq, int Hkv, int Sq, int Sk,
+    int D, const long long* q_strides, const long long* k_strides, const long long* v_strides,
+    const long long* o_strides, float scale, int causal, void* stream) {
+  if (!q_strides || !k_strides || !v_strides || !o_strides) {
+    tsb::set_last_error("flash_attn_strided: null stride array");
+    return tsb::kBadArg;
+  }
+  if (int rc = tsb::ensure_device()) return rc;
+  return tsb::attn_prefill::launch_strided(Q, K, V, O, B, Hq, Hkv, Sq, Sk, D, q_strides, k_strides,
+                                           v_strides, o_strides, scale, causal,
+                                           static_cast<cudaStream_t>(stream));
+}
 
 extern "C" {
 

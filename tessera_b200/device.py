@@ -193,6 +193,63 @@ class DeviceArray:
             pass
 
 
+class StridedView:
+    """A window into a :class:`DeviceArray` whose last dimension is contiguous: pointer, shape and
+    element strides. What a column slice of a fused projection output is (``qkv[..., a:b]``);
+    the strided attention entry point reads such windows in place."""
+
+    def __init__(self, base: DeviceArray, ptr: int, shape, strides):
+        self.base, self.ptr = base, int(ptr)
+        self.shape = tuple(int(x) for x in shape)
+        self.strides = tuple(int(x) for x in strides)
+        self.dtype = base.dtype
+        if self.strides[-1] != 1:
+            raise ValueError("StridedView: the last dimension must be contiguous")
+
+    @property
+    def ndim(self) -> int:
+        return len(self.shape)
+
+    def contiguous(self, stream=None) -> DeviceArray:
+        """Copy into a dense array (rows of the last dimension are moved with 2-D copies)."""
+        rows = int(np.prod(self.shape[:-1], dtype=np.int64))
+        out = DeviceArray(self.shape, self.dtype)
+        if len(self.shape) >= 2:
+            lead = self.strides[-2]
+            for k in range(len(self.shape) - 2):  # leading dims must nest for one 2-D copy
+                if self.strides[k] != self.strides[k + 1] * self.shape[k + 1]:
+                    raise ValueError("StridedView.contiguous: leading dimensions are not nested")
+        else:
+            lead = self.shape[-1]
+        item = self.dtype.itemsize
+        _lib.call("tessera_sm100_device_copy_2d", out.ptr, self.shape[-1] * item, self.ptr, lead * item,
+                  self.shape[-1] * item, rows, _stream_handle(stream))
+        return out
+
+    def download(self) -> np.ndarray:
+        return self.contiguous().download()
+
+
+def slice_last(x, start: int, stop: int) -> StridedView:
+    """``x[..., start:stop]`` of a dense device array as a view (no copy). ``start`` must keep the
+    window 16-byte aligned."""
+    if isinstance(x, StridedView):
+        base, ptr, shape, strides = x.base, x.ptr, x.shape, x.strides
+    else:
+        base, ptr, shape = x, x.ptr, x.shape
+        strides, acc = [], 1
+        for n in reversed(shape):
+            strides.append(acc)
+            acc *= n
+        strides = tuple(reversed(strides))
+    if not (0 <= start < stop <= shape[-1]):
+        raise ValueError(f"slice_last: [{start}:{stop}] outside the last dimension {shape[-1]}")
+    item = np.dtype(base.dtype).itemsize
+    if (start * item) % 16:
+        raise ValueError("slice_last: the window must start on a 16-byte boundary")
+    return StridedView(base, ptr + start * item, tuple(shape[:-1]) + (stop - start,), strides)
+
+
 class PinnedArray:
     """Page-locked host memory exposed as a numpy array (``.array``)."""
 

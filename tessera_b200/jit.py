@@ -89,7 +89,8 @@ class JitFn:
 
     @staticmethod
     def _unstage(value: Any) -> Any:
-        if isinstance(value, DeviceArray):
+        from .device import StridedView
+        if isinstance(value, (DeviceArray, StridedView)):
             from . import device
             host = value.download()
             device.check_device_error("jit")

@@ -26,7 +26,7 @@ from typing import Any, Optional
 import numpy as np
 
 from . import _lib, device
-from .device import DeviceArray, bfloat16
+from .device import DeviceArray, StridedView, bfloat16
 
 GROUPED_KINDS = ("contiguous", "dense", "masked", "k_grouped")
 SUPPORTED_GROUPED_KINDS = ("contiguous", "dense")
@@ -35,7 +35,7 @@ SUPPORTED_GROUPED_KINDS = ("contiguous", "dense")
 def _unwrap(x: Any) -> Any:
     """DeviceArray stays; everything else becomes a numpy array (reference `_as_numpy`,
     python/tessera/runtime.py:44377-44384)."""
-    if isinstance(x, DeviceArray):
+    if isinstance(x, (DeviceArray, StridedView)):
         return x
     if hasattr(x, "_data"):
         return np.asarray(x._data)

@@ -92,6 +92,19 @@ def attention():
         out[f"O{i}"] = np.asarray(O, np.float32)
         out[f"meta{i}"] = np.array([B, Hq, Hkv, Sq, Sk, D, int(causal)])
     out["n"] = np.array(len(cases))
+    # [B, S, H*D] operands: nn.functional.multi_head_attention and linear (nn/functional.py:33-44, 493-548)
+    for i, (B, H, Sq, Sk, causal) in enumerate([(2, 2, 96, 96, True), (1, 3, 40, 130, False), (2, 2, 1, 77, False)]):
+        Q = rt(rng.standard_normal((B, Sq, H * 128)), bf16)
+        K = rt(rng.standard_normal((B, Sk, H * 128)), bf16)
+        V = rt(rng.standard_normal((B, Sk, H * 128)), bf16)
+        out[f"mhaQ{i}"], out[f"mhaK{i}"], out[f"mhaV{i}"] = Q, K, V
+        out[f"mhaO{i}"] = np.asarray(F.multi_head_attention(Q, K, V, H, causal=causal), np.float32)
+        out[f"mhameta{i}"] = np.array([B, H, Sq, Sk, int(causal)])
+    out["mha_n"] = np.array(3)
+    x = rt(rng.standard_normal((2, 24, 64)) / 8, bf16)
+    W = rt(rng.standard_normal((64, 48)), bf16)
+    b = rng.standard_normal(48).astype(np.float32)
+    out.update(lin_x=x, lin_W=W, lin_b=b, lin_y=np.asarray(F.linear(x, W, b), np.float32))
     # split-KV merge states
     oa, ob = rng.standard_normal((2, 5, 16)).astype(np.float32)
     ma, mb = rng.standard_normal((2, 5)).astype(np.float32)

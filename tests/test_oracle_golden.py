@@ -129,3 +129,12 @@ def test_paged_attention_matches_reference(golden_dir):
     np.testing.assert_array_equal(gv, g["sgv"])
     o = orc.paged_attention(g["sQ"], g["sk_pages"], g["sv_pages"], g["stable"], n)
     np.testing.assert_allclose(o, g["sO"], rtol=1e-6, atol=1e-6)
+
+
+def test_multi_head_attention_and_linear_match_reference(golden_dir):
+    g = _load(golden_dir, "attention.npz")
+    for i in range(int(g["mha_n"])):
+        B, H, Sq, Sk, causal = (int(x) for x in g[f"mhameta{i}"])
+        o = orc.multi_head_attention(g[f"mhaQ{i}"], g[f"mhaK{i}"], g[f"mhaV{i}"], H, causal=bool(causal))
+        np.testing.assert_allclose(o, g[f"mhaO{i}"], rtol=2e-6, atol=2e-6)
+    np.testing.assert_allclose(orc.linear(g["lin_x"], g["lin_W"], g["lin_b"]), g["lin_y"], rtol=1e-6, atol=1e-6)

@@ -108,6 +108,15 @@ _SIGNATURES = {
     "tessera_sm100_flash_attn_fwd_strided_device": (c_int, [_VP, _VP, _VP, _VP, c_int, c_int, c_int, c_int,
                                                             c_int, c_int, _VP, _VP, _VP, _VP, c_float, c_int,
                                                             _VP]),
+    "tessera_qos_limit_set": (None, [c_int]),
+    "tessera_qos_acquire": (None, []),
+    "tessera_qos_release": (None, []),
+    "tessera_submit_chunk_async": (None, [_VP, ctypes.c_uint64, c_int, c_int]),
+    "tessera_trace_write": (None, [c_char_p]),
+    "tessera_trace_write_status": (c_int, [c_char_p]),
+    "tessera_shutdown_runtime": (None, []),
+    "tessera_sm100_comm_bind_stream": (c_int, [c_int, c_int, _VP]),
+    "tessera_sm100_qos_state": (c_int, [POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_longlong)]),
     "tessera_sm100_paged_attn_decode_device": (c_int, [_VP, _VP, _VP, _VP, _VP, _VP, c_int, c_int, c_int,
                                                        c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                                                        _VP, _VP]),

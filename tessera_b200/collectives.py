@@ -258,6 +258,52 @@ class CollectiveAdapter:
         arrs = [np.moveaxis(a, axis, 0) for a in _per_rank(values, self.world_size)]
         return [np.ascontiguousarray(np.moveaxis(o, 0, axis)) for o in self._run("all_gather", arrs)]
 
+    def collective_permute(self, values, *, pairs):
+        """Rank ``source`` sends its whole value to rank ``target`` for every ``(source, target)``
+        pair; ranks that are nobody's target get zeros (python/tessera/collectives.py:746-767).
+        On NCCL this is one ragged all-to-all in which each rank sends to at most one peer."""
+        pairs = tuple((int(a), int(b)) for a, b in pairs)
+        sources = tuple(a for a, _ in pairs)
+        targets = tuple(b for _, b in pairs)
+        if not pairs:
+            raise ValueError("collective_permute requires a non-empty peer map")
+        if len(set(sources)) != len(sources) or len(set(targets)) != len(targets):
+            raise ValueError("collective_permute sources and targets must be unique")
+        if any(p < 0 or p >= self.world_size for p in (*sources, *targets)):
+            raise ValueError("collective_permute peer is outside the communicator")
+        arrs = _per_rank(values, self.world_size)
+        if any(a.shape != arrs[0].shape for a in arrs):
+            raise ValueError("collective_permute rank inputs must have identical shapes")
+        W = self.world_size
+        if W == 1:
+            return [np.array(arrs[0], copy=True)]
+        comms = self._ensure()
+        devs = self._topology.device_ordinals
+        send_to = dict(pairs)
+        recv_from = {t: s for s, t in pairs}
+        nbytes = arrs[0].nbytes
+        sends, recvs = [], []
+        for r in range(W):
+            device.set_device(devs[r])
+            sends.append(DeviceArray.from_host(arrs[r]))
+            recvs.append(DeviceArray.zeros(arrs[0].shape, arrs[0].dtype))
+        device.synchronize()
+        _lib.call("tessera_sm100_group_start")
+        try:
+            for r in range(W):
+                device.set_device(devs[r])
+                sb = [nbytes if send_to.get(r) == p else 0 for p in range(W)]
+                rb = [nbytes if recv_from.get(r) == p else 0 for p in range(W)]
+                comms[r].all_to_all_v(sends[r].ptr, sb, recvs[r].ptr, rb)
+        finally:
+            _lib.call("tessera_sm100_group_end")
+        outs = []
+        for r in range(W):
+            device.set_device(devs[r])
+            outs.append(recvs[r].download())
+        device.set_device(devs[0])
+        return outs
+
     def all_to_all(self, values, *, scatter_axis: int = 0, gather_axis: int = 0):
         if scatter_axis != 0 or gather_axis != 0:
             raise ValueError("NCCL all_to_all v1 requires scatter_axis=gather_axis=0")
@@ -272,3 +318,39 @@ class CollectiveAdapter:
 
 def adapter(*, backend: str = "single_process", world_size: int = 1, **kw: Any) -> CollectiveAdapter:
     return CollectiveAdapter(backend=backend, world_size=world_size, **kw)
+
+
+# ------------------------------------------------------------------ chunk-submission hooks
+def qos_limit_set(tokens: int) -> None:
+    """At most ``tokens`` chunks in flight (``tessera_qos_limit_set``)."""
+    _lib.load().tessera_qos_limit_set(int(tokens))
+
+
+def submit_chunk_async(ptr: int, nbytes: int, device_index: int = 0, stream_id: int = 0) -> None:
+    """Submit one transfer chunk through the token limiter and the trace (``tessera_submit_chunk_async``)."""
+    _lib.load().tessera_submit_chunk_async(ctypes.c_void_p(int(ptr)), ctypes.c_uint64(int(nbytes)),
+                                           int(device_index), int(stream_id))
+
+
+def bind_chunk_stream(device_index: int, stream_id: int, stream) -> None:
+    """Chunks submitted for ``(device_index, stream_id)`` complete when ``stream`` reaches them."""
+    _lib.call("tessera_sm100_comm_bind_stream", int(device_index), int(stream_id),
+              device._stream_handle(stream) if stream is not None else None)
+
+
+def qos_state() -> dict:
+    lim, inf, peak, ev = ctypes.c_int(), ctypes.c_int(), ctypes.c_int(), ctypes.c_longlong()
+    rc = _lib.load().tessera_sm100_qos_state(ctypes.byref(lim), ctypes.byref(inf), ctypes.byref(peak),
+                                             ctypes.byref(ev))
+    return {"exists": rc == 0, "limit": lim.value, "inflight": inf.value, "peak_inflight": peak.value,
+            "trace_events": ev.value}
+
+
+def trace_write(path: str) -> None:
+    rc = _lib.load().tessera_trace_write_status(str(path).encode())
+    if rc == 3:
+        raise OSError(f"could not write the collective trace to {path}")
+
+
+def shutdown_runtime() -> None:
+    _lib.load().tessera_shutdown_runtime()

@@ -123,3 +123,47 @@ def test_two_gpu_collectives_tp_gemm_and_ep_moe():
         assert exc is None, f"rank {rank}:\n{exc}"
         assert errs["all_gather"] == 0 and errs["all_reduce"] == 0 and errs["all_to_all_v"] == 0, errs
         assert errs["tp_gemm"] < 1e-2 and errs["ep_moe"] < 1e-2 and errs["ep_moe_device"] < 1e-2, errs
+
+
+def _adapter_worker(q):
+    try:
+        from tessera_b200 import collectives
+        ad = collectives.adapter(backend="nccl", world_size=2)
+        assert ad.status().status == "hardware_runtime"
+        vals = [np.arange(12, dtype=np.float32).reshape(4, 3) + 100 * r for r in range(2)]
+        out = {}
+        out["all_reduce"] = ad.all_reduce(vals)
+        out["all_gather1"] = ad.all_gather(vals, axis=1)
+        out["all_to_all"] = ad.all_to_all(vals)
+        out["permute"] = ad.collective_permute(vals, pairs=((0, 1),))
+        out["swap"] = ad.collective_permute(vals, pairs=((0, 1), (1, 0)))
+        ad.close()
+        q.put((out, None))
+    except Exception:
+        import traceback
+        q.put((None, traceback.format_exc()))
+
+
+def test_single_process_adapter_on_two_gpus():
+    """CollectiveAdapter(backend="nccl", world_size=2) in one process (the reference's executor
+    shape, python/tessera/collectives.py:117-817), including collective_permute."""
+    from tessera_b200 import device
+    if device.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    p = ctx.Process(target=_adapter_worker, args=(q,))
+    p.start()
+    out, exc = q.get(timeout=300)
+    p.join(timeout=60)
+    assert exc is None, exc
+    vals = [np.arange(12, dtype=np.float32).reshape(4, 3) + 100 * r for r in range(2)]
+    for r in range(2):
+        np.testing.assert_array_equal(out["all_reduce"][r], vals[0] + vals[1])
+        np.testing.assert_array_equal(out["all_gather1"][r], np.concatenate(vals, axis=1))
+        np.testing.assert_array_equal(out["all_to_all"][r],
+                                      np.concatenate([vals[0][2 * r:2 * r + 2], vals[1][2 * r:2 * r + 2]]))
+    np.testing.assert_array_equal(out["permute"][1], vals[0])
+    np.testing.assert_array_equal(out["permute"][0], np.zeros_like(vals[0]))
+    np.testing.assert_array_equal(out["swap"][0], vals[1])
+    np.testing.assert_array_equal(out["swap"][1], vals[0])

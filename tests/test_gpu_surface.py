@@ -80,3 +80,32 @@ def test_index_launch_tensor_parallel_column_split():
 
     tessera.index_launch(axis="tp")(tp_gemm)(A, W.parts("tp"), Y.parts("tp"))
     assert rel_err(Y.numpy(), orc.gemm(A, Wd)) < 1e-4
+
+
+def test_chunk_submission_completes_in_stream_order(tmp_path):
+    """A chunk submitted for a (device, stream id) with a CUDA stream bound completes when the
+    stream reaches it: the token stays out while earlier work is queued and returns after it."""
+    import json
+    from tessera_b200 import collectives as coll, device
+    coll.shutdown_runtime()
+    coll.qos_limit_set(2)
+    st = device.Stream()
+    coll.bind_chunk_stream(0, 7, st)
+    for _ in range(100):
+        device.flush_l2(st)                       # ~10 ms of queued work ahead of the chunk
+    coll.submit_chunk_async(0, 1 << 20, 0, 7)
+    early = coll.qos_state()
+    st.synchronize()
+    late = coll.qos_state()
+    assert early["peak_inflight"] == 1 and late["inflight"] == 0 and late["trace_events"] == 3
+    coll.submit_chunk_async(0, 64, 0, 3)          # nothing bound to stream id 3: completes at once
+    assert coll.qos_state()["inflight"] == 0
+    out = tmp_path / "t.json"
+    coll.trace_write(str(out))
+    ev = json.loads(out.read_text())["traceEvents"]
+    b = [e for e in ev if e["ph"] == "B" and e["tid"] == 7][0]
+    e = [e for e in ev if e["ph"] == "E" and e["tid"] == 7][0]
+    assert e["ts"] - b["ts"] > 1000               # microseconds: the end waited for the queued work
+    coll.bind_chunk_stream(0, 7, None)
+    coll.shutdown_runtime()
+    st.close()

@@ -236,6 +236,25 @@ int tessera_sm100_attn_decode_static_device(const void* Q, const void* K, const 
                                             int B, int Hq, int Hkv, int Sk, int D, float scale,
                                             int splits, int check_previous, void* stream);
 
+/* ---- max-shifted attention states -----------------------------------------------------------
+ * ops.softmax_merge / softmax_finalize (python/tessera/_block_attnres_ops.py:104-146): a state is
+ * (o [rows, Dv] = sum e^{s-m} v, m [rows] = max s, l [rows] = sum e^{s-m}), fp32; merging is
+ * associative, so attention over a key set that is split (KV splits inside one GPU, KV shards on
+ * several GPUs) is merge-then-finalize of the per-part states.
+ * tessera_sm100_attn_decode_state_device is the decode kernel stopping before the division: Q
+ * [B,Hq,128], K/V [B,Hkv,Sk,128] bf16 -> o_state [B,Hq,128], m_state, l_state [B,Hq] (m in natural
+ * log units of the scaled scores). scratch: tessera_sm100_attn_decode_scratch_bytes(B, Hq,
+ * max(splits,1)) bytes, always required here. */
+int tessera_sm100_attn_decode_state_device(const void* Q, const void* K, const void* V,
+                                           float* o_state, float* m_state, float* l_state, int B,
+                                           int Hq, int Hkv, int Sk, int D, float scale, int splits,
+                                           void* scratch, void* stream);
+int tessera_sm100_softmax_merge_device(const float* oa, const float* ma, const float* la,
+                                       const float* ob, const float* mb, const float* lb, float* o,
+                                       float* m, float* l, long long rows, int Dv, void* stream);
+int tessera_sm100_softmax_finalize_device(const float* o, const float* l, void* out, long long rows,
+                                          int Dv, int out_dtype, void* stream);
+
 /* Attention forward over strided operands: the same kernels with the layouts described by element
  * strides, one (batch, head, position) triple per tensor; the head dimension (128) is contiguous
  * and every stride is a multiple of 8 elements. Serves nn.functional.multi_head_attention

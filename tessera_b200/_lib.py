@@ -117,6 +117,10 @@ _SIGNATURES = {
     "tessera_shutdown_runtime": (None, []),
     "tessera_sm100_comm_bind_stream": (c_int, [c_int, c_int, _VP]),
     "tessera_sm100_qos_state": (c_int, [POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_longlong)]),
+    "tessera_sm100_attn_decode_state_device": (c_int, [_VP, _VP, _VP, _VP, _VP, _VP, c_int, c_int, c_int, c_int,
+                                                       c_int, c_float, c_int, _VP, _VP]),
+    "tessera_sm100_softmax_merge_device": (c_int, [_VP] * 9 + [c_longlong, c_int, _VP]),
+    "tessera_sm100_softmax_finalize_device": (c_int, [_VP, _VP, _VP, c_longlong, c_int, c_int, _VP]),
     "tessera_sm100_paged_attn_decode_device": (c_int, [_VP, _VP, _VP, _VP, _VP, _VP, c_int, c_int, c_int,
                                                        c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                                                        _VP, _VP]),

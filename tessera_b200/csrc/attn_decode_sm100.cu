@@ -57,6 +57,7 @@ struct Params {
   // Paged mode only: K/V live in pages [P, page_size, Hkv, D]; sequence b reads logical page lp
   // from physical page page_table[b * max_pages + lp] and holds seq_lens[b] positions.
   long long q_sb, q_sh, o_sb, o_sh;  // element strides of Q and O over (batch, head)
+  int force_partial;                 // write split partials even when there is one split
   const int* page_table;
   const int* seq_lens;
   int max_pages, num_pages, page_size, page_shift;
@@ -338,7 +339,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ C
       l += f * s_l[w * 8 + h];
     }
     const long long row = static_cast<long long>(b) * p.Hq + head0 + h;
-    if (p.splits == 1) {
+    if (p.splits == 1 && !p.force_partial) {
       p.O[static_cast<long long>(b) * p.o_sb + (head0 + h) * p.o_sh + d] = __float2bfloat16_rn(acc / l);
     } else {
       p.part_o[(row * p.splits + split) * D + d] = acc;
@@ -368,6 +369,30 @@ __global__ void merge_kernel(const float* __restrict__ part_o, const float* __re
   O[(row / Hq) * o_sb + (row % Hq) * o_sh + d] = __float2bfloat16_rn(acc / l);
 }
 
+// One CTA per (b, hq): merges the split partials into one max-shifted state (o, m, l) with m in
+// natural-log units, the state of python/tessera/_block_attnres_ops.py:104-131 — what a caller
+// needs to merge attention over KV that is sharded further (other GPUs, other cache tiers).
+__global__ void merge_state_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                   float* __restrict__ o_state, float* __restrict__ m_state,
+                                   float* __restrict__ l_state, int splits) {
+  const long long row = blockIdx.x;
+  const int d = threadIdx.x;
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(row * splits + s) * 2]);
+  const float mu = (m == -INFINITY) ? 0.f : m;
+  float acc = 0.f, l = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float f = exp2f(part_ml[(row * splits + s) * 2] - mu);
+    acc += f * part_o[(row * splits + s) * D + d];
+    l += f * part_ml[(row * splits + s) * 2 + 1];
+  }
+  o_state[row * D + d] = acc;
+  if (d == 0) {
+    m_state[row] = m * 0.6931471805599453f;  // log2 units -> natural log
+    l_state[row] = l;
+  }
+}
+
 int choose_splits(int B, int Hkv, int groups_per_kv, int tiles_total) {
   // Aim for about four waves of two CTAs per SM, at least 4 tiles per CTA.
   const long long base = (long long)B * Hkv * groups_per_kv;
@@ -390,8 +415,11 @@ size_t scratch_bytes(int B, int Hq, int splits) {
 int launch(const void* Q, const void* K, const void* V, void* O, int B, int Hq, int Hkv, int Sk,
            int Dh, float scale, int splits, void* scratch, cudaStream_t st,
            const long long* qs = nullptr, const long long* ks = nullptr,
-           const long long* vs = nullptr, const long long* os = nullptr) {
-  if (!Q || !K || !V || !O || B <= 0 || Hq <= 0 || Hkv <= 0 || Sk <= 0) {
+           const long long* vs = nullptr, const long long* os = nullptr, float* o_state = nullptr,
+           float* m_state = nullptr, float* l_state = nullptr) {
+  const bool want_state = o_state != nullptr;
+  if (!Q || !K || !V || (!O && !want_state) || B <= 0 || Hq <= 0 || Hkv <= 0 || Sk <= 0 ||
+      (want_state && (!m_state || !l_state))) {
     set_last_error("attn_decode: null pointer or non-positive size");
     return kBadArg;
   }
@@ -428,7 +456,8 @@ int launch(const void* Q, const void* K, const void* V, void* O, int B, int Hq, 
   p.scale_log2 = scale * 1.4426950408889634f;
   p.err = device_err_word();
   if (!p.err) return kDeviceFailed;
-  if (splits > 1) {
+  p.force_partial = want_state ? 1 : 0;
+  if (splits > 1 || want_state) {
     if (!scratch) {
       set_last_error("attn_decode: %d splits need a scratch buffer", splits);
       return kBadArg;
@@ -472,12 +501,46 @@ int launch(const void* Q, const void* K, const void* V, void* O, int B, int Hq, 
   decode_kernel<false><<<grid, THREADS, SMEM_ALLOC, st>>>(tK, tV, p);
   TSB_CUDA_OK(cudaGetLastError());
   note_launch();
-  if (splits > 1) {
+  if (want_state) {
+    merge_state_kernel<<<B * Hq, D, 0, st>>>(p.part_o, p.part_ml, o_state, m_state, l_state, splits);
+    TSB_CUDA_OK(cudaGetLastError());
+    note_launch();
+  } else if (splits > 1) {
     merge_kernel<<<B * Hq, D, 0, st>>>(p.part_o, p.part_ml, p.O, splits, Hq, p.o_sb, p.o_sh);
     TSB_CUDA_OK(cudaGetLastError());
     note_launch();
   }
   return kOk;
+}
+
+// Elementwise merge of two states and the final division (python/tessera/_block_attnres_ops.py:
+// 104-146): rows x Dv outputs, rows maxima and normalisers, all fp32.
+__global__ void softmax_merge_kernel(const float* __restrict__ oa, const float* __restrict__ ma,
+                                     const float* __restrict__ la, const float* __restrict__ ob,
+                                     const float* __restrict__ mb, const float* __restrict__ lb,
+                                     float* __restrict__ o, float* __restrict__ m,
+                                     float* __restrict__ l, long long rows, int Dv) {
+  const long long row = blockIdx.x;
+  if (row >= rows) return;
+  const float xa = ma[row], xb = mb[row];
+  const float mx = fmaxf(xa, xb);
+  const float sa = expf(xa - mx), sb = expf(xb - mx);
+  for (int d = threadIdx.x; d < Dv; d += blockDim.x)
+    o[row * Dv + d] = sa * oa[row * Dv + d] + sb * ob[row * Dv + d];
+  if (threadIdx.x == 0) {
+    m[row] = mx;
+    l[row] = sa * la[row] + sb * lb[row];
+  }
+}
+
+template <typename T>
+__global__ void softmax_finalize_kernel(const float* __restrict__ o, const float* __restrict__ l,
+                                        T* __restrict__ out, long long rows, int Dv) {
+  const long long row = blockIdx.x;
+  if (row >= rows) return;
+  const float inv = 1.0f / l[row];
+  for (int d = threadIdx.x; d < Dv; d += blockDim.x)
+    out[row * Dv + d] = static_cast<T>(o[row * Dv + d] * inv);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -798,6 +861,59 @@ int tessera_sm100_attn_decode_device(const void* Q, const void* K, const void* V
                                      void* scratch, void* stream) {
   return attn_decode::launch(Q, K, V, O, B, Hq, Hkv, Sk, D, scale, splits, scratch,
                              static_cast<cudaStream_t>(stream));
+}
+
+// Decode attention that stops before the division: the max-shifted state (o [B,Hq,D], m [B,Hq] in
+// natural-log units, l [B,Hq], fp32) over this call's K/V. States over disjoint key sets merge
+// with tessera_sm100_softmax_merge_device in any order. `scratch` is always needed
+// (tessera_sm100_attn_decode_scratch_bytes with max(splits, 1)).
+int tessera_sm100_attn_decode_state_device(const void* Q, const void* K, const void* V,
+                                           float* o_state, float* m_state, float* l_state, int B,
+                                           int Hq, int Hkv, int Sk, int D, float scale, int splits,
+                                           void* scratch, void* stream) {
+  return attn_decode::launch(Q, K, V, nullptr, B, Hq, Hkv, Sk, D, scale, splits, scratch,
+                             static_cast<cudaStream_t>(stream), nullptr, nullptr, nullptr, nullptr,
+                             o_state, m_state, l_state);
+}
+
+int tessera_sm100_softmax_merge_device(const float* oa, const float* ma, const float* la,
+                                       const float* ob, const float* mb, const float* lb, float* o,
+                                       float* m, float* l, long long rows, int Dv, void* stream) {
+  if (!oa || !ma || !la || !ob || !mb || !lb || !o || !m || !l || rows < 0 || Dv <= 0) {
+    set_last_error("softmax_merge: null pointer or bad size");
+    return kBadArg;
+  }
+  if (rows == 0) return kOk;
+  if (int rc = ensure_device()) return rc;
+  attn_decode::softmax_merge_kernel<<<(unsigned)rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      oa, ma, la, ob, mb, lb, o, m, l, rows, Dv);
+  TSB_CUDA_OK(cudaGetLastError());
+  note_launch();
+  return kOk;
+}
+
+int tessera_sm100_softmax_finalize_device(const float* o, const float* l, void* out, long long rows,
+                                          int Dv, int out_dtype, void* stream) {
+  if (!o || !l || !out || rows < 0 || Dv <= 0) {
+    set_last_error("softmax_finalize: null pointer or bad size");
+    return kBadArg;
+  }
+  if (rows == 0) return kOk;
+  if (int rc = ensure_device()) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (out_dtype == TESSERA_SM100_F32)
+    attn_decode::softmax_finalize_kernel<float><<<(unsigned)rows, 128, 0, st>>>(
+        o, l, static_cast<float*>(out), rows, Dv);
+  else if (out_dtype == TESSERA_SM100_BF16)
+    attn_decode::softmax_finalize_kernel<__nv_bfloat16><<<(unsigned)rows, 128, 0, st>>>(
+        o, l, static_cast<__nv_bfloat16*>(out), rows, Dv);
+  else {
+    set_last_error("softmax_finalize: output dtype must be f32 or bf16");
+    return kBadArg;
+  }
+  TSB_CUDA_OK(cudaGetLastError());
+  note_launch();
+  return kOk;
 }
 
 // Attention forward over strided operands (contiguous head dimension; element strides as triples

@@ -240,6 +240,84 @@ def paged_attention(Q, kv_state, *, scale=None, causal: bool = False, token_indi
     return _pa(_unwrap(Q), kv_state, scale=scale, causal=causal, token_indices=token_indices)
 
 
+def _f32_device(x) -> DeviceArray:
+    if isinstance(x, DeviceArray):
+        if x.dtype != np.float32:
+            raise TypeError("attention states are float32")
+        return x
+    return DeviceArray.from_host(np.ascontiguousarray(x, np.float32))
+
+
+def softmax_merge(output_a, maximum_a, normalizer_a, output_b, maximum_b, normalizer_b, *, stream=None):
+    """Associative merge of two max-shifted attention states ``(o, m, l)``
+    (python/tessera/_block_attnres_ops.py:104-131). Host states are checked like the reference
+    (matching shapes, strictly positive normalisers); device states are taken as they are."""
+    ins = [_unwrap(t) for t in (output_a, maximum_a, normalizer_a, output_b, maximum_b, normalizer_b)]
+    on_device = _any_device(*ins)
+    oa, ma, la, ob, mb, lb = ins
+    for name, (o, m, l) in (("state_a", (oa, ma, la)), ("state_b", (ob, mb, lb))):
+        if len(o.shape) < 1 or tuple(o.shape[:-1]) != tuple(m.shape):
+            raise ValueError(f"{name} output prefix {tuple(o.shape[:-1])} must match maximum shape {tuple(m.shape)}")
+        if tuple(l.shape) != tuple(m.shape):
+            raise ValueError(f"{name} normalizer shape {tuple(l.shape)} must match maximum shape {tuple(m.shape)}")
+        if not isinstance(l, DeviceArray) and np.any(np.asarray(l) <= 0.0):
+            raise ValueError(f"{name} normalizer must be strictly positive")
+    if tuple(oa.shape) != tuple(ob.shape) or tuple(ma.shape) != tuple(mb.shape):
+        raise ValueError("softmax_merge states must have identical shapes")
+    d = [_f32_device(t) for t in ins]
+    rows, Dv = int(np.prod(ma.shape, dtype=np.int64)), int(oa.shape[-1])
+    o, m, l = DeviceArray(oa.shape, np.float32), DeviceArray(ma.shape, np.float32), DeviceArray(ma.shape, np.float32)
+    _lib.call("tessera_sm100_softmax_merge_device", *(t.ptr for t in d), o.ptr, m.ptr, l.ptr, rows, Dv,
+              device._stream_handle(stream))
+    if on_device:
+        return o, m, l
+    return o.download(), m.download(), l.download()
+
+
+def softmax_finalize(output, normalizer, *, out_dtype=None, stream=None):
+    """``output / l`` (python/tessera/_block_attnres_ops.py:134-146)."""
+    o, l = _unwrap(output), _unwrap(normalizer)
+    if len(o.shape) < 1 or tuple(o.shape[:-1]) != tuple(l.shape):
+        raise ValueError(f"output prefix {tuple(o.shape[:-1])} must match normalizer shape {tuple(l.shape)}")
+    if not isinstance(l, DeviceArray) and np.any(np.asarray(l) <= 0.0):
+        raise ValueError("normalizer must be strictly positive")
+    on_device = _any_device(o, l)
+    do, dl = _f32_device(o), _f32_device(l)
+    code = _out_code(out_dtype, _lib.F32)
+    out = DeviceArray(o.shape, device.code_dtype(code))
+    _lib.call("tessera_sm100_softmax_finalize_device", do.ptr, dl.ptr, out.ptr,
+              int(np.prod(l.shape, dtype=np.int64)), int(o.shape[-1]), code, device._stream_handle(stream))
+    return out if on_device else out.download()
+
+
+def attn_decode_state(Q, K, V, *, scale=None, stream=None):
+    """Decode attention of ``Q`` ``[B, Hq, 1, 128]`` over ``K``, ``V`` ``[B, Hkv, Sk, 128]`` stopped
+    before the division: the state ``(o [B,Hq,128], m [B,Hq], l [B,Hq])`` of this key set. States of
+    disjoint key sets (KV shards) combine with :func:`softmax_merge` and :func:`softmax_finalize`."""
+    q, k, v = _unwrap(Q), _unwrap(K), _unwrap(V)
+    on_device = _any_device(q, k, v)
+    if len(q.shape) != 4 or q.shape[2] != 1 or len(k.shape) != 4 or tuple(k.shape) != tuple(v.shape):
+        raise ValueError("attn_decode_state: Q must be [B, Hq, 1, D] and K, V equal-shape [B, Hkv, Sk, D]")
+    B, Hq, _, D = q.shape
+    Hkv, Sk = k.shape[1], k.shape[2]
+    if Hq % Hkv:
+        raise ValueError("num_query_heads must be divisible by num_kv_heads")
+    dq, dk, dv = _to_device(q, bfloat16), _to_device(k, bfloat16), _to_device(v, bfloat16)
+    lib = _lib.load()
+    splits = max(1, int(lib.tessera_sm100_attn_decode_splits(B, Hq, Hkv, Sk)))
+    scratch = DeviceArray((int(lib.tessera_sm100_attn_decode_scratch_bytes(B, Hq, splits)),), np.uint8, pooled=True)
+    o, m, l = (DeviceArray((B, Hq, D), np.float32), DeviceArray((B, Hq), np.float32),
+               DeviceArray((B, Hq), np.float32))
+    sc = float(1.0 / np.sqrt(D) if scale is None else scale)
+    _lib.call("tessera_sm100_attn_decode_state_device", dq.ptr, dk.ptr, dv.ptr, o.ptr, m.ptr, l.ptr, B, Hq, Hkv,
+              Sk, D, sc, splits, scratch.ptr, device._stream_handle(stream))
+    if on_device:
+        return o, m, l
+    res = (o.download(), m.download(), l.download())
+    device.check_device_error("attn_decode_state")
+    return res
+
+
 def gqa_attention(Q, K, V, num_query_heads: int, num_kv_heads: int, **kwargs):
     """Grouped-query attention (python/tessera/nn/functional.py:349-356). The KV heads are shared
     inside the kernel instead of being repeated in memory."""

@@ -96,3 +96,46 @@ def test_config4_decode_full_size_properties():
     assert np.abs(o1 - 1.0).max() < TOL
     o8 = attn_device(q, k, v, False, decode_splits=8)
     assert rel_err(o8, o) < TOL
+
+
+def test_softmax_merge_and_finalize_fixture(golden_dir):
+    """ops.softmax_merge / softmax_finalize on the GPU against the reference-made states."""
+    import tessera_b200 as tessera
+    g = np.load(os.path.join(golden_dir, "attention.npz"))
+    o, m, l = tessera.ops.softmax_merge(g["merge_oa"], g["merge_ma"], g["merge_la"], g["merge_ob"], g["merge_mb"],
+                                        g["merge_lb"])
+    ro, rm, rl = orc.softmax_merge(g["merge_oa"], g["merge_ma"], g["merge_la"], g["merge_ob"], g["merge_mb"],
+                                   g["merge_lb"])
+    np.testing.assert_allclose(o, ro, rtol=1e-6, atol=1e-6)
+    np.testing.assert_allclose(m, rm, rtol=0, atol=0)
+    np.testing.assert_allclose(l, rl, rtol=1e-6, atol=1e-6)
+    np.testing.assert_allclose(tessera.ops.softmax_finalize(o, l), orc.softmax_finalize(ro, rl), rtol=1e-6, atol=1e-6)
+    with pytest.raises(ValueError):
+        tessera.ops.softmax_merge(g["merge_oa"], g["merge_ma"], -g["merge_la"], g["merge_ob"], g["merge_mb"],
+                                  g["merge_lb"])
+    with pytest.raises(ValueError):
+        tessera.ops.softmax_finalize(g["merge_oa"], g["merge_la"][:-1])
+
+
+@pytest.mark.parametrize("cuts", [(700,), (64, 1000, 1001)])
+def test_kv_sharded_decode_merges_to_full_attention(cuts):
+    """Attention over a KV sequence cut into shards: per-shard states from the decode kernel,
+    merged in any order, equal the unsharded result (the split-KV contract,
+    python/tessera/_block_attnres_ops.py:104-146)."""
+    import tessera_b200 as tessera
+    rng = np.random.default_rng(sum(cuts))
+    B, Hq, Hkv, Sk = 3, 8, 2, 1500
+    q, k, v = _qkv(rng, B, Hq, Hkv, 1, Sk)
+    edges = [0, *cuts, Sk]
+    states = [tessera.ops.attn_decode_state(q, np.ascontiguousarray(k[:, :, a:b]), np.ascontiguousarray(v[:, :, a:b]))
+              for a, b in zip(edges[:-1], edges[1:])]
+    ref = orc.gqa_attention(q, k, v, Hq, Hkv)[:, :, 0]
+    for order in (states, states[::-1]):
+        o, m, l = order[0]
+        for s in order[1:]:
+            o, m, l = tessera.ops.softmax_merge(o, m, l, *s)
+        assert rel_err(tessera.ops.softmax_finalize(o, l), ref) < TOL
+    # the state itself: m is the row maximum of the scaled scores in natural-log units
+    s0 = np.einsum("bhd,bhkd->bhk", np.asarray(q[:, :, 0], np.float32),
+                   np.repeat(np.asarray(k[:, :, :edges[1]], np.float32), Hq // Hkv, axis=1)) / np.sqrt(128.0)
+    np.testing.assert_allclose(states[0][1], s0.max(-1), rtol=1e-5, atol=1e-5)

@@ -84,6 +84,25 @@ def fused_epilogue(x, bias=None, activation="linear", residual=None) -> np.ndarr
     return x.astype(np.float32)
 
 
+def gated_matmul(A, Wg, Wu) -> np.ndarray:
+    """``silu(A @ Wg) * (A @ Wu)`` (``GatedMatmulRegion.reference``,
+    python/tessera/compiler/fusion_core.py:773-781)."""
+    a = _f32(A)
+    g = a @ _f32(Wg)
+    return ((g / (1.0 + np.exp(-g))) * (a @ _f32(Wu))).astype(np.float32)
+
+
+def attention_region(Q, K, V, scale: float = 1.0, causal: bool = False) -> np.ndarray:
+    """Single-head ``softmax(scale Q K^T) V`` with keys ``n > m`` masked when causal
+    (``AttentionRegion.reference``, python/tessera/compiler/fusion_core.py:672-727)."""
+    s = (_f32(Q) @ _f32(K).T) * np.float32(scale)
+    if causal:
+        m = np.arange(s.shape[0])[:, None]
+        n = np.arange(s.shape[1])[None, :]
+        s = np.where(n > m, -np.inf, s)
+    return (softmax(s) @ _f32(V)).astype(np.float32)
+
+
 # ----------------------------------------------------------------------------- attention
 def softmax(x, axis: int = -1) -> np.ndarray:
     """python/tessera/__init__.py:450-454."""

@@ -72,6 +72,19 @@ def gemm():
     for act in ("linear", "relu", "gelu", "silu"):
         out[f"epi_{act}"] = np.asarray(
             tessera.ops.gemm(A, B, epilogue=dict(bias=bias, activation=act, residual=res)), np.float32)
+    # region oracles behind the arbiter seam (fusion_core.py:672-727, 747-782)
+    A = rt(rng.standard_normal((70, 64)) / 8, bf16)
+    Wg = rt(rng.standard_normal((64, 136)), bf16)
+    Wu = rt(rng.standard_normal((64, 136)), bf16)
+    out.update(gatedA=A, gatedWg=Wg, gatedWu=Wu,
+               gatedO=fusion_core.GatedMatmulRegion(gate_act="silu").reference(A, Wg, Wu))
+    Q = rt(rng.standard_normal((96, 128)), bf16)
+    K = rt(rng.standard_normal((96, 128)), bf16)
+    V = rt(rng.standard_normal((96, 128)), bf16)
+    sc = float(1.0 / np.sqrt(128.0))
+    out.update(regQ=Q, regK=K, regV=V,
+               regO=fusion_core.AttentionRegion(scale=sc, causal=False).reference(Q, K, V),
+               regOc=fusion_core.AttentionRegion(scale=sc, causal=True).reference(Q, K, V))
     np.savez_compressed(os.path.join(HERE, "gemm.npz"), **out)
 
 

@@ -138,3 +138,14 @@ def test_multi_head_attention_and_linear_match_reference(golden_dir):
         o = orc.multi_head_attention(g[f"mhaQ{i}"], g[f"mhaK{i}"], g[f"mhaV{i}"], H, causal=bool(causal))
         np.testing.assert_allclose(o, g[f"mhaO{i}"], rtol=2e-6, atol=2e-6)
     np.testing.assert_allclose(orc.linear(g["lin_x"], g["lin_W"], g["lin_b"]), g["lin_y"], rtol=1e-6, atol=1e-6)
+
+
+def test_region_oracles_match_reference(golden_dir):
+    g = _load(golden_dir, "gemm.npz")
+    np.testing.assert_allclose(orc.gated_matmul(g["gatedA"], g["gatedWg"], g["gatedWu"]), g["gatedO"],
+                               rtol=1e-5, atol=1e-5)
+    sc = float(1.0 / np.sqrt(128.0))
+    np.testing.assert_allclose(orc.attention_region(g["regQ"], g["regK"], g["regV"], sc, False), g["regO"],
+                               rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(orc.attention_region(g["regQ"], g["regK"], g["regV"], sc, True), g["regOc"],
+                               rtol=1e-5, atol=1e-6)

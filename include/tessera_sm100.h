@@ -221,8 +221,8 @@ int tessera_sm100_attn_decode_device(const void* Q, const void* K, const void* V
  * or an allocating library routine. It is meant for serving loops whose device-memory budget is
  * fixed at start-up, and for latency-critical decode steps that cannot afford the device-wide
  * synchronisation an allocation implies.
- *  - Limit: B * Hq * splits * 130 * 4 bytes <= 8 MiB when splits > 1 (the benchmark shape, batch 64
- *    x 32 heads x 3 splits, needs 3.05 MiB). splits <= 0 picks the library's split count, lowered
+ *  - Limit: B * Hq * splits * 130 * 4 bytes <= 8 MiB when splits > 1 (batch 8 x 32 heads x 4
+ *    splits needs 0.5 MiB; the benchmark shape, batch 64, runs as one split and needs none). splits <= 0 picks the library's split count, lowered
  *    until the partials fit; an explicit split count that does not fit returns 1 with an error
  *    text naming the required and the available bytes.
  *  - The first call on each device resolves the array's device address (with that device

@@ -306,6 +306,7 @@ struct HostPipe {
   cudaStream_t up = nullptr, comp = nullptr, down = nullptr;
   cudaEvent_t b_ready = nullptr, up_done[kMaxChunks] = {}, comp_done[kMaxChunks] = {};
   bool ok = false;
+  std::mutex busy;  // one pipelined call at a time per device: the events above are shared
 };
 HostPipe g_pipes[64];
 std::mutex g_pipe_mu;
@@ -412,6 +413,7 @@ int gemm_host(const void* A, const void* B, void* D, int batch, int M, int N, in
   } else {
     // Work queued earlier on the default stream (none by this library's host forms, which all
     // synchronise before returning) is not waited for: the three streams are non-blocking.
+    std::lock_guard<std::mutex> one_at_a_time(pipe->busy);
     if (batch == 1) {
       up2d(pB, Np, B, N, K, pipe->up, "upload of B");
       if (rc == kOk && cudaEventRecord(pipe->b_ready, pipe->up) != cudaSuccess) fail("event record");

@@ -43,7 +43,8 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # captures ran a quarter-size case (heads, batch, experts x slots) and are scaled x4, the traffic
 # of these kernels being proportional to those counts. The MoE figure is the sum of its two
 # grouped GEMM launches.
-NCU_TRAFFIC_BYTES = {"gemm_8192": 1.154e9, "attn_prefill": 1.007e9, "attn_decode": 2.171e9, "moe": 4.78e9}
+NCU_TRAFFIC_BYTES = {"gemm_8192": 1.154e9, "attn_prefill": 1.007e9, "attn_decode": 2.171e9, "attn_decode_paged": 2.166e9,
+                     "moe": 4.78e9}
 
 
 def load_peaks():
@@ -391,7 +392,7 @@ def bench_attn_decode_paged(ranks, args, peaks, peak_kind):
                       f"random physical order, batch sharded /{W}",
             "splits": ns,
             "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": ach / peaks["hbm_gbs"], "traffic": None,
+                         "frac": ach / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES["attn_decode_paged"],
                          "peak_kind": f"copy bandwidth, of {peak_kind}"}}
 
 
@@ -534,6 +535,21 @@ def profile_case(name: str) -> None:
         scr = DeviceArray((max(1, lib.tessera_sm100_attn_decode_scratch_bytes(B, Hq, ns)),), np.uint8)
         fn = lambda: _lib.call("tessera_sm100_attn_decode_device", q.ptr, k.ptr, v.ptr, o.ptr, B, Hq, Hkv, S,
                                D, ctypes.c_float(1 / np.sqrt(D)), ns, scr.ptr, None)
+    elif name == "attn_decode_paged":
+        B, Hq, Hkv, S, D, L = 16, 32, 8, 8192, 128, 64
+        per_seq = S // L
+        P = B * per_seq
+        q = DeviceArray.from_host(rng.standard_normal((B, Hq, D), dtype=np.float32).astype(bfloat16))
+        kp, vp = dev_normal((P, L, Hkv, D)), dev_normal((P, L, Hkv, D))
+        table = DeviceArray.from_host(rng.permutation(P).astype(np.int32).reshape(B, per_seq))
+        lens = DeviceArray.from_host(np.full(B, S, np.int32))
+        o = DeviceArray.zeros((B, Hq, D), bfloat16)
+        lib = _lib.load()
+        ns = lib.tessera_sm100_attn_decode_splits(B, Hq, Hkv, S)
+        scr = DeviceArray((max(1, lib.tessera_sm100_attn_decode_scratch_bytes(B, Hq, ns)),), np.uint8)
+        fn = lambda: _lib.call("tessera_sm100_paged_attn_decode_device", q.ptr, kp.ptr, vp.ptr, table.ptr,
+                               lens.ptr, o.ptr, B, Hq, Hkv, D, L, P, per_seq, S, ctypes.c_float(1 / np.sqrt(D)),
+                               ns, scr.ptr, None)
     elif name == "moe":
         T, H, F, E, k = 2048, 4096, 14336, 2, 2
         x = dev_normal((T, H))

@@ -236,6 +236,21 @@ int tessera_sm100_attn_decode_static_device(const void* Q, const void* K, const 
                                             int B, int Hq, int Hkv, int Sk, int D, float scale,
                                             int splits, int check_previous, void* stream);
 
+/* General attention forward: the contract of the reference's CUDA attention lane
+ * (python/tessera/compiler/emit/nvidia_cuda.py:251-276, ABI :274: q,k,v,bias|NULL,o, B,Hq,Hkv,Sq,Sk,
+ * D,Dv, scale, causal, wl, wr, softcap) on device pointers, for f32 / f16 / bf16 storage (dtype
+ * code), D and Dv up to 512. bias: f32 [B,Hq,Sq,Sk] or NULL, added after the scale; softcap > 0
+ * applies softcap*tanh(s/softcap); key n is masked for query m when (causal && n > m +
+ * causal_shift) || (wl >= 0 && n < m - wl) || (wr >= 0 && n > m + wr); a fully masked row gives
+ * zeros. causal_shift 0 is the lane's mask, max(Sk - Sq, 0) the bottom-right alignment of
+ * tessera.ops.flash_attn. Q [B,Hq,Sq,D], K [B,Hkv,Sk,D], V [B,Hkv,Sk,Dv], O [B,Hq,Sq,Dv], dense. */
+int tessera_sm100_flash_attn_general_device(const void* q, const void* k, const void* v,
+                                            const float* bias, void* o, long long B, int Hq, int Hkv,
+                                            long long Sq, long long Sk, int D, int Dv, float scale,
+                                            int causal, long long causal_shift, long long window_left,
+                                            long long window_right, float softcap, int dtype,
+                                            void* stream);
+
 /* ---- max-shifted attention states -----------------------------------------------------------
  * ops.softmax_merge / softmax_finalize (python/tessera/_block_attnres_ops.py:104-146): a state is
  * (o [rows, Dv] = sum e^{s-m} v, m [rows] = max s, l [rows] = sum e^{s-m}), fp32; merging is

@@ -140,6 +140,51 @@ def flash_attn(Q, K, V, scale: Optional[float] = None, causal: bool = False,
     return out
 
 
+def attention_lane(q, k, v, *, scale, causal: bool = False, window=None, bias=None, softcap=None,
+                   causal_shift: int = 0) -> np.ndarray:
+    """The CUDA attention lane's contract (python/tessera/compiler/emit/nvidia_cuda.py:251-276), as
+    the reference's device test restates it (tests/device/nvidia/test_flash_attention.py:23-58):
+    ``s = scale q.k (+ bias)``, ``s = softcap tanh(s / softcap)``, keys ``n > m + causal_shift``
+    (causal), ``n < m - wl``, ``n > m + wr`` masked (the mask wins over the soft-cap), softmax, ``@ v``;
+    ``hk = hq // (Hq / Hkv)``; ``D`` and ``Dv`` may differ; a fully masked row gives zeros.
+    ``causal_shift`` 0 is the lane (top-left); ``max(Sk - Sq, 0)`` is ``ops.flash_attn``."""
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    B, Hq, Sq, D = q.shape
+    _, Hkv, Sk, _ = k.shape
+    rep = Hq // Hkv
+    if window is None:
+        wl = wr = None
+    elif isinstance(window, (tuple, list)):
+        wl, wr = window
+    else:
+        wl = wr = window
+    m = np.arange(Sq)[:, None]
+    n = np.arange(Sk)[None, :]
+    keep = np.ones((Sq, Sk), bool)
+    if causal:
+        keep &= n <= m + causal_shift
+    if wl is not None and wl >= 0:
+        keep &= n >= m - wl
+    if wr is not None and wr >= 0:
+        keep &= n <= m + wr
+    out = np.zeros((B, Hq, Sq, v.shape[-1]), np.float32)
+    for b in range(B):
+        for hq in range(Hq):
+            hk = hq // rep
+            s = (q[b, hq] @ k[b, hk].T) * np.float32(scale)
+            if bias is not None:
+                s = s + np.asarray(bias, np.float32)[b, hq]
+            if softcap:
+                s = softcap * np.tanh(s / softcap)
+            s = np.where(keep, s, -np.inf)
+            mx = s.max(-1, keepdims=True)
+            mx = np.where(np.isfinite(mx), mx, 0.0)
+            p = np.exp(s - mx)
+            den = p.sum(-1, keepdims=True)
+            out[b, hq] = (p / np.where(den > 0, den, 1.0)) @ v[b, hk]
+    return out
+
+
 def gqa_attention(Q, K, V, num_query_heads: int, num_kv_heads: int, **kwargs) -> np.ndarray:
     """Query head ``hq`` reads KV head ``hq // (Hq/Hkv)``: the reference repeats each KV head
     ``Hq/Hkv`` times along the head axis and calls ``flash_attn``

@@ -121,6 +121,9 @@ _SIGNATURES = {
                                                        c_int, c_float, c_int, _VP, _VP]),
     "tessera_sm100_softmax_merge_device": (c_int, [_VP] * 9 + [c_longlong, c_int, _VP]),
     "tessera_sm100_softmax_finalize_device": (c_int, [_VP, _VP, _VP, c_longlong, c_int, c_int, _VP]),
+    "tessera_sm100_flash_attn_general_device": (c_int, [_VP, _VP, _VP, _VP, _VP, c_longlong, c_int, c_int,
+                                                        c_longlong, c_longlong, c_int, c_int, c_float, c_int,
+                                                        c_longlong, c_longlong, c_longlong, c_float, c_int, _VP]),
     "tessera_sm100_paged_attn_decode_device": (c_int, [_VP, _VP, _VP, _VP, _VP, _VP, c_int, c_int, c_int,
                                                        c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                                                        _VP, _VP]),

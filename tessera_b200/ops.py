@@ -184,17 +184,28 @@ def batched_gemm(A, B, epilogue=None, **kw):
 # --------------------------------------------------------------------------------- attention
 def flash_attn(Q, K=None, V=None, scale=None, causal: bool = False, cache=None,
                dropout_p: float = 0.0, params=None, deterministic=None, seed=None, attn_bias=None,
-               kv_state=None, *, stream=None):
-    """``softmax(scale * Q K^T, causal) V`` (python/tessera/__init__.py:1304-1356). Q [B,Hq,Sq,D],
-    K/V [B,Hkv,Sk,D] bfloat16, D = 128; Hkv may divide Hq (grouped-query attention)."""
+               kv_state=None, *, window=None, softcap=None, causal_alignment: str = "bottom_right",
+               stream=None):
+    """``softmax(scale * Q K^T [+ attn_bias], causal) V`` (python/tessera/__init__.py:1304-1356). Q
+    [B,Hq,Sq,D], K [B,Hkv,Sk,D], V [B,Hkv,Sk,Dv]; Hkv may divide Hq (grouped-query attention).
+
+    bfloat16 operands with D = Dv = 128 and no bias / window / soft-cap run on the tcgen05 prefill
+    kernel or the split-KV decode kernel; every other combination (float32 / float16 / bfloat16
+    storage, any head dimension up to 512, ``attn_bias`` broadcastable to [B,Hq,Sq,Sk], ``window``
+    = n or (left, right), ``softcap``) runs on the general kernel with the semantics of the
+    reference's CUDA lane (python/tessera/compiler/emit/nvidia_cuda.py:251-276).
+    ``causal_alignment``: "bottom_right" masks key j > i + max(Sk - Sq, 0) as the reference op does;
+    "top_left" masks j > i as the reference's launch executor does."""
     if kv_state is not None:  # python/tessera/__init__.py:1318-1321
         return paged_attention(Q, kv_state, scale=scale, causal=causal)
     if cache is not None:
         raise NotImplementedError("flash_attn: cache= is not part of this backend; pass kv_state=")
     if not 0.0 <= dropout_p < 1.0:
         raise ValueError("dropout_p must be in [0.0, 1.0)")
-    if dropout_p > 0.0 or attn_bias is not None:
-        raise NotImplementedError("flash_attn: dropout and attn_bias are not part of this backend")
+    if dropout_p > 0.0:
+        raise NotImplementedError("flash_attn: dropout is not part of this backend")
+    if causal_alignment not in ("bottom_right", "top_left"):
+        raise ValueError("causal_alignment must be 'bottom_right' or 'top_left'")
     if K is None or V is None:
         raise ValueError("flash_attn: K and V are required")
     Q, K, V = _unwrap(Q), _unwrap(K), _unwrap(V)
@@ -208,26 +219,71 @@ def flash_attn(Q, K=None, V=None, scale=None, causal: bool = False, cache=None,
         raise ValueError(f"flash_attn: expected [B, H, S, D] operands, got {Q.shape}, {K.shape}, {V.shape}")
     Bq, Hq, Sq, D = Q.shape
     Bk, Hkv, Sk, Dk = K.shape
-    if V.shape != K.shape or Bk != Bq or Dk != D:
+    Dv = V.shape[3]
+    if tuple(V.shape[:3]) != tuple(K.shape[:3]) or Bk != Bq or Dk != D:
         raise ValueError(f"flash_attn: incompatible shapes Q {Q.shape}, K {K.shape}, V {V.shape}")
     if Hq % Hkv:
         raise ValueError("num_query_heads must be divisible by num_kv_heads")
-    dt = _storage_dtype((Q, K, V), None, "flash_attn")
-    if dt != bfloat16:
-        raise TypeError("flash_attn: the sm_100a attention kernels take bfloat16 operands")
+    dts = {np.dtype(t.dtype) for t in (Q, K, V)}
+    if len(dts) != 1:
+        raise TypeError(f"flash_attn: operands must share one dtype, got {sorted(map(str, dts))}")
+    dt = dts.pop()
+    if dt not in (np.dtype(np.float32), np.dtype(np.float16), bfloat16):
+        raise TypeError(f"flash_attn: operands must be float32, float16 or bfloat16 (got {dt})")
     if scale is None:
         scale = 1.0 / np.sqrt(D)
     cscale = ctypes.c_float(float(scale))
-    if _any_device(Q, K, V):
+    wl = wr = -1
+    if window is not None:
+        wl, wr = (window if isinstance(window, (tuple, list)) else (window, window))
+        wl = -1 if wl is None else int(wl)
+        wr = -1 if wr is None else int(wr)
+        if (wl < 0 and wl != -1) or (wr < 0 and wr != -1):
+            raise ValueError("window bounds must be >= 0")
+    cap = 0.0 if softcap is None else float(softcap)
+    if cap < 0:
+        raise ValueError("softcap must be >= 0")
+    shift = max(Sk - Sq, 0) if causal_alignment == "bottom_right" else 0
+    fast = (dt == bfloat16 and D == 128 and Dv == 128 and attn_bias is None and wl < 0 and wr < 0 and cap == 0.0
+            and (not causal or shift == max(Sk - Sq, 0)))
+    on_device = _any_device(Q, K, V)
+    if fast and on_device:
         dq, dk, dv = _to_device(Q, dt), _to_device(K, dt), _to_device(V, dt)
         out = DeviceArray(Q.shape, dt)
         _lib.call("tessera_sm100_flash_attn_device", dq.ptr, dk.ptr, dv.ptr, out.ptr, Bq, Hq, Hkv, Sq,
                   Sk, D, cscale, int(bool(causal)), device._stream_handle(stream))
         return out
-    q, k, v = (np.ascontiguousarray(t) for t in (Q, K, V))
-    out = np.empty(q.shape, dt)
-    _lib.call("tessera_sm100_flash_attn", q.ctypes.data, k.ctypes.data, v.ctypes.data, out.ctypes.data,
-              Bq, Hq, Hkv, Sq, Sk, D, cscale, int(bool(causal)))
+    if fast:
+        q, k, v = (np.ascontiguousarray(t) for t in (Q, K, V))
+        out = np.empty(q.shape, dt)
+        _lib.call("tessera_sm100_flash_attn", q.ctypes.data, k.ctypes.data, v.ctypes.data, out.ctypes.data,
+                  Bq, Hq, Hkv, Sq, Sk, D, cscale, int(bool(causal)))
+    else:
+        if D > 512 or Dv > 512:
+            raise ValueError(f"flash_attn: head dimensions up to 512 are served (got D={D}, Dv={Dv})")
+        dbias = None
+        if attn_bias is not None:
+            b = _unwrap(attn_bias)
+            if isinstance(b, DeviceArray):
+                if b.shape != (Bq, Hq, Sq, Sk) or b.dtype != np.float32:
+                    raise ValueError("flash_attn: a device attn_bias must be float32 [B, Hq, Sq, Sk]")
+                dbias = b
+            else:
+                try:
+                    full = np.broadcast_to(np.asarray(b, np.float32), (Bq, Hq, Sq, Sk))
+                except ValueError:
+                    raise ValueError(f"flash_attn: attn_bias {np.shape(b)} does not broadcast to "
+                                     f"{(Bq, Hq, Sq, Sk)}") from None
+                dbias = DeviceArray.from_host(np.ascontiguousarray(full), pooled=True)
+        dq, dk, dv = _to_device(Q, dt), _to_device(K, dt), _to_device(V, dt)
+        dout = DeviceArray((Bq, Hq, Sq, Dv), dt)
+        _lib.call("tessera_sm100_flash_attn_general_device", dq.ptr, dk.ptr, dv.ptr,
+                  dbias.ptr if dbias is not None else None, dout.ptr, Bq, Hq, Hkv, Sq, Sk, D, Dv, cscale,
+                  int(bool(causal)), shift, wl, wr, ctypes.c_float(cap), device.dtype_code(dt),
+                  device._stream_handle(stream))
+        if on_device:
+            return dout
+        out = _finish(dout)
     for _ in range(squeeze):
         out = out[0]
     return out

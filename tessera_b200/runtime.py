@@ -206,15 +206,21 @@ def _execute_sm100_flash_attn(artifact: RuntimeArtifact, args: Any) -> Any:
     meta = artifact.metadata or {}
     op = _single_op(meta, COMPILER_PATHS["sm100_flash_attn"], "sm100_flash_attn")
     names = [str(n) for n in op.get("operands", [])]
-    if len(names) != 3:
-        raise ValueError("sm100 flash attention takes Q, K, V (no bias operand)")
+    if len(names) not in (3, 4):
+        raise ValueError("sm100 flash attention requires Q, K, V and optional bias")
     values = _bind_launch_args(args, list(meta.get("arg_names") or []))
     kw = dict(op.get("kwargs") or {})
-    for unsupported in ("window", "window_left", "window_right", "softcap", "logit_softcap"):
-        if kw.get(unsupported) is not None:
-            raise ValueError(f"sm100 flash attention does not implement {unsupported}")
+    window = kw.get("window", None)
+    if window is None and (kw.get("window_left") is not None or kw.get("window_right") is not None):
+        window = (kw.get("window_left"), kw.get("window_right"))
+    bias = values[names[3]] if len(names) == 4 else None
+    if bias is not None and np.dtype(getattr(getattr(bias, "_data", bias), "dtype", np.float32)) != np.float32:
+        raise ValueError("sm100 flash attention bias must use f32 storage")
+    # the launch path masks key n > m (top-left), like the reference's executor and CUDA lane
     return ops.flash_attn(values[names[0]], values[names[1]], values[names[2]],
-                          scale=kw.get("scale"), causal=bool(kw.get("causal", False)))
+                          scale=kw.get("scale"), causal=bool(kw.get("causal", False)), attn_bias=bias,
+                          window=window, softcap=kw.get("softcap", kw.get("logit_softcap", None)),
+                          causal_alignment="top_left")
 
 
 def _execute_sm100_moe(artifact: RuntimeArtifact, args: Any) -> Any:

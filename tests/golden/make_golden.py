@@ -118,6 +118,43 @@ def attention():
     W = rt(rng.standard_normal((64, 48)), bf16)
     b = rng.standard_normal(48).astype(np.float32)
     out.update(lin_x=x, lin_W=W, lin_b=b, lin_y=np.asarray(F.linear(x, W, b), np.float32))
+    # the CUDA lane's contract (bias, top-left causal, window, soft-cap, D != Dv), from the numpy
+    # reference inside the reference's own device test (tests/device/nvidia/test_flash_attention.py:23-58)
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(
+        "ref_test_flash", os.path.join(REF, "tests", "device", "nvidia", "test_flash_attention.py"))
+    ref_test = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref_test)
+    lane = [  # B, Hq, Hkv, Sq, Sk, D, Dv, kwargs, with_bias
+        (2, 4, 4, 5, 7, 8, 6, dict(scale=1 / np.sqrt(8.0)), False),
+        (2, 4, 2, 5, 7, 8, 6, dict(scale=1 / np.sqrt(8.0)), False),
+        (2, 4, 1, 5, 7, 8, 6, dict(scale=1 / np.sqrt(8.0)), False),
+        (1, 4, 2, 6, 8, 8, 8, dict(scale=0.35, causal=True, window=(3, 1), softcap=1.7), True),
+        (1, 2, 1, 70, 45, 40, 72, dict(scale=0.2, causal=True), False),
+        (1, 2, 2, 33, 100, 64, 64, dict(scale=0.125, window=(10, 0)), True),
+        (1, 1, 1, 9, 9, 16, 16, dict(scale=0.3, causal=True, window=(0, 0)), False),
+    ]
+    for i, (B, Hq, Hkv, Sq, Sk, D, Dv, kw, wb) in enumerate(lane):
+        q = rng.standard_normal((B, Hq, Sq, D), dtype=np.float32)
+        k = rng.standard_normal((B, Hkv, Sk, D), dtype=np.float32)
+        v = rng.standard_normal((B, Hkv, Sk, Dv), dtype=np.float32)
+        bias = (rng.standard_normal((B, Hq, Sq, Sk)) * 0.2).astype(np.float32) if wb else None
+        out[f"laneq{i}"], out[f"lanek{i}"], out[f"lanev{i}"] = q, k, v
+        if wb:
+            out[f"laneb{i}"] = bias
+        out[f"laneo{i}"] = ref_test._reference(q, k, v, bias=bias, **kw).astype(np.float32)
+        out[f"lanekw{i}"] = np.array([kw.get("scale"), float(kw.get("causal", False)),
+                                      -1 if "window" not in kw else kw["window"][0],
+                                      -1 if "window" not in kw else kw["window"][1],
+                                      kw.get("softcap", 0.0)], np.float64)
+    out["lane_n"] = np.array(len(lane))
+    # ops.flash_attn with attn_bias (added before the bottom-right causal mask, __init__.py:1340-1350)
+    Q = rt(rng.standard_normal((2, 2, 20, 32)), bf16)
+    K = rt(rng.standard_normal((2, 2, 50, 32)), bf16)
+    V = rt(rng.standard_normal((2, 2, 50, 32)), bf16)
+    ab = (rng.standard_normal((2, 1, 20, 50)) * 0.5).astype(np.float32)
+    out.update(biasQ=Q, biasK=K, biasV=V, biasB=ab,
+               biasO=np.asarray(tessera.ops.flash_attn(Q, K, V, causal=True, attn_bias=ab), np.float32))
     # split-KV merge states
     oa, ob = rng.standard_normal((2, 5, 16)).astype(np.float32)
     ma, mb = rng.standard_normal((2, 5)).astype(np.float32)

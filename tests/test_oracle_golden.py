@@ -149,3 +149,21 @@ def test_region_oracles_match_reference(golden_dir):
                                rtol=1e-5, atol=1e-6)
     np.testing.assert_allclose(orc.attention_region(g["regQ"], g["regK"], g["regV"], sc, True), g["regOc"],
                                rtol=1e-5, atol=1e-6)
+
+
+def _lane_kwargs(kw):
+    scale, causal, wl, wr, cap = (float(x) for x in kw)
+    return dict(scale=scale, causal=bool(causal), window=None if wl < 0 and wr < 0 else (int(wl), int(wr)),
+                softcap=cap or None)
+
+
+def test_attention_lane_contract_matches_reference(golden_dir):
+    g = _load(golden_dir, "attention.npz")
+    for i in range(int(g["lane_n"])):
+        bias = g[f"laneb{i}"] if f"laneb{i}" in g else None
+        o = orc.attention_lane(g[f"laneq{i}"], g[f"lanek{i}"], g[f"lanev{i}"], bias=bias, **_lane_kwargs(g[f"lanekw{i}"]))
+        np.testing.assert_allclose(o, g[f"laneo{i}"], rtol=1e-5, atol=2e-6)
+    Sq, Sk = g["biasQ"].shape[2], g["biasK"].shape[2]
+    o = orc.attention_lane(g["biasQ"], g["biasK"], g["biasV"], scale=1 / np.sqrt(32.0), causal=True,
+                           bias=np.broadcast_to(g["biasB"], (2, 2, Sq, Sk)), causal_shift=max(Sk - Sq, 0))
+    np.testing.assert_allclose(o, g["biasO"], rtol=1e-5, atol=2e-6)

@@ -43,7 +43,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # captures ran a quarter-size case (heads, batch, experts x slots) and are scaled x4, the traffic
 # of these kernels being proportional to those counts. The MoE figure is the sum of its two
 # grouped GEMM launches.
-NCU_TRAFFIC_BYTES = {"gemm_8192": 1.154e9, "attn_prefill": 1.007e9, "attn_decode": 2.171e9, "attn_decode_paged": 2.166e9,
+NCU_TRAFFIC_BYTES = {"gemm_8192": 1.209e9, "attn_prefill": 1.007e9, "attn_decode": 2.171e9, "attn_decode_paged": 2.166e9,
                      "moe": 4.78e9}
 
 
@@ -293,7 +293,9 @@ def bench_gemm(ranks, args, peaks, peak_kind, sampler):
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"],
                      "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
                      "traffic": NCU_TRAFFIC_BYTES["gemm_8192"], "peak_kind": f"burst cuBLAS bf16, of {peak_kind}",
-                     "kernel_ms": k_ms, "kernel": "gemm_kernel<bf16,plain> (tcgen05 128x256x64, 4-stage TMA)"},
+                     "kernel_ms": k_ms, "kernel": ("gemm2_kernel<bf16> (tcgen05 cta_group::2, 256x256x64 per CTA pair, 6-stage TMA)"
+                                if (n // 256) * (-(-nb // 256)) >= 148 else
+                                "gemm_kernel<bf16,plain> (tcgen05 128x256x64, 4-stage TMA)")},
         "e2e": e2e, "check_max_rel_err": rel, "clock_marks": (m0, m1), "probe_marks": probe_marks,
         "tp_mode": tp_mode,
     }

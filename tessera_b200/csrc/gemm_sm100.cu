@@ -1,5 +1,6 @@
 // Host side of the tcgen05 GEMM: tensor-map construction, launch, and the C entry points.
 #include "gemm_sm100.cuh"
+#include "gemm2_sm100.cuh"
 
 #include <algorithm>
 #include <cstdlib>
@@ -46,6 +47,52 @@ int dispatch_out(int out_dtype, const CUtensorMap& tA, const CUtensorMap& tB,
   }
   set_last_error("unsupported output dtype %d for this GEMM mode", out_dtype);
   return kBadArg;
+}
+
+// CTA-pair kernel: cluster of two, as many clusters as the device can hold at once.
+template <typename OutT>
+int launch_pair_kernel(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tD,
+                       const Params& p, long long pair_tiles, cudaStream_t stream) {
+  TSB_CUDA_OK(cudaFuncSetAttribute(gemm2::gemm2_kernel<OutT>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, gemm2::SMEM_ALLOC));
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(gemm2::NUM_THREADS);
+  cfg.dynamicSmemBytes = gemm2::SMEM_ALLOC;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  // How many clusters fit at once (GPCs with an odd SM count leave one SM unpaired).
+  static int max_clusters[64] = {};
+  const int dev = current_device();
+  int mc = (dev >= 0 && dev < 64) ? max_clusters[dev] : 0;
+  if (mc == 0) {
+    cfg.gridDim = dim3(2 * (sm_count() / 2));
+    if (cudaOccupancyMaxActiveClusters(&mc, gemm2::gemm2_kernel<OutT>, &cfg) != cudaSuccess ||
+        mc <= 0) {
+      cudaGetLastError();
+      mc = sm_count() / 2;
+    }
+    if (dev >= 0 && dev < 64) max_clusters[dev] = mc;
+  }
+  const int clusters = (int)std::min<long long>(pair_tiles, mc);
+  cfg.gridDim = dim3(2 * clusters);
+  TSB_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm2::gemm2_kernel<OutT>, tA, tB, tD, p));
+  note_launch();
+  return kOk;
+}
+
+// TESSERA_SM100_GEMM_2CTA=0 keeps every GEMM on the single-CTA kernel.
+bool pair_kernel_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("TESSERA_SM100_GEMM_2CTA");
+    return !(e && e[0] == '0');
+  }();
+  return on;
 }
 
 CUtensorMapDataType tm_dtype(int dt) {
@@ -153,6 +200,20 @@ int launch_plain(const void* A, const void* B, void* D, int batch, int M, int N,
   p.err = device_err_word();
   if (!p.err) return kDeviceFailed;
   const long long total = (long long)p.m_tiles * p.n_tiles * batch;
+  // Large dense problems take the CTA-pair kernel (256 x 256 tiles, M = 256 MMAs): enough pair
+  // tiles to fill the device at least twice, and no per-rank output copies.
+  const long long pair_tiles = (long long)((p.m_tiles + 1) / 2) * p.n_tiles * batch;
+  if (num_peers == 0 && pair_kernel_enabled() && M >= 2 * BM && pair_tiles >= sm_count()) {
+    Params p2 = p;
+    p2.idesc = make_idesc_f16(in_dtype == TESSERA_SM100_BF16, false, true, 2 * BM, BN);
+    switch (out_dtype) {
+      case TESSERA_SM100_F32: return launch_pair_kernel<float>(tA, tB, tD, p2, pair_tiles, stream);
+      case TESSERA_SM100_BF16:
+        return launch_pair_kernel<__nv_bfloat16>(tA, tB, tD, p2, pair_tiles, stream);
+      case TESSERA_SM100_F16: return launch_pair_kernel<__half>(tA, tB, tD, p2, pair_tiles, stream);
+      default: break;
+    }
+  }
   const int grid = (int)std::min<long long>(total, sm_count());
   return dispatch_out<kPlain>(out_dtype, tA, tB, tB, tD, *peers, p, grid, stream);
 }

@@ -153,3 +153,18 @@ def test_host_pointer_form_pipelined_chunks(lib, batch, M, N, K, out_dt):
     if N % 8 == 0 and K % 8 == 0:
         np.testing.assert_array_equal(D, gemm_device(A, B, out_dt))
     no_device_error()
+
+
+@pytest.mark.parametrize("batch,M,N,K,out_dt", [(1, 2304, 4352, 520, np.float32), (1, 2200, 4360, 264, bfloat16),
+                                                (2, 1280, 4096, 256, np.float16), (1, 8192, 1280, 128, np.float32)])
+def test_cta_pair_kernel_shapes(batch, M, N, K, out_dt):
+    """Shapes large enough for the CTA-pair kernel (256 x 256 tiles, cta_group::2 MMAs): an odd
+    number of 128-row tiles (the last pair's second CTA has no rows), ragged M and N, batches."""
+    rng = np.random.default_rng(M + N + K)
+    dt = np.float16 if out_dt == np.float16 else bfloat16
+    shapeA = (batch, M, K) if batch > 1 else (M, K)
+    shapeB = (batch, K, N) if batch > 1 else (K, N)
+    A, B = _rand(rng, shapeA, dt, 1 / np.sqrt(K)), _rand(rng, shapeB, dt)
+    got = gemm_device(A, B, out_dt)
+    assert rel_err(got, orc.gemm(A, B)) < (1e-4 if out_dt == np.float32 else TOL)
+    no_device_error()

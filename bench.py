@@ -294,7 +294,7 @@ def bench_gemm(ranks, args, peaks, peak_kind, sampler):
                      "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
                      "traffic": NCU_TRAFFIC_BYTES["gemm_8192"], "peak_kind": f"burst cuBLAS bf16, of {peak_kind}",
                      "kernel_ms": k_ms, "kernel": ("gemm2_kernel<bf16> (tcgen05 cta_group::2, 256x256x64 per CTA pair, 6-stage TMA)"
-                                if (n // 256) * (-(-nb // 256)) >= 148 else
+                                if (n // 256) * (-(-nb // 256)) >= 74 else
                                 "gemm_kernel<bf16,plain> (tcgen05 128x256x64, 4-stage TMA)")},
         "e2e": e2e, "check_max_rel_err": rel, "clock_marks": (m0, m1), "probe_marks": probe_marks,
         "tp_mode": tp_mode,

@@ -15,6 +15,8 @@
 //              arrival multicast; no data is multicast anywhere).
 //   tfull[a]   one per CTA, same commit form after the last k-block of a tile.
 //   tempty[a]  even CTA only, 8 arrivals: the four epilogue warps of each CTA.
+// With `num_peers` > 0 the epilogue stores every piece through the per-rank output maps (the
+// all-gather of the column-parallel GEMM), as the single-CTA kernel does.
 // Both CTAs allocate TMEM with cta_group::2 from the same warp index, and free it only after
 // a cluster barrier; a second cluster barrier after barrier initialisation keeps either CTA
 // from signalling a barrier the other has not initialised yet.
@@ -82,7 +84,8 @@ struct PairWalker {
 template <typename OutT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-             const __grid_constant__ CUtensorMap tmD, const Params p) {
+             const __grid_constant__ CUtensorMap tmD, const __grid_constant__ gemm::PeerMaps peers,
+             const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -262,7 +265,13 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          tma_store_3d(&tmD, buf, col0, row0, tile.b);
+          if (p.num_peers > 0) {
+            // Column-parallel GEMM: the same piece into every rank's Y (plain TMA stores over
+            // NVLink; this rank's own copy is one of the maps). One bulk group covers them all.
+            for (int i = 0; i < p.num_peers; ++i) tma_store_3d(&peers.m[i], buf, col0, row0, tile.b);
+          } else {
+            tma_store_3d(&tmD, buf, col0, row0, tile.b);
+          }
           tma_store_commit();
         }
         sbuf ^= 1;

@@ -52,7 +52,8 @@ int dispatch_out(int out_dtype, const CUtensorMap& tA, const CUtensorMap& tB,
 // CTA-pair kernel: cluster of two, as many clusters as the device can hold at once.
 template <typename OutT>
 int launch_pair_kernel(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tD,
-                       const Params& p, long long pair_tiles, cudaStream_t stream) {
+                       const PeerMaps& peers, const Params& p, long long pair_tiles,
+                       cudaStream_t stream) {
   TSB_CUDA_OK(cudaFuncSetAttribute(gemm2::gemm2_kernel<OutT>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, gemm2::SMEM_ALLOC));
   cudaLaunchConfig_t cfg{};
@@ -81,7 +82,7 @@ int launch_pair_kernel(const CUtensorMap& tA, const CUtensorMap& tB, const CUten
   }
   const int clusters = (int)std::min<long long>(pair_tiles, mc);
   cfg.gridDim = dim3(2 * clusters);
-  TSB_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm2::gemm2_kernel<OutT>, tA, tB, tD, p));
+  TSB_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm2::gemm2_kernel<OutT>, tA, tB, tD, peers, p));
   note_launch();
   return kOk;
 }
@@ -156,6 +157,11 @@ int launch_plain(const void* A, const void* B, void* D, int batch, int M, int N,
     if (!encode_tmap(&tD, tm_dtype(out_dtype), 3, D, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
       return kBadArg;
   }
+  // Large dense problems take the CTA-pair kernel (256 x 256 tiles, M = 256 MMAs): at least one
+  // full wave of clusters.
+  const long long pair_tiles =
+      (long long)(((M + BM - 1) / BM + 1) / 2) * ((N + BN - 1) / BN) * batch;
+  const bool use_pairs = pair_kernel_enabled() && M >= 2 * BM && pair_tiles >= sm_count() / 2;
   static PeerMaps no_peers{};
   PeerMaps peer_maps;
   const PeerMaps* peers = &no_peers;
@@ -166,8 +172,9 @@ int launch_plain(const void* A, const void* B, void* D, int batch, int M, int N,
     }
     uint64_t dims[3] = {(uint64_t)N, (uint64_t)M, (uint64_t)batch};
     uint64_t str[2] = {(uint64_t)ldd * osz, (uint64_t)sD * osz};
-    // 16-bit outputs take the wide epilogue: 128-column (256-byte) rows, unswizzled staging.
-    const bool wide = (osz == 2);
+    // 16-bit outputs on the single-CTA kernel take the wide epilogue: 128-column (256-byte)
+    // rows, unswizzled staging. The CTA-pair kernel stores swizzled 128-byte rows.
+    const bool wide = (osz == 2) && !use_pairs;
     uint32_t box[3] = {wide ? 128u : (uint32_t)(128 / osz), 32, 1};
     for (int i = 0; i < num_peers; ++i) {
       if (!peer_D[i] || !aligned16(peer_D[i])) {
@@ -200,17 +207,16 @@ int launch_plain(const void* A, const void* B, void* D, int batch, int M, int N,
   p.err = device_err_word();
   if (!p.err) return kDeviceFailed;
   const long long total = (long long)p.m_tiles * p.n_tiles * batch;
-  // Large dense problems take the CTA-pair kernel (256 x 256 tiles, M = 256 MMAs): enough pair
-  // tiles to fill the device at least twice, and no per-rank output copies.
-  const long long pair_tiles = (long long)((p.m_tiles + 1) / 2) * p.n_tiles * batch;
-  if (num_peers == 0 && pair_kernel_enabled() && M >= 2 * BM && pair_tiles >= sm_count()) {
+  if (use_pairs) {
     Params p2 = p;
     p2.idesc = make_idesc_f16(in_dtype == TESSERA_SM100_BF16, false, true, 2 * BM, BN);
     switch (out_dtype) {
-      case TESSERA_SM100_F32: return launch_pair_kernel<float>(tA, tB, tD, p2, pair_tiles, stream);
+      case TESSERA_SM100_F32:
+        return launch_pair_kernel<float>(tA, tB, tD, *peers, p2, pair_tiles, stream);
       case TESSERA_SM100_BF16:
-        return launch_pair_kernel<__nv_bfloat16>(tA, tB, tD, p2, pair_tiles, stream);
-      case TESSERA_SM100_F16: return launch_pair_kernel<__half>(tA, tB, tD, p2, pair_tiles, stream);
+        return launch_pair_kernel<__nv_bfloat16>(tA, tB, tD, *peers, p2, pair_tiles, stream);
+      case TESSERA_SM100_F16:
+        return launch_pair_kernel<__half>(tA, tB, tD, *peers, p2, pair_tiles, stream);
       default: break;
     }
   }

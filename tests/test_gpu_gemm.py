@@ -168,3 +168,26 @@ def test_cta_pair_kernel_shapes(batch, M, N, K, out_dt):
     got = gemm_device(A, B, out_dt)
     assert rel_err(got, orc.gemm(A, B)) < (1e-4 if out_dt == np.float32 else TOL)
     no_device_error()
+
+
+@pytest.mark.parametrize("M,N,K,out_dt", [(2048, 8192, 264, bfloat16), (384, 1024, 512, bfloat16),
+                                          (2304, 8192, 128, np.float32)])
+def test_fused_all_gather_epilogue_with_local_copies(lib, M, N, K, out_dt):
+    """The column-parallel GEMM's epilogue stores each tile into every rank's Y. Here the two
+    "ranks" run one after the other on one GPU with both Y copies local, which exercises the
+    per-copy stores of both kernels (CTA pairs for the large shapes, single CTA for the small
+    one); every copy must hold the complete product."""
+    from tessera_b200 import _lib, device
+    from tessera_b200.device import DeviceArray
+    rng = np.random.default_rng(M + K)
+    A, B = _rand(rng, (M, K), bfloat16, 1 / np.sqrt(K)), _rand(rng, (K, N), bfloat16)
+    dA, dB = DeviceArray.from_host(A), DeviceArray.from_host(B)
+    ys = [DeviceArray.zeros((M, N), out_dt) for _ in range(2)]
+    ptrs = (ctypes.c_void_p * 2)(ys[0].ptr, ys[1].ptr)
+    for rank in range(2):
+        _lib.call("tessera_sm100_gemm_allgather_device", dA.ptr, dB.ptr, ptrs, 2, rank, M, N, K, 1,
+                  device.dtype_code(out_dt), None)
+    ref = orc.gemm(A, B)
+    for y in ys:
+        assert rel_err(y.download(), ref) < (1e-4 if out_dt == np.float32 else TOL)
+    no_device_error()

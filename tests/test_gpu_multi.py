@@ -64,6 +64,17 @@ def _worker(rank, world, port, q):
         errs["tp_gemm"] = orc.max_rel_err(tp.Y.download(), orc.gemm(A, Wm))
         dist.barrier()
         tp.close()
+        # large enough for the CTA-pair kernel to do the per-rank stores
+        M, N, K = 2048, 8192, 256
+        A = (rng.standard_normal((M, K), dtype=np.float32) / np.sqrt(K)).astype(bfloat16)
+        Wm = rng.standard_normal((K, N), dtype=np.float32).astype(bfloat16)
+        tp = parallel.TensorParallelGemm(M, N, K, world, rank, gather, bfloat16, bfloat16)
+        tp(DeviceArray.from_host(A), DeviceArray.from_host(Wm))
+        device.synchronize()
+        dist.barrier()
+        errs["tp_gemm_pairs"] = orc.max_rel_err(tp.Y.download(), orc.gemm(A, Wm))
+        dist.barrier()
+        tp.close()
         # --- expert-parallel MoE
         T, H, F, E, k = 256, 128, 256, 8, 2
         xs = rng.standard_normal((T, H), dtype=np.float32).astype(bfloat16)
@@ -122,7 +133,7 @@ def test_two_gpu_collectives_tp_gemm_and_ep_moe():
     for rank, errs, exc in results:
         assert exc is None, f"rank {rank}:\n{exc}"
         assert errs["all_gather"] == 0 and errs["all_reduce"] == 0 and errs["all_to_all_v"] == 0, errs
-        assert errs["tp_gemm"] < 1e-2 and errs["ep_moe"] < 1e-2 and errs["ep_moe_device"] < 1e-2, errs
+        assert errs["tp_gemm"] < 1e-2 and errs["tp_gemm_pairs"] < 1e-2 and errs["ep_moe"] < 1e-2 and errs["ep_moe_device"] < 1e-2, errs
 
 
 def _adapter_worker(q):

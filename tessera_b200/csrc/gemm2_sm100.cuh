@@ -1,4 +1,4 @@
-// CTA-pair variant of the dense tcgen05 GEMM (plain / batched mode only).
+// CTA-pair variant of the tcgen05 GEMM: dense / batched, ragged grouped, and grouped SwiGLU.
 //
 // Two CTAs of a cluster share one 256 x 256 output tile: CTA r of the pair owns rows
 // [m0 + 128 r, m0 + 128 r + 128), loads its own A tile (128 x 64) and ITS HALF of the B tile
@@ -15,6 +15,11 @@
 //              arrival multicast; no data is multicast anywhere).
 //   tfull[a]   one per CTA, same commit form after the last k-block of a tile.
 //   tempty[a]  even CTA only, 8 arrivals: the four epilogue warps of each CTA.
+// Grouped modes: a pair tile is 256 rows of ONE group; a CTA whose 128 rows reach past the end of
+// the group computes on whatever rows follow (the next group's, or zeros past the end) and stores
+// only its valid rows, as the single-CTA kernel does for partial tiles. In the SwiGLU mode the B
+// halves are the two weight matrices: the even CTA loads the 128 gate columns, the odd CTA the
+// matching 128 up columns, and every CTA's accumulator holds gate | up for its own rows.
 // With `num_peers` > 0 the epilogue stores every piece through the per-rank output maps (the
 // all-gather of the column-parallel GEMM), as the single-CTA kernel does.
 // Both CTAs allocate TMEM with cta_group::2 from the same warp index, and free it only after
@@ -31,6 +36,9 @@ using gemm::BM;
 using gemm::BN;
 using gemm::EPI_BUF_BYTES;
 using gemm::Params;
+using gemm::kGrouped;
+using gemm::kGroupedSwiGLU;
+using gemm::kPlain;
 
 #ifndef TESSERA_GEMM2_STAGES
 #define TESSERA_GEMM2_STAGES 6
@@ -55,37 +63,63 @@ constexpr int GROUP_PAIRS = TESSERA_GEMM2_GROUP;  // 256-row tile pairs per rast
 
 struct PairTile {
   int m0, n0, b;  // m0 = first row of the PAIR
+  int rows;       // valid rows of the pair from m0 (grouped modes; 2 * BM when plain)
 };
 
-// Static tile list shared by both CTAs of a pair: pair-tiles of 256 x 256, rastered in groups of
-// GROUP_PAIRS row blocks so consecutive clusters reuse the same B columns out of L2.
+// Static tile list shared by both CTAs of a pair. Plain: pair tiles of 256 x 256, rastered in
+// groups of GROUP_PAIRS row blocks so consecutive clusters reuse the same B columns out of L2.
+// Grouped: per group, ceil(rows / 256) pair tiles per output column block, m fastest.
+template <int kMode>
 struct PairWalker {
   int t, step;
+  int e = 0, base = 0;  // grouped cursor
   __device__ PairWalker(int first, int stride) : t(first), step(stride) {}
   __device__ bool next(const Params& p, PairTile& out) {
-    const int m_pairs = (p.m_tiles + 1) / 2;
-    const int per_b = m_pairs * p.n_tiles;
-    if (t >= per_b * p.batch) return false;
-    const int b = t / per_b;
-    const int r = t - b * per_b;
-    const int gspan = GROUP_PAIRS * p.n_tiles;
-    const int g = r / gspan;
-    const int first_m = g * GROUP_PAIRS;
-    const int gsz = min(m_pairs - first_m, GROUP_PAIRS);
-    const int rr = r - g * gspan;
-    out.m0 = (first_m + rr % gsz) * 2 * BM;
-    out.n0 = (rr / gsz) * BN;
-    out.b = b;
+    if constexpr (kMode == kPlain) {
+      const int m_pairs = (p.m_tiles + 1) / 2;
+      const int per_b = m_pairs * p.n_tiles;
+      if (t >= per_b * p.batch) return false;
+      const int b = t / per_b;
+      const int r = t - b * per_b;
+      const int gspan = GROUP_PAIRS * p.n_tiles;
+      const int g = r / gspan;
+      const int first_m = g * GROUP_PAIRS;
+      const int gsz = min(m_pairs - first_m, GROUP_PAIRS);
+      const int rr = r - g * gspan;
+      out.m0 = (first_m + rr % gsz) * 2 * BM;
+      out.n0 = (rr / gsz) * BN;
+      out.b = b;
+      out.rows = 2 * BM;
+    } else {
+      constexpr int kOutW = (kMode == kGroupedSwiGLU) ? BN / 2 : BN;
+      int rows_e = 0, mp = 0;
+      while (e < p.batch) {
+        rows_e = p.group_offsets[e + 1] - p.group_offsets[e];
+        mp = (rows_e + 2 * BM - 1) / (2 * BM);
+        const int cnt = mp * p.n_tiles;
+        if (t < base + cnt) break;
+        base += cnt;
+        ++e;
+      }
+      if (e >= p.batch) return false;
+      const int local = t - base;
+      const int n_idx = local / mp;
+      const int m_idx = local - n_idx * mp;
+      out.m0 = p.group_offsets[e] + m_idx * 2 * BM;
+      out.n0 = n_idx * kOutW;
+      out.b = e;
+      out.rows = min(2 * BM, rows_e - m_idx * 2 * BM);
+    }
     t += step;
     return true;
   }
 };
 
-template <typename OutT>
+template <typename OutT, int kMode>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-             const __grid_constant__ CUtensorMap tmD, const __grid_constant__ gemm::PeerMaps peers,
-             const Params p) {
+             const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmD,
+             const __grid_constant__ gemm::PeerMaps peers, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -109,7 +143,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   const int cluster_id = blockIdx.x >> 1;
   const int num_clusters = gridDim.x >> 1;
   const int num_kb = (p.K + BK - 1) / BK;
-  constexpr int kChunk = (sizeof(OutT) == 4) ? 32 : 64;  // output columns per store
+  constexpr int kOutW = (kMode == kGroupedSwiGLU) ? BN / 2 : BN;  // output columns per tile
+  constexpr int kChunk = (sizeof(OutT) == 4) ? 32 : 64;            // output columns per store
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -126,6 +161,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   if (warp == 4 && lane == 0) {
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if constexpr (kMode == kGroupedSwiGLU) tma_prefetch_desc(&tmB2);
     tma_prefetch_desc(&tmD);
   }
   if (warp == 5) {
@@ -143,14 +179,18 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   if (warp == 4) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0) {
-      PairWalker walk(cluster_id, num_clusters);
+      PairWalker<kMode> walk(cluster_id, num_clusters);
       PairTile tile;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      // SwiGLU: the even CTA fetches gate columns, the odd CTA the same columns of the up matrix.
+      const CUtensorMap* my_b = (kMode == kGroupedSwiGLU && rank == 1) ? &tmB2 : &tmB;
       while (ok && walk.next(p, tile)) {
         const int my_m0 = tile.m0 + static_cast<int>(rank) * BM;
-        const int my_n0 = tile.n0 + static_cast<int>(rank) * (BN / 2);
+        const int my_n0 =
+            (kMode == kGroupedSwiGLU) ? tile.n0 : tile.n0 + static_cast<int>(rank) * (BN / 2);
+        const int a_b = (kMode == kPlain) ? tile.b : 0;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.err, kErrWaitEmpty, kb)) {
             ok = false;
@@ -158,11 +198,11 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
           }
           if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), PAIR_TX_BYTES);
           const int k0 = kb * BK;
-          tma_load_3d_2cta(sA + stage * A_STAGE_BYTES, &tmA, full_bar(stage), k0, my_m0, tile.b);
+          tma_load_3d_2cta(sA + stage * A_STAGE_BYTES, &tmA, full_bar(stage), k0, my_m0, a_b);
           const uint32_t b_dst = sB + stage * B_STAGE_BYTES;
 #pragma unroll
           for (int j = 0; j < 2; ++j)
-            tma_load_3d_2cta(b_dst + j * B_BLOCK_BYTES, &tmB, full_bar(stage), my_n0 + 64 * j, k0,
+            tma_load_3d_2cta(b_dst + j * B_BLOCK_BYTES, my_b, full_bar(stage), my_n0 + 64 * j, k0,
                              tile.b);
           if (++stage == STAGES) {
             stage = 0;
@@ -174,7 +214,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   } else if (warp == 5) {
     // ------------------------------------------------------------ MMA issuer (even CTA only)
     if (lane == 0 && rank == 0) {
-      PairWalker walk(cluster_id, num_clusters);
+      PairWalker<kMode> walk(cluster_id, num_clusters);
       PairTile tile;
       int stage = 0;
       uint32_t phase = 0;
@@ -219,7 +259,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     }
   } else {
     // ------------------------------------------------------------ epilogue warps 0..3 (both CTAs)
-    PairWalker walk(cluster_id, num_clusters);
+    PairWalker<kMode> walk(cluster_id, num_clusters);
     PairTile tile;
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -232,10 +272,13 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         break;
       }
       tc_fence_after();
-      const int row0 = tile.m0 + static_cast<int>(rank) * BM + 32 * warp;
-      const bool warp_has_rows = row0 < p.M;
+      const int cta_m0 = tile.m0 + static_cast<int>(rank) * BM;  // first row of this CTA's half
+      const int row0 = cta_m0 + 32 * warp;                        // first output row of this warp
+      // valid rows of this warp: all 32 in plain mode (TMA clips at M), the group's tail otherwise
+      const int rows_w = max(0, min(32, tile.rows - static_cast<int>(rank) * BM - 32 * warp));
+      const bool warp_has_rows = (kMode == kPlain) ? (row0 < p.M) : (rows_w > 0);
       const uint32_t t_acc = tmem_base + static_cast<uint32_t>(acc * BN) + lane_base;
-      constexpr int kChunks = BN / kChunk;
+      constexpr int kChunks = kOutW / kChunk;
       bool released = false;
 #pragma unroll 1
       for (int c = 0; c < kChunks; ++c) {
@@ -244,17 +287,35 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         const uint32_t buf = sEpi + static_cast<uint32_t>((warp * 2 + sbuf) * EPI_BUF_BYTES);
         if (lane == 0) tma_store_wait_read<1>();
         __syncwarp();
+        if constexpr (kMode == kGroupedSwiGLU) {
+          // kChunk == 64 (16-bit output): two halves of 32 output columns each.
 #pragma unroll
-        for (int h = 0; h < kChunk / 32; ++h) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(t_acc + c * kChunk + h * 32, r);
-          tmem_ld_wait();
-          float v[32];
+          for (int h = 0; h < 2; ++h) {
+            uint32_t g[32], u[32];
+            tmem_ld_32x32b_x32(t_acc + c * 64 + h * 32, g);
+            tmem_ld_32x32b_x32(t_acc + (BN / 2) + c * 64 + h * 32, u);
+            tmem_ld_wait();
+            float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-          if (p.bias || p.residual || p.activation)
-            gemm::apply_epilogue<OutT>(v, p, row0 + lane, col0 + h * 32);
-          gemm::stage_row32<OutT>(buf, lane, h * 32 * sizeof(OutT), v);
+            for (int j = 0; j < 32; ++j)
+              v[j] = gemm::silu_mul(__uint_as_float(g[j]), __uint_as_float(u[j]));
+            gemm::stage_row32<OutT>(buf, lane, h * 64, v);
+          }
+        } else {
+#pragma unroll
+          for (int h = 0; h < kChunk / 32; ++h) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(t_acc + c * kChunk + h * 32, r);
+            tmem_ld_wait();
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            if constexpr (kMode == kPlain) {
+              if (p.bias || p.residual || p.activation)
+                gemm::apply_epilogue<OutT>(v, p, row0 + lane, col0 + h * 32);
+            }
+            gemm::stage_row32<OutT>(buf, lane, h * 32 * sizeof(OutT), v);
+          }
         }
         if (c == kChunks - 1 || col0 + kChunk >= p.N) {
           tc_fence_before();
@@ -262,17 +323,41 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
           if (lane == 0) mbar_arrive_even_cta(tempty_bar(acc));
           released = true;
         }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          if (p.num_peers > 0) {
-            // Column-parallel GEMM: the same piece into every rank's Y (plain TMA stores over
-            // NVLink; this rank's own copy is one of the maps). One bulk group covers them all.
-            for (int i = 0; i < p.num_peers; ++i) tma_store_3d(&peers.m[i], buf, col0, row0, tile.b);
-          } else {
-            tma_store_3d(&tmD, buf, col0, row0, tile.b);
+        const bool full_rows = (kMode == kPlain) || (rows_w == 32);
+        if (full_rows) {
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int d_b = (kMode == kPlain) ? tile.b : 0;
+            if (kMode == kPlain && p.num_peers > 0) {
+              // Column-parallel GEMM: the same piece into every rank's Y (plain TMA stores over
+              // NVLink; this rank's own copy is one of the maps). One bulk group covers them all.
+              for (int i = 0; i < p.num_peers; ++i) tma_store_3d(&peers.m[i], buf, col0, row0, d_b);
+            } else {
+              tma_store_3d(&tmD, buf, col0, row0, d_b);
+            }
+            tma_store_commit();
           }
-          tma_store_commit();
+        } else {
+          // Tail of a ragged group: copy the valid rows out with predicated 16-byte stores.
+          __syncwarp();
+          constexpr int kElemsPer16 = 16 / sizeof(OutT);
+          OutT* Dp = reinterpret_cast<OutT*>(p.D);
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int r = it * 4 + (lane >> 3);
+            const int ch = lane & 7;
+            const int col = col0 + ch * kElemsPer16;
+            if (r < rows_w && col < p.N) {
+              uint4 val;
+              const uint32_t addr = buf + swz128(r, ch);
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(val.x), "=r"(val.y), "=r"(val.z), "=r"(val.w)
+                           : "r"(addr));
+              *reinterpret_cast<uint4*>(Dp + static_cast<long long>(row0 + r) * p.ldd + col) = val;
+            }
+          }
+          __syncwarp();
         }
         sbuf ^= 1;
       }

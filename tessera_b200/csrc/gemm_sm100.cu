@@ -50,11 +50,11 @@ int dispatch_out(int out_dtype, const CUtensorMap& tA, const CUtensorMap& tB,
 }
 
 // CTA-pair kernel: cluster of two, as many clusters as the device can hold at once.
-template <typename OutT>
-int launch_pair_kernel(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tD,
-                       const PeerMaps& peers, const Params& p, long long pair_tiles,
-                       cudaStream_t stream) {
-  TSB_CUDA_OK(cudaFuncSetAttribute(gemm2::gemm2_kernel<OutT>,
+template <typename OutT, int kMode>
+int launch_pair_kernel(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2,
+                       const CUtensorMap& tD, const PeerMaps& peers, const Params& p,
+                       long long pair_tiles, cudaStream_t stream) {
+  TSB_CUDA_OK(cudaFuncSetAttribute(gemm2::gemm2_kernel<OutT, kMode>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, gemm2::SMEM_ALLOC));
   cudaLaunchConfig_t cfg{};
   cudaLaunchAttribute attr[1];
@@ -73,7 +73,7 @@ int launch_pair_kernel(const CUtensorMap& tA, const CUtensorMap& tB, const CUten
   int mc = (dev >= 0 && dev < 64) ? max_clusters[dev] : 0;
   if (mc == 0) {
     cfg.gridDim = dim3(2 * (sm_count() / 2));
-    if (cudaOccupancyMaxActiveClusters(&mc, gemm2::gemm2_kernel<OutT>, &cfg) != cudaSuccess ||
+    if (cudaOccupancyMaxActiveClusters(&mc, gemm2::gemm2_kernel<OutT, kMode>, &cfg) != cudaSuccess ||
         mc <= 0) {
       cudaGetLastError();
       mc = sm_count() / 2;
@@ -82,7 +82,7 @@ int launch_pair_kernel(const CUtensorMap& tA, const CUtensorMap& tB, const CUten
   }
   const int clusters = (int)std::min<long long>(pair_tiles, mc);
   cfg.gridDim = dim3(2 * clusters);
-  TSB_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm2::gemm2_kernel<OutT>, tA, tB, tD, peers, p));
+  TSB_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm2::gemm2_kernel<OutT, kMode>, tA, tB, tB2, tD, peers, p));
   note_launch();
   return kOk;
 }
@@ -212,11 +212,11 @@ int launch_plain(const void* A, const void* B, void* D, int batch, int M, int N,
     p2.idesc = make_idesc_f16(in_dtype == TESSERA_SM100_BF16, false, true, 2 * BM, BN);
     switch (out_dtype) {
       case TESSERA_SM100_F32:
-        return launch_pair_kernel<float>(tA, tB, tD, *peers, p2, pair_tiles, stream);
+        return launch_pair_kernel<float, kPlain>(tA, tB, tB, tD, *peers, p2, pair_tiles, stream);
       case TESSERA_SM100_BF16:
-        return launch_pair_kernel<__nv_bfloat16>(tA, tB, tD, *peers, p2, pair_tiles, stream);
+        return launch_pair_kernel<__nv_bfloat16, kPlain>(tA, tB, tB, tD, *peers, p2, pair_tiles, stream);
       case TESSERA_SM100_F16:
-        return launch_pair_kernel<__half>(tA, tB, tD, *peers, p2, pair_tiles, stream);
+        return launch_pair_kernel<__half, kPlain>(tA, tB, tB, tD, *peers, p2, pair_tiles, stream);
       default: break;
     }
   }
@@ -292,6 +292,30 @@ int launch_grouped(const void* x, const void* w, const void* w2, const int* offs
   const long long max_tiles = ((long long)(T + BM - 1) / BM + E) * p.n_tiles;
   const int grid = (int)std::min<long long>(max_tiles, sm_count());
   static PeerMaps no_peers{};
+  // Enough rows for at least one wave of 256-row pair tiles: the CTA-pair kernel.
+  const long long max_pair_tiles = ((long long)(T + 2 * BM - 1) / (2 * BM) + E) * p.n_tiles;
+  if (pair_kernel_enabled() && (long long)(T / (2 * BM)) * p.n_tiles >= sm_count() / 2) {
+    Params p2 = p;
+    p2.idesc = make_idesc_f16(in_dtype == TESSERA_SM100_BF16, false, true, 2 * BM, BN);
+    if (swiglu) {
+      if (out_dtype == TESSERA_SM100_BF16)
+        return launch_pair_kernel<__nv_bfloat16, kGroupedSwiGLU>(tA, tB, tB2, tD, no_peers, p2,
+                                                                 max_pair_tiles, stream);
+      if (out_dtype == TESSERA_SM100_F16)
+        return launch_pair_kernel<__half, kGroupedSwiGLU>(tA, tB, tB2, tD, no_peers, p2,
+                                                          max_pair_tiles, stream);
+    } else {
+      if (out_dtype == TESSERA_SM100_F32)
+        return launch_pair_kernel<float, kGrouped>(tA, tB, tB2, tD, no_peers, p2, max_pair_tiles,
+                                                   stream);
+      if (out_dtype == TESSERA_SM100_BF16)
+        return launch_pair_kernel<__nv_bfloat16, kGrouped>(tA, tB, tB2, tD, no_peers, p2,
+                                                           max_pair_tiles, stream);
+      if (out_dtype == TESSERA_SM100_F16)
+        return launch_pair_kernel<__half, kGrouped>(tA, tB, tB2, tD, no_peers, p2, max_pair_tiles,
+                                                    stream);
+    }
+  }
   if (swiglu)
     return dispatch_out<kGroupedSwiGLU>(out_dtype, tA, tB, tB2, tD, no_peers, p, grid, stream);
   return dispatch_out<kGrouped>(out_dtype, tA, tB, tB2, tD, no_peers, p, grid, stream);

@@ -64,7 +64,10 @@ def test_routing_golden(golden_dir):
 
 
 @pytest.mark.parametrize("sizes,K,N", [([100, 0, 129, 33, 127], 192, 128), ([256, 128], 64, 256),
-                                       ([5, 300, 1, 0, 0, 700], 136, 520), ([0, 0, 7], 8, 8)])
+                                       ([5, 300, 1, 0, 0, 700], 136, 520), ([0, 0, 7], 8, 8),
+                                       # large enough for the CTA-pair kernel: ragged tails in both CTAs
+                                       # of a pair, an empty group, a group smaller than one CTA's rows
+                                       ([300, 0, 777, 100, 871], 136, 2568), ([256, 512, 1280], 64, 2560)])
 def test_grouped_gemm_and_swiglu(sizes, K, N):
     import tessera_b200 as tessera
     rng = np.random.default_rng(len(sizes) + K)

@@ -444,20 +444,32 @@ int gemm_host(const void* A, const void* B, void* D, int batch, int M, int N, in
   const long long Kp = round_up8(K), Np = round_up8(N);
   const size_t bytes = ((size_t)batch * M * K + (size_t)batch * K * N) * 2 + (size_t)batch * M * N * osz;
   // Chunk plan: rows of one matrix, or whole batch entries.
-  int chunks = 1, rows_per_chunk = M;
+  int chunks = 1;
+  int row_start[kMaxChunks + 1] = {0};  // row chunks: [row_start[c], row_start[c + 1])
   HostPipe* pipe = nullptr;
   if (bytes >= (size_t)(32u << 20) && (pipe = host_pipe()) != nullptr) {
     if (batch > 1) {
       chunks = std::min(batch, kMaxChunks);
     } else {
-      chunks = std::max(1, std::min({M / 1024, kMaxChunks, 16}));  // 8 chunks measured best at 8192^3
+      chunks = std::max(1, std::min({M / 820, kMaxChunks, 16}));  // 10 chunks at 8192 rows
       // Tuning override: TESSERA_SM100_HOST_GEMM_CHUNKS=<1..32> fixes the number of row chunks.
       if (const char* env = std::getenv("TESSERA_SM100_HOST_GEMM_CHUNKS")) {
         const int v = std::atoi(env);
         if (v >= 1) chunks = std::min({v, kMaxChunks, std::max(1, M / 128)});
       }
-      rows_per_chunk = (((M + chunks - 1) / chunks) + 127) / 128 * 128;
-      chunks = (M + rows_per_chunk - 1) / rows_per_chunk;
+      // Chunk sizes fall off linearly (weights c+1, c, ..., 2): what cannot overlap with anything is
+      // the GEMM and the download of the LAST chunk, so that one is small, while early chunks are
+      // large enough to keep per-chunk overheads off the upload stream. Multiples of 128 rows.
+      const long long wsum = (long long)chunks * (chunks + 3) / 2;
+      int n = 0, r = 0;
+      for (int c = 0; c < chunks && r < M; ++c) {
+        long long rows = (long long)M * (chunks + 1 - c) / wsum;
+        rows = std::max<long long>(128, (rows + 64) / 128 * 128);
+        r = (int)std::min<long long>(M, r + rows);
+        row_start[++n] = r;
+      }
+      row_start[n] = M;  // rounding leftovers go to the last chunk
+      chunks = n;
     }
   }
   void* pA = pool_alloc((size_t)batch * M * Kp * 2);
@@ -518,8 +530,8 @@ int gemm_host(const void* A, const void* B, void* D, int batch, int M, int N, in
         e0 = (int)((long long)batch * c / chunks);
         e1 = (int)((long long)batch * (c + 1) / chunks);
       } else {
-        r0 = c * rows_per_chunk;
-        r1 = std::min(M, r0 + rows_per_chunk);
+        r0 = row_start[c];
+        r1 = row_start[c + 1];
       }
       const long long a_off = (long long)e0 * M + r0;  // first row of A / D in this chunk
       const long long rows = batch > 1 ? (long long)(e1 - e0) * M : (r1 - r0);

@@ -26,7 +26,9 @@ import sys
 
 import numpy as np
 
-REF = os.environ.get("TESSERA_REFERENCE", "/root/reference")
+REF = os.environ.get("TESSERA_REFERENCE")
+if not REF or not os.path.isdir(os.path.join(REF, "python", "tessera")):
+    raise SystemExit("set TESSERA_REFERENCE to a checkout of the reference project (it is imported to make the fixtures)")
 sys.dont_write_bytecode = True
 sys.path.insert(0, os.path.join(REF, "python"))
 sys.path.insert(1, REF)

@@ -456,6 +456,56 @@ def bench_moe(ranks, args, peaks, peak_kind):
                          "peak_kind": f"sustained cuBLAS bf16 (two multi-ms GEMMs per step), of {peak_kind}"}}
 
 
+def bench_moe_fp8(ranks, args, peaks, peak_kind):
+    """The expert FFN of the MoE workload with e4m3 operands (quant="fp8_e4m3"): activations
+    quantised per tensor inside the timed step, expert weights quantised once beforehand (they are
+    static), gate/up GEMMs fused with silu_mul, hidden re-quantised, down GEMM. Single GPU."""
+    import ctypes
+    from tessera_b200 import _lib, device, ops
+    from tessera_b200.device import DeviceArray, bfloat16
+    if ranks.world != 1:
+        return {"skipped": "single-GPU workload"}
+    T, H, F, E, k = 8192, 4096, 14336, 8, 2
+    S = T * k
+    sizes = np.array([1994, 2066, 2065, 2092, 2074, 2036, 1965, 2092], np.int32)   # the seed-1005 routing
+    off = np.zeros(E + 1, np.int32)
+    off[1:] = np.cumsum(sizes)
+    rng = np.random.default_rng(1007)
+    xs = tiled_normal(rng, (S, H), 64, 1.0, bfloat16)
+    wg = tiled_normal(rng, (E, H, F), 1, 1 / np.sqrt(H), bfloat16)
+    wu = tiled_normal(rng, (E, H, F), 1, 1 / np.sqrt(H), bfloat16)
+    wd = tiled_normal(rng, (E, F, H), 1, 1 / np.sqrt(F), bfloat16)
+    gq, uq, dq = (ops.quantize_fp8_experts(w) for w in (wg, wu, wd))
+    dx, doff = DeviceArray.from_host(xs), DeviceArray.from_host(off)
+    xq, sx = DeviceArray((S, H), np.uint8), DeviceArray((3,), np.float32)
+    hidden, hq, sh = DeviceArray((S, F), np.float32), DeviceArray((S, F), np.uint8), DeviceArray((3,), np.float32)
+    amax = DeviceArray.zeros((1,), np.uint32)
+    out = DeviceArray((S, H), bfloat16)
+
+    def fn():
+        _lib.call("tessera_sm100_quantize_fp8_device", dx.ptr, S * H, _lib.BF16, xq.ptr, sx.ptr, None, None)
+        _lib.call("tessera_sm100_device_memset", amax.ptr, 0, 4, None)
+        _lib.call("tessera_sm100_grouped_swiglu_fp8_device", xq.ptr, gq.q.ptr, uq.q.ptr, doff.ptr, hidden.ptr, S, H,
+                  F, E, sx.ptr, gq.scales.ptr, uq.scales.ptr, _lib.F32, amax.ptr, None)
+        _lib.call("tessera_sm100_quantize_fp8_device", hidden.ptr, S * F, _lib.F32, hq.ptr, sh.ptr, amax.ptr, None)
+        _lib.call("tessera_sm100_grouped_gemm_fp8_device", hq.ptr, dq.q.ptr, doff.ptr, out.ptr, S, F, H, E, sh.ptr,
+                  dq.scales.ptr, _lib.BF16, None)
+
+    times = timed_steps(ranks, device, fn, max(2, args.steps // 2), min(args.warmup, 3))
+    ms = statistics.mean(times)
+    flops = 3 * 2.0 * S * H * F
+    ach = flops / ms / 1e9
+    return {"metric": "MoE expert FFN TFLOP/s, e4m3 operands (quant=fp8_e4m3)", "value": ach, "unit": "TFLOP/s",
+            "ms_per_step": ms,
+            "config": f"{S} routed slots in {E} ragged groups, H={H} F={F}; step = quantise x, fused gate/up GEMM + "
+                      f"silu_mul (fp32 hidden, so its quantisation matches the reference's), quantise hidden, down GEMM (weights "
+                      f"quantised once)",
+            "roofline": {"bound": "tensor", "achieved": ach, "peak": 2 * peaks["bf16_tflops_sustained"],
+                         "unit": "TFLOP/s", "frac": ach / (2 * peaks["bf16_tflops_sustained"]), "traffic": None,
+                         "peak_kind": f"2 x sustained cuBLAS bf16 (no fp8 peak was measured: the dense fp8 rate is "
+                                      f"nominally twice the bf16 rate), of {peak_kind}"}}
+
+
 # ------------------------------------------------------------------------------ CPU baseline
 def cpu_gemm_baseline(target_seconds: float = 10.0, max_reps: int = 10):
     from oracle import tessera_oracle as orc
@@ -578,7 +628,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="all", choices=["all", "gemm", "attn_prefill", "attn_decode", "attn_decode_paged", "moe"])
+    ap.add_argument("--workload", default="all", choices=["all", "gemm", "attn_prefill", "attn_decode", "attn_decode_paged", "moe", "moe_fp8"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tp-mode", default="fused", choices=["fused", "nccl"],
                     help="N>1 GEMM: all-gather fused into the epilogue (peer TMA stores) or NCCL after it")
@@ -612,9 +662,10 @@ def main():
 
     g = bench_gemm(ranks, args, peaks, peak_kind, sampler)
     extras = {}
-    if args.workload in ("all", "attn_prefill", "attn_decode", "attn_decode_paged", "moe"):
+    if args.workload in ("all", "attn_prefill", "attn_decode", "attn_decode_paged", "moe", "moe_fp8"):
         for name, fn in (("attn_prefill", bench_attn_prefill), ("attn_decode", bench_attn_decode),
-                         ("attn_decode_paged", bench_attn_decode_paged), ("moe", bench_moe)):
+                         ("attn_decode_paged", bench_attn_decode_paged), ("moe", bench_moe),
+                         ("moe_fp8", bench_moe_fp8)):
             if args.workload not in ("all", name):
                 continue
             try:

@@ -130,6 +130,41 @@ int tessera_sm100_grouped_swiglu_device(const void* x, const void* w_gate, const
                                         const int* offsets, void* out, int T, int K, int F, int E,
                                         int in_dtype, int out_dtype, void* stream);
 
+/* ---- fp8 (e4m3) operands -------------------------------------------------------------------
+ * The quantised grouped GEMM of tessera.ops.grouped_gemm(..., quant="fp8_e4m3")
+ * (python/tessera/__init__.py:337-342; python/tessera/compiler/grouped_layout.py:353-392): the
+ * reference quantises x per tensor and each expert's weights per expert with quantize_fp8
+ * (python/tessera/__init__.py:3340-3374), dequantises on the host and runs an f32 GEMM. Here the
+ * e4m3 bytes go to the tensor cores (tcgen05 kind::f8f6f4, f32 accumulate) and the two scales are
+ * applied in the epilogue; the result differs from the reference's only by fp32 summation order.
+ *
+ * tessera_sm100_quantize_fp8_device: x (n elements of `dtype`) -> q (n bytes). scale_out holds 3
+ * device floats: [0] scale = max(amax/448, 1e-12), [1] amax, [2] scratch. amax_in (optional): a
+ * device uint32 with the bits of a known amax, which skips the reduction pass.
+ * tessera_sm100_quantize_fp8_weights_device: w [E,K,N] -> q_t [E,N,K] (TRANSPOSED: both GEMM
+ * operands are K-major), one scale per expert; scales holds 3E device floats: [0,E) scales,
+ * [E,2E) amax, [2E,3E) scratch. Weights are static: quantise once, reuse.
+ * GEMMs: xq [T,K] / Aq [M,K] bytes, wq_t [E,N,K] / Bq_t [N,K] bytes, K a multiple of 16, N of 8;
+ * scale_x one device float, scale_w one per expert. The SwiGLU form writes the 16-bit hidden
+ * activation silu(x Wg) * (x Wu) and, when amax_out is given (device uint32, zeroed by the
+ * caller), max |hidden| as stored, ready for the next quantisation. */
+int tessera_sm100_quantize_fp8_device(const void* x, long long n, int dtype, void* q,
+                                      float* scale_out, const unsigned int* amax_in, void* stream);
+int tessera_sm100_quantize_fp8_weights_device(const void* w, int E, int K, int N, int dtype,
+                                              void* q_t, float* scales, void* stream);
+int tessera_sm100_gemm_fp8_device(const void* Aq, const void* Bq_t, void* D, int M, int N, int K,
+                                  const float* scale_a, const float* scale_b, int out_dtype,
+                                  void* stream);
+int tessera_sm100_grouped_gemm_fp8_device(const void* xq, const void* wq_t, const int* offsets,
+                                          void* out, int T, int K, int N, int E,
+                                          const float* scale_x, const float* scale_w,
+                                          int out_dtype, void* stream);
+int tessera_sm100_grouped_swiglu_fp8_device(const void* xq, const void* wgq_t, const void* wuq_t,
+                                            const int* offsets, void* hidden, int T, int K, int F,
+                                            int E, const float* scale_x, const float* scale_wg,
+                                            const float* scale_wu, int out_dtype,
+                                            unsigned int* amax_out, void* stream);
+
 /* ---- MoE layer pieces --------------------------------------------------------------------
  * Router: top-k over f32 gate logits [T,E]; selection order and tie rule of route_tokens
  * (python/tessera/distributed/moe.py:160-172: descending, the higher expert index first on a

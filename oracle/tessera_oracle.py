@@ -238,6 +238,36 @@ def softmax_finalize(o, l) -> np.ndarray:
     return np.asarray(o / l[..., None], dtype=np.float32)
 
 
+# ----------------------------------------------------------------------------- fp8 quantisation
+def quantize_fp8(x):
+    """Per-tensor symmetric e4m3 quantisation, returned dequantised: ``scale = max(amax/448,
+    1e-12)``, ``q = e4m3(clip(x/scale, -448, 448))``, result ``q * scale`` and ``scale``, all in
+    float32 (python/tessera/__init__.py:3340-3374)."""
+    x = np.asarray(x, np.float32)
+    amax = np.max(np.abs(x)) if x.size else np.float32(0)
+    scale = np.float32(np.maximum(np.float32(amax) / np.float32(448.0), np.float32(1e-12)))
+    scaled = np.clip(x / scale, -448.0, 448.0)
+    q = scaled.astype(ml_dtypes.float8_e4m3fn).astype(np.float32)
+    return (q * scale).astype(np.float32), scale
+
+
+def grouped_gemm_fp8(x, w, group_sizes) -> np.ndarray:
+    """``grouped_gemm(..., quant="fp8_e4m3")``: x quantised per tensor, each expert's weights per
+    expert, then the f32 grouped GEMM (python/tessera/__init__.py:337-351,
+    python/tessera/compiler/grouped_layout.py:371-392)."""
+    xq = quantize_fp8(_f32(x))[0]
+    wq = np.stack([quantize_fp8(_f32(w)[e])[0] for e in range(np.asarray(w).shape[0])])
+    return grouped_gemm(xq, wq, group_sizes)
+
+
+def moe_swiglu_block_fp8(x, w_gate, w_up, w_down, group_sizes) -> np.ndarray:
+    """``moe_swiglu_block(..., quant="fp8_e4m3")``: every grouped GEMM of the block quantises its
+    operands (python/tessera/__init__.py:592-616)."""
+    gate = grouped_gemm_fp8(x, w_gate, group_sizes)
+    up = grouped_gemm_fp8(x, w_up, group_sizes)
+    return grouped_gemm_fp8(silu_mul(gate, up), w_down, group_sizes)
+
+
 # ----------------------------------------------------------------------------- paged KV
 def paged_pack(k, v, page_size: int):
     """Tokens ``[n, H, D]`` -> identity-mapped pages ``[P, L, H, D]`` + table

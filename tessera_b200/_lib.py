@@ -124,6 +124,13 @@ _SIGNATURES = {
     "tessera_sm100_flash_attn_general_device": (c_int, [_VP, _VP, _VP, _VP, _VP, c_longlong, c_int, c_int,
                                                         c_longlong, c_longlong, c_int, c_int, c_float, c_int,
                                                         c_longlong, c_longlong, c_longlong, c_float, c_int, _VP]),
+    "tessera_sm100_quantize_fp8_device": (c_int, [_VP, c_longlong, c_int, _VP, _VP, _VP, _VP]),
+    "tessera_sm100_quantize_fp8_weights_device": (c_int, [_VP, c_int, c_int, c_int, c_int, _VP, _VP, _VP]),
+    "tessera_sm100_gemm_fp8_device": (c_int, [_VP, _VP, _VP, c_int, c_int, c_int, _VP, _VP, c_int, _VP]),
+    "tessera_sm100_grouped_gemm_fp8_device": (c_int, [_VP, _VP, _VP, _VP, c_int, c_int, c_int, c_int, _VP, _VP,
+                                                      c_int, _VP]),
+    "tessera_sm100_grouped_swiglu_fp8_device": (c_int, [_VP, _VP, _VP, _VP, _VP, c_int, c_int, c_int, c_int,
+                                                        _VP, _VP, _VP, c_int, _VP, _VP]),
     "tessera_sm100_paged_attn_decode_device": (c_int, [_VP, _VP, _VP, _VP, _VP, _VP, c_int, c_int, c_int,
                                                        c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                                                        _VP, _VP]),

@@ -115,7 +115,7 @@ struct PairWalker {
   }
 };
 
-template <typename OutT, int kMode>
+template <typename OutT, int kMode, bool kFp8 = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
              const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmD,
@@ -142,7 +142,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   const uint32_t rank = cluster_ctarank();  // 0 = even CTA (issues the MMAs), 1 = its peer
   const int cluster_id = blockIdx.x >> 1;
   const int num_clusters = gridDim.x >> 1;
-  const int num_kb = (p.K + BK - 1) / BK;
+  constexpr int kBKe = kFp8 ? 2 * BK : BK;  // K elements per stage
+  const int num_kb = (p.K + kBKe - 1) / kBKe;
   constexpr int kOutW = (kMode == kGroupedSwiGLU) ? BN / 2 : BN;  // output columns per tile
   constexpr int kChunk = (sizeof(OutT) == 4) ? 32 : 64;            // output columns per store
 
@@ -197,13 +198,18 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             break;
           }
           if (rank == 0) mbar_arrive_expect_tx(full_bar(stage), PAIR_TX_BYTES);
-          const int k0 = kb * BK;
+          const int k0 = kb * kBKe;
           tma_load_3d_2cta(sA + stage * A_STAGE_BYTES, &tmA, full_bar(stage), k0, my_m0, a_b);
           const uint32_t b_dst = sB + stage * B_STAGE_BYTES;
+          if constexpr (kFp8) {
+            // this CTA's 128 rows of Bt[N,K]: one box of 128 rows x 128 B
+            tma_load_3d_2cta(b_dst, my_b, full_bar(stage), k0, my_n0, tile.b);
+          } else {
 #pragma unroll
-          for (int j = 0; j < 2; ++j)
-            tma_load_3d_2cta(b_dst + j * B_BLOCK_BYTES, my_b, full_bar(stage), my_n0 + 64 * j, k0,
-                             tile.b);
+            for (int j = 0; j < 2; ++j)
+              tma_load_3d_2cta(b_dst + j * B_BLOCK_BYTES, my_b, full_bar(stage), my_n0 + 64 * j, k0,
+                               tile.b);
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
@@ -223,7 +229,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       bool ok = true;
       const uint32_t desc_hi = smem_desc_hi(1024);
       const uint32_t a_lo0 = smem_desc_lo(sA, 16);
-      const uint32_t b_lo0 = smem_desc_lo(sB, B_BLOCK_BYTES);
+      const uint32_t b_lo0 = smem_desc_lo(sB, kFp8 ? 16 : B_BLOCK_BYTES);
       while (ok && walk.next(p, tile)) {
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.err, kErrWaitTmemEmpty)) {
           ok = false;
@@ -240,9 +246,14 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
           const uint32_t a_lo = a_lo0 + stage * (A_STAGE_BYTES >> 4);
           const uint32_t b_lo = b_lo0 + stage * (B_STAGE_BYTES >> 4);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)
-            umma_f16_ss_parts_2cta(d_tmem, a_lo + k * 2, desc_hi, b_lo + k * 128, desc_hi, p.idesc,
-                                   (kb > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < 4; ++k) {
+            if constexpr (kFp8)
+              umma_f8_ss_parts_2cta(d_tmem, a_lo + k * 2, desc_hi, b_lo + k * 2, desc_hi, p.idesc,
+                                    (kb > 0 || k > 0) ? 1u : 0u);
+            else
+              umma_f16_ss_parts_2cta(d_tmem, a_lo + k * 2, desc_hi, b_lo + k * 128, desc_hi, p.idesc,
+                                     (kb > 0 || k > 0) ? 1u : 0u);
+          }
           umma_commit_2cta(empty_bar(stage), 3);  // this stage is free again in both CTAs
           if (++stage == STAGES) {
             stage = 0;
@@ -279,6 +290,13 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       const bool warp_has_rows = (kMode == kPlain) ? (row0 < p.M) : (rows_w > 0);
       const uint32_t t_acc = tmem_base + static_cast<uint32_t>(acc * BN) + lane_base;
       constexpr int kChunks = kOutW / kChunk;
+      float sc = 1.f, sc2 = 1.f, amax = 0.f;  // dequantisation scales of this tile (fp8 operands)
+      if constexpr (kFp8) {
+        const float sa = __ldg(p.scale_a);
+        sc = sa * __ldg(p.scale_b + tile.b);
+        if constexpr (kMode == kGroupedSwiGLU) sc2 = sa * __ldg(p.scale_b2 + tile.b);
+      }
+      (void)sc2;
       bool released = false;
 #pragma unroll 1
       for (int c = 0; c < kChunks; ++c) {
@@ -288,18 +306,19 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         if (lane == 0) tma_store_wait_read<1>();
         __syncwarp();
         if constexpr (kMode == kGroupedSwiGLU) {
-          // kChunk == 64 (16-bit output): two halves of 32 output columns each.
+          // kChunk output columns (64 for 16-bit, 32 for fp32) in halves of 32.
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
+          for (int h = 0; h < kChunk / 32; ++h) {
             uint32_t g[32], u[32];
-            tmem_ld_32x32b_x32(t_acc + c * 64 + h * 32, g);
-            tmem_ld_32x32b_x32(t_acc + (BN / 2) + c * 64 + h * 32, u);
+            tmem_ld_32x32b_x32(t_acc + c * kChunk + h * 32, g);
+            tmem_ld_32x32b_x32(t_acc + (BN / 2) + c * kChunk + h * 32, u);
             tmem_ld_wait();
             float v[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              v[j] = gemm::silu_mul(__uint_as_float(g[j]), __uint_as_float(u[j]));
-            gemm::stage_row32<OutT>(buf, lane, h * 64, v);
+              v[j] = gemm::silu_mul(__uint_as_float(g[j]) * sc, __uint_as_float(u[j]) * sc2);
+            if constexpr (kFp8) amax = fmaxf(amax, gemm::stored_amax32<OutT>(v));
+            gemm::stage_row32<OutT>(buf, lane, h * 32 * sizeof(OutT), v);
           }
         } else {
 #pragma unroll
@@ -309,11 +328,12 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             tmem_ld_wait();
             float v[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * sc;
             if constexpr (kMode == kPlain) {
               if (p.bias || p.residual || p.activation)
                 gemm::apply_epilogue<OutT>(v, p, row0 + lane, col0 + h * 32);
             }
+            if constexpr (kFp8) amax = fmaxf(amax, gemm::stored_amax32<OutT>(v));
             gemm::stage_row32<OutT>(buf, lane, h * 32 * sizeof(OutT), v);
           }
         }
@@ -365,6 +385,13 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_even_cta(tempty_bar(acc));
+      }
+      if constexpr (kFp8) {
+        const bool lane_valid = (kMode == kPlain) ? (row0 + lane < p.M) : (lane < rows_w);
+        float a = lane_valid ? amax : 0.f;
+#pragma unroll
+        for (int sh = 16; sh; sh >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, sh));
+        if (p.amax_out && lane == 0 && a > 0.f) atomicMax(p.amax_out, __float_as_uint(a));
       }
       if (++acc == 2) {
         acc = 0;

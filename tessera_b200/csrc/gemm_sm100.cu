@@ -572,12 +572,169 @@ int gemm_host(const void* A, const void* B, void* D, int batch, int M, int N, in
   return rc;
 }
 
+// fp8 (e4m3) operands, both K-major: Aq[T or M, K] bytes and Bq_t[E or 1][N, K] bytes (B
+// transposed). offsets == nullptr: one dense product (batch 1); otherwise ragged groups, with
+// `swiglu` the fused gate/up form (Bq2_t = up weights). scale_a: one device float; scale_b /
+// scale_b2: one device float per group. amax_out (optional, device uint32 zeroed by the caller)
+// receives max |out| as stored.
+template <typename OutT, int kMode>
+int launch_fp8_kernel(bool pairs, const CUtensorMap& tA, const CUtensorMap& tB,
+                      const CUtensorMap& tB2, const CUtensorMap& tD, const Params& p,
+                      long long tiles, cudaStream_t stream) {
+  static PeerMaps no_peers{};
+  if (pairs) {
+    TSB_CUDA_OK(cudaFuncSetAttribute(gemm2::gemm2_kernel<OutT, kMode, true>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     gemm2::SMEM_ALLOC));
+    cudaLaunchConfig_t cfg{};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3(gemm2::NUM_THREADS);
+    cfg.dynamicSmemBytes = gemm2::SMEM_ALLOC;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const int clusters = (int)std::min<long long>(tiles, sm_count() / 2);
+    cfg.gridDim = dim3(2 * clusters);
+    TSB_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm2::gemm2_kernel<OutT, kMode, true>, tA, tB, tB2, tD,
+                                   no_peers, p));
+  } else {
+    TSB_CUDA_OK(cudaFuncSetAttribute(gemm_kernel<OutT, kMode, true>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));
+    const int grid = (int)std::min<long long>(tiles, sm_count());
+    gemm_kernel<OutT, kMode, true><<<grid, NUM_THREADS, SMEM_ALLOC, stream>>>(tA, tB, tB2, tD,
+                                                                               no_peers, p);
+    TSB_CUDA_OK(cudaGetLastError());
+  }
+  note_launch();
+  return kOk;
+}
+
+int launch_fp8(const void* Aq, const void* Bq_t, const void* Bq2_t, const int* offsets, void* out,
+               int T, int K, int N, int E, const float* scale_a, const float* scale_b,
+               const float* scale_b2, int out_dtype, bool swiglu, unsigned int* amax_out,
+               cudaStream_t stream) {
+  const bool grouped = offsets != nullptr;
+  if (!Aq || !Bq_t || !out || !scale_a || !scale_b || (swiglu && (!Bq2_t || !scale_b2 || !grouped)) ||
+      T < 0 || K <= 0 || N <= 0 || E <= 0) {
+    set_last_error("gemm_fp8: null pointer or bad size (T %d K %d N %d E %d)", T, K, N, E);
+    return kBadArg;
+  }
+  if (T == 0) return kOk;
+  const size_t osz = out_size(out_dtype);
+  if ((K % 16) || (N % 8) || !aligned16(Aq) || !aligned16(Bq_t) || !aligned16(out) ||
+      (swiglu && !aligned16(Bq2_t))) {
+    set_last_error("gemm_fp8: K must be a multiple of 16, N of 8, pointers 16-byte aligned");
+    return kBadArg;
+  }
+  CUtensorMap tA, tB, tB2, tD;
+  {
+    uint64_t dims[3] = {(uint64_t)K, (uint64_t)T, 1};
+    uint64_t str[2] = {(uint64_t)K, (uint64_t)T * K};
+    uint32_t box[3] = {128, BM, 1};
+    if (!encode_tmap(&tA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, Aq, dims, str, box,
+                     CU_TENSOR_MAP_SWIZZLE_128B))
+      return kBadArg;
+  }
+  {
+    uint64_t dims[3] = {(uint64_t)K, (uint64_t)N, (uint64_t)E};
+    uint64_t str[2] = {(uint64_t)K, (uint64_t)N * K};
+    uint32_t box[3] = {128, 128, 1};
+    if (!encode_tmap(&tB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, Bq_t, dims, str, box,
+                     CU_TENSOR_MAP_SWIZZLE_128B))
+      return kBadArg;
+    tB2 = tB;
+    if (swiglu && !encode_tmap(&tB2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, Bq2_t, dims, str, box,
+                               CU_TENSOR_MAP_SWIZZLE_128B))
+      return kBadArg;
+  }
+  {
+    uint64_t dims[3] = {(uint64_t)N, (uint64_t)T, 1};
+    uint64_t str[2] = {(uint64_t)N * osz, (uint64_t)T * N * osz};
+    uint32_t box[3] = {(uint32_t)(128 / osz), 32, 1};
+    if (!encode_tmap(&tD, tm_dtype(out_dtype), 3, out, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return kBadArg;
+  }
+  Params p{};
+  p.M = T;
+  p.N = N;
+  p.K = K;
+  p.batch = grouped ? E : 1;
+  const int out_w = swiglu ? BN / 2 : BN;
+  p.m_tiles = grouped ? 0 : (T + BM - 1) / BM;
+  p.n_tiles = (N + out_w - 1) / out_w;
+  p.group_offsets = offsets;
+  p.D = out;
+  p.ldd = N;
+  p.scale_a = scale_a;
+  p.scale_b = scale_b;
+  p.scale_b2 = scale_b2;
+  p.amax_out = amax_out;
+  p.err = device_err_word();
+  if (!p.err) return kDeviceFailed;
+  const bool pairs = pair_kernel_enabled() && (long long)(T / (2 * BM)) * p.n_tiles >= sm_count() / 2;
+  p.idesc = make_idesc_f8(pairs ? 2 * BM : BM, BN);
+  const long long tiles =
+      pairs ? ((long long)(T + 2 * BM - 1) / (2 * BM) + (grouped ? E : 0)) * p.n_tiles
+            : ((long long)(T + BM - 1) / BM + (grouped ? E : 0)) * p.n_tiles;
+#define TSB_FP8_CASE(OUT, MODE) return launch_fp8_kernel<OUT, MODE>(pairs, tA, tB, tB2, tD, p, tiles, stream)
+  if (swiglu) {
+    if (out_dtype == TESSERA_SM100_F32) TSB_FP8_CASE(float, kGroupedSwiGLU);
+    if (out_dtype == TESSERA_SM100_BF16) TSB_FP8_CASE(__nv_bfloat16, kGroupedSwiGLU);
+    if (out_dtype == TESSERA_SM100_F16) TSB_FP8_CASE(__half, kGroupedSwiGLU);
+  } else if (grouped) {
+    if (out_dtype == TESSERA_SM100_F32) TSB_FP8_CASE(float, kGrouped);
+    if (out_dtype == TESSERA_SM100_BF16) TSB_FP8_CASE(__nv_bfloat16, kGrouped);
+    if (out_dtype == TESSERA_SM100_F16) TSB_FP8_CASE(__half, kGrouped);
+  } else {
+    if (out_dtype == TESSERA_SM100_F32) TSB_FP8_CASE(float, kPlain);
+    if (out_dtype == TESSERA_SM100_BF16) TSB_FP8_CASE(__nv_bfloat16, kPlain);
+    if (out_dtype == TESSERA_SM100_F16) TSB_FP8_CASE(__half, kPlain);
+  }
+#undef TSB_FP8_CASE
+  set_last_error("gemm_fp8: unsupported output dtype %d", out_dtype);
+  return kBadArg;
+}
+
 }  // namespace gemm
 }  // namespace tsb
 
 using namespace tsb;
 
 extern "C" {
+
+int tessera_sm100_gemm_fp8_device(const void* Aq, const void* Bq_t, void* D, int M, int N, int K,
+                                  const float* scale_a, const float* scale_b, int out_dtype,
+                                  void* stream) {
+  return gemm::launch_fp8(Aq, Bq_t, nullptr, nullptr, D, M, K, N, 1, scale_a, scale_b, nullptr,
+                          out_dtype, false, nullptr, static_cast<cudaStream_t>(stream));
+}
+int tessera_sm100_grouped_gemm_fp8_device(const void* xq, const void* wq_t, const int* offsets,
+                                          void* out, int T, int K, int N, int E,
+                                          const float* scale_x, const float* scale_w,
+                                          int out_dtype, void* stream) {
+  if (!offsets) {
+    set_last_error("grouped_gemm_fp8: null offsets");
+    return kBadArg;
+  }
+  return gemm::launch_fp8(xq, wq_t, nullptr, offsets, out, T, K, N, E, scale_x, scale_w, nullptr,
+                          out_dtype, false, nullptr, static_cast<cudaStream_t>(stream));
+}
+int tessera_sm100_grouped_swiglu_fp8_device(const void* xq, const void* wgq_t, const void* wuq_t,
+                                            const int* offsets, void* hidden, int T, int K, int F,
+                                            int E, const float* scale_x, const float* scale_wg,
+                                            const float* scale_wu, int out_dtype,
+                                            unsigned int* amax_out, void* stream) {
+  if (!offsets) {
+    set_last_error("grouped_swiglu_fp8: null offsets");
+    return kBadArg;
+  }
+  return gemm::launch_fp8(xq, wgq_t, wuq_t, offsets, hidden, T, K, F, E, scale_x, scale_wg, scale_wu,
+                          out_dtype, true, amax_out, static_cast<cudaStream_t>(stream));
+}
 
 int tessera_sm100_mma_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K) {
   return gemm::gemm_host(A, B, D, 1, M, N, K, TESSERA_SM100_BF16, TESSERA_SM100_F32);

@@ -11,6 +11,11 @@
 // 64 x 256 (N-major: four [64 k][64 n] 128-byte-swizzled blocks of 8 KB). Each 64-deep stage
 // feeds four tcgen05.mma (M128 N256 K16).
 //
+// With kFp8 the operands are e4m3 bytes, both K-major: A[M,K] as before and B given TRANSPOSED as
+// Bt[N,K] (per batch / expert), a stage covers 128 elements of K (same bytes: A 16 KB, B 32 KB as
+// 256 rows of 128 B), the MMA is kind::f8f6f4 (K 32 per instruction) and the epilogue applies the
+// dequantisation scales. Everything else — ring, barriers, tile walk, epilogue paths — is shared.
+//
 // Three tile sources share the kernel:
 //   kPlain          batched dense GEMM (TMA clips ragged edges)
 //   kGrouped        ragged grouped GEMM: rows of group e (contiguous, from `group_offsets`)
@@ -62,6 +67,13 @@ struct Params {
   const void* residual;      // [M, N] in the output dtype, leading dimension ldr, or null
   long long ldr;
   int activation;            // 0 none, 1 relu, 2 gelu (tanh form), 3 silu
+  // fp8 operands (kFp8): D = (A_q * B_q) * scale_a[0] * scale_b[group or batch index]; the SwiGLU
+  // mode scales the up half with scale_b2. amax_out (optional) receives max |D| of the values as
+  // stored (bit pattern of a non-negative float, combined with atomicMax).
+  const float* scale_a;
+  const float* scale_b;
+  const float* scale_b2;
+  unsigned int* amax_out;
   int* err;
 };
 
@@ -184,11 +196,20 @@ __device__ __forceinline__ void apply_epilogue(float (&v)[32], const Params& p, 
   }
 }
 
+// max |x| over 32 values after rounding to the stored type (what a later quantisation will see).
+template <typename OutT>
+__device__ __forceinline__ float stored_amax32(const float (&v)[32]) {
+  float a = 0.f;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) a = fmaxf(a, fabsf(static_cast<float>(static_cast<OutT>(v[j]))));
+  return a;
+}
+
 __device__ __forceinline__ float silu_mul(float g, float u) {
   return __fdividef(g, 1.0f + __expf(-g)) * u;
 }
 
-template <typename OutT, int kMode>
+template <typename OutT, int kMode, bool kFp8 = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmD,
@@ -213,7 +234,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_kb = (p.K + BK - 1) / BK;
+  constexpr int kBKe = kFp8 ? 2 * BK : BK;  // K elements per stage (128 bytes of K either way)
+  const int num_kb = (p.K + kBKe - 1) / kBKe;
   constexpr int kOutW = (kMode == kGroupedSwiGLU) ? BN / 2 : BN;   // output columns per tile
   constexpr int kChunk = (sizeof(OutT) == 4) ? 32 : 64;            // output columns per store
 
@@ -259,11 +281,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             break;
           }
           mbar_arrive_expect_tx(full_bar(stage), STAGE_TX_BYTES);
-          const int k0 = kb * BK;
+          const int k0 = kb * kBKe;
           const int a_b = (kMode == kPlain) ? tile.b : 0;
           tma_load_3d(sA + stage * A_STAGE_BYTES, &tmA, full_bar(stage), k0, tile.m0, a_b);
           const uint32_t b_dst = sB + stage * B_STAGE_BYTES;
-          if constexpr (kMode == kGroupedSwiGLU) {
+          if constexpr (kFp8) {
+            // Bt[N,K]: two boxes of 128 rows x 128 B. SwiGLU: gate rows, then the same rows of up.
+            const CUtensorMap* second = (kMode == kGroupedSwiGLU) ? &tmB2 : &tmB;
+            const int n1 = (kMode == kGroupedSwiGLU) ? tile.n0 : tile.n0 + 128;
+            tma_load_3d(b_dst, &tmB, full_bar(stage), k0, tile.n0, tile.b);
+            tma_load_3d(b_dst + B_STAGE_BYTES / 2, second, full_bar(stage), k0, n1, tile.b);
+          } else if constexpr (kMode == kGroupedSwiGLU) {
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
               tma_load_3d(b_dst + j * B_BLOCK_BYTES, &tmB, full_bar(stage), tile.n0 + 64 * j, k0,
@@ -296,7 +324,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       bool ok = true;
       const uint32_t desc_hi = smem_desc_hi(1024);
       const uint32_t a_lo0 = smem_desc_lo(sA, 16);
-      const uint32_t b_lo0 = smem_desc_lo(sB, B_BLOCK_BYTES);
+      const uint32_t b_lo0 = smem_desc_lo(sB, kFp8 ? 16 : B_BLOCK_BYTES);
       while (ok && walk.next(p, tile)) {
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.err, kErrWaitTmemEmpty)) {
           ok = false;
@@ -316,9 +344,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const uint32_t a_lo = a_lo0 + stage * (A_STAGE_BYTES >> 4);
           const uint32_t b_lo = b_lo0 + stage * (B_STAGE_BYTES >> 4);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)
-            umma_f16_ss_parts(d_tmem, a_lo + k * 2, desc_hi, b_lo + k * 128, desc_hi, p.idesc,
-                              (kb > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < 4; ++k) {
+            // 32 bytes of K per step in a K-major operand; 16 k-rows = 2048 B in the N-major B.
+            if constexpr (kFp8)
+              umma_f8_ss_parts(d_tmem, a_lo + k * 2, desc_hi, b_lo + k * 2, desc_hi, p.idesc,
+                               (kb > 0 || k > 0) ? 1u : 0u);
+            else
+              umma_f16_ss_parts(d_tmem, a_lo + k * 2, desc_hi, b_lo + k * 128, desc_hi, p.idesc,
+                                (kb > 0 || k > 0) ? 1u : 0u);
+          }
           umma_commit(empty_bar(stage));
           if (++stage == STAGES) {
             stage = 0;
@@ -354,6 +388,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const bool warp_has_rows = (kMode == kPlain) ? (row0 < p.M) : (rows_w > 0);
       const uint32_t t_acc = tmem_base + static_cast<uint32_t>(acc * BN) + lane_base;
       constexpr int kChunks = kOutW / kChunk;
+      // dequantisation scales of this tile (1 when the operands are 16-bit)
+      float sc = 1.f, sc2 = 1.f, amax = 0.f;
+      if constexpr (kFp8) {
+        const float sa = __ldg(p.scale_a);
+        sc = sa * __ldg(p.scale_b + tile.b);
+        if constexpr (kMode == kGroupedSwiGLU) sc2 = sa * __ldg(p.scale_b2 + tile.b);
+      }
+      (void)sc2;
       bool wide_done = false;
       if constexpr (kMode == kPlain && sizeof(OutT) == 2) {
         if (p.num_peers > 0) {
@@ -416,17 +458,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (lane == 0) tma_store_wait_read<1>();
         __syncwarp();
         if constexpr (kMode == kGroupedSwiGLU) {
-          // kChunk == 64 (16-bit output): two halves of 32 output columns each.
+          // kChunk output columns (64 for 16-bit, 32 for fp32) in halves of 32.
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
+          for (int h = 0; h < kChunk / 32; ++h) {
             uint32_t g[32], u[32];
-            tmem_ld_32x32b_x32(t_acc + c * 64 + h * 32, g);
-            tmem_ld_32x32b_x32(t_acc + (BN / 2) + c * 64 + h * 32, u);
+            tmem_ld_32x32b_x32(t_acc + c * kChunk + h * 32, g);
+            tmem_ld_32x32b_x32(t_acc + (BN / 2) + c * kChunk + h * 32, u);
             tmem_ld_wait();
             float v[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = silu_mul(__uint_as_float(g[j]), __uint_as_float(u[j]));
-            stage_row32<OutT>(buf, lane, h * 64, v);
+            for (int j = 0; j < 32; ++j)
+              v[j] = silu_mul(__uint_as_float(g[j]) * sc, __uint_as_float(u[j]) * sc2);
+            if constexpr (kFp8) amax = fmaxf(amax, stored_amax32<OutT>(v));
+            stage_row32<OutT>(buf, lane, h * 32 * sizeof(OutT), v);
           }
         } else {
 #pragma unroll
@@ -436,11 +480,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             tmem_ld_wait();
             float v[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * sc;
             if constexpr (kMode == kPlain) {
               if (p.bias || p.residual || p.activation)
                 apply_epilogue<OutT>(v, p, row0 + lane, col0 + h * 32);
             }
+            if constexpr (kFp8) amax = fmaxf(amax, stored_amax32<OutT>(v));
             stage_row32<OutT>(buf, lane, h * 32 * sizeof(OutT), v);
           }
         }
@@ -495,6 +540,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (lane == 0) mbar_arrive(tempty_bar(acc));
       }
       (void)m_limit;
+      if constexpr (kFp8) {
+        // rows beyond the valid range hold products of foreign rows: only lanes with a valid row count
+        const bool lane_valid = (kMode == kPlain) ? (row0 + lane < p.M) : (lane < rows_w);
+        float a = lane_valid ? amax : 0.f;
+#pragma unroll
+        for (int sh = 16; sh; sh >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, sh));
+        if (p.amax_out && lane == 0 && a > 0.f) atomicMax(p.amax_out, __float_as_uint(a));
+      }
       if (++acc == 2) {
         acc = 0;
         acc_phase ^= 1u;

@@ -226,6 +226,28 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
                    bar)
                : "memory");
 }
+// 8-bit float operands (kind::f8f6f4, K = 32 per instruction), both operands from shared memory.
+__device__ __forceinline__ void umma_f8_ss_parts(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi,
+                                                 uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 da, db;\n"
+      "mov.b64 da, {%1, %2};\n"
+      "mov.b64 db, {%3, %4};\n"
+      "setp.ne.b32 p, %6, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %5, p;\n"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Instruction descriptor for kind::f8f6f4 with e4m3 A and B, both K-major, f32 accumulate
+// (format code 0 = e4m3 in the A and B format fields).
+__host__ __device__ constexpr uint32_t make_idesc_f8(int m, int n) {
+  return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
 // ---------------------------------------------------------------- CTA pairs (cta_group::2)
 // Two CTAs of a cluster (ranks 2i and 2i+1) drive one M = 256 MMA: each holds its 128 rows of A,
 // its half of the B columns and its 128 accumulator lanes; the even CTA issues. Shared-memory
@@ -268,6 +290,21 @@ __device__ __forceinline__ void umma_f16_ss_parts_2cta(uint32_t d_tmem, uint32_t
       "mov.b64 db, {%3, %4};\n"
       "setp.ne.b32 p, %6, 0;\n"
       "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f8_ss_parts_2cta(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi,
+                                                      uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                                      uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 da, db;\n"
+      "mov.b64 da, {%1, %2};\n"
+      "mov.b64 db, {%3, %4};\n"
+      "setp.ne.b32 p, %6, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], da, db, %5, p;\n"
       "}\n"
       ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
       : "memory");

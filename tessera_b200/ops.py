@@ -402,24 +402,106 @@ def _group_offsets(group_sizes, T: int, op: str) -> np.ndarray:
     return off
 
 
+_FP8_QUANTS = ("fp8", "fp8_e4m3")
+_OTHER_QUANTS = ("fp8_e5m2", "nvfp4", "fp8xfp4", "fp8_e4m3xnvfp4", "fp8_e5m2xnvfp4")
+
+
 def _check_kind(kind: str, alignment, group_sizes, quant, op: str) -> None:
     if kind not in GROUPED_KINDS:
         raise ValueError(f"{op}: unknown kind {kind!r}; expected one of {GROUPED_KINDS}")
     if kind not in SUPPORTED_GROUPED_KINDS:
         raise NotImplementedError(f"{op}: kind={kind!r} is not implemented yet")
-    if quant is not None:
-        raise NotImplementedError(f"{op}: quantised grouped GEMM is not part of this backend")
+    if quant is not None and str(quant).lower() not in _FP8_QUANTS:
+        if str(quant).lower() in _OTHER_QUANTS:
+            raise NotImplementedError(f"{op}: quant={quant!r} is not part of this backend (fp8_e4m3 is)")
+        raise ValueError(f"{op}: quant {quant!r} has no grouped path; expected one of "
+                         f"{_FP8_QUANTS + _OTHER_QUANTS}")
     if alignment is not None:
         gs = np.asarray(group_sizes).astype(np.int64).reshape(-1)
         if np.any(gs % int(alignment)):
             raise ValueError(f"{op}: every group size must be a multiple of alignment={alignment}")
 
 
+class Fp8Tensor:
+    """e4m3 bytes on the device with their scale(s): ``q`` uint8, ``scales`` float32 device array
+    whose first element(s) are the scale(s) (``tessera_sm100_quantize_fp8*_device`` layouts)."""
+
+    def __init__(self, q: DeviceArray, scales: DeviceArray, shape, per_expert: bool):
+        self.q, self.scales, self.shape, self.per_expert = q, scales, tuple(shape), per_expert
+
+    def scale_values(self) -> np.ndarray:
+        n = self.shape[0] if self.per_expert else 1
+        return self.scales.download()[:n]
+
+
+def quantize_fp8_activations(x, *, amax_bits: Optional[DeviceArray] = None, stream=None) -> Fp8Tensor:
+    """Per-tensor e4m3 quantisation of ``x`` (any shape; float32 / float16 / bfloat16) on the
+    device: ``scale = max(amax/448, 1e-12)``, ``q = e4m3(x / scale)``
+    (python/tessera/__init__.py:3340-3374)."""
+    xa = _unwrap(x)
+    dx = xa if isinstance(xa, DeviceArray) else DeviceArray.from_host(np.ascontiguousarray(xa), pooled=True)
+    q = DeviceArray(dx.shape, np.uint8)
+    scales = DeviceArray((3,), np.float32)
+    _lib.call("tessera_sm100_quantize_fp8_device", dx.ptr, int(dx.size), device.dtype_code(dx.dtype), q.ptr,
+              scales.ptr, amax_bits.ptr if amax_bits is not None else None, device._stream_handle(stream))
+    return Fp8Tensor(q, scales, dx.shape, False)
+
+
+def quantize_fp8_experts(weights, *, stream=None) -> Fp8Tensor:
+    """Per-expert e4m3 quantisation of ``weights`` (E, K, N), stored transposed as (E, N, K) so both
+    GEMM operands are K-major (python/tessera/compiler/grouped_layout.py:371-392). Expert weights are
+    static: quantise once and pass the result wherever weights are expected."""
+    w = _unwrap(weights)
+    if len(w.shape) != 3:
+        raise ValueError(f"quantize_fp8_experts: weights must be (E, K, N); got {tuple(w.shape)}")
+    dw = w if isinstance(w, DeviceArray) else DeviceArray.from_host(np.ascontiguousarray(w), pooled=True)
+    E, K, N = dw.shape
+    q = DeviceArray((E, N, K), np.uint8)
+    scales = DeviceArray((3 * E,), np.float32)
+    _lib.call("tessera_sm100_quantize_fp8_weights_device", dw.ptr, E, K, N, device.dtype_code(dw.dtype), q.ptr,
+              scales.ptr, device._stream_handle(stream))
+    return Fp8Tensor(q, scales, (E, K, N), True)
+
+
+def _as_fp8_experts(w, stream) -> Fp8Tensor:
+    return w if isinstance(w, Fp8Tensor) else quantize_fp8_experts(w, stream=stream)
+
+
+def _grouped_gemm_fp8(x, weights, group_sizes, out_dtype, stream):
+    xa = _unwrap(x)
+    if len(xa.shape) != 2:
+        raise ValueError(f"grouped_gemm: x must be (T, K); got {tuple(xa.shape)}")
+    wq = _as_fp8_experts(weights, stream)
+    E, K, N = wq.shape
+    T = xa.shape[0]
+    if xa.shape[1] != K:
+        raise ValueError(f"grouped_gemm: K mismatch — x K={xa.shape[1]}, weights K={K}")
+    off = _group_offsets(group_sizes, T, "grouped_gemm")
+    if off.shape[0] != E + 1:
+        raise ValueError(f"grouped_gemm: weights {wq.shape} must be (E, K, N) with E == len(group_sizes)="
+                         f"{off.shape[0] - 1}")
+    if K % 16 or N % 8:
+        raise ValueError("grouped_gemm: the fp8 path needs K a multiple of 16 and N a multiple of 8")
+    on_device = isinstance(xa, DeviceArray)
+    xq = quantize_fp8_activations(xa, stream=stream)
+    odt = np.dtype(out_dtype) if out_dtype is not None else np.dtype(xa.dtype)
+    out = DeviceArray((T, N), odt)      # group sizes sum to T: every row is written
+    doff = DeviceArray.from_host(off, pooled=True)
+    _lib.call("tessera_sm100_grouped_gemm_fp8_device", xq.q.ptr, wq.q.ptr, doff.ptr, out.ptr, T, K, N, E,
+              xq.scales.ptr, wq.scales.ptr, device.dtype_code(odt), device._stream_handle(stream))
+    return out if on_device else _finish(out)
+
+
 def grouped_gemm(x, weights, group_sizes, *, kind="contiguous", alignment=None, quant=None,
                  out_dtype=None, stream=None):
     """Ragged grouped matmul: row block e of ``x`` (T, K) times ``weights[e]`` (E, K, N)
-    (python/tessera/__init__.py:291-351). Output dtype follows ``x``."""
+    (python/tessera/__init__.py:291-351). Output dtype follows ``x``. ``quant="fp8_e4m3"`` quantises
+    ``x`` per tensor and each expert's weights per expert and multiplies the e4m3 values on the
+    tensor cores (the reference dequantises on the host and multiplies in f32); ``weights`` may be
+    an :class:`Fp8Tensor` from :func:`quantize_fp8_experts`."""
     _check_kind(kind, alignment, group_sizes, quant, "grouped_gemm")
+    if quant is not None or isinstance(weights, Fp8Tensor):
+        return _grouped_gemm_fp8(x, weights, group_sizes, out_dtype, stream)
     x, w = _unwrap(x), _unwrap(weights)
     if x.ndim != 2:
         raise ValueError(f"grouped_gemm: x must be (T, K); got {x.shape}")
@@ -468,6 +550,8 @@ def moe_swiglu_block(x, w_gate, w_up, w_down, group_sizes, *, kind="contiguous",
     """Expert FFN over grouped tokens: gate and up grouped GEMMs fused with ``silu_mul`` in one
     kernel, then the down grouped GEMM (python/tessera/__init__.py:592-616)."""
     _check_kind(kind, alignment, group_sizes, quant, "moe_swiglu_block")
+    if quant is not None or isinstance(w_gate, Fp8Tensor):
+        return _moe_swiglu_block_fp8(x, w_gate, w_up, w_down, group_sizes, stream)
     x, wg, wu, wd = _unwrap(x), _unwrap(w_gate), _unwrap(w_up), _unwrap(w_down)
     if x.ndim != 2 or wg.ndim != 3 or wu.shape != wg.shape or wd.ndim != 3:
         raise ValueError("moe_swiglu_block: expected x (T,K), w_gate/w_up (E,K,F), w_down (E,F,N)")
@@ -492,6 +576,44 @@ def moe_swiglu_block(x, w_gate, w_up, w_down, group_sizes, *, kind="contiguous",
               K, F, E, code, code, sh)
     _lib.call("tessera_sm100_grouped_gemm_device", hidden.ptr, dd.ptr, doff.ptr, out.ptr, T, F, N, E,
               code, code, sh)
+    return out if on_device else _finish(out)
+
+
+def _moe_swiglu_block_fp8(x, w_gate, w_up, w_down, group_sizes, stream):
+    """fp8 expert FFN: x quantised once, gate and up GEMMs fused with silu_mul (16-bit hidden plus its
+    amax from the epilogue), hidden quantised per tensor, down GEMM — the reference applies ``quant``
+    to every grouped GEMM of the block (python/tessera/__init__.py:592-616)."""
+    xa = _unwrap(x)
+    if len(xa.shape) != 2:
+        raise ValueError("moe_swiglu_block: expected x (T,K)")
+    gq, uq, dq = (_as_fp8_experts(w, stream) for w in (w_gate, w_up, w_down))
+    E, K, F = gq.shape
+    if uq.shape != gq.shape or dq.shape[0] != E or dq.shape[1] != F or xa.shape[1] != K:
+        raise ValueError(f"moe_swiglu_block: shape mismatch x {tuple(xa.shape)}, w_gate {gq.shape}, "
+                         f"w_down {dq.shape}")
+    N = dq.shape[2]
+    T = xa.shape[0]
+    off = _group_offsets(group_sizes, T, "moe_swiglu_block")
+    if off.shape[0] != E + 1:
+        raise ValueError(f"moe_swiglu_block: len(group_sizes)={off.shape[0] - 1} != E={E}")
+    if K % 16 or F % 16 or N % 8:
+        raise ValueError("moe_swiglu_block: the fp8 path needs K and F multiples of 16 and N of 8")
+    on_device = isinstance(xa, DeviceArray)
+    odt = np.dtype(xa.dtype)
+    # The hidden activation stays fp32 between the two GEMMs: e4m3 keeps 3 mantissa bits, so rounding
+    # it to 16 bits first would move about one element in 32 across a quantisation boundary.
+    hdt = np.dtype(np.float32)
+    sh = device._stream_handle(stream)
+    xq = quantize_fp8_activations(xa, stream=stream)
+    doff = DeviceArray.from_host(off, pooled=True)
+    hidden = DeviceArray((T, F), hdt, pooled=True)
+    amax = DeviceArray.zeros((1,), np.uint32)
+    _lib.call("tessera_sm100_grouped_swiglu_fp8_device", xq.q.ptr, gq.q.ptr, uq.q.ptr, doff.ptr, hidden.ptr, T, K,
+              F, E, xq.scales.ptr, gq.scales.ptr, uq.scales.ptr, device.dtype_code(hdt), amax.ptr, sh)
+    hq = quantize_fp8_activations(hidden, amax_bits=amax, stream=stream)
+    out = DeviceArray((T, N), odt)
+    _lib.call("tessera_sm100_grouped_gemm_fp8_device", hq.q.ptr, dq.q.ptr, doff.ptr, out.ptr, T, F, N, E,
+              hq.scales.ptr, dq.scales.ptr, device.dtype_code(odt), sh)
     return out if on_device else _finish(out)
 
 

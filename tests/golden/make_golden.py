@@ -207,6 +207,18 @@ def moe():
                                         capacity=T * k)
         out[f"megamoe_w{R}"] = np.asarray(y, np.float32)
         out[f"megamoe_dropped_w{R}"] = np.array(dropped)
+    # quantised grouped GEMM (quant="fp8_e4m3"): per-tensor x, per-expert w (__init__.py:337-351, 3340-3374)
+    sizes = np.array([40, 0, 100, 52])
+    xq = rt(rng.standard_normal((192, 64)), bf16)
+    wgq = rt(rng.standard_normal((4, 64, 96)) / 8, bf16)
+    wuq = rt(rng.standard_normal((4, 64, 96)) / 8, bf16)
+    wdq = rt(rng.standard_normal((4, 96, 48)) / 10, bf16)
+    dq, sc = tessera.ops.quantize_fp8(xq)
+    out.update(q_sizes=sizes, q_x=xq, q_wg=wgq, q_wu=wuq, q_wd=wdq, q_x_dq=np.asarray(dq, np.float32),
+               q_x_scale=np.float32(sc),
+               q_gg=np.asarray(tessera.ops.grouped_gemm(xq, wgq, sizes, quant="fp8_e4m3"), np.float32),
+               q_block=np.asarray(tessera.ops.moe_swiglu_block(xq, wgq, wuq, wdq, sizes, quant="fp8_e4m3"),
+                                  np.float32))
     np.savez_compressed(os.path.join(HERE, "moe.npz"), **out)
 
 

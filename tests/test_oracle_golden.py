@@ -167,3 +167,13 @@ def test_attention_lane_contract_matches_reference(golden_dir):
     o = orc.attention_lane(g["biasQ"], g["biasK"], g["biasV"], scale=1 / np.sqrt(32.0), causal=True,
                            bias=np.broadcast_to(g["biasB"], (2, 2, Sq, Sk)), causal_shift=max(Sk - Sq, 0))
     np.testing.assert_allclose(o, g["biasO"], rtol=1e-5, atol=2e-6)
+
+
+def test_fp8_quantised_grouped_gemm_matches_reference(golden_dir):
+    g = _load(golden_dir, "moe.npz")
+    dq, sc = orc.quantize_fp8(g["q_x"])
+    np.testing.assert_array_equal(dq, g["q_x_dq"])
+    assert sc == g["q_x_scale"]
+    np.testing.assert_allclose(orc.grouped_gemm_fp8(g["q_x"], g["q_wg"], g["q_sizes"]), g["q_gg"], rtol=1e-6, atol=1e-6)
+    np.testing.assert_allclose(orc.moe_swiglu_block_fp8(g["q_x"], g["q_wg"], g["q_wu"], g["q_wd"], g["q_sizes"]),
+                               g["q_block"], rtol=1e-5, atol=1e-6)

@@ -44,7 +44,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # of these kernels being proportional to those counts. The MoE figure is the sum of its two
 # grouped GEMM launches.
 NCU_TRAFFIC_BYTES = {"gemm_8192": 1.209e9, "attn_prefill": 1.007e9, "attn_decode": 2.171e9, "attn_decode_paged": 2.166e9,
-                     "moe": 4.78e9}
+                     "attn_decode_int8": 1.093e9, "moe": 4.78e9}
 
 
 def load_peaks():
@@ -398,6 +398,45 @@ def bench_attn_decode_paged(ranks, args, peaks, peak_kind):
                          "peak_kind": f"copy bandwidth, of {peak_kind}"}}
 
 
+def bench_attn_decode_int8(ranks, args, peaks, peak_kind):
+    """The decode workload over an int8 KV cache (per-token scales): half the bytes of the bf16
+    cache. The metric counts the bytes the kernel has to read (int8 K + V plus the scales)."""
+    import ctypes
+    from tessera_b200 import _lib, device
+    from tessera_b200.device import DeviceArray, bfloat16
+    B, Hq, Hkv, S, D = 64, 32, 8, 8192, 128
+    W = ranks.world
+    Bl = B // W
+    rng = np.random.default_rng(1008 + ranks.rank)
+    q = rng.standard_normal((Bl, Hq, D), dtype=np.float32).astype(bfloat16)
+    base = rng.integers(1, 256, (2, Hkv, S, D), dtype=np.uint8)   # stored form: value + 128
+    kq = np.concatenate([np.roll(base, r, axis=-1) for r in range(-(-Bl // 2))])[:Bl]
+    vq = np.roll(kq, 3, axis=2)
+    ks = rng.uniform(0.005, 0.03, (Bl, S)).astype(np.float32)
+    vs = rng.uniform(0.005, 0.03, (Bl, S)).astype(np.float32)
+    dq, dk, dv, dks, dvs = (DeviceArray.from_host(t) for t in (q, kq, vq, ks, vs))
+    do = DeviceArray.zeros((Bl, Hq, D), bfloat16)
+    lib = _lib.load()
+    ns = lib.tessera_sm100_attn_decode_int8_splits(Bl, Hq, Hkv, S)
+    scr = DeviceArray((max(1, lib.tessera_sm100_attn_decode_scratch_bytes(Bl, Hq, ns)),), np.uint8)
+    scale = ctypes.c_float(1.0 / np.sqrt(D))
+    fn = lambda: _lib.call("tessera_sm100_attn_decode_int8_device", dq.ptr, dk.ptr, dv.ptr, dks.ptr, dvs.ptr,
+                           do.ptr, Bl, Hq, Hkv, S, D, scale, ns, scr.ptr, None)
+    times = timed_steps(ranks, device, fn, args.steps, args.warmup)
+    ms = statistics.mean(times)
+    code = device.consume_device_error()[0]
+    nbytes = 2.0 * B * Hkv * S * D + 2.0 * B * S * 4
+    ach = nbytes / W / ms / 1e6
+    return {"metric": "GQA decode attention over an int8 KV cache, GB/s (int8 K+V bytes + scales)",
+            "value": nbytes / ms / 1e6, "unit": "GB/s", "ms_per_step": ms, "device_error": code,
+            "config": f"batch={B} Hq={Hq} Hkv={Hkv} KV={S} D={D}, int8 K/V with per-token fp32 scales, "
+                      f"batch sharded /{W}",
+            "splits": ns, "equivalent_bf16_gbs": 2.0 * B * Hkv * S * D * 2 / ms / 1e6,
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": ach / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES["attn_decode_int8"] / W,
+                         "peak_kind": f"copy bandwidth, of {peak_kind}"}}
+
+
 def bench_moe(ranks, args, peaks, peak_kind):
     from tessera_b200 import _lib, collectives, device, parallel
     from tessera_b200.device import DeviceArray, bfloat16
@@ -602,6 +641,20 @@ def profile_case(name: str) -> None:
         fn = lambda: _lib.call("tessera_sm100_paged_attn_decode_device", q.ptr, kp.ptr, vp.ptr, table.ptr,
                                lens.ptr, o.ptr, B, Hq, Hkv, D, L, P, per_seq, S, ctypes.c_float(1 / np.sqrt(D)),
                                ns, scr.ptr, None)
+    elif name == "attn_decode_int8":
+        B, Hq, Hkv, S, D = 32, 32, 8, 8192, 128
+        q = DeviceArray.from_host(rng.standard_normal((B, Hq, D), dtype=np.float32).astype(bfloat16))
+        base = rng.integers(1, 256, (2, Hkv, S, D), dtype=np.uint8)
+        kq = np.concatenate([base] * (B // 2))
+        k, v = DeviceArray.from_host(kq), DeviceArray.from_host(np.roll(kq, 3, axis=2))
+        ks = DeviceArray.from_host(rng.uniform(0.005, 0.03, (B, S)).astype(np.float32))
+        vs = DeviceArray.from_host(rng.uniform(0.005, 0.03, (B, S)).astype(np.float32))
+        o = DeviceArray.zeros((B, Hq, D), bfloat16)
+        lib = _lib.load()
+        ns = lib.tessera_sm100_attn_decode_int8_splits(B, Hq, Hkv, S)
+        scr = DeviceArray((max(1, lib.tessera_sm100_attn_decode_scratch_bytes(B, Hq, ns)),), np.uint8)
+        fn = lambda: _lib.call("tessera_sm100_attn_decode_int8_device", q.ptr, k.ptr, v.ptr, ks.ptr, vs.ptr, o.ptr,
+                               B, Hq, Hkv, S, D, ctypes.c_float(1 / np.sqrt(D)), ns, scr.ptr, None)
     elif name == "moe":
         T, H, F, E, k = 2048, 4096, 14336, 2, 2
         x = dev_normal((T, H))
@@ -628,7 +681,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="all", choices=["all", "gemm", "attn_prefill", "attn_decode", "attn_decode_paged", "moe", "moe_fp8"])
+    ap.add_argument("--workload", default="all", choices=["all", "gemm", "attn_prefill", "attn_decode", "attn_decode_paged", "attn_decode_int8", "moe",
+                             "moe_fp8"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tp-mode", default="fused", choices=["fused", "nccl"],
                     help="N>1 GEMM: all-gather fused into the epilogue (peer TMA stores) or NCCL after it")
@@ -662,9 +716,11 @@ def main():
 
     g = bench_gemm(ranks, args, peaks, peak_kind, sampler)
     extras = {}
-    if args.workload in ("all", "attn_prefill", "attn_decode", "attn_decode_paged", "moe", "moe_fp8"):
+    if args.workload in ("all", "attn_prefill", "attn_decode", "attn_decode_paged", "attn_decode_int8", "moe",
+                         "moe_fp8"):
         for name, fn in (("attn_prefill", bench_attn_prefill), ("attn_decode", bench_attn_decode),
-                         ("attn_decode_paged", bench_attn_decode_paged), ("moe", bench_moe),
+                         ("attn_decode_paged", bench_attn_decode_paged),
+                         ("attn_decode_int8", bench_attn_decode_int8), ("moe", bench_moe),
                          ("moe_fp8", bench_moe_fp8)):
             if args.workload not in ("all", name):
                 continue

@@ -305,6 +305,41 @@ int tessera_sm100_softmax_merge_device(const float* oa, const float* ma, const f
 int tessera_sm100_softmax_finalize_device(const float* o, const float* l, void* out, long long rows,
                                           int Dv, int out_dtype, void* stream);
 
+/* ---- int8 KV cache --------------------------------------------------------------------------
+ * KVCacheHandle(quantize_bits=8) stores K and V as int8 with one fp32 scale per token, shared by
+ * all heads (python/tessera/cache/handle.py:72-215; quantize_kv / dequantize_kv,
+ * python/tessera/__init__.py:3196-3265), and reads dequantise. Here decode attention reads the
+ * 8-bit values directly — half the bytes of a bf16 cache on a bandwidth-bound kernel. STORAGE
+ * FORM: each quantised value q in [-127, 127] is kept as the unsigned byte q + 128 (an int8 array
+ * of the reference becomes this with one xor 0x80 per byte). A byte placed under an f16 exponent
+ * is then already the f16 number q + 1152, so widening costs two byte permutes per four values;
+ * the constant is removed from the dot products in fp32 (exactly linear), and the per-token
+ * scales fold into the scores (K) and into P before P.V (V), so the result equals attention
+ * over the dequantised cache.
+ * Dense: Kq, Vq [B,Hkv,Sk,128] bytes, k_scale, v_scale [B,Sk]. Paged: pages
+ * [num_pages,page_size,Hkv,128] bytes, scale pages [num_pages,page_size]; other arguments as the
+ * 16-bit entry points. tessera_sm100_quantize_kv_int8_device: k, v [T, row] (row = heads*dim) ->
+ * byte rows (q + 128) and scales with the reference's arithmetic (scale = max(amax/127, 1e-12),
+ * q = clip(rint(x/scale), -127, 127)); dst_rows (optional device int64[T]) sends token t to row
+ * dst_rows[t] of the outputs (a page slot), negative = skip. */
+/* The split count the 8-bit kernels pick for splits <= 0 (they want more, shorter CTAs than the
+ * 16-bit kernels); size the scratch with tessera_sm100_attn_decode_scratch_bytes(B, Hq, that). */
+int tessera_sm100_attn_decode_int8_splits(int B, int Hq, int Hkv, int Sk);
+int tessera_sm100_attn_decode_int8_device(const void* Q, const void* Kq, const void* Vq,
+                                          const float* k_scale, const float* v_scale, void* O,
+                                          int B, int Hq, int Hkv, int Sk, int D, float scale,
+                                          int splits, void* scratch, void* stream);
+int tessera_sm100_paged_attn_decode_int8_device(const void* Q, const void* k_pages,
+                                                const void* v_pages, const float* k_scale,
+                                                const float* v_scale, const int* page_table,
+                                                const int* seq_lens, void* O, int B, int Hq, int Hkv,
+                                                int D, int page_size, int num_pages, int max_pages,
+                                                int max_seq_len, float scale, int splits,
+                                                void* scratch, void* stream);
+int tessera_sm100_quantize_kv_int8_device(const void* k, const void* v, void* kq, void* vq,
+                                          float* k_scale, float* v_scale, const long long* dst_rows,
+                                          long long T, int row, int dtype, void* stream);
+
 /* Attention forward over strided operands: the same kernels with the layouts described by element
  * strides, one (batch, head, position) triple per tensor; the head dimension (128) is contiguous
  * and every stride is a multiple of 8 elements. Serves nn.functional.multi_head_attention

@@ -268,6 +268,26 @@ def moe_swiglu_block_fp8(x, w_gate, w_up, w_down, group_sizes) -> np.ndarray:
     return grouped_gemm_fp8(silu_mul(gate, up), w_down, group_sizes)
 
 
+def quantize_kv(k, v, bits: int = 8):
+    """Per-token symmetric integer quantisation of ``(seq, heads, dim)`` K and V: one scale per
+    token and tensor, ``scale = max(amax / qmax, 1e-12)``, ``q = clip(round(x / scale), -qmax,
+    qmax)`` with ``qmax = 2^(bits-1) - 1``; returns ``(k_q, v_q, scale)`` with ``scale`` of shape
+    ``(2, seq, 1, 1)`` (python/tessera/__init__.py:3196-3249)."""
+    k, v = np.asarray(k, np.float32), np.asarray(v, np.float32)
+    qmax = (1 << (bits - 1)) - 1
+    ks = np.maximum(np.max(np.abs(k), axis=(1, 2), keepdims=True) / qmax, 1e-12).astype(np.float32)
+    vs = np.maximum(np.max(np.abs(v), axis=(1, 2), keepdims=True) / qmax, 1e-12).astype(np.float32)
+    kq = np.clip(np.round(k / ks), -qmax, qmax).astype(np.int8)
+    vq = np.clip(np.round(v / vs), -qmax, qmax).astype(np.int8)
+    return kq, vq, np.stack([ks, vs], axis=0)
+
+
+def dequantize_kv(k_q, v_q, scale):
+    """``q * scale`` per token (python/tessera/__init__.py:3251-3265)."""
+    scale = np.asarray(scale, np.float32)
+    return (np.asarray(k_q).astype(np.float32) * scale[0], np.asarray(v_q).astype(np.float32) * scale[1])
+
+
 # ----------------------------------------------------------------------------- paged KV
 def paged_pack(k, v, page_size: int):
     """Tokens ``[n, H, D]`` -> identity-mapped pages ``[P, L, H, D]`` + table

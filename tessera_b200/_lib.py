@@ -100,6 +100,7 @@ _SIGNATURES = {
     "tessera_sm100_ep_combine_device": (c_int, [POINTER(_VP), _VP, _VP, _VP, _VP, _VP, _VP, c_int, c_int,
                                                 c_int, c_int, c_int, c_int, c_int, _VP]),
     "tessera_sm100_attn_decode_splits": (c_int, [c_int, c_int, c_int, c_int]),
+    "tessera_sm100_attn_decode_int8_splits": (c_int, [c_int, c_int, c_int, c_int]),
     "tessera_sm100_attn_decode_scratch_bytes": (c_size_t, [c_int, c_int, c_int]),
     "tessera_sm100_attn_decode_device": (c_int, [_VP, _VP, _VP, _VP, c_int, c_int, c_int, c_int,
                                                  c_int, c_float, c_int, _VP, _VP]),
@@ -131,6 +132,13 @@ _SIGNATURES = {
                                                       c_int, _VP]),
     "tessera_sm100_grouped_swiglu_fp8_device": (c_int, [_VP, _VP, _VP, _VP, _VP, c_int, c_int, c_int, c_int,
                                                         _VP, _VP, _VP, c_int, _VP, _VP]),
+    "tessera_sm100_attn_decode_int8_device": (c_int, [_VP, _VP, _VP, _VP, _VP, _VP, c_int, c_int, c_int, c_int,
+                                                      c_int, c_float, c_int, _VP, _VP]),
+    "tessera_sm100_paged_attn_decode_int8_device": (c_int, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, c_int, c_int,
+                                                            c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                                            c_int, _VP, _VP]),
+    "tessera_sm100_quantize_kv_int8_device": (c_int, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, c_longlong, c_int, c_int,
+                                                      _VP]),
     "tessera_sm100_paged_attn_decode_device": (c_int, [_VP, _VP, _VP, _VP, _VP, _VP, c_int, c_int, c_int,
                                                        c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                                                        _VP, _VP]),

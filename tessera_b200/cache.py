@@ -147,7 +147,7 @@ class PagedKVCache:
     kind = KVKind.FULL
 
     def __init__(self, num_seqs: int, num_kv_heads: int, head_dim: int = HEAD_DIM, *, page_size: int = 64,
-                 num_pages: int, max_pages_per_seq: Optional[int] = None):
+                 num_pages: int, max_pages_per_seq: Optional[int] = None, quantize_bits: Optional[int] = None):
         if head_dim != HEAD_DIM:
             raise ValueError(f"PagedKVCache: head_dim must be {HEAD_DIM}; got {head_dim}")
         if num_seqs <= 0 or num_kv_heads <= 0 or num_pages <= 0:
@@ -156,9 +156,20 @@ class PagedKVCache:
         self.num_seqs, self.num_kv_heads, self.head_dim = int(num_seqs), int(num_kv_heads), int(head_dim)
         self.page_size, self.num_pages = int(page_size), int(num_pages)
         self.max_pages = int(max_pages_per_seq) if max_pages_per_seq else max(1, num_pages // num_seqs)
+        if quantize_bits not in (None, 8):
+            raise ValueError("PagedKVCache: quantize_bits must be None or 8")
+        # quantize_bits=8: 8-bit pages (each value stored as the byte q + 128, the form the decode
+        # kernel widens for free) with one fp32 scale per token for K and for V, shared by the
+        # heads (KVCacheHandle(quantize_bits=8), python/tessera/cache/handle.py:72-137)
+        self.quantize_bits = quantize_bits
         shape = (self.num_pages, self.page_size, self.num_kv_heads, self.head_dim)
-        self.k_pages = DeviceArray.zeros(shape, bfloat16)
-        self.v_pages = DeviceArray.zeros(shape, bfloat16)
+        page_dtype = np.uint8 if quantize_bits else bfloat16
+        self.k_pages = DeviceArray.zeros(shape, page_dtype)
+        self.v_pages = DeviceArray.zeros(shape, page_dtype)
+        self.k_scales = self.v_scales = None
+        if quantize_bits:
+            self.k_scales = DeviceArray.zeros((self.num_pages, self.page_size), np.float32)
+            self.v_scales = DeviceArray.zeros((self.num_pages, self.page_size), np.float32)
         self._table = np.zeros((self.num_seqs, self.max_pages), np.int32)
         self._owned = np.zeros(self.num_seqs, np.int64)          # pages assigned per sequence
         self._lens = np.zeros(self.num_seqs, np.int32)
@@ -173,6 +184,7 @@ class PagedKVCache:
         k = np.asarray(abi.k_pages)
         P, L, H, D = k.shape
         self = cls.__new__(cls)
+        self.quantize_bits, self.k_scales, self.v_scales = None, None, None
         if D != HEAD_DIM:
             raise ValueError(f"PagedKVCache: head_dim must be {HEAD_DIM}; got {D}")
         _check_page_size(L)
@@ -193,7 +205,7 @@ class PagedKVCache:
     @classmethod
     def from_dense(cls, K, V, *, page_size: int = 64, seq_lens: Optional[Sequence[int]] = None,
                    num_pages: Optional[int] = None, page_order: Optional[Sequence[int]] = None,
-                   max_pages_per_seq: Optional[int] = None) -> "PagedKVCache":
+                   max_pages_per_seq: Optional[int] = None, quantize_bits: Optional[int] = None) -> "PagedKVCache":
         """Build from dense host ``K``, ``V`` ``[B, S, Hkv, 128]``; sequence b keeps its first
         ``seq_lens[b]`` tokens. ``page_order`` (a permutation of the physical pages) scatters the
         pages so the table is not the identity."""
@@ -210,29 +222,57 @@ class PagedKVCache:
         if P < need:
             raise ValueError(f"from_dense: {need} pages needed, num_pages={P}")
         self = cls(B, H, D, page_size=page_size, num_pages=P,
-                   max_pages_per_seq=max_pages_per_seq or int(per_seq.max()))
+                   max_pages_per_seq=max_pages_per_seq or int(per_seq.max()), quantize_bits=quantize_bits)
         order = list(range(P)) if page_order is None else [int(x) for x in page_order]
         if sorted(order) != list(range(P)):
             raise ValueError("from_dense: page_order must be a permutation of range(num_pages)")
         self._free = order[::-1]
-        hk = np.zeros((P, page_size, H, D), bfloat16)
-        hv = np.zeros((P, page_size, H, D), bfloat16)
         for b in range(B):
-            n = int(lens[b])
             for lp in range(int(per_seq[b])):
-                pp = self._free.pop()
-                self._table[b, lp] = pp
-                t0, t1 = lp * page_size, min(n, (lp + 1) * page_size)
-                if t1 > t0:
-                    hk[pp, :t1 - t0] = K[b, t0:t1].astype(bfloat16)
-                    hv[pp, :t1 - t0] = V[b, t0:t1].astype(bfloat16)
+                self._table[b, lp] = self._free.pop()
             self._owned[b] = per_seq[b]
         self._lens[:] = lens
-        self.k_pages.upload(hk)
-        self.v_pages.upload(hv)
+        if quantize_bits:
+            # tokens go to their page slots through the quantisation kernel itself
+            toks_k = np.concatenate([K[b, :int(lens[b])] for b in range(B)]).reshape(-1, H * D)
+            toks_v = np.concatenate([V[b, :int(lens[b])] for b in range(B)]).reshape(-1, H * D)
+            rows = np.concatenate([self._slot_rows(b, np.arange(int(lens[b]))) for b in range(B)])
+            self._quantize_into_pages(toks_k, toks_v, rows)
+        else:
+            hk = np.zeros((P, page_size, H, D), bfloat16)
+            hv = np.zeros((P, page_size, H, D), bfloat16)
+            for b in range(B):
+                n = int(lens[b])
+                for lp in range(int(per_seq[b])):
+                    pp = int(self._table[b, lp])
+                    t0, t1 = lp * page_size, min(n, (lp + 1) * page_size)
+                    if t1 > t0:
+                        hk[pp, :t1 - t0] = K[b, t0:t1].astype(bfloat16)
+                        hv[pp, :t1 - t0] = V[b, t0:t1].astype(bfloat16)
+            self.k_pages.upload(hk)
+            self.v_pages.upload(hv)
         self.page_table.upload(self._table)
         self.seq_lens.upload(self._lens)
         return self
+
+    def _slot_rows(self, b: int, positions: np.ndarray) -> np.ndarray:
+        """Row index (physical page * page_size + offset) of each position of sequence ``b``."""
+        lp, off = np.divmod(np.asarray(positions, np.int64), self.page_size)
+        return self._table[b, lp].astype(np.int64) * self.page_size + off
+
+    def _quantize_into_pages(self, k_rows, v_rows, dst_rows: np.ndarray, stream=None) -> None:
+        """Per-token int8 quantisation of ``[T, Hkv*D]`` rows straight into their page slots."""
+        T, row = k_rows.shape
+        if T == 0:
+            return
+        dk = k_rows if isinstance(k_rows, DeviceArray) else DeviceArray.from_host(np.ascontiguousarray(k_rows), pooled=True)
+        dv = v_rows if isinstance(v_rows, DeviceArray) else DeviceArray.from_host(np.ascontiguousarray(v_rows), pooled=True)
+        drows = DeviceArray.from_host(np.ascontiguousarray(dst_rows, np.int64), pooled=True)
+        _lib.call("tessera_sm100_quantize_kv_int8_device", dk.ptr, dv.ptr, self.k_pages.ptr, self.v_pages.ptr,
+                  self.k_scales.ptr, self.v_scales.ptr, drows.ptr, T, row, device.dtype_code(dk.dtype),
+                  device._stream_handle(stream))
+        if stream is None:
+            device.synchronize()
 
     # ------------------------------------------------------------------ decode-step append
     def append(self, k_new, v_new, stream=None) -> "PagedKVCache":
@@ -253,6 +293,18 @@ class PagedKVCache:
         if dirty:
             self.page_table.upload(self._table, stream)
         shape = (self.num_seqs, self.num_kv_heads, self.head_dim)
+        if self.quantize_bits:
+            # quantise the new rows straight into their slots, then publish the new lengths
+            rows = np.array([self._slot_rows(b, np.array([int(self._lens[b])]))[0] for b in range(self.num_seqs)])
+            row = self.num_kv_heads * self.head_dim
+            kn = k_new.view((self.num_seqs, row)) if isinstance(k_new, DeviceArray) else \
+                np.asarray(k_new).reshape(self.num_seqs, row)
+            vn = v_new.view((self.num_seqs, row)) if isinstance(v_new, DeviceArray) else \
+                np.asarray(v_new).reshape(self.num_seqs, row)
+            self._quantize_into_pages(kn, vn, rows, stream)
+            self._lens += 1
+            self.seq_lens.upload(self._lens, stream)
+            return self
         dk, dv = _as_device_bf16(k_new, shape, "k_new"), _as_device_bf16(v_new, shape, "v_new")
         _lib.call("tessera_sm100_paged_kv_append_device", dk.ptr, dv.ptr, self.k_pages.ptr, self.v_pages.ptr,
                   self.page_table.ptr, self.seq_lens.ptr, self.num_seqs, self.num_kv_heads, self.head_dim,
@@ -307,6 +359,8 @@ class PagedKVCache:
         return k, v
 
     def gather_device(self, token_indices, seq: int = 0, stream=None, pad_to: int = 1):
+        if self.quantize_bits:
+            raise NotImplementedError("PagedKVCache.gather: not available for an int8 cache")
         idx = np.asarray(list(token_indices) if not isinstance(token_indices, np.ndarray) else token_indices,
                          dtype=np.int64).reshape(-1)
         n = int(self._lens[seq])
@@ -345,15 +399,22 @@ def _as_device_bf16(x, shape, name: str) -> DeviceArray:
 
 
 def _decode(Q: DeviceArray, cache_like, table: DeviceArray, lens: DeviceArray, B: int, Hq: int,
-            max_pages: int, max_seq_len: int, scale: float, stream) -> DeviceArray:
+            max_pages: int, max_seq_len: int, scale: float, stream, scales=None) -> DeviceArray:
     k_pages, v_pages, Hkv, L, P = cache_like
     lib = _lib.load()
-    splits = int(lib.tessera_sm100_attn_decode_splits(B, Hq, Hkv, max_seq_len))
+    pick = lib.tessera_sm100_attn_decode_int8_splits if scales is not None else lib.tessera_sm100_attn_decode_splits
+    splits = int(pick(B, Hq, Hkv, max_seq_len))
     scratch = None
     if splits > 1:
         nbytes = int(lib.tessera_sm100_attn_decode_scratch_bytes(B, Hq, splits))
         scratch = DeviceArray((nbytes,), np.uint8, pooled=True)
     out = DeviceArray((B, Hq, HEAD_DIM), bfloat16)
+    if scales is not None:
+        _lib.call("tessera_sm100_paged_attn_decode_int8_device", Q.ptr, k_pages.ptr, v_pages.ptr, scales[0].ptr,
+                  scales[1].ptr, table.ptr, lens.ptr, out.ptr, B, Hq, Hkv, HEAD_DIM, L, P, max_pages, max_seq_len,
+                  float(scale), splits, scratch.ptr if scratch is not None else None,
+                  device._stream_handle(stream))
+        return out
     _lib.call("tessera_sm100_paged_attn_decode_device", Q.ptr, k_pages.ptr, v_pages.ptr, table.ptr, lens.ptr,
               out.ptr, B, Hq, Hkv, HEAD_DIM, L, P, max_pages, max_seq_len, float(scale), splits,
               scratch.ptr if scratch is not None else None, device._stream_handle(stream))
@@ -378,7 +439,7 @@ def paged_decode(Q, cache: PagedKVCache, *, scale: Optional[float] = None, strea
     sc = 1.0 / np.sqrt(HEAD_DIM) if scale is None else float(scale)
     out = _decode(dq, (cache.k_pages, cache.v_pages, cache.num_kv_heads, cache.page_size, cache.num_pages),
                   cache.page_table, cache.seq_lens, cache.num_seqs, Hq, cache.max_pages, int(lens.max()), sc,
-                  stream)
+                  stream, scales=(cache.k_scales, cache.v_scales) if cache.quantize_bits else None)
     if on_device:
         return out
     host = out.download().astype(np.float32)
@@ -411,6 +472,7 @@ def paged_attention(Q, kv_state, *, scale: Optional[float] = None, causal: bool 
     if Hkv < 1 or Hq % Hkv:
         raise ValueError(f"attention query heads must be divisible by KV heads; got Q={Hq} KV={Hkv}")
     sc = 1.0 / np.sqrt(D) if scale is None else float(scale)
+    scales = (cache.k_scales, cache.v_scales) if cache.quantize_bits else None
     if token_indices is None:
         n = cache.seq_len()
         pages = (cache.k_pages, cache.v_pages, Hkv, cache.page_size, cache.num_pages)
@@ -441,7 +503,8 @@ def paged_attention(Q, kv_state, *, scale: Optional[float] = None, causal: bool 
                                   pooled=True)
     dl = DeviceArray.from_host(lens, pooled=True)
     dq = DeviceArray.from_host(qd.astype(bfloat16), pooled=True)
-    out = _decode(dq, pages, table, dl, B, heads, max_pages, int(lens.max()), sc, stream)
+    out = _decode(dq, pages, table, dl, B, heads, max_pages, int(lens.max()), sc, stream,
+                  scales=scales if token_indices is None else None)
     host = out.download().astype(np.float32)
     device.check_device_error("paged_attention")
     del keep

@@ -278,6 +278,17 @@ def paged():
     out.update(sQ=Q, sO=_reference_attention(Q, np.transpose(kk, (1, 0, 2)), np.transpose(vv, (1, 0, 2)),
                                              1.0 / np.sqrt(128.0), False).astype(np.float32))
     out["n"] = np.array(len(cases))
+    # an int8 cache: KVCacheHandle(quantize_bits=8) quantises per token on append and dequantises on
+    # read (python/tessera/cache/handle.py:72-215, python/tessera/__init__.py:3196-3265)
+    n, Hkv, Hq = 140, 2, 8
+    h8 = KVCacheHandle(num_heads=Hkv, head_dim=128, max_seq=n + 8, page_size=16, quantize_bits=8)
+    k = rt(rng.standard_normal((n, Hkv, 128)) * np.linspace(0.2, 3.0, n)[:, None, None], bf16)
+    v = rt(rng.standard_normal((n, Hkv, 128)), bf16)
+    h8.append(k, v)
+    Q = rt(rng.standard_normal((Hq, 1, 128)), bf16)
+    kq, vq, sc, _ = tessera.ops.quantize_kv(k, v, bits=8)
+    out.update(q8_k=k, q8_v=v, q8_Q=Q, q8_kq=kq, q8_vq=vq, q8_scale=np.asarray(sc, np.float32),
+               q8_O=np.asarray(paged_attention(Q, h8), np.float32))
     np.savez_compressed(os.path.join(HERE, "paged.npz"), **out)
 
 

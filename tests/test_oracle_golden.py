@@ -177,3 +177,15 @@ def test_fp8_quantised_grouped_gemm_matches_reference(golden_dir):
     np.testing.assert_allclose(orc.grouped_gemm_fp8(g["q_x"], g["q_wg"], g["q_sizes"]), g["q_gg"], rtol=1e-6, atol=1e-6)
     np.testing.assert_allclose(orc.moe_swiglu_block_fp8(g["q_x"], g["q_wg"], g["q_wu"], g["q_wd"], g["q_sizes"]),
                                g["q_block"], rtol=1e-5, atol=1e-6)
+
+
+def test_int8_kv_cache_matches_reference(golden_dir):
+    g = _load(golden_dir, "paged.npz")
+    kq, vq, sc = orc.quantize_kv(g["q8_k"], g["q8_v"], 8)
+    np.testing.assert_array_equal(kq, g["q8_kq"])
+    np.testing.assert_array_equal(vq, g["q8_vq"])
+    np.testing.assert_array_equal(sc, g["q8_scale"])
+    kd, vd = orc.dequantize_kv(kq, vq, sc)
+    kp, vp, table = orc.paged_pack(kd, vd, 16)
+    o = orc.paged_attention(g["q8_Q"], kp, vp, table, kd.shape[0])
+    np.testing.assert_allclose(o, g["q8_O"], rtol=1e-5, atol=1e-6)

@@ -286,6 +286,31 @@ int tessera_sm100_flash_attn_general_device(const void* q, const void* k, const 
                                             long long window_right, float softcap, int dtype,
                                             void* stream);
 
+/* Attention backward (VJP): (dO, Q, K, V [, bias]) -> (dQ, dK, dV), the contract of the reference's
+ * CUDA lane (python/tessera/compiler/emit/nvidia_cuda.py:590-635, entry tessera_nvidia_flash_attn_bwd;
+ * tests/device/nvidia/test_flash_attention_backward.py:23-50). Masks, bias, soft-cap and head mapping
+ * as tessera_sm100_flash_attn_general_device; ds = p (dO.v - delta) (1 - tanh^2) with delta = dO.o;
+ * dQ = sum ds scale k, dK = sum over the group's query heads and rows of ds scale q, dV = sum p dO.
+ * f32 / f16 / bf16 storage (dtype code), fp32 math, gradients in the storage type, D and Dv up to
+ * 256 (the reference's cap). Every output row is summed by one warp in a fixed order: the result is
+ * deterministic (the reference's default route uses atomics) and the outputs need no clearing.
+ * dO [B,Hq,Sq,Dv], dQ like Q, dK like K, dV like V. workspace: device memory of
+ * tessera_sm100_flash_attn_bwd_workspace_bytes(B, Hq, Sq) bytes (softmax statistics per row).
+ * tessera_sm100_flash_attn_bwd is the host-pointer form with the reference entry's argument order
+ * (upload, run, synchronise, download); its causal mask is the lane's (key n > query m). */
+size_t tessera_sm100_flash_attn_bwd_workspace_bytes(long long B, int Hq, long long Sq);
+int tessera_sm100_flash_attn_bwd_device(const void* dO, const void* Q, const void* K, const void* V,
+                                        const float* bias, void* dQ, void* dK, void* dV, long long B,
+                                        int Hq, int Hkv, long long Sq, long long Sk, int D, int Dv,
+                                        float scale, int causal, long long causal_shift,
+                                        long long window_left, long long window_right, float softcap,
+                                        int dtype, void* workspace, void* stream);
+int tessera_sm100_flash_attn_bwd(const void* dO, const void* Q, const void* K, const void* V,
+                                 const float* bias, void* dQ, void* dK, void* dV, long long B, int Hq,
+                                 int Hkv, long long Sq, long long Sk, int D, int Dv, float scale,
+                                 int causal, long long window_left, long long window_right,
+                                 float softcap, int dtype);
+
 /* ---- max-shifted attention states -----------------------------------------------------------
  * ops.softmax_merge / softmax_finalize (python/tessera/_block_attnres_ops.py:104-146): a state is
  * (o [rows, Dv] = sum e^{s-m} v, m [rows] = max s, l [rows] = sum e^{s-m}), fp32; merging is

@@ -185,6 +185,62 @@ def attention_lane(q, k, v, *, scale, causal: bool = False, window=None, bias=No
     return out
 
 
+def attention_lane_backward(do, q, k, v, *, scale, causal: bool = False, window=None, bias=None,
+                            softcap=None, causal_shift: int = 0):
+    """Gradients ``(dQ, dK, dV)`` of :func:`attention_lane`: the CUDA backward lane's contract
+    (python/tessera/compiler/emit/nvidia_cuda.py:590-635) as the reference's device test restates it
+    (tests/device/nvidia/test_flash_attention_backward.py:23-50): ``p`` = softmax over the legal
+    keys, ``delta = dO . o``, ``ds = p (dO . v - delta) (1 - tanh^2(raw / softcap))``,
+    ``dQ += ds scale k``, ``dK += ds scale q`` and ``dV += p dO`` summed over the query heads of a
+    KV head; a row with no legal key contributes nothing (the device lane's ``z > 0`` guard)."""
+    do, q, k, v = _f32(do), _f32(q), _f32(k), _f32(v)
+    B, Hq, Sq, D = q.shape
+    _, Hkv, Sk, _ = k.shape
+    rep = Hq // Hkv
+    if window is None:
+        wl = wr = None
+    elif isinstance(window, (tuple, list)):
+        wl, wr = window
+    else:
+        wl = wr = window
+    m = np.arange(Sq)[:, None]
+    n = np.arange(Sk)[None, :]
+    keep = np.ones((Sq, Sk), bool)
+    if causal:
+        keep &= n <= m + causal_shift
+    if wl is not None and wl >= 0:
+        keep &= n >= m - wl
+    if wr is not None and wr >= 0:
+        keep &= n <= m + wr
+    dq, dk, dv = np.zeros_like(q), np.zeros_like(k), np.zeros_like(v)
+    sc = np.float32(scale)
+    for b in range(B):
+        for hq in range(Hq):
+            hk = hq // rep
+            raw = (q[b, hq] @ k[b, hk].T) * sc
+            if bias is not None:
+                raw = raw + np.asarray(bias, np.float32)[b, hq]
+            deriv = np.ones_like(raw)
+            s = raw
+            if softcap:
+                t = np.tanh(raw / softcap)
+                s = softcap * t
+                deriv = 1 - t * t
+            s = np.where(keep, s, -np.inf)
+            mx = s.max(-1, keepdims=True)
+            mx = np.where(np.isfinite(mx), mx, 0.0)
+            e = np.exp(s - mx)
+            den = e.sum(-1, keepdims=True)
+            p = e / np.where(den > 0, den, 1.0)
+            dp = do[b, hq] @ v[b, hk].T
+            delta = (p * dp).sum(-1, keepdims=True)
+            ds = p * (dp - delta) * deriv
+            dq[b, hq] = (ds @ k[b, hk]) * sc
+            dk[b, hk] += (ds.T @ q[b, hq]) * sc
+            dv[b, hk] += p.T @ do[b, hq]
+    return dq, dk, dv
+
+
 def gqa_attention(Q, K, V, num_query_heads: int, num_kv_heads: int, **kwargs) -> np.ndarray:
     """Query head ``hq`` reads KV head ``hq // (Hq/Hkv)``: the reference repeats each KV head
     ``Hq/Hkv`` times along the head axis and calls ``flash_attn``

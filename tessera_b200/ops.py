@@ -289,6 +289,67 @@ def flash_attn(Q, K=None, V=None, scale=None, causal: bool = False, cache=None,
     return out
 
 
+def flash_attn_backward(dO, Q, K, V, *, scale=None, causal: bool = False, window=None, attn_bias=None,
+                        softcap=None, causal_alignment: str = "top_left", stream=None):
+    """Gradients ``(dQ, dK, dV)`` of ``flash_attn`` with respect to Q, K and V for the output
+    gradient ``dO``: the contract of the reference's CUDA backward lane
+    (python/tessera/compiler/emit/nvidia_cuda.py:590-635, 675-750). dO [B,Hq,Sq,Dv], Q [B,Hq,Sq,D],
+    K [B,Hkv,Sk,D], V [B,Hkv,Sk,Dv] in one of float32 / float16 / bfloat16; the gradients come back
+    in that dtype (fp32 math). ``causal_alignment`` defaults to the lane's "top_left" (key j > i
+    masked); "bottom_right" is the mask of ``ops.flash_attn``. Device operands give device
+    results. Deterministic: every gradient row is summed in a fixed order."""
+    if causal_alignment not in ("bottom_right", "top_left"):
+        raise ValueError("causal_alignment must be 'bottom_right' or 'top_left'")
+    dO, Q, K, V = _unwrap(dO), _unwrap(Q), _unwrap(K), _unwrap(V)
+    if any(t.ndim != 4 for t in (dO, Q, K, V)):
+        raise ValueError("flash_attn_backward requires rank-4 dO/Q/K/V tensors")
+    Bq, Hq, Sq, D = Q.shape
+    Bk, Hkv, Sk, Dk = K.shape
+    Dv = V.shape[3]
+    if (tuple(V.shape[:3]) != tuple(K.shape[:3]) or Bk != Bq or Dk != D or tuple(dO.shape) != (Bq, Hq, Sq, Dv)
+            or Hq % Hkv or max(D, Dv) > 256):
+        raise ValueError("invalid flash_attn_backward Q/K/V/dO shape or head mapping")
+    dts = {np.dtype(t.dtype) for t in (dO, Q, K, V)}
+    if len(dts) != 1 or next(iter(dts)) not in (np.dtype(np.float32), np.dtype(np.float16), bfloat16):
+        raise TypeError("flash_attn_backward requires matching float32, float16 or bfloat16 dO/Q/K/V storage")
+    dt = dts.pop()
+    if scale is None:
+        scale = 1.0 / np.sqrt(D)
+    wl = wr = -1
+    if window is not None:
+        wl, wr = (window if isinstance(window, (tuple, list)) else (window, window))
+        wl = -1 if wl is None else int(wl)
+        wr = -1 if wr is None else int(wr)
+    cap = 0.0 if softcap is None else float(softcap)
+    if wl < -1 or wr < -1 or cap < 0.0:
+        raise ValueError("window bounds must be >= 0 and softcap must be >= 0")
+    dbias = None
+    if attn_bias is not None:
+        b = _unwrap(attn_bias)
+        if isinstance(b, DeviceArray):
+            if b.shape != (Bq, Hq, Sq, Sk) or b.dtype != np.float32:
+                raise ValueError("flash_attn_backward: a device attn_bias must be float32 [B, Hq, Sq, Sk]")
+            dbias = b
+        else:
+            b = np.asarray(b)
+            if b.dtype != np.float32 or b.shape != (Bq, Hq, Sq, Sk):
+                raise ValueError("flash_attn_backward bias must be float32 with shape [B,Hq,Sq,Sk]")
+            dbias = DeviceArray.from_host(np.ascontiguousarray(b), pooled=True)
+    shift = max(Sk - Sq, 0) if causal_alignment == "bottom_right" else 0
+    on_device = _any_device(dO, Q, K, V)
+    dgo, dq_, dk_, dv_ = (_to_device(t, dt) for t in (dO, Q, K, V))
+    gq, gk, gv = DeviceArray(Q.shape, dt), DeviceArray(K.shape, dt), DeviceArray(V.shape, dt)
+    nws = int(_lib.load().tessera_sm100_flash_attn_bwd_workspace_bytes(Bq, Hq, Sq))
+    ws = DeviceArray((nws,), np.uint8, pooled=True)
+    _lib.call("tessera_sm100_flash_attn_bwd_device", dgo.ptr, dq_.ptr, dk_.ptr, dv_.ptr,
+              dbias.ptr if dbias is not None else None, gq.ptr, gk.ptr, gv.ptr, Bq, Hq, Hkv, Sq, Sk, D, Dv,
+              ctypes.c_float(float(scale)), int(bool(causal)), shift, wl, wr, ctypes.c_float(cap),
+              device.dtype_code(dt), ws.ptr, device._stream_handle(stream))
+    if on_device:
+        return gq, gk, gv
+    return _finish(gq), _finish(gk), _finish(gv)
+
+
 def paged_attention(Q, kv_state, *, scale=None, causal: bool = False, token_indices=None):
     """Attention over a paged KV state (python/tessera/__init__.py:1291-1302): ``Q`` is
     ``(num_heads, q_len, 128)``; the pages are read in place by the paged decode kernel."""

@@ -65,6 +65,8 @@ COMPILER_PATHS = {
     "sm100_flash_attn": ("tessera.flash_attn", "flash_attn", "tessera.gqa_attention"),
     "sm100_moe": ("tessera.grouped_gemm", "tessera.moe_swiglu_block", "tessera.moe_layer",
                   "tessera.moe_dispatch", "tessera.moe_combine"),
+    "sm100_flash_attn_bwd": ("tessera.flash_attn", "flash_attn", "tessera.flash_attn_bwd",
+                             "tessera.flash_attn_vjp"),
 }
 
 
@@ -223,6 +225,28 @@ def _execute_sm100_flash_attn(artifact: RuntimeArtifact, args: Any) -> Any:
                           causal_alignment="top_left")
 
 
+def _execute_sm100_flash_attn_bwd(artifact: RuntimeArtifact, args: Any) -> Any:
+    """One attention VJP: operands ``(dO, Q, K, V[, bias])``, result ``(dQ, dK, dV)``
+    (python/tessera/runtime.py:9935-9990)."""
+    from . import ops
+    meta = artifact.metadata or {}
+    op = _single_op(meta, COMPILER_PATHS["sm100_flash_attn_bwd"], "sm100_flash_attn_bwd")
+    names = [str(n) for n in op.get("operands", [])]
+    if len(names) not in (4, 5):
+        raise ValueError("sm100 flash backward requires dO, Q, K, V and optional bias")
+    values = _bind_launch_args(args, list(meta.get("arg_names") or []))
+    kw = dict(op.get("kwargs") or {})
+    window = kw.get("window", None)
+    if window is None and (kw.get("window_left") is not None or kw.get("window_right") is not None):
+        window = (kw.get("window_left"), kw.get("window_right"))
+    bias = values[names[4]] if len(names) == 5 else None
+    if bias is not None and np.dtype(getattr(getattr(bias, "_data", bias), "dtype", np.float32)) != np.float32:
+        raise ValueError("sm100 flash backward bias must use f32 storage")
+    return ops.flash_attn_backward(values[names[0]], values[names[1]], values[names[2]], values[names[3]],
+                                   scale=kw.get("scale"), causal=bool(kw.get("causal", False)), window=window,
+                                   attn_bias=bias, softcap=kw.get("softcap", kw.get("logit_softcap", None)))
+
+
 def _execute_sm100_moe(artifact: RuntimeArtifact, args: Any) -> Any:
     """grouped_gemm / moe_swiglu_block / moe_layer (python/tessera/runtime.py:9256-9281)."""
     from . import ops
@@ -246,7 +270,7 @@ def _execute_sm100_moe(artifact: RuntimeArtifact, args: Any) -> Any:
 
 def _executor_table() -> dict:
     return {"sm100_gemm": _execute_sm100_gemm, "sm100_flash_attn": _execute_sm100_flash_attn,
-            "sm100_moe": _execute_sm100_moe}
+            "sm100_moe": _execute_sm100_moe, "sm100_flash_attn_bwd": _execute_sm100_flash_attn_bwd}
 
 
 def backend_capabilities(target: Any) -> BackendCapability:

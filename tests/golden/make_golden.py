@@ -167,6 +167,47 @@ def attention():
     np.savez_compressed(os.path.join(HERE, "attention.npz"), **out)
 
 
+def attention_backward():
+    """(dQ, dK, dV) from the numpy reference inside the reference's own device test of the CUDA
+    backward lane (tests/device/nvidia/test_flash_attention_backward.py:23-50), on that test's
+    shapes and seeds plus larger ones."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(
+        "ref_test_flash_bwd", os.path.join(REF, "tests", "device", "nvidia", "test_flash_attention_backward.py"))
+    ref_test = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref_test)
+    out = {}
+    cases = [  # seed, q shape, (Hkv, Sk), Dv, kwargs, with_bias
+        (913, (1, 4, 4, 4), (2, 5), 3, dict(scale=.5), False),
+        (912, (1, 4, 4, 4), (1, 5), 3, dict(scale=.5), False),
+        (919, (1, 2, 5, 4), (1, 6), 3, dict(scale=.5, causal=True, window=(2, 1), softcap=1.4), True),
+        (929, (1, 4, 7, 8), (2, 9), 6, dict(scale=8 ** -0.5, causal=True), False),
+        (1001, (2, 4, 40, 40), (2, 70), 24, dict(scale=0.15, causal=True), False),
+        (1002, (1, 2, 33, 128), (1, 50), 128, dict(scale=128 ** -0.5, window=(10, 5)), True),
+        (1003, (1, 2, 12, 8), (2, 7), 8, dict(scale=0.3, window=(20, 3), softcap=2.0), False),
+        (1004, (1, 3, 65, 16), (3, 65), 16, dict(scale=0.25, causal=True), False),
+    ]
+    for i, (seed, qs, (Hkv, Sk), Dv, kw, wb) in enumerate(cases):
+        rng = np.random.default_rng(seed)
+        B, Hq, Sq, D = qs
+        q = rng.standard_normal(qs, dtype=np.float32)
+        k = rng.standard_normal((B, Hkv, Sk, D), dtype=np.float32)
+        v = rng.standard_normal((B, Hkv, Sk, Dv), dtype=np.float32)
+        do = rng.standard_normal((B, Hq, Sq, Dv), dtype=np.float32)
+        bias = (rng.standard_normal((B, Hq, Sq, Sk)) * .1).astype(np.float32) if wb else None
+        dq, dk, dv = ref_test._ref(do, q, k, v, bias=bias, **kw)
+        out[f"q{i}"], out[f"k{i}"], out[f"v{i}"], out[f"do{i}"] = q, k, v, do
+        if wb:
+            out[f"b{i}"] = bias
+        out[f"dq{i}"], out[f"dk{i}"], out[f"dv{i}"] = (np.asarray(g, np.float32) for g in (dq, dk, dv))
+        out[f"kw{i}"] = np.array([kw["scale"], float(kw.get("causal", False)),
+                                  -1 if "window" not in kw else kw["window"][0],
+                                  -1 if "window" not in kw else kw["window"][1],
+                                  kw.get("softcap", 0.0)], np.float64)
+    out["n"] = np.array(len(cases))
+    np.savez_compressed(os.path.join(HERE, "attention_bwd.npz"), **out)
+
+
 def moe():
     rng = np.random.default_rng(303)
     out = {}
@@ -293,8 +334,9 @@ def paged():
 
 
 if __name__ == "__main__":
-    gemm()
-    attention()
-    moe()
-    paged()
+    # no arguments: every fixture; otherwise only the named generators (each owns one .npz)
+    every = {"gemm": gemm, "attention": attention, "attention_backward": attention_backward, "moe": moe,
+             "paged": paged}
+    for name in (sys.argv[1:] or list(every)):
+        every[name]()
     print("wrote", sorted(f for f in os.listdir(HERE) if f.endswith(".npz")))

@@ -189,3 +189,58 @@ def test_int8_kv_cache_matches_reference(golden_dir):
     kp, vp, table = orc.paged_pack(kd, vd, 16)
     o = orc.paged_attention(g["q8_Q"], kp, vp, table, kd.shape[0])
     np.testing.assert_allclose(o, g["q8_O"], rtol=1e-5, atol=1e-6)
+
+
+def test_attention_backward_lane_matches_reference(golden_dir):
+    g = _load(golden_dir, "attention_bwd.npz")
+    for i in range(int(g["n"])):
+        bias = g[f"b{i}"] if f"b{i}" in g else None
+        got = orc.attention_lane_backward(g[f"do{i}"], g[f"q{i}"], g[f"k{i}"], g[f"v{i}"], bias=bias,
+                                          **_lane_kwargs(g[f"kw{i}"]))
+        for name, a in zip(("dq", "dk", "dv"), got):
+            np.testing.assert_allclose(a, g[f"{name}{i}"], rtol=2e-5, atol=5e-6, err_msg=f"case {i} {name}")
+
+
+def test_attention_backward_is_the_gradient_of_the_forward_lane():
+    """Central differences of sum(O * dO) through the forward oracle, in float64."""
+    rng = np.random.default_rng(3)
+    q = rng.standard_normal((1, 2, 4, 3)); k = rng.standard_normal((1, 1, 5, 3)); v = rng.standard_normal((1, 1, 5, 2))
+    do = rng.standard_normal((1, 2, 4, 2))
+    bias = rng.standard_normal((1, 2, 4, 5)) * 0.2
+    kw = dict(scale=0.6, causal=True, window=(3, 2), softcap=1.5, causal_shift=1)
+
+    def loss(q_, k_, v_):
+        # float64 forward with the same masks (the float32 oracle is too coarse to differentiate)
+        m = np.arange(4)[:, None]; n = np.arange(5)[None, :]
+        keep = (n <= m + 1) & (n >= m - 3) & (n <= m + 2)
+        tot = 0.0
+        for h in range(2):
+            s = q_[0, h] @ k_[0, 0].T * 0.6 + bias[0, h]
+            s = 1.5 * np.tanh(s / 1.5)
+            s = np.where(keep, s, -np.inf)
+            p = np.exp(s - s.max(-1, keepdims=True)); p /= p.sum(-1, keepdims=True)
+            tot += ((p @ v_[0, 0]) * do[0, h]).sum()
+        return tot
+
+    dq, dk, dv = orc.attention_lane_backward(do, q, k, v, bias=bias, **kw)
+    eps = 1e-5
+    for arr, grad in ((q, dq), (k, dk), (v, dv)):
+        num = np.zeros_like(arr)
+        it = np.nditer(arr, flags=["multi_index"])
+        for _ in it:
+            idx = it.multi_index
+            old = arr[idx]
+            arr[idx] = old + eps; hi = loss(q, k, v)
+            arr[idx] = old - eps; lo = loss(q, k, v)
+            arr[idx] = old
+            num[idx] = (hi - lo) / (2 * eps)
+        np.testing.assert_allclose(grad, num, rtol=2e-3, atol=2e-4)
+
+
+def test_attention_backward_rows_without_legal_keys_contribute_nothing():
+    rng = np.random.default_rng(4)
+    q = rng.standard_normal((1, 1, 10, 4), dtype=np.float32); k = rng.standard_normal((1, 1, 4, 4), dtype=np.float32)
+    v = rng.standard_normal((1, 1, 4, 4), dtype=np.float32); do = rng.standard_normal((1, 1, 10, 4), dtype=np.float32)
+    dq, dk, dv = orc.attention_lane_backward(do, q, k, v, scale=0.5, causal=True, window=(1, 0))
+    assert np.isfinite(dq).all() and np.isfinite(dk).all() and np.isfinite(dv).all()
+    assert not dq[0, 0, 5:].any()   # rows 5.. see only keys >= 4, which do not exist

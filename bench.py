@@ -327,6 +327,37 @@ def bench_attn_prefill(ranks, args, peaks, peak_kind):
                          "peak_kind": f"burst cuBLAS bf16, of {peak_kind}"}}
 
 
+def bench_attn_backward(ranks, args, peaks, peak_kind):
+    """Gradients of the prefill workload (same shape): forward recompute for O and the row
+    log-sum-exps, delta, the dQ kernel and the dK/dV kernel, all inside the timed step."""
+    import ctypes
+    from tessera_b200 import _lib, device
+    from tessera_b200.device import DeviceArray, bfloat16
+    B, H, S, D = 8, 32, 4096, 128
+    W = ranks.world
+    Hl = H // W
+    rng = np.random.default_rng(1010 + ranks.rank)
+    q, k, v, g = (tiled_normal(rng, (B, Hl, S, D), 2, 1.0, bfloat16) for _ in range(4))
+    dq, dk, dv, dg = (DeviceArray.from_host(t) for t in (q, k, v, g))
+    gq, gk, gv = (DeviceArray.zeros((B, Hl, S, D), bfloat16) for _ in range(3))
+    ws = DeviceArray((int(_lib.load().tessera_sm100_flash_attn_bwd_bf16_workspace_bytes(B, Hl, S)),), np.uint8)
+    scale = ctypes.c_float(1.0 / np.sqrt(D))
+    fn = lambda: _lib.call("tessera_sm100_flash_attn_bwd_bf16_device", dg.ptr, dq.ptr, dk.ptr, dv.ptr, gq.ptr,
+                           gk.ptr, gv.ptr, B, Hl, Hl, S, S, scale, 1, ws.ptr, None)
+    times = timed_steps(ranks, device, fn, args.steps, args.warmup)
+    ms = statistics.mean(times)
+    flops = 10.0 * B * H * S * S * D / 2
+    ach = flops / W / ms / 1e9
+    return {"metric": "causal flash-attention backward TFLOP/s", "value": flops / ms / 1e9, "unit": "TFLOP/s",
+            "ms_per_step": ms, "config": f"B={B} H={H} S={S} D={D} bf16 causal, heads sharded /{W}",
+            "flops_convention": "10*B*H*S^2*D/2 (five S x S x D products; the kernels form seven, plus the "
+                                "forward recompute, all inside the timed step)",
+            "device_error": device.consume_device_error()[0],
+            "roofline": {"bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": ach / peaks["bf16_tflops"], "traffic": None,
+                         "peak_kind": f"burst cuBLAS bf16, of {peak_kind}"}}
+
+
 def bench_attn_decode(ranks, args, peaks, peak_kind):
     import ctypes
     from tessera_b200 import _lib, device
@@ -681,7 +712,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="all", choices=["all", "gemm", "attn_prefill", "attn_decode", "attn_decode_paged", "attn_decode_int8", "moe",
+    ap.add_argument("--workload", default="all", choices=["all", "gemm", "attn_prefill", "attn_backward", "attn_decode", "attn_decode_paged", "attn_decode_int8", "moe",
                              "moe_fp8"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tp-mode", default="fused", choices=["fused", "nccl"],
@@ -716,9 +747,10 @@ def main():
 
     g = bench_gemm(ranks, args, peaks, peak_kind, sampler)
     extras = {}
-    if args.workload in ("all", "attn_prefill", "attn_decode", "attn_decode_paged", "attn_decode_int8", "moe",
+    if args.workload in ("all", "attn_prefill", "attn_backward", "attn_decode", "attn_decode_paged", "attn_decode_int8", "moe",
                          "moe_fp8"):
-        for name, fn in (("attn_prefill", bench_attn_prefill), ("attn_decode", bench_attn_decode),
+        for name, fn in (("attn_prefill", bench_attn_prefill), ("attn_backward", bench_attn_backward),
+                         ("attn_decode", bench_attn_decode),
                          ("attn_decode_paged", bench_attn_decode_paged),
                          ("attn_decode_int8", bench_attn_decode_int8), ("moe", bench_moe),
                          ("moe_fp8", bench_moe_fp8)):

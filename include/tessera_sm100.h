@@ -311,6 +311,24 @@ int tessera_sm100_flash_attn_bwd(const void* dO, const void* Q, const void* K, c
                                  int causal, long long window_left, long long window_right,
                                  float softcap, int dtype);
 
+/* The same gradients on the tensor cores for the training shape: bf16, D = Dv = 128, no bias /
+ * window / soft-cap, causal with the bottom-right alignment of tessera.ops.flash_attn (key n legal
+ * for query m when n <= m + max(Sk - Sq, 0); the lane's mask when Sq >= Sk). It runs the forward
+ * kernel once more to get O and each row's log-sum-exp (into the workspace), then delta = dO.O, a
+ * dQ kernel (one CTA per 64 query rows) and a dK/dV kernel (one CTA per 64 keys, over the query
+ * heads of the KV head): mma.sync m16n8k16 with fp32 accumulation, no atomics, bit-identical
+ * reruns. workspace: tessera_sm100_flash_attn_bwd_bf16_workspace_bytes(B, Hq, Sq) bytes.
+ * tessera_sm100_flash_attn_fwd_lse_device is that forward pass on its own: O plus lse2[B,Hq,Sq] =
+ * log2(sum_n exp2(scale*log2(e)*s_n)) over the legal keys (multiply by ln 2 for the natural-log LSE). */
+size_t tessera_sm100_flash_attn_bwd_bf16_workspace_bytes(int B, int Hq, int Sq);
+int tessera_sm100_flash_attn_bwd_bf16_device(const void* dO, const void* Q, const void* K, const void* V,
+                                             void* dQ, void* dK, void* dV, int B, int Hq, int Hkv, int Sq,
+                                             int Sk, float scale, int causal, void* workspace,
+                                             void* stream);
+int tessera_sm100_flash_attn_fwd_lse_device(const void* Q, const void* K, const void* V, void* O,
+                                            float* lse2, int B, int Hq, int Hkv, int Sq, int Sk, int D,
+                                            float scale, int causal, void* stream);
+
 /* ---- max-shifted attention states -----------------------------------------------------------
  * ops.softmax_merge / softmax_finalize (python/tessera/_block_attnres_ops.py:104-146): a state is
  * (o [rows, Dv] = sum e^{s-m} v, m [rows] = max s, l [rows] = sum e^{s-m}), fp32; merging is

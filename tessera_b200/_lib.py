@@ -131,6 +131,11 @@ _SIGNATURES = {
                                                     c_longlong, c_float, c_int, _VP, _VP]),
     "tessera_sm100_flash_attn_bwd": (c_int, [_VP] * 8 + [c_longlong, c_int, c_int, c_longlong, c_longlong, c_int,
                                              c_int, c_float, c_int, c_longlong, c_longlong, c_float, c_int]),
+    "tessera_sm100_flash_attn_bwd_bf16_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "tessera_sm100_flash_attn_bwd_bf16_device": (c_int, [_VP] * 7 + [c_int, c_int, c_int, c_int, c_int, c_float,
+                                                         c_int, _VP, _VP]),
+    "tessera_sm100_flash_attn_fwd_lse_device": (c_int, [_VP] * 5 + [c_int, c_int, c_int, c_int, c_int, c_int,
+                                                        c_float, c_int, _VP]),
     "tessera_sm100_quantize_fp8_device": (c_int, [_VP, c_longlong, c_int, _VP, _VP, _VP, _VP]),
     "tessera_sm100_quantize_fp8_weights_device": (c_int, [_VP, c_int, c_int, c_int, c_int, _VP, _VP, _VP]),
     "tessera_sm100_gemm_fp8_device": (c_int, [_VP, _VP, _VP, c_int, c_int, c_int, _VP, _VP, c_int, _VP]),

@@ -49,6 +49,7 @@ struct Params {
   int causal;
   float scale_log2;
   int* err;
+  float* lse2;   // optional [B, H, Sq]: log2-sum-exp2 of scale_log2 * s per row (the backward's input)
 };
 
 // Optional timeline of one CTA (compile with -DTESSERA_PREFILL_TRACE): clock64 stamps of the
@@ -448,6 +449,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     if (nblk[i] > 0) {
       tc_fence_after();
       const float inv = 1.0f / l;
+      if (p.lse2 && row_q < p.Sq)
+        p.lse2[(static_cast<long long>(b) * p.H + h) * p.Sq + row_q] = l > 0.f ? m_used + log2f(l) : INFINITY;
       const uint32_t t_o = tO(i) + lane_base;
       const uint32_t obuf = sQ + i * TILE_BYTES;
 #pragma unroll 1
@@ -499,7 +502,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
 int launch_strided(const void* Q, const void* K, const void* V, void* O, int B, int H, int Hkv,
                    int Sq, int Sk, int Dh, const long long* qs, const long long* ks,
                    const long long* vs, const long long* os, float scale, int causal,
-                   cudaStream_t st) {
+                   cudaStream_t st, float* lse2 = nullptr) {
   if (!Q || !K || !V || !O || B <= 0 || H <= 0 || Hkv <= 0 || Sq <= 0 || Sk <= 0) {
     set_last_error("attn_prefill: null pointer or non-positive size");
     return kBadArg;
@@ -549,6 +552,7 @@ int launch_strided(const void* Q, const void* K, const void* V, void* O, int B, 
   p.scale_log2 = scale * 1.4426950408889634f;
   p.err = device_err_word();
   if (!p.err) return kDeviceFailed;
+  p.lse2 = lse2;
   TSB_CUDA_OK(cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    SMEM_ALLOC));
   dim3 grid((Sq + 2 * BQ - 1) / (2 * BQ), H, B);
@@ -563,6 +567,15 @@ int launch(const void* Q, const void* K, const void* V, void* O, int B, int H, i
   const long long qs[3] = {(long long)H * Sq * D, (long long)Sq * D, D};
   const long long ks[3] = {(long long)Hkv * Sk * D, (long long)Sk * D, D};
   return launch_strided(Q, K, V, O, B, H, Hkv, Sq, Sk, Dh, qs, ks, ks, qs, scale, causal, st);
+}
+
+// The forward pass that also records each row's log-sum-exp (base 2, of scale * log2(e) * s):
+// what the backward kernels recompute P from.
+int launch_with_lse(const void* Q, const void* K, const void* V, void* O, float* lse2, int B, int H,
+                    int Hkv, int Sq, int Sk, int Dh, float scale, int causal, cudaStream_t st) {
+  const long long qs[3] = {(long long)H * Sq * D, (long long)Sq * D, D};
+  const long long ks[3] = {(long long)Hkv * Sk * D, (long long)Sk * D, D};
+  return launch_strided(Q, K, V, O, B, H, Hkv, Sq, Sk, Dh, qs, ks, ks, qs, scale, causal, st, lse2);
 }
 
 }  // namespace attn_prefill

@@ -339,6 +339,17 @@ def flash_attn_backward(dO, Q, K, V, *, scale=None, causal: bool = False, window
     on_device = _any_device(dO, Q, K, V)
     dgo, dq_, dk_, dv_ = (_to_device(t, dt) for t in (dO, Q, K, V))
     gq, gk, gv = DeviceArray(Q.shape, dt), DeviceArray(K.shape, dt), DeviceArray(V.shape, dt)
+    # the training shape runs on the tensor cores (its causal mask is the bottom-right one)
+    if (dt == bfloat16 and D == 128 and Dv == 128 and dbias is None and wl < 0 and wr < 0 and cap == 0.0
+            and (not causal or shift == max(Sk - Sq, 0))):
+        nws = int(_lib.load().tessera_sm100_flash_attn_bwd_bf16_workspace_bytes(Bq, Hq, Sq))
+        ws = DeviceArray((nws,), np.uint8, pooled=True)
+        _lib.call("tessera_sm100_flash_attn_bwd_bf16_device", dgo.ptr, dq_.ptr, dk_.ptr, dv_.ptr, gq.ptr, gk.ptr,
+                  gv.ptr, Bq, Hq, Hkv, Sq, Sk, ctypes.c_float(float(scale)), int(bool(causal)), ws.ptr,
+                  device._stream_handle(stream))
+        if on_device:
+            return gq, gk, gv
+        return _finish(gq), _finish(gk), _finish(gv)
     nws = int(_lib.load().tessera_sm100_flash_attn_bwd_workspace_bytes(Bq, Hq, Sq))
     ws = DeviceArray((nws,), np.uint8, pooled=True)
     _lib.call("tessera_sm100_flash_attn_bwd_device", dgo.ptr, dq_.ptr, dk_.ptr, dv_.ptr,

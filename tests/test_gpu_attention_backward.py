@@ -126,3 +126,56 @@ def test_host_pointer_entry_has_the_reference_argument_order():
                                           dq.ctypes.data, dk.ctypes.data, dv.ctypes.data, B, 3, Hkv, Sq, Sk, D, Dv,
                                           ctypes.c_float(1.0), 0, -1, -1, ctypes.c_float(0.0), _lib.F32)
     assert rc != 0   # Hq not divisible by Hkv
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Sq,Sk,causal", [
+    (1, 2, 2, 64, 64, False),
+    (1, 2, 2, 64, 64, True),
+    (2, 4, 2, 200, 200, True),
+    (1, 8, 2, 130, 333, True),     # bottom-right mask, ragged tiles, grouped heads
+    (1, 4, 1, 257, 100, False),
+    (1, 2, 2, 300, 77, True),      # Sq > Sk: the lane's top-left mask
+    (1, 4, 4, 1, 190, False),
+])
+def test_tensor_core_path_bf16_d128(B, Hq, Hkv, Sq, Sk, causal):
+    """bf16, D = 128: the mma.sync kernels. The reference for bf16 storage is the fp32 oracle on the
+    same bf16-rounded operands; the gradients are rounded to bf16 on output."""
+    rng = np.random.default_rng(Sq * 13 + Sk + causal)
+    D = 128
+    q = rng.standard_normal((B, Hq, Sq, D), dtype=np.float32).astype(bfloat16)
+    k = rng.standard_normal((B, Hkv, Sk, D), dtype=np.float32).astype(bfloat16)
+    v = rng.standard_normal((B, Hkv, Sk, D), dtype=np.float32).astype(bfloat16)
+    do = rng.standard_normal((B, Hq, Sq, D), dtype=np.float32).astype(bfloat16)
+    scale = 1 / np.sqrt(D)
+    got = tessera.ops.flash_attn_backward(do, q, k, v, scale=scale, causal=causal, causal_alignment="bottom_right")
+    ref = orc.attention_lane_backward(do, q, k, v, scale=scale, causal=causal, causal_shift=max(Sk - Sq, 0))
+    for name, a, e in zip(("dq", "dk", "dv"), got, ref):
+        assert a.dtype == bfloat16
+        assert rel_err(a.astype(np.float32), e) < 2e-2, name
+    again = tessera.ops.flash_attn_backward(do, q, k, v, scale=scale, causal=causal, causal_alignment="bottom_right")
+    for a, b2 in zip(got, again):
+        np.testing.assert_array_equal(a.view(np.uint16), b2.view(np.uint16))
+    no_device_error()
+
+
+def test_forward_with_lse_matches_the_oracle():
+    rng = np.random.default_rng(8)
+    B, Hq, Hkv, Sq, Sk, D = 1, 4, 2, 150, 210, 128
+    q = rng.standard_normal((B, Hq, Sq, D), dtype=np.float32).astype(bfloat16)
+    k = rng.standard_normal((B, Hkv, Sk, D), dtype=np.float32).astype(bfloat16)
+    v = rng.standard_normal((B, Hkv, Sk, D), dtype=np.float32).astype(bfloat16)
+    dq_, dk_, dv_ = (DeviceArray.from_host(t) for t in (q, k, v))
+    o, lse = DeviceArray((B, Hq, Sq, D), bfloat16), DeviceArray((B, Hq, Sq), np.float32)
+    scale = 1 / np.sqrt(D)
+    _lib.call("tessera_sm100_flash_attn_fwd_lse_device", dq_.ptr, dk_.ptr, dv_.ptr, o.ptr, lse.ptr, B, Hq, Hkv, Sq,
+              Sk, D, ctypes.c_float(scale), 1, None)
+    qf, kf = q.astype(np.float32), k.astype(np.float32)
+    shift = Sk - Sq
+    for h in range(Hq):
+        s = qf[0, h] @ kf[0, h // 2].T * scale
+        keep = np.arange(Sk)[None, :] <= np.arange(Sq)[:, None] + shift
+        s = np.where(keep, s, -np.inf)
+        want = (np.log(np.exp(s - s.max(-1, keepdims=True)).sum(-1)) + s.max(-1)) / np.log(2.0)
+        np.testing.assert_allclose(lse.download()[0, h], want, atol=2e-3, rtol=0)
+    assert rel_err(o.download().astype(np.float32),
+                   orc.attention_lane(q, k, v, scale=scale, causal=True, causal_shift=shift)) < 2e-2

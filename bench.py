@@ -672,6 +672,13 @@ def profile_case(name: str) -> None:
         fn = lambda: _lib.call("tessera_sm100_paged_attn_decode_device", q.ptr, kp.ptr, vp.ptr, table.ptr,
                                lens.ptr, o.ptr, B, Hq, Hkv, D, L, P, per_seq, S, ctypes.c_float(1 / np.sqrt(D)),
                                ns, scr.ptr, None)
+    elif name == "attn_backward":
+        B, H, S, D = 2, 16, 4096, 128
+        q, k, v, g = (dev_normal((B, H, S, D)) for _ in range(4))
+        gq, gk, gv = (DeviceArray.zeros((B, H, S, D), bfloat16) for _ in range(3))
+        ws = DeviceArray((int(_lib.load().tessera_sm100_flash_attn_bwd_bf16_workspace_bytes(B, H, S)),), np.uint8)
+        fn = lambda: _lib.call("tessera_sm100_flash_attn_bwd_bf16_device", g.ptr, q.ptr, k.ptr, v.ptr, gq.ptr,
+                               gk.ptr, gv.ptr, B, H, H, S, S, ctypes.c_float(1 / np.sqrt(D)), 1, ws.ptr, None)
     elif name == "attn_decode_int8":
         B, Hq, Hkv, S, D = 32, 32, 8, 8192, 128
         q = DeviceArray.from_host(rng.standard_normal((B, Hq, D), dtype=np.float32).astype(bfloat16))

@@ -165,6 +165,32 @@ int tessera_sm100_grouped_swiglu_fp8_device(const void* xq, const void* wgq_t, c
                                             const float* scale_wu, int out_dtype,
                                             unsigned int* amax_out, void* stream);
 
+/* ---- NVFP4 expert weights (quant = "nvfp4", "fp8xfp4") ----------------------------------------
+ * The reference's grouped GEMM with quant="nvfp4" / "fp8xfp4" quantises and dequantises on the host
+ * and multiplies in f32 (python/tessera/__init__.py:337-351; python/tessera/compiler/grouped_layout.py:
+ * 319-392): NVFP4 = e2m1 codes in blocks of 16 along the LAST axis with one e4m3 scale per block,
+ * scale = e4m3(max(amax/6, 1e-30)) (python/tessera/compiler/microscaling.py:319-362); for expert
+ * weights [E,K,N] the blocks therefore run along N, which no block-scaled MMA consumes, so the
+ * weights are kept packed at rest (4.5 bits per element) and expanded to bf16 for the GEMM: an e2m1
+ * value times an e4m3 scale has at most 5 significant bits, so bf16 holds it exactly and the bf16
+ * tensor-core GEMM forms exactly the reference's products. e4m3 activations ride as bf16 too
+ * (tessera_sm100_fp8_to_bf16_device) with their per-tensor scale applied to the fp32 accumulators by
+ * the *_scaled_device grouped GEMMs (scale_a: one device float, or NULL for 1).
+ * quantize: x [rows, cols] (cols % 16 == 0) -> codes [rows, cols/2] (two codes per byte, even element
+ * in the low nibble) and scales [rows, cols/16] e4m3 bytes; weights: rows = E*K, cols = N. */
+int tessera_sm100_quantize_nvfp4_device(const void* x, long long rows, long long cols, int dtype,
+                                        void* codes, void* scales, void* stream);
+int tessera_sm100_dequantize_nvfp4_device(const void* codes, const void* scales, long long rows,
+                                          long long cols, void* out, int out_dtype, void* stream);
+int tessera_sm100_fp8_to_bf16_device(const void* q, long long n, void* out, void* stream);
+int tessera_sm100_grouped_gemm_scaled_device(const void* x, const void* w, const int* offsets, void* out,
+                                             int T, int K, int N, int E, int in_dtype, int out_dtype,
+                                             const float* scale_a, void* stream);
+int tessera_sm100_grouped_swiglu_scaled_device(const void* x, const void* w_gate, const void* w_up,
+                                               const int* offsets, void* out, int T, int K, int F, int E,
+                                               int in_dtype, int out_dtype, const float* scale_a,
+                                               void* stream);
+
 /* ---- MoE layer pieces --------------------------------------------------------------------
  * Router: top-k over f32 gate logits [T,E]; selection order and tie rule of route_tokens
  * (python/tessera/distributed/moe.py:160-172: descending, the higher expert index first on a

@@ -324,6 +324,52 @@ def moe_swiglu_block_fp8(x, w_gate, w_up, w_down, group_sizes) -> np.ndarray:
     return grouped_gemm_fp8(silu_mul(gate, up), w_down, group_sizes)
 
 
+def quantize_nvfp4(x, block_size: int = 16):
+    """NVFP4 along the last axis: per block of 16, ``scale = e4m3(max(amax/6, 1e-30))`` and
+    ``code = e2m1(x / (scale or 1))``; returns ``(dequantised, scales, codes)`` as float32, the
+    dequantised value being ``code * scale`` (python/tessera/__init__.py:3472-3500,
+    python/tessera/compiler/microscaling.py:319-384)."""
+    x = np.asarray(x, np.float32)
+    n = x.shape[-1]
+    if n % block_size:
+        raise ValueError(f"last dim {n} must be divisible by block_size {block_size} for NVFP4")
+    blocks = x.reshape(x.shape[:-1] + (n // block_size, block_size))
+    amax = np.abs(blocks).max(axis=-1)
+    raw = np.maximum(amax / np.float32(6.0), np.float32(1e-30)).astype(np.float32)
+    scale = raw.astype(ml_dtypes.float8_e4m3fn).astype(np.float32)
+    safe = np.where(scale == 0.0, np.float32(1.0), scale)[..., None]
+    codes = (blocks / safe).astype(ml_dtypes.float4_e2m1fn).astype(np.float32)
+    dq = (codes * scale[..., None]).reshape(x.shape).astype(np.float32)
+    return dq, scale, codes.reshape(x.shape)
+
+
+def _fp4_scheme(quant: str):
+    q = str(quant).lower()
+    return {"nvfp4": ("nvfp4", "nvfp4"), "fp8xfp4": ("fp8_e4m3", "nvfp4"),
+            "fp8_e4m3xnvfp4": ("fp8_e4m3", "nvfp4")}[q]
+
+
+def _qdq(a, fmt: str):
+    return quantize_fp8(a)[0] if fmt == "fp8_e4m3" else quantize_nvfp4(a)[0]
+
+
+def grouped_gemm_fp4(x, w, group_sizes, quant: str = "fp8xfp4") -> np.ndarray:
+    """``grouped_gemm(..., quant="nvfp4" | "fp8xfp4")``: x and each expert's (K, N) weights are
+    quantised and dequantised per the scheme's formats, then the f32 grouped GEMM
+    (python/tessera/compiler/grouped_layout.py:319-392)."""
+    act, wf = _fp4_scheme(quant)
+    w = _f32(w)
+    return grouped_gemm(_qdq(_f32(x), act), np.stack([_qdq(w[e], wf) for e in range(w.shape[0])]), group_sizes)
+
+
+def moe_swiglu_block_fp4(x, w_gate, w_up, w_down, group_sizes, quant: str = "fp8xfp4") -> np.ndarray:
+    """``moe_swiglu_block(..., quant=...)`` with NVFP4 weights: every grouped GEMM of the block
+    quantises its operands (python/tessera/__init__.py:592-616)."""
+    gate = grouped_gemm_fp4(x, w_gate, group_sizes, quant)
+    up = grouped_gemm_fp4(x, w_up, group_sizes, quant)
+    return grouped_gemm_fp4(silu_mul(gate, up), w_down, group_sizes, quant)
+
+
 def quantize_kv(k, v, bits: int = 8):
     """Per-token symmetric integer quantisation of ``(seq, heads, dim)`` K and V: one scale per
     token and tensor, ``scale = max(amax / qmax, 1e-12)``, ``q = clip(round(x / scale), -qmax,

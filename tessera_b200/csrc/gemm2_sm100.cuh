@@ -295,6 +295,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         const float sa = __ldg(p.scale_a);
         sc = sa * __ldg(p.scale_b + tile.b);
         if constexpr (kMode == kGroupedSwiGLU) sc2 = sa * __ldg(p.scale_b2 + tile.b);
+      } else if (p.scale_a) {
+        // 16-bit operands that stand for quantised values with one scale for A (e.g. e4m3 values
+        // held as bf16 against dequantised 4-bit weights): applied to the fp32 accumulators
+        sc = sc2 = __ldg(p.scale_a);
       }
       (void)sc2;
       bool released = false;

@@ -228,7 +228,7 @@ int launch_plain(const void* A, const void* B, void* D, int batch, int M, int N,
 // the SwiGLU form), offsets[E+1] int32 in device memory, out[T,N]. K and N multiples of 8.
 int launch_grouped(const void* x, const void* w, const void* w2, const int* offsets, void* out,
                    int T, int K, int N, int E, int in_dtype, int out_dtype, bool swiglu,
-                   cudaStream_t stream) {
+                   cudaStream_t stream, const float* scale_a) {
   if (!x || !w || !offsets || !out || (swiglu && !w2) || T < 0 || K <= 0 || N <= 0 || E <= 0) {
     set_last_error("grouped_gemm: null pointer or bad size (T %d K %d N %d E %d)", T, K, N, E);
     return kBadArg;
@@ -286,6 +286,7 @@ int launch_grouped(const void* x, const void* w, const void* w2, const int* offs
   p.group_offsets = offsets;
   p.D = out;
   p.ldd = N;
+  p.scale_a = scale_a;
   p.err = device_err_word();
   if (!p.err) return kDeviceFailed;
   // Upper bound on the number of tiles: every group may add one partial m-tile.
@@ -825,13 +826,28 @@ int tessera_sm100_grouped_gemm_device(const void* x, const void* w, const int* o
                                       int T, int K, int N, int E, int in_dtype, int out_dtype,
                                       void* stream) {
   return gemm::launch_grouped(x, w, nullptr, offsets, out, T, K, N, E, in_dtype, out_dtype, false,
-                              static_cast<cudaStream_t>(stream));
+                              static_cast<cudaStream_t>(stream), nullptr);
+}
+// The same two with one fp32 scale (a device float) applied to the accumulators: operands that
+// hold quantised values exactly (e4m3 activations as bf16 against dequantised NVFP4 weights).
+int tessera_sm100_grouped_gemm_scaled_device(const void* x, const void* w, const int* offsets, void* out,
+                                             int T, int K, int N, int E, int in_dtype, int out_dtype,
+                                             const float* scale_a, void* stream) {
+  return gemm::launch_grouped(x, w, nullptr, offsets, out, T, K, N, E, in_dtype, out_dtype, false,
+                              static_cast<cudaStream_t>(stream), scale_a);
+}
+int tessera_sm100_grouped_swiglu_scaled_device(const void* x, const void* w_gate, const void* w_up,
+                                               const int* offsets, void* out, int T, int K, int F, int E,
+                                               int in_dtype, int out_dtype, const float* scale_a,
+                                               void* stream) {
+  return gemm::launch_grouped(x, w_gate, w_up, offsets, out, T, K, F, E, in_dtype, out_dtype, true,
+                              static_cast<cudaStream_t>(stream), scale_a);
 }
 int tessera_sm100_grouped_swiglu_device(const void* x, const void* w_gate, const void* w_up,
                                         const int* offsets, void* out, int T, int K, int F, int E,
                                         int in_dtype, int out_dtype, void* stream) {
   return gemm::launch_grouped(x, w_gate, w_up, offsets, out, T, K, F, E, in_dtype, out_dtype, true,
-                              static_cast<cudaStream_t>(stream));
+                              static_cast<cudaStream_t>(stream), nullptr);
 }
 
 }  // extern "C"

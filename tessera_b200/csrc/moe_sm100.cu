@@ -16,7 +16,7 @@ namespace tsb {
 namespace gemm {
 int launch_grouped(const void* x, const void* w, const void* w2, const int* offsets, void* out,
                    int T, int K, int N, int E, int in_dtype, int out_dtype, bool swiglu,
-                   cudaStream_t stream);
+                   cudaStream_t stream, const float* scale_a = nullptr);
 }
 
 namespace moe {

@@ -122,6 +122,75 @@ int quantize_weights_t(const void* w, int E, int K, int N, void* q_t, float* sca
   return kOk;
 }
 
+// ---- NVFP4: blocks of 16 along the last axis, e2m1 codes, one e4m3 scale per block --------------
+// The arithmetic of the reference's quantize_nvfp4 (python/tessera/__init__.py:3472-3500 ->
+// python/tessera/compiler/microscaling.py:319-362), all in fp32:
+//     scale = e4m3(max(amax(|block|) / 6, 1e-30))   (round to nearest even, subnormals kept);
+//     code  = e2m1(x / (scale == 0 ? 1 : scale))    (round to nearest even, saturating at +-6);
+//     dequantised value = e2m1(code) * scale        (so a block whose scale rounds to 0 reads as 0).
+// e2m1 magnitudes: 0, 0.5, 1, 1.5, 2, 3, 4, 6 (codes 0..7), sign in bit 3. Two codes per byte,
+// the even element in the low nibble.
+__device__ __forceinline__ uint8_t to_e2m1(float x) {
+  const float a = fabsf(x);
+  // ties go to the code with an even mantissa bit: 0.25 -> 0, 0.75 -> 1, 1.25 -> 1, 1.75 -> 2,
+  // 2.5 -> 2, 3.5 -> 4, 5 -> 4
+  uint8_t c = a <= 0.25f ? 0 : a < 0.75f ? 1 : a <= 1.25f ? 2 : a < 1.75f ? 3 : a <= 2.5f ? 4
+            : a < 3.5f ? 5 : a <= 5.0f ? 6 : 7;
+  if (!(a == a)) c = 7;  // NaN cannot be stored; keep the sign and saturate
+  return static_cast<uint8_t>(c | (x < 0.f ? 8 : 0));
+}
+__device__ __forceinline__ float from_e2m1(uint8_t c) {
+  const float mag[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+  const float m = mag[c & 7];
+  return (c & 8) ? -m : m;
+}
+__device__ __forceinline__ float e4m3_to_f32(uint8_t b) {
+  return __half2float(__half(__nv_cvt_fp8_to_halfraw(b, __NV_E4M3)));
+}
+
+template <typename T>
+__global__ void nvfp4_quantize_kernel(const T* __restrict__ x, long long nblocks,
+                                      uint8_t* __restrict__ codes, uint8_t* __restrict__ scales) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= nblocks) return;
+  float v[16];
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    v[j] = to_f32(x[i * 16 + j]);
+    amax = fmaxf(amax, fabsf(v[j]));
+  }
+  const uint8_t sb = __nv_cvt_float_to_fp8(fmaxf(__fdiv_rn(amax, 6.0f), 1e-30f), __NV_SATFINITE, __NV_E4M3);
+  float sf = e4m3_to_f32(sb);
+  if (sf == 0.f) sf = 1.f;
+  uint32_t w[2] = {0u, 0u};
+#pragma unroll
+  for (int j = 0; j < 16; ++j) w[j >> 3] |= static_cast<uint32_t>(to_e2m1(__fdiv_rn(v[j], sf))) << (4 * (j & 7));
+  *reinterpret_cast<uint2*>(codes + i * 8) = make_uint2(w[0], w[1]);
+  scales[i] = sb;
+}
+
+template <typename OutT>
+__global__ void nvfp4_dequantize_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ scales,
+                                        long long nblocks, OutT* __restrict__ out) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= nblocks) return;
+  const uint2 w = *reinterpret_cast<const uint2*>(codes + i * 8);
+  const float sf = e4m3_to_f32(scales[i]);
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const uint32_t word = j < 8 ? w.x : w.y;
+    out[i * 16 + j] = static_cast<OutT>(from_e2m1((word >> (4 * (j & 7))) & 15u) * sf);
+  }
+}
+
+// e4m3 bytes -> the same values as bf16 (exact: 4 significant bits into 8)
+__global__ void fp8_to_bf16_kernel(const uint8_t* __restrict__ q, long long n, __nv_bfloat16* __restrict__ out) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    out[i] = __float2bfloat16_rn(e4m3_to_f32(q[i]));
+}
+
 }  // namespace quant
 }  // namespace tsb
 
@@ -172,6 +241,84 @@ int tessera_sm100_quantize_fp8_weights_device(const void* w, int E, int K, int N
   }
   set_last_error("quantize_fp8_weights: unsupported dtype %d", dtype);
   return kBadArg;
+}
+
+// x [rows, cols] (cols a multiple of 16; dtype code) -> codes [rows, cols/2] bytes and scales
+// [rows, cols/16] e4m3 bytes. For expert weights [E, K, N] pass rows = E*K, cols = N: the blocks
+// run along N, as the reference quantises each expert's (K, N) matrix along its last axis.
+int tessera_sm100_quantize_nvfp4_device(const void* x, long long rows, long long cols, int dtype,
+                                        void* codes, void* scales, void* stream) {
+  if (!x || !codes || !scales || rows < 0 || cols < 0 || (cols % 16)) {
+    set_last_error("quantize_nvfp4: null pointer, negative size, or last dim %lld not divisible by 16", cols);
+    return kBadArg;
+  }
+  const long long nblocks = rows * (cols / 16);
+  if (nblocks == 0) return kOk;
+  if (int rc = ensure_device()) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = static_cast<unsigned>((nblocks + 127) / 128);
+  auto c8 = static_cast<uint8_t*>(codes);
+  auto s8 = static_cast<uint8_t*>(scales);
+  switch (dtype) {
+    case TESSERA_SM100_F32:
+      quant::nvfp4_quantize_kernel<float><<<grid, 128, 0, st>>>(static_cast<const float*>(x), nblocks, c8, s8);
+      break;
+    case TESSERA_SM100_BF16:
+      quant::nvfp4_quantize_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(x), nblocks, c8, s8);
+      break;
+    case TESSERA_SM100_F16:
+      quant::nvfp4_quantize_kernel<__half><<<grid, 128, 0, st>>>(static_cast<const __half*>(x), nblocks, c8, s8);
+      break;
+    default:
+      set_last_error("quantize_nvfp4: unsupported dtype %d", dtype);
+      return kBadArg;
+  }
+  TSB_CUDA_OK(cudaGetLastError());
+  note_launch();
+  return kOk;
+}
+
+// codes + scales -> the dequantised values as bf16 (exact: at most 5 significant bits) or f32.
+int tessera_sm100_dequantize_nvfp4_device(const void* codes, const void* scales, long long rows,
+                                          long long cols, void* out, int out_dtype, void* stream) {
+  if (!codes || !scales || !out || rows < 0 || cols < 0 || (cols % 16)) {
+    set_last_error("dequantize_nvfp4: null pointer, negative size, or last dim %lld not divisible by 16", cols);
+    return kBadArg;
+  }
+  const long long nblocks = rows * (cols / 16);
+  if (nblocks == 0) return kOk;
+  if (int rc = ensure_device()) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = static_cast<unsigned>((nblocks + 127) / 128);
+  auto c8 = static_cast<const uint8_t*>(codes);
+  auto s8 = static_cast<const uint8_t*>(scales);
+  if (out_dtype == TESSERA_SM100_BF16)
+    quant::nvfp4_dequantize_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(c8, s8, nblocks, static_cast<__nv_bfloat16*>(out));
+  else if (out_dtype == TESSERA_SM100_F32)
+    quant::nvfp4_dequantize_kernel<float><<<grid, 128, 0, st>>>(c8, s8, nblocks, static_cast<float*>(out));
+  else {
+    set_last_error("dequantize_nvfp4: output dtype must be bf16 or f32");
+    return kBadArg;
+  }
+  TSB_CUDA_OK(cudaGetLastError());
+  note_launch();
+  return kOk;
+}
+
+// e4m3 bytes -> bf16 holding the same values (the activation operand of the fp8 x fp4 GEMM).
+int tessera_sm100_fp8_to_bf16_device(const void* q, long long n, void* out, void* stream) {
+  if (!q || !out || n < 0) {
+    set_last_error("fp8_to_bf16: null pointer or negative size");
+    return kBadArg;
+  }
+  if (n == 0) return kOk;
+  if (int rc = ensure_device()) return rc;
+  const int blocks = (int)std::min<long long>((n + 255) / 256, 148 * 8);
+  quant::fp8_to_bf16_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(q), n, static_cast<__nv_bfloat16*>(out));
+  TSB_CUDA_OK(cudaGetLastError());
+  note_launch();
+  return kOk;
 }
 
 }  // extern "C"

@@ -475,7 +475,9 @@ def _group_offsets(group_sizes, T: int, op: str) -> np.ndarray:
 
 
 _FP8_QUANTS = ("fp8", "fp8_e4m3")
-_OTHER_QUANTS = ("fp8_e5m2", "nvfp4", "fp8xfp4", "fp8_e4m3xnvfp4", "fp8_e5m2xnvfp4")
+# activation format of the schemes whose weights are NVFP4 (python/tessera/compiler/grouped_layout.py:321-350)
+_FP4_QUANTS = {"nvfp4": "nvfp4", "fp8xfp4": "fp8_e4m3", "fp8_e4m3xnvfp4": "fp8_e4m3"}
+_OTHER_QUANTS = ("fp8_e5m2", "fp8_e5m2xnvfp4")
 
 
 def _check_kind(kind: str, alignment, group_sizes, quant, op: str) -> None:
@@ -483,11 +485,12 @@ def _check_kind(kind: str, alignment, group_sizes, quant, op: str) -> None:
         raise ValueError(f"{op}: unknown kind {kind!r}; expected one of {GROUPED_KINDS}")
     if kind not in SUPPORTED_GROUPED_KINDS:
         raise NotImplementedError(f"{op}: kind={kind!r} is not implemented yet")
-    if quant is not None and str(quant).lower() not in _FP8_QUANTS:
+    if quant is not None and str(quant).lower() not in _FP8_QUANTS + tuple(_FP4_QUANTS):
         if str(quant).lower() in _OTHER_QUANTS:
-            raise NotImplementedError(f"{op}: quant={quant!r} is not part of this backend (fp8_e4m3 is)")
+            raise NotImplementedError(f"{op}: quant={quant!r} is not part of this backend (fp8_e4m3, nvfp4 "
+                                      f"and fp8xfp4 are)")
         raise ValueError(f"{op}: quant {quant!r} has no grouped path; expected one of "
-                         f"{_FP8_QUANTS + _OTHER_QUANTS}")
+                         f"{_FP8_QUANTS + tuple(_FP4_QUANTS) + _OTHER_QUANTS}")
     if alignment is not None:
         gs = np.asarray(group_sizes).astype(np.int64).reshape(-1)
         if np.any(gs % int(alignment)):
@@ -539,6 +542,123 @@ def _as_fp8_experts(w, stream) -> Fp8Tensor:
     return w if isinstance(w, Fp8Tensor) else quantize_fp8_experts(w, stream=stream)
 
 
+class Nvfp4Tensor:
+    """NVFP4 storage on the device: ``codes`` uint8, two e2m1 codes per byte along the last axis
+    (even element in the low nibble), ``scales`` uint8 e4m3, one per block of 16; ``shape`` is the
+    logical shape. 4.5 bits per element."""
+
+    def __init__(self, codes: DeviceArray, scales: DeviceArray, shape):
+        self.codes, self.scales, self.shape = codes, scales, tuple(int(d) for d in shape)
+
+    def dequantize(self, dtype=bfloat16, *, stream=None) -> DeviceArray:
+        rows = int(np.prod(self.shape[:-1], dtype=np.int64))
+        out = DeviceArray(self.shape, dtype, pooled=True)
+        _lib.call("tessera_sm100_dequantize_nvfp4_device", self.codes.ptr, self.scales.ptr, rows, self.shape[-1],
+                  out.ptr, device.dtype_code(np.dtype(dtype)), device._stream_handle(stream))
+        return out
+
+
+def quantize_nvfp4(x, *, block_size: int = 16, stream=None) -> Nvfp4Tensor:
+    """Block-scaled e2m1 quantisation along the last axis with the reference's arithmetic
+    (python/tessera/__init__.py:3472-3500, python/tessera/compiler/microscaling.py:319-362): one e4m3
+    scale ``max(amax/6, 1e-30)`` per 16 elements. For expert weights (E, K, N) the blocks run along
+    N, as the reference quantises each expert's matrix."""
+    if block_size != 16:
+        raise NotImplementedError("quantize_nvfp4: block_size 16 (the NVFP4 layout) is the one served")
+    xa = _unwrap(x)
+    if xa.shape[-1] % 16:
+        raise ValueError(f"last dim {xa.shape[-1]} must be divisible by block_size 16 for NVFP4")
+    dx = xa if isinstance(xa, DeviceArray) else DeviceArray.from_host(np.ascontiguousarray(xa), pooled=True)
+    rows = int(np.prod(xa.shape[:-1], dtype=np.int64))
+    cols = int(xa.shape[-1])
+    codes = DeviceArray(tuple(xa.shape[:-1]) + (cols // 2,), np.uint8)
+    scales = DeviceArray(tuple(xa.shape[:-1]) + (cols // 16,), np.uint8)
+    _lib.call("tessera_sm100_quantize_nvfp4_device", dx.ptr, rows, cols, device.dtype_code(dx.dtype), codes.ptr,
+              scales.ptr, device._stream_handle(stream))
+    return Nvfp4Tensor(codes, scales, xa.shape)
+
+
+def dequantize_nvfp4(t: Nvfp4Tensor, *, dtype=np.float32, stream=None):
+    """The values an :class:`Nvfp4Tensor` stands for, on the host."""
+    return _finish(t.dequantize(dtype, stream=stream))
+
+
+def _fp4_operand(x, act: str, stream):
+    """x -> (bf16 device array holding the quantised values exactly, device scale or None)."""
+    if act == "nvfp4":
+        return quantize_nvfp4(x, stream=stream).dequantize(bfloat16, stream=stream), None
+    xq = quantize_fp8_activations(x, stream=stream)
+    vals = DeviceArray(tuple(xq.q.shape), bfloat16, pooled=True)
+    _lib.call("tessera_sm100_fp8_to_bf16_device", xq.q.ptr, int(xq.q.size), vals.ptr, device._stream_handle(stream))
+    return vals, xq.scales
+
+
+def _fp4_weights(w, stream) -> DeviceArray:
+    t = w if isinstance(w, Nvfp4Tensor) else quantize_nvfp4(w, stream=stream)
+    if len(t.shape) != 3:
+        raise ValueError(f"grouped weights must be (E, K, N); got {t.shape}")
+    return t.dequantize(bfloat16, stream=stream)
+
+
+def _grouped_gemm_fp4(x, weights, group_sizes, act, out_dtype, stream):
+    """Grouped GEMM with NVFP4 weights and nvfp4 or e4m3 activations. Both operands are turned into
+    bf16 arrays that hold the quantised values exactly (e2m1 x e4m3-scale has at most 5 significant
+    bits, an e4m3 value 4), multiplied on the bf16 tensor-core path with fp32 accumulation, and the
+    per-tensor activation scale of the fp8 scheme is applied to the accumulators: the products are
+    those of the reference's dequantise-then-f32-matmul."""
+    xa = _unwrap(x)
+    if len(xa.shape) != 2:
+        raise ValueError(f"grouped_gemm: x must be (T, K); got {tuple(xa.shape)}")
+    T, K = xa.shape
+    on_device = isinstance(xa, DeviceArray)
+    wd = _fp4_weights(weights, stream)
+    E, Kw, N = wd.shape
+    if Kw != K:
+        raise ValueError(f"grouped_gemm: K mismatch — x K={K}, weights K={Kw}")
+    off = _group_offsets(group_sizes, T, "grouped_gemm")
+    if off.shape[0] != E + 1:
+        raise ValueError(f"grouped_gemm: weights {wd.shape} must be (E, K, N) with E == len(group_sizes)="
+                         f"{off.shape[0] - 1}")
+    xv, xs = _fp4_operand(xa, act, stream)
+    odt = np.dtype(out_dtype) if out_dtype is not None else np.dtype(xa.dtype)
+    out = DeviceArray((T, N), odt)
+    doff = DeviceArray.from_host(off, pooled=True)
+    _lib.call("tessera_sm100_grouped_gemm_scaled_device", xv.ptr, wd.ptr, doff.ptr, out.ptr, T, K, N, E, _lib.BF16,
+              device.dtype_code(odt), xs.ptr if xs is not None else None, device._stream_handle(stream))
+    return out if on_device else _finish(out)
+
+
+def _moe_swiglu_block_fp4(x, w_gate, w_up, w_down, group_sizes, act, stream):
+    """Expert FFN with NVFP4 weights: as the fp8 block, every grouped GEMM quantises its activation
+    operand (python/tessera/__init__.py:592-616); the hidden activation stays fp32 in between."""
+    xa = _unwrap(x)
+    if len(xa.shape) != 2:
+        raise ValueError("moe_swiglu_block: expected x (T,K)")
+    T, K = xa.shape
+    on_device = isinstance(xa, DeviceArray)
+    gd, ud, dd = (_fp4_weights(w, stream) for w in (w_gate, w_up, w_down))
+    E, Kw, F = gd.shape
+    if ud.shape != gd.shape or dd.shape[0] != E or dd.shape[1] != F or Kw != K:
+        raise ValueError(f"moe_swiglu_block: shape mismatch x {tuple(xa.shape)}, w_gate {gd.shape}, "
+                         f"w_down {dd.shape}")
+    N = dd.shape[2]
+    off = _group_offsets(group_sizes, T, "moe_swiglu_block")
+    if off.shape[0] != E + 1:
+        raise ValueError(f"moe_swiglu_block: len(group_sizes)={off.shape[0] - 1} != E={E}")
+    sh = device._stream_handle(stream)
+    doff = DeviceArray.from_host(off, pooled=True)
+    xv, xs = _fp4_operand(xa, act, stream)
+    hidden = DeviceArray((T, F), np.float32, pooled=True)
+    _lib.call("tessera_sm100_grouped_swiglu_scaled_device", xv.ptr, gd.ptr, ud.ptr, doff.ptr, hidden.ptr, T, K, F, E,
+              _lib.BF16, _lib.F32, xs.ptr if xs is not None else None, sh)
+    hv, hs = _fp4_operand(hidden, act, stream)
+    odt = np.dtype(xa.dtype)
+    out = DeviceArray((T, N), odt)
+    _lib.call("tessera_sm100_grouped_gemm_scaled_device", hv.ptr, dd.ptr, doff.ptr, out.ptr, T, F, N, E, _lib.BF16,
+              device.dtype_code(odt), hs.ptr if hs is not None else None, sh)
+    return out if on_device else _finish(out)
+
+
 def _grouped_gemm_fp8(x, weights, group_sizes, out_dtype, stream):
     xa = _unwrap(x)
     if len(xa.shape) != 2:
@@ -572,6 +692,9 @@ def grouped_gemm(x, weights, group_sizes, *, kind="contiguous", alignment=None, 
     tensor cores (the reference dequantises on the host and multiplies in f32); ``weights`` may be
     an :class:`Fp8Tensor` from :func:`quantize_fp8_experts`."""
     _check_kind(kind, alignment, group_sizes, quant, "grouped_gemm")
+    if isinstance(weights, Nvfp4Tensor) or (quant is not None and str(quant).lower() in _FP4_QUANTS):
+        act = _FP4_QUANTS[str(quant).lower()] if quant is not None else "fp8_e4m3"
+        return _grouped_gemm_fp4(x, weights, group_sizes, act, out_dtype, stream)
     if quant is not None or isinstance(weights, Fp8Tensor):
         return _grouped_gemm_fp8(x, weights, group_sizes, out_dtype, stream)
     x, w = _unwrap(x), _unwrap(weights)
@@ -622,6 +745,9 @@ def moe_swiglu_block(x, w_gate, w_up, w_down, group_sizes, *, kind="contiguous",
     """Expert FFN over grouped tokens: gate and up grouped GEMMs fused with ``silu_mul`` in one
     kernel, then the down grouped GEMM (python/tessera/__init__.py:592-616)."""
     _check_kind(kind, alignment, group_sizes, quant, "moe_swiglu_block")
+    if isinstance(w_gate, Nvfp4Tensor) or (quant is not None and str(quant).lower() in _FP4_QUANTS):
+        act = _FP4_QUANTS[str(quant).lower()] if quant is not None else "fp8_e4m3"
+        return _moe_swiglu_block_fp4(x, w_gate, w_up, w_down, group_sizes, act, stream)
     if quant is not None or isinstance(w_gate, Fp8Tensor):
         return _moe_swiglu_block_fp8(x, w_gate, w_up, w_down, group_sizes, stream)
     x, wg, wu, wd = _unwrap(x), _unwrap(w_gate), _unwrap(w_up), _unwrap(w_down)

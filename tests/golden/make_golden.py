@@ -263,6 +263,32 @@ def moe():
     np.savez_compressed(os.path.join(HERE, "moe.npz"), **out)
 
 
+def quant4():
+    """NVFP4 quantisation and the grouped GEMMs with quant="nvfp4" / "fp8xfp4", from the reference's
+    own ops (python/tessera/__init__.py:291-351, 592-616, 3472-3500)."""
+    import tessera
+    rng = np.random.default_rng(4242)
+    out = {}
+    x = (rng.standard_normal((37, 64)) * np.exp(rng.standard_normal((37, 1)))).astype(np.float32)
+    x[3, 16:32] = 0.0                      # an all-zero block
+    x[5, :16] *= 1e-4                      # a block whose scale rounds to zero in e4m3
+    x[7, 5] = 0.75 * 6 / 6 ; x[7, 0] = 6.0  # a tie on the e2m1 grid under scale 1
+    dq, sc = tessera.ops.quantize_nvfp4(x)
+    out.update(n_x=x, n_dq=np.asarray(dq, np.float32), n_scales=np.asarray(sc, np.float32))
+    T, K, N, F, E = 96, 64, 48, 80, 3
+    sizes = np.array([40, 0, 56])
+    xs = rt(rng.standard_normal((T, K)), bf16)
+    w = rt(rng.standard_normal((E, K, N)) / 8, bf16)
+    wg = rt(rng.standard_normal((E, K, F)) / 8, bf16)
+    wu = rt(rng.standard_normal((E, K, F)) / 8, bf16)
+    wd = rt(rng.standard_normal((E, F, N)) / 9, bf16)
+    out.update(g_x=xs, g_w=w, g_wg=wg, g_wu=wu, g_wd=wd, g_sizes=sizes)
+    for q in ("nvfp4", "fp8xfp4"):
+        out[f"gg_{q}"] = np.asarray(tessera.ops.grouped_gemm(xs, w, sizes, quant=q), np.float32)
+        out[f"blk_{q}"] = np.asarray(tessera.ops.moe_swiglu_block(xs, wg, wu, wd, sizes, quant=q), np.float32)
+    np.savez_compressed(os.path.join(HERE, "quant4.npz"), **out)
+
+
 def paged():
     """cache.paged_attention over a KVCacheHandle, and the page ABI it is materialised into
     (python/tessera/cache/paged_kv.py:421-559)."""
@@ -335,7 +361,7 @@ def paged():
 
 if __name__ == "__main__":
     # no arguments: every fixture; otherwise only the named generators (each owns one .npz)
-    every = {"gemm": gemm, "attention": attention, "attention_backward": attention_backward, "moe": moe,
+    every = {"gemm": gemm, "attention": attention, "attention_backward": attention_backward, "moe": moe, "quant4": quant4,
              "paged": paged}
     for name in (sys.argv[1:] or list(every)):
         every[name]()

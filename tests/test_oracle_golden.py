@@ -244,3 +244,16 @@ def test_attention_backward_rows_without_legal_keys_contribute_nothing():
     dq, dk, dv = orc.attention_lane_backward(do, q, k, v, scale=0.5, causal=True, window=(1, 0))
     assert np.isfinite(dq).all() and np.isfinite(dk).all() and np.isfinite(dv).all()
     assert not dq[0, 0, 5:].any()   # rows 5.. see only keys >= 4, which do not exist
+
+
+def test_nvfp4_quantisation_and_grouped_gemms_match_reference(golden_dir):
+    g = _load(golden_dir, "quant4.npz")
+    dq, sc, _ = orc.quantize_nvfp4(g["n_x"])
+    np.testing.assert_array_equal(dq, g["n_dq"])
+    np.testing.assert_array_equal(sc, g["n_scales"])
+    assert not dq[5, :16].any() and g["n_x"][5, :16].any()      # scale rounded to zero: block reads as 0
+    for q in ("nvfp4", "fp8xfp4"):
+        np.testing.assert_allclose(orc.grouped_gemm_fp4(g["g_x"], g["g_w"], g["g_sizes"], q), g[f"gg_{q}"],
+                                   rtol=1e-6, atol=1e-6)
+        np.testing.assert_allclose(orc.moe_swiglu_block_fp4(g["g_x"], g["g_wg"], g["g_wu"], g["g_wd"], g["g_sizes"], q),
+                                   g[f"blk_{q}"], rtol=1e-5, atol=1e-6)

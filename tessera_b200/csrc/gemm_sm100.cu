@@ -36,8 +36,7 @@ int dispatch_out(int out_dtype, const CUtensorMap& tA, const CUtensorMap& tB,
                  const Params& p, int grid, cudaStream_t stream) {
   switch (out_dtype) {
     case TESSERA_SM100_F32:
-      if constexpr (kMode == kGroupedSwiGLU) break;
-      else return launch_kernel<float, kMode>(tA, tB, tB2, tD, peers, p, grid, stream);
+      return launch_kernel<float, kMode>(tA, tB, tB2, tD, peers, p, grid, stream);
     case TESSERA_SM100_BF16:
       return launch_kernel<__nv_bfloat16, kMode>(tA, tB, tB2, tD, peers, p, grid, stream);
     case TESSERA_SM100_F16:
@@ -299,6 +298,9 @@ int launch_grouped(const void* x, const void* w, const void* w2, const int* offs
     Params p2 = p;
     p2.idesc = make_idesc_f16(in_dtype == TESSERA_SM100_BF16, false, true, 2 * BM, BN);
     if (swiglu) {
+      if (out_dtype == TESSERA_SM100_F32)
+        return launch_pair_kernel<float, kGroupedSwiGLU>(tA, tB, tB2, tD, no_peers, p2, max_pair_tiles,
+                                                         stream);
       if (out_dtype == TESSERA_SM100_BF16)
         return launch_pair_kernel<__nv_bfloat16, kGroupedSwiGLU>(tA, tB, tB2, tD, no_peers, p2,
                                                                  max_pair_tiles, stream);

@@ -82,6 +82,8 @@ def test_grouped_fp8_against_oracle(sizes, K, N):
 def test_unsupported_quant_names():
     x, w = np.zeros((8, 16), np.float32), np.zeros((1, 16, 8), np.float32)
     with pytest.raises(NotImplementedError):
+        tessera.ops.grouped_gemm(x, w, [8], quant="fp8_e5m2")
+    with pytest.raises(ValueError):          # the reference's message: NVFP4 blocks of 16 along N
         tessera.ops.grouped_gemm(x, w, [8], quant="nvfp4")
     with pytest.raises(ValueError):
         tessera.ops.grouped_gemm(x, w, [8], quant="int3")

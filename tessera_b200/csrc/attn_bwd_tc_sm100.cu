@@ -21,6 +21,7 @@
 #include <cuda_bf16.h>
 
 #include <cmath>
+#include <cstdlib>
 
 #include "../../include/tessera_sm100.h"
 #include "device_ctx.h"
@@ -30,6 +31,11 @@ namespace tsb {
 namespace attn_prefill {
 int launch_with_lse(const void* Q, const void* K, const void* V, void* O, float* lse2, int B, int H,
                     int Hkv, int Sq, int Sk, int Dh, float scale, int causal, cudaStream_t st);
+}
+namespace attn_bwd5 {
+int launch(const void* dO, const void* Q, const void* K, const void* V, void* dQ, void* dK, void* dV,
+           const float* lse2, const float* delta, int B, int Hq, int Hkv, int Sq, int Sk, float scale,
+           int causal, cudaStream_t st);
 }
 namespace attn_bwd_tc {
 
@@ -379,6 +385,14 @@ int tessera_sm100_flash_attn_bwd_bf16_device(const void* dO, const void* Q, cons
       static_cast<long long>(rows));
   TSB_CUDA_OK(cudaGetLastError());
   note_launch();
+  // The tcgen05 kernels are the default; TESSERA_SM100_ATTN_BWD=mma selects the mma.sync ones
+  // (same inputs, same ownership of the gradient rows), kept for comparison.
+  static const bool use_mma = [] {
+    const char* e = getenv("TESSERA_SM100_ATTN_BWD");
+    return e && e[0] == 'm';
+  }();
+  if (!use_mma)
+    return attn_bwd5::launch(dO, Q, K, V, dQ, dK, dV, lse2, delta, B, Hq, Hkv, Sq, Sk, scale, causal, st);
   attn_bwd_tc::Params p{};
   p.Q = static_cast<const __nv_bfloat16*>(Q);
   p.K = static_cast<const __nv_bfloat16*>(K);

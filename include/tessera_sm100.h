@@ -341,9 +341,9 @@ int tessera_sm100_flash_attn_bwd(const void* dO, const void* Q, const void* K, c
  * window / soft-cap, causal with the bottom-right alignment of tessera.ops.flash_attn (key n legal
  * for query m when n <= m + max(Sk - Sq, 0); the lane's mask when Sq >= Sk). It runs the forward
  * kernel once more to get O and each row's log-sum-exp (into the workspace), then delta = dO.O, a
- * dQ kernel (one CTA per 64 query rows) and a dK/dV kernel (one CTA per 64 keys, over the query
- * heads of the KV head): mma.sync m16n8k16 with fp32 accumulation, no atomics, bit-identical
- * reruns. workspace: tessera_sm100_flash_attn_bwd_bf16_workspace_bytes(B, Hq, Sq) bytes.
+ * dQ kernel (one CTA per 128 query rows) and a dK/dV kernel (one CTA per 128 keys, over the query
+ * heads of the KV head): tcgen05 MMA with TMEM accumulators, no atomics, bit-identical reruns
+ * (TESSERA_SM100_ATTN_BWD=mma in the environment selects the earlier mma.sync kernels). workspace: tessera_sm100_flash_attn_bwd_bf16_workspace_bytes(B, Hq, Sq) bytes.
  * tessera_sm100_flash_attn_fwd_lse_device is that forward pass on its own: O plus lse2[B,Hq,Sq] =
  * log2(sum_n exp2(scale*log2(e)*s_n)) over the legal keys (multiply by ln 2 for the natural-log LSE). */
 size_t tessera_sm100_flash_attn_bwd_bf16_workspace_bytes(int B, int Hq, int Sq);

@@ -8,11 +8,13 @@
 // Per tile the MMA warp forms the TRANSPOSED products S^T = K Q^T and dP^T = V dO^T into TMEM
 // (keys on the 128 lanes, query rows along the columns), the four softmax warps (thread = key)
 // turn them in place into bf16 P^T and dS^T, and the MMA warp accumulates dV += P^T dO and
-// dK += dS^T Q with the A operand read straight from TMEM. TMEM: S^T | dP^T | dV | dK, 128 fp32
-// columns each.
+// dK += dS^T Q with the A operand read straight from TMEM. The tile's 128 query rows are handled as
+// two halves of 64 with their own score buffers, so the softmax warps convert one half while the
+// tensor core finishes the other and starts the next tile. TMEM: (S^T_h | dP^T_h) x 2 halves of
+// 64 fp32 columns, then dV and dK, 128 columns each.
 // dq5_kernel: one CTA per 128 query rows of one head. Q and dO stay, K and V stream; S = Q K^T and
 // dP = dO V^T, dS in place (thread = query row, so lse and delta are per-thread scalars), and
-// dQ += dS K. TMEM: S | dP | dQ.
+// dQ += dS K, with the same two-half schedule over the 128 keys of a tile. TMEM: (S_h | dP_h) x 2, dQ.
 // Warps 0-3 softmax + epilogue (TMEM lane = 32 * warp + lane), warp 4 MMA issuer and TMEM owner,
 // warp 5 TMA producer. Every wait is bounded (error word + abort flag), as in the forward kernel.
 #include <cuda_bf16.h>
@@ -55,22 +57,23 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// [128 rows of A] x [128 rows of B]^T over d = 128, both tiles K-major (two swizzled 64-wide halves)
-__device__ __forceinline__ void issue_rows_x_rows(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
+// Half-tile forms for the two-buffer schedule: 64 rows of B per product.
+// d_tmem[128 x 64] = A(128 rows) . B(rows 64h .. 64h+63)^T over d
+__device__ __forceinline__ void issue_rows_x_half(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, int h,
                                                   uint32_t desc_hi, uint32_t idesc) {
+  const uint32_t brow = static_cast<uint32_t>(h * 64 * 128) >> 4;   // 64 rows of 128 B inside each half-tile
 #pragma unroll
   for (int ks = 0; ks < D / 16; ++ks) {
     const uint32_t off = ((ks >> 2) * HALF_BYTES + (ks & 3) * 32) >> 4;
-    umma_f16_ss_parts(d_tmem, a_lo + off, desc_hi, b_lo + off, desc_hi, idesc, ks > 0 ? 1u : 0u);
+    umma_f16_ss_parts(d_tmem, a_lo + off, desc_hi, b_lo + brow + off, desc_hi, idesc, ks > 0 ? 1u : 0u);
   }
 }
-// d_tmem[128 x 128 d] (+)= A (bf16 in TMEM, 128 lanes x 128 contraction) . B (smem tile whose 128
-// rows are the contraction and whose 128 d are contiguous: MN-major, halves HALF_BYTES apart)
-__device__ __forceinline__ void issue_tmem_x_tile(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
+// d_tmem[128 x 128 d] (+)= A (bf16 in TMEM, 128 lanes x 64) . B rows 64h .. 64h+63 of an MN-major tile
+__device__ __forceinline__ void issue_tmem_x_half(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, int h,
                                                   uint32_t desc_hi, uint32_t idesc, bool accumulate) {
 #pragma unroll
-  for (int ks = 0; ks < BLK / 16; ++ks)
-    umma_f16_ts_parts(d_tmem, a_tmem + 8u * ks, b_lo + ((ks * 2048) >> 4), desc_hi, idesc,
+  for (int ks = 0; ks < 4; ++ks)
+    umma_f16_ts_parts(d_tmem, a_tmem + 8u * ks, b_lo + (((4 * h + ks) * 2048) >> 4), desc_hi, idesc,
                       (accumulate || ks > 0) ? 1u : 0u);
 }
 
@@ -114,7 +117,9 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
   const uint32_t kv_full = bars;
   auto q_full = [&](int s) { return bars + 8u * (1 + s); };
   auto q_empty = [&](int s) { return bars + 8u * (3 + s); };
-  const uint32_t s_full = bars + 8u * 5, p_full = bars + 8u * 6, o_full = bars + 8u * 7;
+  auto s_full = [&](int h) { return bars + 8u * (5 + h); };   // scores of half h (64 query rows) ready
+  auto p_full = [&](int h) { return bars + 8u * (7 + h); };   // P^T / dS^T of half h written
+  const uint32_t o_full = bars + 8u * 9;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + SMEM_BAR_OFF + 128);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + SMEM_BAR_OFF + 132);
   float* s_lse = reinterpret_cast<float*>(smem_gen + SMEM_STAT_OFF);   // [2][128]
@@ -137,8 +142,10 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       mbar_init(q_full(s), 1);
       mbar_init(q_empty(s), 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(p_full, 4);   // one arrival per softmax warp
+    for (int h = 0; h < 2; ++h) {
+      mbar_init(s_full(h), 1);
+      mbar_init(p_full(h), 4);   // one arrival per softmax warp
+    }
     mbar_init(o_full, 1);
     fence_mbar_init();
   }
@@ -150,7 +157,10 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdV = tmem_base + 256, tdK = tmem_base + 384;
+  // TMEM: per half h of the query tile S^T_h (64 columns) | dP^T_h (64), then dV and dK
+  auto tS = [&](int h) { return tmem_base + static_cast<uint32_t>(128 * h); };
+  auto tdP = [&](int h) { return tmem_base + static_cast<uint32_t>(128 * h + 64); };
+  const uint32_t tdV = tmem_base + 256, tdK = tmem_base + 384;
 
   if (warp == 5) {
     // ------------------------------------------------------------------ TMA producer
@@ -179,7 +189,7 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
   } else if (warp == 4) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && iters > 0) {
-      const uint32_t idesc_ss = make_idesc_f16(true, false, false, BLK, BLK);   // rows x rows over d
+      const uint32_t idesc_ss = make_idesc_f16(true, false, false, BLK, 64);    // 128 keys x 64 query rows
       const uint32_t idesc_ts = make_idesc_f16(true, false, true, BLK, D);      // TMEM A, N-major B
       const uint32_t desc_hi = smem_desc_hi(1024);
       const uint32_t k_lo = smem_desc_lo(sK, 16), v_lo = smem_desc_lo(sV, 16);
@@ -188,24 +198,32 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       const uint32_t qn_lo[2] = {smem_desc_lo(sQ, HALF_BYTES), smem_desc_lo(sQ + TILE_BYTES, HALF_BYTES)};
       const uint32_t gn_lo[2] = {smem_desc_lo(sdO, HALF_BYTES), smem_desc_lo(sdO + TILE_BYTES, HALF_BYTES)};
       bool ok = mbar_wait(kv_full, 0, abort_flag, p.err, kErrWaitFull, 1000);
-      auto issue_scores = [&](int it) {
+      // The tile's 128 query rows are handled as two halves with their own TMEM buffers, so the
+      // softmax warps work on one half while the tensor core finishes the other and starts the
+      // next tile's scores.
+      auto issue_scores = [&](int it, int h) {
         const int st = it & 1;
-        if (!(ok = mbar_wait(q_full(st), (it >> 1) & 1, abort_flag, p.err, kErrWaitFull, it))) return;
-        tc_fence_after();
-        issue_rows_x_rows(tS, k_lo, q_lo[st], desc_hi, idesc_ss);     // S^T  = K Q^T
-        issue_rows_x_rows(tdP, v_lo, g_lo[st], desc_hi, idesc_ss);    // dP^T = V dO^T
-        umma_commit(s_full);
+        if (h == 0) {
+          if (!(ok = mbar_wait(q_full(st), (it >> 1) & 1, abort_flag, p.err, kErrWaitFull, it))) return;
+          tc_fence_after();
+        }
+        issue_rows_x_half(tS(h), k_lo, q_lo[st], h, desc_hi, idesc_ss);     // S^T_h  = K Q_h^T
+        issue_rows_x_half(tdP(h), v_lo, g_lo[st], h, desc_hi, idesc_ss);    // dP^T_h = V dO_h^T
+        umma_commit(s_full(h));
       };
-      if (ok) issue_scores(0);
+      if (ok) issue_scores(0, 0);
+      if (ok) issue_scores(0, 1);
       for (int it = 0; it < iters && ok; ++it) {
         const int st = it & 1;
-        if (!(ok = mbar_wait(p_full, it & 1, abort_flag, p.err, kErrWaitOther, 2000 + it))) break;
-        tc_fence_after();
-        issue_tmem_x_tile(tdV, tS, gn_lo[st], desc_hi, idesc_ts, it > 0);    // dV += P^T dO
-        issue_tmem_x_tile(tdK, tdP, qn_lo[st], desc_hi, idesc_ts, it > 0);   // dK += dS^T Q
-        umma_commit(q_empty(st));
-        if (it + 1 < iters) issue_scores(it + 1);
-        else umma_commit(o_full);
+        for (int h = 0; h < 2 && ok; ++h) {
+          if (!(ok = mbar_wait(p_full(h), it & 1, abort_flag, p.err, kErrWaitOther, 2000 + it))) break;
+          tc_fence_after();
+          issue_tmem_x_half(tdV, tS(h), gn_lo[st], h, desc_hi, idesc_ts, it > 0 || h > 0);    // dV += P^T_h dO_h
+          issue_tmem_x_half(tdK, tdP(h), qn_lo[st], h, desc_hi, idesc_ts, it > 0 || h > 0);   // dK += dS^T_h Q_h
+          if (h == 1) umma_commit(q_empty(st));
+          if (it + 1 < iters) issue_scores(it + 1, h);
+          else if (h == 1) umma_commit(o_full);
+        }
       }
     }
   } else {
@@ -223,33 +241,36 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       del_n = m < p.Sq ? p.delta[row] : 0.f;
     };
     if (iters > 0) fetch_stats(0);
-    for (int it = 0; it < iters && ok; ++it) {
+    // Every thread runs every iteration and meets the named barrier even after a wait has given up
+    // (`ok` only gates the work): a thread that left early would leave the others at the barrier.
+    for (int it = 0; it < iters; ++it) {
       const int sl = (it & 1) * BLK;
       s_lse[sl + r] = lse_n;
       s_del[sl + r] = del_n;
       if (it + 1 < iters) fetch_stats(it + 1);
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (!(ok = mbar_wait(s_full, it & 1, abort_flag, p.err, kErrWaitTmemFull, it))) break;
-      tc_fence_after();
       const int m0 = m0_of(it);
       // query rows of this tile the key is legal for: m >= key - shift (causal)
       const int m_first = p.causal ? key - p.shift : -0x40000000;
 #pragma unroll 1
-      for (int cp = 0; cp < 2; ++cp) {            // 64 query columns per pass
+      for (int h = 0; h < 2; ++h) {            // 64 query columns per half
+        if (ok) ok = mbar_wait(s_full(h), it & 1, abort_flag, p.err, kErrWaitTmemFull, it);
+        if (!ok) continue;
+        tc_fence_after();
         uint32_t pk[32], dk[32];
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-          const int c0 = (cp * 2 + half) * 32;
+          const int c0 = half * 32;
           uint32_t s[32], g[32];
-          tmem_ld_32x32b_x32(tS + lane_base + c0, s);
-          tmem_ld_32x32b_x32(tdP + lane_base + c0, g);
+          tmem_ld_32x32b_x32(tS(h) + lane_base + c0, s);
+          tmem_ld_32x32b_x32(tdP(h) + lane_base + c0, g);
           tmem_ld_wait();
 #pragma unroll
           for (int k = 0; k < 32; k += 2) {
             float pe[2], ds[2];
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-              const int col = c0 + k + e;
+              const int col = 64 * h + c0 + k + e;
               const bool legal = key_ok && (m0 + col >= m_first);
               const float x = __uint_as_float(s[k + e]) * p.scale_log2 - s_lse[sl + col];
               pe[e] = legal ? ex2(x) : 0.f;
@@ -259,14 +280,14 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
             dk[half * 16 + (k >> 1)] = pack_bf16(ds[0], ds[1]);
           }
         }
-        // bf16 P^T / dS^T over the columns already consumed: 64 fp32 columns -> 32 packed columns
-        tmem_st_32x32b_x32(tS + lane_base + cp * 32, pk);
-        tmem_st_32x32b_x32(tdP + lane_base + cp * 32, dk);
+        // bf16 P^T_h / dS^T_h over the columns just consumed: 64 fp32 columns -> 32 packed columns
+        tmem_st_32x32b_x32(tS(h) + lane_base, pk);
+        tmem_st_32x32b_x32(tdP(h) + lane_base, dk);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full(h));
       }
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
     }
     // ---- epilogue: dV, scale * dK -> bf16 -> swizzled smem (the Q ring) -> TMA store
     if (iters > 0) {
@@ -315,7 +336,9 @@ dq5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   const uint32_t q_full = bars;
   auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
   auto kv_empty = [&](int s) { return bars + 8u * (3 + s); };
-  const uint32_t s_full = bars + 8u * 5, p_full = bars + 8u * 6, o_full = bars + 8u * 7;
+  auto s_full = [&](int h) { return bars + 8u * (5 + h); };
+  auto p_full = [&](int h) { return bars + 8u * (7 + h); };
+  const uint32_t o_full = bars + 8u * 9;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + SMEM_BAR_OFF + 128);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + SMEM_BAR_OFF + 132);
 
@@ -334,8 +357,10 @@ dq5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       mbar_init(kv_full(s), 1);
       mbar_init(kv_empty(s), 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(p_full, 4);
+    for (int h = 0; h < 2; ++h) {
+      mbar_init(s_full(h), 1);
+      mbar_init(p_full(h), 4);
+    }
     mbar_init(o_full, 1);
     fence_mbar_init();
   }
@@ -347,7 +372,10 @@ dq5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdQ = tmem_base + 256;
+  // TMEM: per half h of the key tile S_h (64 columns) | dP_h (64), then dQ
+  auto tS = [&](int h) { return tmem_base + static_cast<uint32_t>(128 * h); };
+  auto tdP = [&](int h) { return tmem_base + static_cast<uint32_t>(128 * h + 64); };
+  const uint32_t tdQ = tmem_base + 256;
 
   if (warp == 5) {
     if (lane == 0 && iters > 0) {
@@ -373,7 +401,7 @@ dq5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     }
   } else if (warp == 4) {
     if (lane == 0 && iters > 0) {
-      const uint32_t idesc_ss = make_idesc_f16(true, false, false, BLK, BLK);
+      const uint32_t idesc_ss = make_idesc_f16(true, false, false, BLK, 64);
       const uint32_t idesc_ts = make_idesc_f16(true, false, true, BLK, D);
       const uint32_t desc_hi = smem_desc_hi(1024);
       const uint32_t q_lo = smem_desc_lo(sQ, 16), g_lo = smem_desc_lo(sdO, 16);
@@ -381,23 +409,28 @@ dq5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       const uint32_t v_lo[2] = {smem_desc_lo(sV, 16), smem_desc_lo(sV + TILE_BYTES, 16)};
       const uint32_t kn_lo[2] = {smem_desc_lo(sK, HALF_BYTES), smem_desc_lo(sK + TILE_BYTES, HALF_BYTES)};
       bool ok = mbar_wait(q_full, 0, abort_flag, p.err, kErrWaitFull, 1000);
-      auto issue_scores = [&](int it) {
+      auto issue_scores = [&](int it, int h) {
         const int st = it & 1;
-        if (!(ok = mbar_wait(kv_full(st), (it >> 1) & 1, abort_flag, p.err, kErrWaitFull, it))) return;
-        tc_fence_after();
-        issue_rows_x_rows(tS, q_lo, k_lo[st], desc_hi, idesc_ss);     // S  = Q K^T
-        issue_rows_x_rows(tdP, g_lo, v_lo[st], desc_hi, idesc_ss);    // dP = dO V^T
-        umma_commit(s_full);
+        if (h == 0) {
+          if (!(ok = mbar_wait(kv_full(st), (it >> 1) & 1, abort_flag, p.err, kErrWaitFull, it))) return;
+          tc_fence_after();
+        }
+        issue_rows_x_half(tS(h), q_lo, k_lo[st], h, desc_hi, idesc_ss);     // S_h  = Q K_h^T
+        issue_rows_x_half(tdP(h), g_lo, v_lo[st], h, desc_hi, idesc_ss);    // dP_h = dO V_h^T
+        umma_commit(s_full(h));
       };
-      if (ok) issue_scores(0);
+      if (ok) issue_scores(0, 0);
+      if (ok) issue_scores(0, 1);
       for (int it = 0; it < iters && ok; ++it) {
         const int st = it & 1;
-        if (!(ok = mbar_wait(p_full, it & 1, abort_flag, p.err, kErrWaitOther, 2000 + it))) break;
-        tc_fence_after();
-        issue_tmem_x_tile(tdQ, tdP, kn_lo[st], desc_hi, idesc_ts, it > 0);   // dQ += dS K
-        umma_commit(kv_empty(st));
-        if (it + 1 < iters) issue_scores(it + 1);
-        else umma_commit(o_full);
+        for (int h = 0; h < 2 && ok; ++h) {
+          if (!(ok = mbar_wait(p_full(h), it & 1, abort_flag, p.err, kErrWaitOther, 2000 + it))) break;
+          tc_fence_after();
+          issue_tmem_x_half(tdQ, tdP(h), kn_lo[st], h, desc_hi, idesc_ts, it > 0 || h > 0);   // dQ += dS_h K_h
+          if (h == 1) umma_commit(kv_empty(st));
+          if (it + 1 < iters) issue_scores(it + 1, h);
+          else if (h == 1) umma_commit(o_full);
+        }
       }
     }
   } else {
@@ -411,18 +444,18 @@ dq5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     const int n_last = p.causal ? min(m + p.shift, p.Sk - 1) : p.Sk - 1;   // last legal key
     bool ok = true;
     for (int it = 0; it < iters && ok; ++it) {
-      if (!(ok = mbar_wait(s_full, it & 1, abort_flag, p.err, kErrWaitTmemFull, it))) break;
-      tc_fence_after();
-      const int nb = it * BLK;
 #pragma unroll 1
-      for (int cp = 0; cp < 2; ++cp) {
+      for (int h = 0; h < 2 && ok; ++h) {
+        if (!(ok = mbar_wait(s_full(h), it & 1, abort_flag, p.err, kErrWaitTmemFull, it))) break;
+        tc_fence_after();
+        const int nb = it * BLK + 64 * h;
         uint32_t dk[32];
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-          const int c0 = (cp * 2 + half) * 32;
+          const int c0 = half * 32;
           uint32_t s[32], g[32];
-          tmem_ld_32x32b_x32(tS + lane_base + c0, s);
-          tmem_ld_32x32b_x32(tdP + lane_base + c0, g);
+          tmem_ld_32x32b_x32(tS(h) + lane_base + c0, s);
+          tmem_ld_32x32b_x32(tdP(h) + lane_base + c0, g);
           tmem_ld_wait();
 #pragma unroll
           for (int k = 0; k < 32; k += 2) {
@@ -436,12 +469,12 @@ dq5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             dk[half * 16 + (k >> 1)] = pack_bf16(ds[0], ds[1]);
           }
         }
-        tmem_st_32x32b_x32(tdP + lane_base + cp * 32, dk);
+        tmem_st_32x32b_x32(tdP(h) + lane_base, dk);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full(h));
       }
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
     }
     if (iters > 0) {
       if (ok) ok = mbar_wait(o_full, 0, abort_flag, p.err, kErrWaitTmemFull, 9000);

@@ -346,10 +346,21 @@ def bench_attn_backward(ranks, args, peaks, peak_kind):
                            gk.ptr, gv.ptr, B, Hl, Hl, S, S, scale, 1, ws.ptr, None)
     times = timed_steps(ranks, device, fn, args.steps, args.warmup)
     ms = statistics.mean(times)
+    # the same gradients from a kept forward state (O and the row log-sum-exps): no recompute
+    o = DeviceArray.zeros((B, Hl, S, D), bfloat16)
+    lse = DeviceArray.zeros((B, Hl, S), np.float32)
+    dscr = DeviceArray.zeros((B, Hl, S), np.float32)
+    _lib.call("tessera_sm100_flash_attn_fwd_lse_device", dq.ptr, dk.ptr, dv.ptr, o.ptr, lse.ptr, B, Hl, Hl, S, S, D,
+              scale, 1, None)
+    fn2 = lambda: _lib.call("tessera_sm100_flash_attn_bwd_bf16_saved_device", dg.ptr, dq.ptr, dk.ptr, dv.ptr, o.ptr,
+                            lse.ptr, gq.ptr, gk.ptr, gv.ptr, B, Hl, Hl, S, S, scale, 1, dscr.ptr, None)
+    ms_saved = statistics.mean(timed_steps(ranks, device, fn2, args.steps, args.warmup))
     flops = 10.0 * B * H * S * S * D / 2
     ach = flops / W / ms / 1e9
     return {"metric": "causal flash-attention backward TFLOP/s", "value": flops / ms / 1e9, "unit": "TFLOP/s",
-            "ms_per_step": ms, "config": f"B={B} H={H} S={S} D={D} bf16 causal, heads sharded /{W}",
+            "ms_per_step": ms, "ms_per_step_from_saved_forward_state": ms_saved,
+            "tflops_from_saved_forward_state": flops / ms_saved / 1e9,
+            "config": f"B={B} H={H} S={S} D={D} bf16 causal, heads sharded /{W}",
             "flops_convention": "10*B*H*S^2*D/2 (five S x S x D products; the kernels form seven, plus the "
                                 "forward recompute, all inside the timed step)",
             "device_error": device.consume_device_error()[0],

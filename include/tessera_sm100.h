@@ -354,6 +354,13 @@ int tessera_sm100_flash_attn_bwd_bf16_device(const void* dO, const void* Q, cons
 int tessera_sm100_flash_attn_fwd_lse_device(const void* Q, const void* K, const void* V, void* O,
                                             float* lse2, int B, int Hq, int Hkv, int Sq, int Sk, int D,
                                             float scale, int causal, void* stream);
+/* The backward of a step that kept O and lse2 from tessera_sm100_flash_attn_fwd_lse_device: no
+ * forward recompute. delta_scratch: B*Hq*Sq device floats. Same gradients, bit for bit. */
+int tessera_sm100_flash_attn_bwd_bf16_saved_device(const void* dO, const void* Q, const void* K,
+                                                   const void* V, const void* O, const float* lse2,
+                                                   void* dQ, void* dK, void* dV, int B, int Hq, int Hkv,
+                                                   int Sq, int Sk, float scale, int causal,
+                                                   float* delta_scratch, void* stream);
 
 /* ---- max-shifted attention states -----------------------------------------------------------
  * ops.softmax_merge / softmax_finalize (python/tessera/_block_attnres_ops.py:104-146): a state is

@@ -134,6 +134,8 @@ _SIGNATURES = {
     "tessera_sm100_flash_attn_bwd_bf16_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "tessera_sm100_flash_attn_bwd_bf16_device": (c_int, [_VP] * 7 + [c_int, c_int, c_int, c_int, c_int, c_float,
                                                          c_int, _VP, _VP]),
+    "tessera_sm100_flash_attn_bwd_bf16_saved_device": (c_int, [_VP] * 9 + [c_int, c_int, c_int, c_int, c_int,
+                                                               c_float, c_int, _VP, _VP]),
     "tessera_sm100_flash_attn_fwd_lse_device": (c_int, [_VP] * 5 + [c_int, c_int, c_int, c_int, c_int, c_int,
                                                         c_float, c_int, _VP]),
     "tessera_sm100_quantize_nvfp4_device": (c_int, [_VP, c_longlong, c_longlong, c_int, _VP, _VP, _VP]),

@@ -361,6 +361,10 @@ size_t tessera_sm100_flash_attn_bwd_bf16_workspace_bytes(int B, int Hq, int Sq) 
 
 // dO, Q, dQ [B,Hq,Sq,128]; K, V, dK, dV [B,Hkv,Sk,128], bf16, dense. causal uses the bottom-right
 // alignment of tessera.ops.flash_attn (identical to the lane's mask when Sq >= Sk).
+static int bwd_bf16_from_state(const void* dO, const void* Q, const void* K, const void* V, const void* O,
+                               const float* lse2, float* delta, void* dQ, void* dK, void* dV, int B, int Hq,
+                               int Hkv, int Sq, int Sk, float scale, int causal, cudaStream_t st);
+
 int tessera_sm100_flash_attn_bwd_bf16_device(const void* dO, const void* Q, const void* K, const void* V,
                                              void* dQ, void* dK, void* dV, int B, int Hq, int Hkv, int Sq,
                                              int Sk, float scale, int causal, void* workspace,
@@ -380,6 +384,30 @@ int tessera_sm100_flash_attn_bwd_bf16_device(const void* dO, const void* Q, cons
   if (int rc = attn_prefill::launch_with_lse(Q, K, V, O, lse2, B, Hq, Hkv, Sq, Sk, attn_bwd_tc::D, scale,
                                              causal, st))
     return rc;
+  return bwd_bf16_from_state(dO, Q, K, V, O, lse2, delta, dQ, dK, dV, B, Hq, Hkv, Sq, Sk, scale, causal, st);
+}
+
+// The backward of a training step that kept the forward's output and row log-sum-exps
+// (tessera_sm100_flash_attn_fwd_lse_device): no forward recompute. delta_scratch: B*Hq*Sq floats.
+int tessera_sm100_flash_attn_bwd_bf16_saved_device(const void* dO, const void* Q, const void* K,
+                                                   const void* V, const void* O, const float* lse2,
+                                                   void* dQ, void* dK, void* dV, int B, int Hq, int Hkv,
+                                                   int Sq, int Sk, float scale, int causal,
+                                                   float* delta_scratch, void* stream) {
+  if (!dO || !Q || !K || !V || !O || !lse2 || !dQ || !dK || !dV || !delta_scratch || B <= 0 || Hq <= 0 ||
+      Hkv <= 0 || Hq % Hkv || Sq <= 0 || Sk <= 0 || !(scale > 0.f)) {
+    set_last_error("flash_attn_bwd_bf16_saved: null pointer, non-positive size or scale, or Hq not divisible by Hkv");
+    return kBadArg;
+  }
+  if (int rc = ensure_device()) return rc;
+  return bwd_bf16_from_state(dO, Q, K, V, O, lse2, delta_scratch, dQ, dK, dV, B, Hq, Hkv, Sq, Sk, scale, causal,
+                             static_cast<cudaStream_t>(stream));
+}
+
+static int bwd_bf16_from_state(const void* dO, const void* Q, const void* K, const void* V, const void* O,
+                               const float* lse2, float* delta, void* dQ, void* dK, void* dV, int B, int Hq,
+                               int Hkv, int Sq, int Sk, float scale, int causal, cudaStream_t st) {
+  const size_t rows = static_cast<size_t>(B) * Hq * Sq;
   attn_bwd_tc::delta_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, st>>>(
       static_cast<const __nv_bfloat16*>(dO), static_cast<const __nv_bfloat16*>(O), delta,
       static_cast<long long>(rows));

@@ -179,3 +179,50 @@ def test_forward_with_lse_matches_the_oracle():
         np.testing.assert_allclose(lse.download()[0, h], want, atol=2e-3, rtol=0)
     assert rel_err(o.download().astype(np.float32),
                    orc.attention_lane(q, k, v, scale=scale, causal=True, causal_shift=shift)) < 2e-2
+
+
+def test_backward_from_saved_forward_state_is_bit_identical():
+    rng = np.random.default_rng(21)
+    B, Hq, Hkv, Sq, Sk, D = 1, 4, 2, 200, 260, 128
+    q, k, v, do = (rng.standard_normal(s, dtype=np.float32).astype(bfloat16)
+                   for s in ((B, Hq, Sq, D), (B, Hkv, Sk, D), (B, Hkv, Sk, D), (B, Hq, Sq, D)))
+    scale = 1 / np.sqrt(D)
+    want = tessera.ops.flash_attn_backward(do, q, k, v, scale=scale, causal=True, causal_alignment="bottom_right")
+    dq_, dk_, dv_, dg = (DeviceArray.from_host(t) for t in (q, k, v, do))
+    o, lse = DeviceArray((B, Hq, Sq, D), bfloat16), DeviceArray((B, Hq, Sq), np.float32)
+    _lib.call("tessera_sm100_flash_attn_fwd_lse_device", dq_.ptr, dk_.ptr, dv_.ptr, o.ptr, lse.ptr, B, Hq, Hkv, Sq,
+              Sk, D, ctypes.c_float(scale), 1, None)
+    gq, gk, gv = DeviceArray(q.shape, bfloat16), DeviceArray(k.shape, bfloat16), DeviceArray(v.shape, bfloat16)
+    scr = DeviceArray((B, Hq, Sq), np.float32)
+    _lib.call("tessera_sm100_flash_attn_bwd_bf16_saved_device", dg.ptr, dq_.ptr, dk_.ptr, dv_.ptr, o.ptr, lse.ptr,
+              gq.ptr, gk.ptr, gv.ptr, B, Hq, Hkv, Sq, Sk, ctypes.c_float(scale), 1, scr.ptr, None)
+    for a, e in zip((gq, gk, gv), want):
+        np.testing.assert_array_equal(a.download().view(np.uint16), e.view(np.uint16))
+    no_device_error()
+
+
+def test_mma_sync_kernels_stay_correct():
+    """The earlier mma.sync kernels are selected by an environment variable read once per process."""
+    import subprocess
+    import sys
+    code = (
+        "import numpy as np\n"
+        "import tessera_b200 as tessera\n"
+        "from tessera_b200.device import bfloat16\n"
+        "from oracle import tessera_oracle as orc\n"
+        "rng = np.random.default_rng(5)\n"
+        "q = rng.standard_normal((1, 4, 150, 128), dtype=np.float32).astype(bfloat16)\n"
+        "k = rng.standard_normal((1, 2, 220, 128), dtype=np.float32).astype(bfloat16)\n"
+        "v = rng.standard_normal((1, 2, 220, 128), dtype=np.float32).astype(bfloat16)\n"
+        "g = rng.standard_normal((1, 4, 150, 128), dtype=np.float32).astype(bfloat16)\n"
+        "s = 128 ** -0.5\n"
+        "got = tessera.ops.flash_attn_backward(g, q, k, v, scale=s, causal=True, causal_alignment='bottom_right')\n"
+        "ref = orc.attention_lane_backward(g, q, k, v, scale=s, causal=True, causal_shift=70)\n"
+        "err = max(orc.max_rel_err(a.astype(np.float32), e) for a, e in zip(got, ref))\n"
+        "assert err < 2e-2, err\n"
+        "print('ok', err)\n")
+    env = dict(os.environ, TESSERA_SM100_ATTN_BWD="mma")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
+    res = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0 and "ok" in res.stdout, res.stdout + res.stderr

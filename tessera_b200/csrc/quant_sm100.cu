@@ -34,8 +34,16 @@ template <typename T>
 __global__ void amax_kernel(const T* __restrict__ x, long long seg, unsigned int* __restrict__ out) {
   const T* xs = x + static_cast<long long>(blockIdx.y) * seg;
   float a = 0.f;
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < seg;
-       i += static_cast<long long>(gridDim.x) * blockDim.x)
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  constexpr int kVec = 16 / sizeof(T);   // elements per 16-byte load
+  const long long nv = (reinterpret_cast<uintptr_t>(xs) & 15) ? 0 : seg / kVec;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nv; i += stride) {
+    const uint4 w = reinterpret_cast<const uint4*>(xs)[i];
+    const T* h = reinterpret_cast<const T*>(&w);
+#pragma unroll
+    for (int j = 0; j < kVec; ++j) a = fmaxf(a, fabsf(to_f32(h[j])));
+  }
+  for (long long i = nv * kVec + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < seg; i += stride)
     a = fmaxf(a, fabsf(to_f32(xs[i])));
 #pragma unroll
   for (int sh = 16; sh; sh >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, sh));
@@ -53,8 +61,26 @@ __global__ void quantize_kernel(const T* __restrict__ x, long long n,
     scale_out[0] = scale;
     scale_out[1] = amax;
   }
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
-       i += static_cast<long long>(gridDim.x) * blockDim.x)
+  // four elements per thread and step: one packed 4-byte store (this pass is pure memory traffic)
+  const long long n4 = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(q)) & 15) ? 0 : n / 4;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    float v[4];
+    if constexpr (sizeof(T) == 4) {
+      const float4 f = reinterpret_cast<const float4*>(x)[i];
+      v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+    } else {
+      const uint2 w = reinterpret_cast<const uint2*>(x)[i];
+      const T* h = reinterpret_cast<const T*>(&w);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = to_f32(h[j]);
+    }
+    uint32_t packed = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) packed |= static_cast<uint32_t>(to_e4m3(v[j], scale)) << (8 * j);
+    reinterpret_cast<uint32_t*>(q)[i] = packed;
+  }
+  for (long long i = 4 * n4 + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
     q[i] = to_e4m3(to_f32(x[i]), scale);
 }
 
@@ -89,7 +115,7 @@ __global__ void quantize_transpose_kernel(const T* __restrict__ w, int K, int N,
 template <typename T>
 int quantize_t(const void* x, long long n, void* q, float* scale_out, unsigned int* amax_bits,
                bool have_amax, cudaStream_t st) {
-  const int blocks = (int)std::min<long long>((n + 255) / 256, 148 * 8);
+  const int blocks = (int)std::min<long long>((n / 4 + 255) / 256 + 1, 148 * 16);
   if (!have_amax) {
     TSB_CUDA_OK(cudaMemsetAsync(amax_bits, 0, sizeof(unsigned int), st));
     amax_kernel<T><<<dim3(blocks, 1), 256, 0, st>>>(static_cast<const T*>(x), n, amax_bits);

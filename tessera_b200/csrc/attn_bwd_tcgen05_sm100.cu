@@ -47,6 +47,21 @@ struct Params {
   int* err;
 };
 
+// Optional timeline of one dK/dV CTA (compile with -DTESSERA_BWD_TRACE): clock64 stamps of the hand-offs
+// between the softmax warps and the MMA warp, read back with tessera_sm100_bwd_trace_read. Not part
+// of the normal build.
+#ifdef TESSERA_BWD_TRACE
+__device__ long long g_bwd_trace[2 * 4096];
+#define BW_TRACE(role, idx)                                                              \
+  do {                                                                                   \
+    if (trace_on && (idx) < 4096) g_bwd_trace[(role) * 4096 + (idx)] = clock64();        \
+  } while (0)
+#else
+#define BW_TRACE(role, idx) \
+  do {                      \
+  } while (0)
+#endif
+
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -141,6 +156,9 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BLK, hk = blockIdx.y, b = blockIdx.z;
+#ifdef TESSERA_BWD_TRACE
+  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp == 0 || warp == 4);
+#endif
   const int ratio = p.Hq / p.Hkv;
   const int nqb = (p.Sq + BLK - 1) / BLK;
   const int i_start = p.causal ? max(0, n0 - p.shift) / BLK : 0;   // first block with a legal row
@@ -230,13 +248,17 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       for (int it = 0; it < iters && ok; ++it) {
         const int st = it & 1;
         for (int h = 0; h < 2 && ok; ++h) {
+          BW_TRACE(1, (it * 2 + h) * 4 + 0);
           if (!(ok = mbar_wait(p_full(h), it & 1, abort_flag, p.err, kErrWaitOther, 2000 + it))) break;
+          BW_TRACE(1, (it * 2 + h) * 4 + 1);
           tc_fence_after();
           issue_tmem_x_half(tdV, tS(h), gn_lo[st], h, desc_hi, idesc_ts, it > 0 || h > 0);    // dV += P^T_h dO_h
           issue_tmem_x_half(tdK, tdP(h), qn_lo[st], h, desc_hi, idesc_ts, it > 0 || h > 0);   // dK += dS^T_h Q_h
           if (h == 1) umma_commit(q_empty(st));
+          BW_TRACE(1, (it * 2 + h) * 4 + 2);
           if (it + 1 < iters) issue_scores(it + 1, h);
           else if (h == 1) umma_commit(o_full);
+          BW_TRACE(1, (it * 2 + h) * 4 + 3);
         }
       }
     }
@@ -268,8 +290,10 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       const int m_first = p.causal ? key - p.shift : -0x40000000;
 #pragma unroll 1
       for (int h = 0; h < 2; ++h) {            // 64 query columns per half
+        BW_TRACE(0, (it * 2 + h) * 4 + 0);
         if (ok) ok = mbar_wait(s_full(h), it & 1, abort_flag, p.err, kErrWaitTmemFull, it);
         if (!ok) continue;
+        BW_TRACE(0, (it * 2 + h) * 4 + 1);
         tc_fence_after();
         uint32_t pk[32], dk[32];
 #pragma unroll
@@ -295,12 +319,14 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
           }
         }
         // bf16 P^T_h / dS^T_h over the columns just consumed: 64 fp32 columns -> 32 packed columns
+        BW_TRACE(0, (it * 2 + h) * 4 + 2);
         tmem_st_32x32b_x32(tS(h) + lane_base, pk);
         tmem_st_32x32b_x32(tdP(h) + lane_base, dk);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(p_full(h));
+        BW_TRACE(0, (it * 2 + h) * 4 + 3);
       }
     }
     // ---- epilogue: dV, scale * dK -> bf16 -> swizzled smem (the Q ring) -> TMA store
@@ -567,3 +593,9 @@ int launch(const void* dO, const void* Q, const void* K, const void* V, void* dQ
 
 }  // namespace attn_bwd5
 }  // namespace tsb
+
+#ifdef TESSERA_BWD_TRACE
+extern "C" int tessera_sm100_bwd_trace_read(long long* out, int n) {
+  return cudaMemcpyFromSymbol(out, tsb::attn_bwd5::g_bwd_trace, sizeof(long long) * n) == cudaSuccess ? 0 : 3;
+}
+#endif

@@ -8,13 +8,16 @@
 // Per tile the MMA warp forms the TRANSPOSED products S^T = K Q^T and dP^T = V dO^T into TMEM
 // (keys on the 128 lanes, query rows along the columns), the four softmax warps (thread = key)
 // turn them in place into bf16 P^T and dS^T, and the MMA warp accumulates dV += P^T dO and
-// dK += dS^T Q with the A operand read straight from TMEM. The tile's 128 query rows are handled as
-// two halves of 64 with their own score buffers, so the softmax warps convert one half while the
-// tensor core finishes the other and starts the next tile. TMEM: (S^T_h | dP^T_h) x 2 halves of
-// 64 fp32 columns, then dV and dK, 128 columns each.
+// dK += dS^T Q with the A operand read straight from TMEM. TMEM: S^T | dP^T | dV | dK, 128 fp32
+// columns each, all four products at full width (a 128 x 64 shared-shared MMA is bound by operand
+// delivery, measured). The overlap comes from handing the two score buffers over separately:
+//   softmax:  P^T(t) from S^T(t) (kept packed in registers too) | dS^T(t) from dP^T(t) and P^T(t) | P^T(t+1) ...
+//   tensor :  dV += P^T(t) dO(t), then S^T(t+1) over the freed buffer | dK += dS^T(t) Q(t), then dP^T(t+1)
+// so the conversion of one buffer runs while the tensor core works on the other.
 // dq5_kernel: one CTA per 128 query rows of one head. Q and dO stay, K and V stream; S = Q K^T and
-// dP = dO V^T, dS in place (thread = query row, so lse and delta are per-thread scalars), and
-// dQ += dS K, with the same two-half schedule over the 128 keys of a tile. TMEM: (S_h | dP_h) x 2, dQ.
+// dP = dO V^T; thread = query row, so lse and delta are per-thread scalars. P is only needed in
+// registers, so the S buffer is handed back as soon as it has been read (S(t+1) is formed while
+// dS(t) = P(t) (dP(t) - delta) is computed), and dQ += dS K. TMEM: S | dP | dQ.
 // Warps 0-3 softmax + epilogue (TMEM lane = 32 * warp + lane), warp 4 MMA issuer and TMEM owner,
 // warp 5 TMA producer. Every wait is bounded (error word + abort flag), as in the forward kernel.
 #include <cuda_bf16.h>
@@ -86,25 +89,47 @@ __device__ __forceinline__ uint32_t pack_bf16_alu(float lo, float hi) {
 #define PACK_PROB pack_bf16
 #endif
 
-// Half-tile forms for the two-buffer schedule: 64 rows of B per product.
-// d_tmem[128 x 64] = A(128 rows) . B(rows 64h .. 64h+63)^T over d
-__device__ __forceinline__ void issue_rows_x_half(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, int h,
+// [128 rows of A] x [128 rows of B]^T over d = 128, both tiles K-major (two swizzled 64-wide halves)
+__device__ __forceinline__ void issue_rows_x_rows(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
                                                   uint32_t desc_hi, uint32_t idesc) {
-  const uint32_t brow = static_cast<uint32_t>(h * 64 * 128) >> 4;   // 64 rows of 128 B inside each half-tile
 #pragma unroll
   for (int ks = 0; ks < D / 16; ++ks) {
     const uint32_t off = ((ks >> 2) * HALF_BYTES + (ks & 3) * 32) >> 4;
-    umma_f16_ss_parts(d_tmem, a_lo + off, desc_hi, b_lo + brow + off, desc_hi, idesc, ks > 0 ? 1u : 0u);
+    umma_f16_ss_parts(d_tmem, a_lo + off, desc_hi, b_lo + off, desc_hi, idesc, ks > 0 ? 1u : 0u);
   }
 }
-// d_tmem[128 x 128 d] (+)= A (bf16 in TMEM, 128 lanes x 64) . B rows 64h .. 64h+63 of an MN-major tile
-__device__ __forceinline__ void issue_tmem_x_half(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, int h,
+// d_tmem[128 x 128 d] (+)= A (bf16 in TMEM, 128 lanes x 128 contraction) . B (smem tile whose 128
+// rows are the contraction and whose 128 d are contiguous: MN-major, halves HALF_BYTES apart)
+__device__ __forceinline__ void issue_tmem_x_tile(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
                                                   uint32_t desc_hi, uint32_t idesc, bool accumulate) {
 #pragma unroll
-  for (int ks = 0; ks < 4; ++ks)
-    umma_f16_ts_parts(d_tmem, a_tmem + 8u * ks, b_lo + (((4 * h + ks) * 2048) >> 4), desc_hi, idesc,
+  for (int ks = 0; ks < BLK / 16; ++ks)
+    umma_f16_ts_parts(d_tmem, a_tmem + 8u * ks, b_lo + ((ks * 2048) >> 4), desc_hi, idesc,
                       (accumulate || ks > 0) ? 1u : 0u);
 }
+__device__ __forceinline__ uint64_t pack2f(float lo, float hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(__float_as_uint(lo)), "r"(__float_as_uint(hi)));
+  return d;
+}
+__device__ __forceinline__ void unpack2f(uint64_t v, float& lo, float& hi) {
+  uint32_t a, b2;
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b2) : "l"(v));
+  lo = __uint_as_float(a);
+  hi = __uint_as_float(b2);
+}
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b2, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b2), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b2) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b2));
+  return d;
+}
+__device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 
 // accumulator (128 lanes x 128 fp32 columns at t_acc) * mul -> bf16 -> swizzled tile at obuf
 __device__ __forceinline__ void acc_to_smem(uint32_t t_acc, uint32_t obuf, int r, float mul) {
@@ -146,8 +171,10 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
   const uint32_t kv_full = bars;
   auto q_full = [&](int s) { return bars + 8u * (1 + s); };
   auto q_empty = [&](int s) { return bars + 8u * (3 + s); };
-  auto s_full = [&](int h) { return bars + 8u * (5 + h); };   // scores of half h (64 query rows) ready
-  auto p_full = [&](int h) { return bars + 8u * (7 + h); };   // P^T / dS^T of half h written
+  const uint32_t s_full = bars + 8u * 5;     // S^T formed
+  const uint32_t dp_full = bars + 8u * 6;    // dP^T formed
+  const uint32_t p_full = bars + 8u * 7;     // P^T written over S^T
+  const uint32_t ds_full = bars + 8u * 8;    // dS^T written over dP^T
   const uint32_t o_full = bars + 8u * 9;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + SMEM_BAR_OFF + 128);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + SMEM_BAR_OFF + 132);
@@ -174,10 +201,10 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       mbar_init(q_full(s), 1);
       mbar_init(q_empty(s), 1);
     }
-    for (int h = 0; h < 2; ++h) {
-      mbar_init(s_full(h), 1);
-      mbar_init(p_full(h), 4);   // one arrival per softmax warp
-    }
+    mbar_init(s_full, 1);
+    mbar_init(dp_full, 1);
+    mbar_init(p_full, 4);    // one arrival per softmax warp
+    mbar_init(ds_full, 4);
     mbar_init(o_full, 1);
     fence_mbar_init();
   }
@@ -189,10 +216,7 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // TMEM: per half h of the query tile S^T_h (64 columns) | dP^T_h (64), then dV and dK
-  auto tS = [&](int h) { return tmem_base + static_cast<uint32_t>(128 * h); };
-  auto tdP = [&](int h) { return tmem_base + static_cast<uint32_t>(128 * h + 64); };
-  const uint32_t tdV = tmem_base + 256, tdK = tmem_base + 384;
+  const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdV = tmem_base + 256, tdK = tmem_base + 384;
 
   if (warp == 5) {
     // ------------------------------------------------------------------ TMA producer
@@ -221,7 +245,7 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
   } else if (warp == 4) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && iters > 0) {
-      const uint32_t idesc_ss = make_idesc_f16(true, false, false, BLK, 64);    // 128 keys x 64 query rows
+      const uint32_t idesc_ss = make_idesc_f16(true, false, false, BLK, BLK);   // rows x rows over d
       const uint32_t idesc_ts = make_idesc_f16(true, false, true, BLK, D);      // TMEM A, N-major B
       const uint32_t desc_hi = smem_desc_hi(1024);
       const uint32_t k_lo = smem_desc_lo(sK, 16), v_lo = smem_desc_lo(sV, 16);
@@ -230,36 +254,44 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       const uint32_t qn_lo[2] = {smem_desc_lo(sQ, HALF_BYTES), smem_desc_lo(sQ + TILE_BYTES, HALF_BYTES)};
       const uint32_t gn_lo[2] = {smem_desc_lo(sdO, HALF_BYTES), smem_desc_lo(sdO + TILE_BYTES, HALF_BYTES)};
       bool ok = mbar_wait(kv_full, 0, abort_flag, p.err, kErrWaitFull, 1000);
-      // The tile's 128 query rows are handled as two halves with their own TMEM buffers, so the
-      // softmax warps work on one half while the tensor core finishes the other and starts the
-      // next tile's scores.
-      auto issue_scores = [&](int it, int h) {
-        const int st = it & 1;
-        if (h == 0) {
-          if (!(ok = mbar_wait(q_full(st), (it >> 1) & 1, abort_flag, p.err, kErrWaitFull, it))) return;
-          tc_fence_after();
-        }
-        issue_rows_x_half(tS(h), k_lo, q_lo[st], h, desc_hi, idesc_ss);     // S^T_h  = K Q_h^T
-        issue_rows_x_half(tdP(h), v_lo, g_lo[st], h, desc_hi, idesc_ss);    // dP^T_h = V dO_h^T
-        umma_commit(s_full(h));
-      };
-      if (ok) issue_scores(0, 0);
-      if (ok) issue_scores(0, 1);
+      if (ok) ok = mbar_wait(q_full(0), 0, abort_flag, p.err, kErrWaitFull, 0);
+      if (ok) {
+        tc_fence_after();
+        issue_rows_x_rows(tS, k_lo, q_lo[0], desc_hi, idesc_ss);      // S^T(0)  = K Q^T
+        umma_commit(s_full);
+        issue_rows_x_rows(tdP, v_lo, g_lo[0], desc_hi, idesc_ss);     // dP^T(0) = V dO^T
+        umma_commit(dp_full);
+      }
       for (int it = 0; it < iters && ok; ++it) {
-        const int st = it & 1;
-        for (int h = 0; h < 2 && ok; ++h) {
-          BW_TRACE(1, (it * 2 + h) * 4 + 0);
-          if (!(ok = mbar_wait(p_full(h), it & 1, abort_flag, p.err, kErrWaitOther, 2000 + it))) break;
-          BW_TRACE(1, (it * 2 + h) * 4 + 1);
+        const int st = it & 1, nst = st ^ 1;
+        const bool more = it + 1 < iters;
+        BW_TRACE(1, it * 8 + 0);
+        if (!(ok = mbar_wait(p_full, it & 1, abort_flag, p.err, kErrWaitOther, 2000 + it))) break;
+        BW_TRACE(1, it * 8 + 1);
+        tc_fence_after();
+        issue_tmem_x_tile(tdV, tS, gn_lo[st], desc_hi, idesc_ts, it > 0);       // dV += P^T dO
+        BW_TRACE(1, it * 8 + 2);
+        if (more) {
+          // the S^T buffer is free once dV's MMAs (issued just above, executed in order) have read P^T
+          if (!(ok = mbar_wait(q_full(nst), ((it + 1) >> 1) & 1, abort_flag, p.err, kErrWaitFull, it + 1))) break;
           tc_fence_after();
-          issue_tmem_x_half(tdV, tS(h), gn_lo[st], h, desc_hi, idesc_ts, it > 0 || h > 0);    // dV += P^T_h dO_h
-          issue_tmem_x_half(tdK, tdP(h), qn_lo[st], h, desc_hi, idesc_ts, it > 0 || h > 0);   // dK += dS^T_h Q_h
-          if (h == 1) umma_commit(q_empty(st));
-          BW_TRACE(1, (it * 2 + h) * 4 + 2);
-          if (it + 1 < iters) issue_scores(it + 1, h);
-          else if (h == 1) umma_commit(o_full);
-          BW_TRACE(1, (it * 2 + h) * 4 + 3);
+          issue_rows_x_rows(tS, k_lo, q_lo[nst], desc_hi, idesc_ss);            // S^T(t+1)
+          umma_commit(s_full);
         }
+        BW_TRACE(1, it * 8 + 3);
+        if (!(ok = mbar_wait(ds_full, it & 1, abort_flag, p.err, kErrWaitOther, 3000 + it))) break;
+        BW_TRACE(1, it * 8 + 4);
+        tc_fence_after();
+        issue_tmem_x_tile(tdK, tdP, qn_lo[st], desc_hi, idesc_ts, it > 0);      // dK += dS^T Q
+        umma_commit(q_empty(st));
+        BW_TRACE(1, it * 8 + 5);
+        if (more) {
+          issue_rows_x_rows(tdP, v_lo, g_lo[nst], desc_hi, idesc_ss);           // dP^T(t+1)
+          umma_commit(dp_full);
+        } else {
+          umma_commit(o_full);
+        }
+        BW_TRACE(1, it * 8 + 6);
       }
     }
   } else {
@@ -281,53 +313,92 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     // (`ok` only gates the work): a thread that left early would leave the others at the barrier.
     for (int it = 0; it < iters; ++it) {
       const int sl = (it & 1) * BLK;
-      s_lse[sl + r] = lse_n;
-      s_del[sl + r] = del_n;
+      s_lse[sl + r] = -lse_n;   // negated: x = s * scale - lse and dp - delta become packed fmas
+      s_del[sl + r] = -del_n;
       if (it + 1 < iters) fetch_stats(it + 1);
       asm volatile("bar.sync 1, 128;" ::: "memory");
       const int m0 = m0_of(it);
       // query rows of this tile the key is legal for: m >= key - shift (causal)
       const int m_first = p.causal ? key - p.shift : -0x40000000;
-#pragma unroll 1
-      for (int h = 0; h < 2; ++h) {            // 64 query columns per half
-        BW_TRACE(0, (it * 2 + h) * 4 + 0);
-        if (ok) ok = mbar_wait(s_full(h), it & 1, abort_flag, p.err, kErrWaitTmemFull, it);
-        if (!ok) continue;
-        BW_TRACE(0, (it * 2 + h) * 4 + 1);
+      const bool tile_legal = n0 + BLK <= p.Sk && (!p.causal || m0 >= n0 + BLK - 1 - p.shift);
+      const uint64_t scale2 = pack2f(p.scale_log2, p.scale_log2);
+      uint32_t pk[64];   // bf16 P^T of this key row, kept for the dS^T phase
+      // ---- phase 1: P^T = exp2(scale * S^T - lse), written over S^T; dV's MMAs may start
+      BW_TRACE(0, it * 8 + 0);
+      if (ok) ok = mbar_wait(s_full, it & 1, abort_flag, p.err, kErrWaitTmemFull, it);
+      BW_TRACE(0, it * 8 + 1);
+      if (ok) {
         tc_fence_after();
-        uint32_t pk[32], dk[32];
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          const int c0 = half * 32;
-          uint32_t s[32], g[32];
-          tmem_ld_32x32b_x32(tS(h) + lane_base + c0, s);
-          tmem_ld_32x32b_x32(tdP(h) + lane_base + c0, g);
+        for (int c = 0; c < 4; ++c) {
+          uint32_t sv[32];
+          tmem_ld_32x32b_x32(tS + lane_base + 32 * c, sv);
           tmem_ld_wait();
+          if (tile_legal) {   // no mask anywhere in this tile (uniform over the CTA)
 #pragma unroll
-          for (int k = 0; k < 32; k += 2) {
-            float pe[2], ds[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const int col = 64 * h + c0 + k + e;
-              const bool legal = key_ok && (m0 + col >= m_first);
-              const float x = __uint_as_float(s[k + e]) * p.scale_log2 - s_lse[sl + col];
-              pe[e] = legal ? ex2(x) : 0.f;
-              ds[e] = pe[e] * (__uint_as_float(g[k + e]) - s_del[sl + col]);
+            for (int k = 0; k < 32; k += 2) {
+              const uint64_t nl = *reinterpret_cast<const uint64_t*>(s_lse + sl + 32 * c + k);
+              float x0, x1;
+              unpack2f(ffma2(pack2f(__uint_as_float(sv[k]), __uint_as_float(sv[k + 1])), scale2, nl), x0, x1);
+              pk[16 * c + (k >> 1)] = PACK_PROB(ex2(x0), ex2(x1));
             }
-            pk[half * 16 + (k >> 1)] = PACK_PROB(pe[0], pe[1]);
-            dk[half * 16 + (k >> 1)] = PACK_PROB(ds[0], ds[1]);
+          } else {
+#pragma unroll
+            for (int k = 0; k < 32; k += 2) {
+              float pe[2];
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const int col = 32 * c + k + e;
+                const bool legal = key_ok && (m0 + col >= m_first);
+                pe[e] = legal ? ex2(__uint_as_float(sv[k + e]) * p.scale_log2 + s_lse[sl + col]) : 0.f;
+              }
+              pk[16 * c + (k >> 1)] = PACK_PROB(pe[0], pe[1]);
+            }
+          }
+          if (c & 1) {   // 64 fp32 columns consumed -> their 32 packed columns
+            uint32_t (&half)[32] = *reinterpret_cast<uint32_t (*)[32]>(&pk[32 * (c >> 1)]);
+            tmem_st_32x32b_x32(tS + lane_base + 32 * (c >> 1), half);
           }
         }
-        // bf16 P^T_h / dS^T_h over the columns just consumed: 64 fp32 columns -> 32 packed columns
-        BW_TRACE(0, (it * 2 + h) * 4 + 2);
-        tmem_st_32x32b_x32(tS(h) + lane_base, pk);
-        tmem_st_32x32b_x32(tdP(h) + lane_base, dk);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(p_full(h));
-        BW_TRACE(0, (it * 2 + h) * 4 + 3);
+        if (lane == 0) mbar_arrive(p_full);
       }
+      BW_TRACE(0, it * 8 + 2);
+      // ---- phase 2: dS^T = P^T (dP^T - delta), written over dP^T; dK's MMAs may start
+      if (ok) ok = mbar_wait(dp_full, it & 1, abort_flag, p.err, kErrWaitTmemFull, 500 + it);
+      BW_TRACE(0, it * 8 + 3);
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int cp = 0; cp < 2; ++cp) {
+          uint32_t dk[32];
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int c = 2 * cp + half;
+            uint32_t g[32];
+            tmem_ld_32x32b_x32(tdP + lane_base + 32 * c, g);
+            tmem_ld_wait();
+#pragma unroll
+            for (int k = 0; k < 32; k += 2) {
+              const uint32_t pw = pk[16 * c + (k >> 1)];
+              const uint64_t nd = *reinterpret_cast<const uint64_t*>(s_del + sl + 32 * c + k);
+              const uint64_t pp = pack2f(bf16lo(pw), bf16hi(pw));
+              // p * dp + p * (-delta)
+              float d0, d1;
+              unpack2f(ffma2(pp, pack2f(__uint_as_float(g[k]), __uint_as_float(g[k + 1])), fmul2(pp, nd)), d0, d1);
+              dk[16 * half + (k >> 1)] = PACK_PROB(d0, d1);
+            }
+          }
+          tmem_st_32x32b_x32(tdP + lane_base + 32 * cp, dk);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ds_full);
+      }
+      BW_TRACE(0, it * 8 + 4);
     }
     // ---- epilogue: dV, scale * dK -> bf16 -> swizzled smem (the Q ring) -> TMA store
     if (iters > 0) {
@@ -376,8 +447,12 @@ dq5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   const uint32_t q_full = bars;
   auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
   auto kv_empty = [&](int s) { return bars + 8u * (3 + s); };
-  auto s_full = [&](int h) { return bars + 8u * (5 + h); };
-  auto p_full = [&](int h) { return bars + 8u * (7 + h); };
+  const uint32_t s_full = bars + 8u * 5;     // S formed
+  // dP formed, one barrier per dP buffer (each completes every second tile, so a commit for tile t+1
+  // can never run a phase ahead of a warp still waiting for tile t)
+  auto dp_full = [&](int st) { return bars + 8u * (st ? 10 : 6); };
+  const uint32_t s_free = bars + 8u * 7;     // S has been read into registers: the buffer may be overwritten
+  const uint32_t ds_full = bars + 8u * 8;    // dS written over dP
   const uint32_t o_full = bars + 8u * 9;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + SMEM_BAR_OFF + 128);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + SMEM_BAR_OFF + 132);
@@ -397,10 +472,11 @@ dq5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       mbar_init(kv_full(s), 1);
       mbar_init(kv_empty(s), 1);
     }
-    for (int h = 0; h < 2; ++h) {
-      mbar_init(s_full(h), 1);
-      mbar_init(p_full(h), 4);
-    }
+    mbar_init(s_full, 1);
+    mbar_init(dp_full(0), 1);
+    mbar_init(dp_full(1), 1);
+    mbar_init(s_free, 4);    // one arrival per softmax warp
+    mbar_init(ds_full, 4);
     mbar_init(o_full, 1);
     fence_mbar_init();
   }
@@ -412,10 +488,9 @@ dq5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // TMEM: per half h of the key tile S_h (64 columns) | dP_h (64), then dQ
-  auto tS = [&](int h) { return tmem_base + static_cast<uint32_t>(128 * h); };
-  auto tdP = [&](int h) { return tmem_base + static_cast<uint32_t>(128 * h + 64); };
-  const uint32_t tdQ = tmem_base + 256;
+  // TMEM: S | dP (even tiles) | dQ | dP (odd tiles): dP has two buffers, so dP(t+1) never waits for dS(t)
+  const uint32_t tS = tmem_base, tdQ = tmem_base + 256;
+  auto tdP = [&](int st) { return tmem_base + static_cast<uint32_t>(st ? 384 : 128); };
 
   if (warp == 5) {
     if (lane == 0 && iters > 0) {
@@ -441,7 +516,7 @@ dq5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     }
   } else if (warp == 4) {
     if (lane == 0 && iters > 0) {
-      const uint32_t idesc_ss = make_idesc_f16(true, false, false, BLK, 64);
+      const uint32_t idesc_ss = make_idesc_f16(true, false, false, BLK, BLK);
       const uint32_t idesc_ts = make_idesc_f16(true, false, true, BLK, D);
       const uint32_t desc_hi = smem_desc_hi(1024);
       const uint32_t q_lo = smem_desc_lo(sQ, 16), g_lo = smem_desc_lo(sdO, 16);
@@ -449,28 +524,31 @@ dq5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       const uint32_t v_lo[2] = {smem_desc_lo(sV, 16), smem_desc_lo(sV + TILE_BYTES, 16)};
       const uint32_t kn_lo[2] = {smem_desc_lo(sK, HALF_BYTES), smem_desc_lo(sK + TILE_BYTES, HALF_BYTES)};
       bool ok = mbar_wait(q_full, 0, abort_flag, p.err, kErrWaitFull, 1000);
-      auto issue_scores = [&](int it, int h) {
-        const int st = it & 1;
-        if (h == 0) {
-          if (!(ok = mbar_wait(kv_full(st), (it >> 1) & 1, abort_flag, p.err, kErrWaitFull, it))) return;
-          tc_fence_after();
-        }
-        issue_rows_x_half(tS(h), q_lo, k_lo[st], h, desc_hi, idesc_ss);     // S_h  = Q K_h^T
-        issue_rows_x_half(tdP(h), g_lo, v_lo[st], h, desc_hi, idesc_ss);    // dP_h = dO V_h^T
-        umma_commit(s_full(h));
-      };
-      if (ok) issue_scores(0, 0);
-      if (ok) issue_scores(0, 1);
+      if (ok) ok = mbar_wait(kv_full(0), 0, abort_flag, p.err, kErrWaitFull, 0);
+      if (ok) {
+        tc_fence_after();
+        issue_rows_x_rows(tS, q_lo, k_lo[0], desc_hi, idesc_ss);        // S(0)  = Q K^T
+        umma_commit(s_full);
+        issue_rows_x_rows(tdP(0), g_lo, v_lo[0], desc_hi, idesc_ss);    // dP(0) = dO V^T
+        umma_commit(dp_full(0));
+      }
       for (int it = 0; it < iters && ok; ++it) {
-        const int st = it & 1;
-        for (int h = 0; h < 2 && ok; ++h) {
-          if (!(ok = mbar_wait(p_full(h), it & 1, abort_flag, p.err, kErrWaitOther, 2000 + it))) break;
+        const int st = it & 1, nst = st ^ 1;
+        if (it + 1 < iters) {
+          // the softmax warps hold P(t) in registers: S(t+1) and dP(t+1) are formed while they work on dS(t)
+          if (!(ok = mbar_wait(s_free, it & 1, abort_flag, p.err, kErrWaitOther, 2000 + it))) break;
+          if (!(ok = mbar_wait(kv_full(nst), ((it + 1) >> 1) & 1, abort_flag, p.err, kErrWaitFull, it + 1))) break;
           tc_fence_after();
-          issue_tmem_x_half(tdQ, tdP(h), kn_lo[st], h, desc_hi, idesc_ts, it > 0 || h > 0);   // dQ += dS_h K_h
-          if (h == 1) umma_commit(kv_empty(st));
-          if (it + 1 < iters) issue_scores(it + 1, h);
-          else if (h == 1) umma_commit(o_full);
+          issue_rows_x_rows(tS, q_lo, k_lo[nst], desc_hi, idesc_ss);
+          umma_commit(s_full);
+          issue_rows_x_rows(tdP(nst), g_lo, v_lo[nst], desc_hi, idesc_ss);
+          umma_commit(dp_full(nst));
         }
+        if (!(ok = mbar_wait(ds_full, it & 1, abort_flag, p.err, kErrWaitOther, 3000 + it))) break;
+        tc_fence_after();
+        issue_tmem_x_tile(tdQ, tdP(st), kn_lo[st], desc_hi, idesc_ts, it > 0);   // dQ += dS K
+        umma_commit(kv_empty(st));
+        if (it + 1 == iters) umma_commit(o_full);
       }
     }
   } else {
@@ -482,39 +560,74 @@ dq5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     const float lse = m < p.Sq ? p.lse2[row] : INFINITY;
     const float del = m < p.Sq ? p.delta[row] : 0.f;
     const int n_last = p.causal ? min(m + p.shift, p.Sk - 1) : p.Sk - 1;   // last legal key
+    const uint64_t scale2 = pack2f(p.scale_log2, p.scale_log2);
+    const uint64_t nlse2 = pack2f(-lse, -lse), ndel2 = pack2f(-del, -del);
     bool ok = true;
     for (int it = 0; it < iters && ok; ++it) {
-#pragma unroll 1
-      for (int h = 0; h < 2 && ok; ++h) {
-        if (!(ok = mbar_wait(s_full(h), it & 1, abort_flag, p.err, kErrWaitTmemFull, it))) break;
-        tc_fence_after();
-        const int nb = it * BLK + 64 * h;
+      const int nb = it * BLK;
+      const bool tile_legal = nb + BLK - 1 <= (p.causal ? min(m0 + p.shift, p.Sk - 1) : p.Sk - 1);
+      uint32_t pk[64];   // bf16 P of this query row
+      // ---- phase 1: P = exp2(scale * S - lse) into registers, then the S buffer is handed back
+      if (!(ok = mbar_wait(s_full, it & 1, abort_flag, p.err, kErrWaitTmemFull, it))) break;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sv[32];
+        tmem_ld_32x32b_x32(tS + lane_base + 32 * c, sv);
+        tmem_ld_wait();
+        if (c == 3) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(s_free);
+        }
+        if (tile_legal) {   // no mask anywhere in this tile (uniform over the CTA)
+#pragma unroll
+          for (int k = 0; k < 32; k += 2) {
+            float x0, x1;
+            unpack2f(ffma2(pack2f(__uint_as_float(sv[k]), __uint_as_float(sv[k + 1])), scale2, nlse2), x0, x1);
+            pk[16 * c + (k >> 1)] = PACK_PROB(ex2(x0), ex2(x1));
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < 32; k += 2) {
+            float pe[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const bool legal = nb + 32 * c + k + e <= n_last;
+              pe[e] = legal ? ex2(__uint_as_float(sv[k + e]) * p.scale_log2 - lse) : 0.f;
+            }
+            pk[16 * c + (k >> 1)] = PACK_PROB(pe[0], pe[1]);
+          }
+        }
+      }
+      // ---- phase 2: dS = P (dP - delta), written over dP; dQ's MMAs may start
+      if (!(ok = mbar_wait(dp_full(it & 1), (it >> 1) & 1, abort_flag, p.err, kErrWaitTmemFull, 500 + it))) break;
+      tc_fence_after();
+      const uint32_t t_dp = tdP(it & 1) + lane_base;
+#pragma unroll
+      for (int cp = 0; cp < 2; ++cp) {
         uint32_t dk[32];
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-          const int c0 = half * 32;
-          uint32_t s[32], g[32];
-          tmem_ld_32x32b_x32(tS(h) + lane_base + c0, s);
-          tmem_ld_32x32b_x32(tdP(h) + lane_base + c0, g);
+          const int c = 2 * cp + half;
+          uint32_t g[32];
+          tmem_ld_32x32b_x32(t_dp + 32 * c, g);
           tmem_ld_wait();
 #pragma unroll
           for (int k = 0; k < 32; k += 2) {
-            float ds[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const bool legal = nb + c0 + k + e <= n_last;
-              const float pe = legal ? ex2(__uint_as_float(s[k + e]) * p.scale_log2 - lse) : 0.f;
-              ds[e] = pe * (__uint_as_float(g[k + e]) - del);
-            }
-            dk[half * 16 + (k >> 1)] = PACK_PROB(ds[0], ds[1]);
+            const uint32_t pw = pk[16 * c + (k >> 1)];
+            const uint64_t pp = pack2f(bf16lo(pw), bf16hi(pw));
+            float d0, d1;   // p * dp + p * (-delta)
+            unpack2f(ffma2(pp, pack2f(__uint_as_float(g[k]), __uint_as_float(g[k + 1])), fmul2(pp, ndel2)), d0, d1);
+            dk[16 * half + (k >> 1)] = PACK_PROB(d0, d1);
           }
         }
-        tmem_st_32x32b_x32(tdP(h) + lane_base, dk);
-        tmem_st_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(p_full(h));
+        tmem_st_32x32b_x32(t_dp + 32 * cp, dk);
       }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_full);
     }
     if (iters > 0) {
       if (ok) ok = mbar_wait(o_full, 0, abort_flag, p.err, kErrWaitTmemFull, 9000);

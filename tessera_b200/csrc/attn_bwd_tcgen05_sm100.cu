@@ -17,7 +17,7 @@
 // dq5_kernel: one CTA per 128 query rows of one head. Q and dO stay, K and V stream; S = Q K^T and
 // dP = dO V^T; thread = query row, so lse and delta are per-thread scalars. P is only needed in
 // registers, so the S buffer is handed back as soon as it has been read (S(t+1) is formed while
-// dS(t) = P(t) (dP(t) - delta) is computed), and dQ += dS K. TMEM: S | dP | dQ.
+// dS(t) = P(t) (dP(t) - delta) is computed), and dQ += dS K. TMEM: S | dP (even tiles) | dQ | dP (odd tiles).
 // Warps 0-3 softmax + epilogue (TMEM lane = 32 * warp + lane), warp 4 MMA issuer and TMEM owner,
 // warp 5 TMA producer. Every wait is bounded (error word + abort flag), as in the forward kernel.
 #include <cuda_bf16.h>

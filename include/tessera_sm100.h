@@ -148,6 +148,25 @@ int tessera_sm100_grouped_swiglu_device(const void* x, const void* w_gate, const
  * scale_x one device float, scale_w one per expert. The SwiGLU form writes the 16-bit hidden
  * activation silu(x Wg) * (x Wu) and, when amax_out is given (device uint32, zeroed by the
  * caller), max |hidden| as stored, ready for the next quantisation. */
+/* 8-bit float formats of the *_fmt_device entry points (quantize_fp8(format=...),
+ * python/tessera/__init__.py:3340-3374; grouped quant "fp8_e5m2"): the plain entry points are e4m3. */
+#define TESSERA_SM100_FP8_E4M3 0
+#define TESSERA_SM100_FP8_E5M2 1
+int tessera_sm100_quantize_fp8_fmt_device(const void* x, long long n, int dtype, int fmt, void* q,
+                                          float* scale_out, const unsigned int* amax_in, void* stream);
+int tessera_sm100_quantize_fp8_weights_fmt_device(const void* w, int E, int K, int N, int dtype, int fmt,
+                                                  void* q_t, float* scales, void* stream);
+int tessera_sm100_gemm_fp8_fmt_device(const void* Aq, const void* Bq_t, void* D, int M, int N, int K,
+                                      const float* scale_a, const float* scale_b, int out_dtype, int fmt,
+                                      void* stream);
+int tessera_sm100_grouped_gemm_fp8_fmt_device(const void* xq, const void* wq_t, const int* offsets,
+                                              void* out, int T, int K, int N, int E, const float* scale_x,
+                                              const float* scale_w, int out_dtype, int fmt, void* stream);
+int tessera_sm100_grouped_swiglu_fp8_fmt_device(const void* xq, const void* wgq_t, const void* wuq_t,
+                                                const int* offsets, void* hidden, int T, int K, int F,
+                                                int E, const float* scale_x, const float* scale_wg,
+                                                const float* scale_wu, int out_dtype,
+                                                unsigned int* amax_out, int fmt, void* stream);
 int tessera_sm100_quantize_fp8_device(const void* x, long long n, int dtype, void* q,
                                       float* scale_out, const unsigned int* amax_in, void* stream);
 int tessera_sm100_quantize_fp8_weights_device(const void* w, int E, int K, int N, int dtype,
@@ -174,7 +193,7 @@ int tessera_sm100_grouped_swiglu_fp8_device(const void* xq, const void* wgq_t, c
  * weights are kept packed at rest (4.5 bits per element) and expanded to bf16 for the GEMM: an e2m1
  * value times an e4m3 scale has at most 5 significant bits, so bf16 holds it exactly and the bf16
  * tensor-core GEMM forms exactly the reference's products. e4m3 activations ride as bf16 too
- * (tessera_sm100_fp8_to_bf16_device) with their per-tensor scale applied to the fp32 accumulators by
+ * (tessera_sm100_fp8_to_bf16_device, fmt 0 = e4m3, 1 = e5m2) with their per-tensor scale applied to the fp32 accumulators by
  * the *_scaled_device grouped GEMMs (scale_a: one device float, or NULL for 1).
  * quantize: x [rows, cols] (cols % 16 == 0) -> codes [rows, cols/2] (two codes per byte, even element
  * in the low nibble) and scales [rows, cols/16] e4m3 bytes; weights: rows = E*K, cols = N. */
@@ -182,7 +201,7 @@ int tessera_sm100_quantize_nvfp4_device(const void* x, long long rows, long long
                                         void* codes, void* scales, void* stream);
 int tessera_sm100_dequantize_nvfp4_device(const void* codes, const void* scales, long long rows,
                                           long long cols, void* out, int out_dtype, void* stream);
-int tessera_sm100_fp8_to_bf16_device(const void* q, long long n, void* out, void* stream);
+int tessera_sm100_fp8_to_bf16_device(const void* q, long long n, int fmt, void* out, void* stream);
 int tessera_sm100_grouped_gemm_scaled_device(const void* x, const void* w, const int* offsets, void* out,
                                              int T, int K, int N, int E, int in_dtype, int out_dtype,
                                              const float* scale_a, void* stream);

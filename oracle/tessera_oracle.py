@@ -295,33 +295,35 @@ def softmax_finalize(o, l) -> np.ndarray:
 
 
 # ----------------------------------------------------------------------------- fp8 quantisation
-def quantize_fp8(x):
-    """Per-tensor symmetric e4m3 quantisation, returned dequantised: ``scale = max(amax/448,
-    1e-12)``, ``q = e4m3(clip(x/scale, -448, 448))``, result ``q * scale`` and ``scale``, all in
+def quantize_fp8(x, format: str = "e4m3"):
+    """Per-tensor symmetric 8-bit float quantisation, returned dequantised: ``scale =
+    max(amax/max_normal, 1e-12)`` with ``max_normal`` 448 (e4m3) or 57344 (e5m2), ``q =
+    fp8(clip(x/scale, -max_normal, max_normal))``, result ``q * scale`` and ``scale``, all in
     float32 (python/tessera/__init__.py:3340-3374)."""
     x = np.asarray(x, np.float32)
+    top, dt = {"e4m3": (448.0, ml_dtypes.float8_e4m3fn), "e5m2": (57344.0, ml_dtypes.float8_e5m2)}[format]
     amax = np.max(np.abs(x)) if x.size else np.float32(0)
-    scale = np.float32(np.maximum(np.float32(amax) / np.float32(448.0), np.float32(1e-12)))
-    scaled = np.clip(x / scale, -448.0, 448.0)
-    q = scaled.astype(ml_dtypes.float8_e4m3fn).astype(np.float32)
+    scale = np.float32(np.maximum(np.float32(amax) / np.float32(top), np.float32(1e-12)))
+    scaled = np.clip(x / scale, -top, top)
+    q = scaled.astype(dt).astype(np.float32)
     return (q * scale).astype(np.float32), scale
 
 
-def grouped_gemm_fp8(x, w, group_sizes) -> np.ndarray:
+def grouped_gemm_fp8(x, w, group_sizes, format: str = "e4m3") -> np.ndarray:
     """``grouped_gemm(..., quant="fp8_e4m3")``: x quantised per tensor, each expert's weights per
     expert, then the f32 grouped GEMM (python/tessera/__init__.py:337-351,
     python/tessera/compiler/grouped_layout.py:371-392)."""
-    xq = quantize_fp8(_f32(x))[0]
-    wq = np.stack([quantize_fp8(_f32(w)[e])[0] for e in range(np.asarray(w).shape[0])])
+    xq = quantize_fp8(_f32(x), format)[0]
+    wq = np.stack([quantize_fp8(_f32(w)[e], format)[0] for e in range(np.asarray(w).shape[0])])
     return grouped_gemm(xq, wq, group_sizes)
 
 
-def moe_swiglu_block_fp8(x, w_gate, w_up, w_down, group_sizes) -> np.ndarray:
+def moe_swiglu_block_fp8(x, w_gate, w_up, w_down, group_sizes, format: str = "e4m3") -> np.ndarray:
     """``moe_swiglu_block(..., quant="fp8_e4m3")``: every grouped GEMM of the block quantises its
     operands (python/tessera/__init__.py:592-616)."""
-    gate = grouped_gemm_fp8(x, w_gate, group_sizes)
-    up = grouped_gemm_fp8(x, w_up, group_sizes)
-    return grouped_gemm_fp8(silu_mul(gate, up), w_down, group_sizes)
+    gate = grouped_gemm_fp8(x, w_gate, group_sizes, format)
+    up = grouped_gemm_fp8(x, w_up, group_sizes, format)
+    return grouped_gemm_fp8(silu_mul(gate, up), w_down, group_sizes, format)
 
 
 def quantize_nvfp4(x, block_size: int = 16):
@@ -346,11 +348,13 @@ def quantize_nvfp4(x, block_size: int = 16):
 def _fp4_scheme(quant: str):
     q = str(quant).lower()
     return {"nvfp4": ("nvfp4", "nvfp4"), "fp8xfp4": ("fp8_e4m3", "nvfp4"),
-            "fp8_e4m3xnvfp4": ("fp8_e4m3", "nvfp4")}[q]
+            "fp8_e4m3xnvfp4": ("fp8_e4m3", "nvfp4"), "fp8_e5m2xnvfp4": ("fp8_e5m2", "nvfp4")}[q]
 
 
 def _qdq(a, fmt: str):
-    return quantize_fp8(a)[0] if fmt == "fp8_e4m3" else quantize_nvfp4(a)[0]
+    if fmt == "nvfp4":
+        return quantize_nvfp4(a)[0]
+    return quantize_fp8(a, "e5m2" if fmt == "fp8_e5m2" else "e4m3")[0]
 
 
 def grouped_gemm_fp4(x, w, group_sizes, quant: str = "fp8xfp4") -> np.ndarray:

@@ -140,7 +140,14 @@ _SIGNATURES = {
                                                         c_float, c_int, _VP]),
     "tessera_sm100_quantize_nvfp4_device": (c_int, [_VP, c_longlong, c_longlong, c_int, _VP, _VP, _VP]),
     "tessera_sm100_dequantize_nvfp4_device": (c_int, [_VP, _VP, c_longlong, c_longlong, _VP, c_int, _VP]),
-    "tessera_sm100_fp8_to_bf16_device": (c_int, [_VP, c_longlong, _VP, _VP]),
+    "tessera_sm100_fp8_to_bf16_device": (c_int, [_VP, c_longlong, c_int, _VP, _VP]),
+    "tessera_sm100_quantize_fp8_fmt_device": (c_int, [_VP, c_longlong, c_int, c_int, _VP, _VP, _VP, _VP]),
+    "tessera_sm100_quantize_fp8_weights_fmt_device": (c_int, [_VP, c_int, c_int, c_int, c_int, c_int, _VP, _VP, _VP]),
+    "tessera_sm100_gemm_fp8_fmt_device": (c_int, [_VP, _VP, _VP, c_int, c_int, c_int, _VP, _VP, c_int, c_int, _VP]),
+    "tessera_sm100_grouped_gemm_fp8_fmt_device": (c_int, [_VP, _VP, _VP, _VP, c_int, c_int, c_int, c_int, _VP, _VP,
+                                                          c_int, c_int, _VP]),
+    "tessera_sm100_grouped_swiglu_fp8_fmt_device": (c_int, [_VP, _VP, _VP, _VP, _VP, c_int, c_int, c_int, c_int,
+                                                            _VP, _VP, _VP, c_int, _VP, c_int, _VP]),
     "tessera_sm100_grouped_gemm_scaled_device": (c_int, [_VP, _VP, _VP, _VP, c_int, c_int, c_int, c_int, c_int,
                                                          c_int, _VP, _VP]),
     "tessera_sm100_grouped_swiglu_scaled_device": (c_int, [_VP, _VP, _VP, _VP, _VP, c_int, c_int, c_int, c_int,

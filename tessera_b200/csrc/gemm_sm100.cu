@@ -619,8 +619,12 @@ int launch_fp8_kernel(bool pairs, const CUtensorMap& tA, const CUtensorMap& tB,
 int launch_fp8(const void* Aq, const void* Bq_t, const void* Bq2_t, const int* offsets, void* out,
                int T, int K, int N, int E, const float* scale_a, const float* scale_b,
                const float* scale_b2, int out_dtype, bool swiglu, unsigned int* amax_out,
-               cudaStream_t stream) {
+               cudaStream_t stream, int fmt = 0) {
   const bool grouped = offsets != nullptr;
+  if (fmt != TESSERA_SM100_FP8_E4M3 && fmt != TESSERA_SM100_FP8_E5M2) {
+    set_last_error("gemm_fp8: format must be 0 (e4m3) or 1 (e5m2), got %d", fmt);
+    return kBadArg;
+  }
   if (!Aq || !Bq_t || !out || !scale_a || !scale_b || (swiglu && (!Bq2_t || !scale_b2 || !grouped)) ||
       T < 0 || K <= 0 || N <= 0 || E <= 0) {
     set_last_error("gemm_fp8: null pointer or bad size (T %d K %d N %d E %d)", T, K, N, E);
@@ -679,7 +683,7 @@ int launch_fp8(const void* Aq, const void* Bq_t, const void* Bq2_t, const int* o
   p.err = device_err_word();
   if (!p.err) return kDeviceFailed;
   const bool pairs = pair_kernel_enabled() && (long long)(T / (2 * BM)) * p.n_tiles >= sm_count() / 2;
-  p.idesc = make_idesc_f8(pairs ? 2 * BM : BM, BN);
+  p.idesc = make_idesc_f8(pairs ? 2 * BM : BM, BN, fmt);
   const long long tiles =
       pairs ? ((long long)(T + 2 * BM - 1) / (2 * BM) + (grouped ? E : 0)) * p.n_tiles
             : ((long long)(T + BM - 1) / BM + (grouped ? E : 0)) * p.n_tiles;
@@ -714,6 +718,35 @@ int tessera_sm100_gemm_fp8_device(const void* Aq, const void* Bq_t, void* D, int
                                   void* stream) {
   return gemm::launch_fp8(Aq, Bq_t, nullptr, nullptr, D, M, K, N, 1, scale_a, scale_b, nullptr,
                           out_dtype, false, nullptr, static_cast<cudaStream_t>(stream));
+}
+// The same three with the operand format as an argument: 0 = e4m3, 1 = e5m2 (both operands).
+int tessera_sm100_gemm_fp8_fmt_device(const void* Aq, const void* Bq_t, void* D, int M, int N, int K,
+                                      const float* scale_a, const float* scale_b, int out_dtype, int fmt,
+                                      void* stream) {
+  return gemm::launch_fp8(Aq, Bq_t, nullptr, nullptr, D, M, K, N, 1, scale_a, scale_b, nullptr,
+                          out_dtype, false, nullptr, static_cast<cudaStream_t>(stream), fmt);
+}
+int tessera_sm100_grouped_gemm_fp8_fmt_device(const void* xq, const void* wq_t, const int* offsets,
+                                              void* out, int T, int K, int N, int E, const float* scale_x,
+                                              const float* scale_w, int out_dtype, int fmt, void* stream) {
+  if (!offsets) {
+    set_last_error("grouped_gemm_fp8: null offsets");
+    return kBadArg;
+  }
+  return gemm::launch_fp8(xq, wq_t, nullptr, offsets, out, T, K, N, E, scale_x, scale_w, nullptr,
+                          out_dtype, false, nullptr, static_cast<cudaStream_t>(stream), fmt);
+}
+int tessera_sm100_grouped_swiglu_fp8_fmt_device(const void* xq, const void* wgq_t, const void* wuq_t,
+                                                const int* offsets, void* hidden, int T, int K, int F,
+                                                int E, const float* scale_x, const float* scale_wg,
+                                                const float* scale_wu, int out_dtype,
+                                                unsigned int* amax_out, int fmt, void* stream) {
+  if (!offsets) {
+    set_last_error("grouped_swiglu_fp8: null offsets");
+    return kBadArg;
+  }
+  return gemm::launch_fp8(xq, wgq_t, wuq_t, offsets, hidden, T, K, F, E, scale_x, scale_wg, scale_wu,
+                          out_dtype, true, amax_out, static_cast<cudaStream_t>(stream), fmt);
 }
 int tessera_sm100_grouped_gemm_fp8_device(const void* xq, const void* wq_t, const int* offsets,
                                           void* out, int T, int K, int N, int E,

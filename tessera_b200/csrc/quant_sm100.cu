@@ -21,11 +21,13 @@ namespace quant {
 template <typename T>
 __device__ __forceinline__ float to_f32(T v) { return static_cast<float>(v); }
 
-__device__ __forceinline__ float scale_from_amax(float amax) {
-  return fmaxf(__fdiv_rn(amax, 448.0f), 1e-12f);
+// fmt: 0 = e4m3 (largest finite value 448), 1 = e5m2 (57344); the same arithmetic otherwise
+__device__ __forceinline__ float scale_from_amax(float amax, int fmt) {
+  return fmaxf(__fdiv_rn(amax, fmt ? 57344.0f : 448.0f), 1e-12f);
 }
-__device__ __forceinline__ uint8_t to_e4m3(float x, float scale) {
-  return __nv_cvt_float_to_fp8(__fdiv_rn(x, scale), __NV_SATFINITE, __NV_E4M3);
+__device__ __forceinline__ uint8_t to_e4m3(float x, float scale, int fmt) {
+  const float v = __fdiv_rn(x, scale);
+  return fmt ? __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E5M2) : __nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
 }
 
 // amax over n elements of segment blockIdx.y (segments of `seg` elements): non-negative float
@@ -54,9 +56,9 @@ __global__ void amax_kernel(const T* __restrict__ x, long long seg, unsigned int
 template <typename T>
 __global__ void quantize_kernel(const T* __restrict__ x, long long n,
                                 const unsigned int* __restrict__ amax_bits,
-                                uint8_t* __restrict__ q, float* __restrict__ scale_out) {
+                                uint8_t* __restrict__ q, float* __restrict__ scale_out, int fmt) {
   const float amax = __uint_as_float(*amax_bits);
-  const float scale = scale_from_amax(amax);
+  const float scale = scale_from_amax(amax, fmt);
   if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out) {
     scale_out[0] = scale;
     scale_out[1] = amax;
@@ -77,11 +79,11 @@ __global__ void quantize_kernel(const T* __restrict__ x, long long n,
     }
     uint32_t packed = 0;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) packed |= static_cast<uint32_t>(to_e4m3(v[j], scale)) << (8 * j);
+    for (int j = 0; j < 4; ++j) packed |= static_cast<uint32_t>(to_e4m3(v[j], scale, fmt)) << (8 * j);
     reinterpret_cast<uint32_t*>(q)[i] = packed;
   }
   for (long long i = 4 * n4 + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
-    q[i] = to_e4m3(to_f32(x[i]), scale);
+    q[i] = to_e4m3(to_f32(x[i]), scale, fmt);
 }
 
 // w[e][k][n] -> q_t[e][n][k] through a 32 x 32 shared-memory tile (both sides coalesced);
@@ -89,11 +91,11 @@ __global__ void quantize_kernel(const T* __restrict__ x, long long n,
 template <typename T>
 __global__ void quantize_transpose_kernel(const T* __restrict__ w, int K, int N, int E,
                                           const unsigned int* __restrict__ amax_bits,
-                                          uint8_t* __restrict__ q_t, float* __restrict__ scales) {
+                                          uint8_t* __restrict__ q_t, float* __restrict__ scales, int fmt) {
   __shared__ float tile[32][33];
   const int e = blockIdx.z;
   const float amax = __uint_as_float(amax_bits[e]);
-  const float scale = scale_from_amax(amax);
+  const float scale = scale_from_amax(amax, fmt);
   if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && threadIdx.y == 0) {
     scales[e] = scale;
     scales[E + e] = amax;
@@ -108,13 +110,13 @@ __global__ void quantize_transpose_kernel(const T* __restrict__ w, int K, int N,
   __syncthreads();
   for (int r = threadIdx.y; r < 32; r += blockDim.y) {
     const int n = n0 + r, k = k0 + threadIdx.x;
-    if (n < N && k < K) qe[static_cast<long long>(n) * K + k] = to_e4m3(tile[threadIdx.x][r], scale);
+    if (n < N && k < K) qe[static_cast<long long>(n) * K + k] = to_e4m3(tile[threadIdx.x][r], scale, fmt);
   }
 }
 
 template <typename T>
 int quantize_t(const void* x, long long n, void* q, float* scale_out, unsigned int* amax_bits,
-               bool have_amax, cudaStream_t st) {
+               bool have_amax, cudaStream_t st, int fmt) {
   const int blocks = (int)std::min<long long>((n / 4 + 255) / 256 + 1, 148 * 16);
   if (!have_amax) {
     TSB_CUDA_OK(cudaMemsetAsync(amax_bits, 0, sizeof(unsigned int), st));
@@ -123,7 +125,7 @@ int quantize_t(const void* x, long long n, void* q, float* scale_out, unsigned i
     note_launch();
   }
   quantize_kernel<T><<<blocks, 256, 0, st>>>(static_cast<const T*>(x), n, amax_bits,
-                                            static_cast<uint8_t*>(q), scale_out);
+                                            static_cast<uint8_t*>(q), scale_out, fmt);
   TSB_CUDA_OK(cudaGetLastError());
   note_launch();
   return kOk;
@@ -131,7 +133,7 @@ int quantize_t(const void* x, long long n, void* q, float* scale_out, unsigned i
 
 template <typename T>
 int quantize_weights_t(const void* w, int E, int K, int N, void* q_t, float* scales,
-                       cudaStream_t st) {
+                       cudaStream_t st, int fmt) {
   // the amax words live in the caller's scales buffer: [2E, 3E) as uint32
   unsigned int* amax_bits = reinterpret_cast<unsigned int*>(scales + 2 * E);
   TSB_CUDA_OK(cudaMemsetAsync(amax_bits, 0, sizeof(unsigned int) * E, st));
@@ -142,7 +144,7 @@ int quantize_weights_t(const void* w, int E, int K, int N, void* q_t, float* sca
   note_launch();
   dim3 grid((N + 31) / 32, (K + 31) / 32, E);
   quantize_transpose_kernel<T><<<grid, dim3(32, 8), 0, st>>>(static_cast<const T*>(w), K, N, E, amax_bits,
-                                                            static_cast<uint8_t*>(q_t), scales);
+                                                            static_cast<uint8_t*>(q_t), scales, fmt);
   TSB_CUDA_OK(cudaGetLastError());
   note_launch();
   return kOk;
@@ -211,10 +213,11 @@ __global__ void nvfp4_dequantize_kernel(const uint8_t* __restrict__ codes, const
 }
 
 // e4m3 bytes -> the same values as bf16 (exact: 4 significant bits into 8)
-__global__ void fp8_to_bf16_kernel(const uint8_t* __restrict__ q, long long n, __nv_bfloat16* __restrict__ out) {
+__global__ void fp8_to_bf16_kernel(const uint8_t* __restrict__ q, long long n, __nv_bfloat16* __restrict__ out,
+                                   int fmt) {
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
        i += static_cast<long long>(gridDim.x) * blockDim.x)
-    out[i] = __float2bfloat16_rn(e4m3_to_f32(q[i]));
+    out[i] = __float2bfloat16_rn(fmt ? __half2float(__half(__nv_cvt_fp8_to_halfraw(q[i], __NV_E5M2))) : e4m3_to_f32(q[i]));
 }
 
 }  // namespace quant
@@ -229,6 +232,15 @@ extern "C" {
 // float, e.g. the amax the fused SwiGLU GEMM recorded) the amax pass is skipped.
 int tessera_sm100_quantize_fp8_device(const void* x, long long n, int dtype, void* q,
                                       float* scale_out, const unsigned int* amax_in, void* stream) {
+  return tessera_sm100_quantize_fp8_fmt_device(x, n, dtype, TESSERA_SM100_FP8_E4M3, q, scale_out, amax_in, stream);
+}
+// The same with the 8-bit format as an argument: 0 = e4m3 (scale = amax / 448), 1 = e5m2 (amax / 57344).
+int tessera_sm100_quantize_fp8_fmt_device(const void* x, long long n, int dtype, int fmt, void* q,
+                                          float* scale_out, const unsigned int* amax_in, void* stream) {
+  if (fmt != TESSERA_SM100_FP8_E4M3 && fmt != TESSERA_SM100_FP8_E5M2) {
+    set_last_error("quantize_fp8: format must be 0 (e4m3) or 1 (e5m2), got %d", fmt);
+    return kBadArg;
+  }
   if (!x || !q || !scale_out || n < 0) {
     set_last_error("quantize_fp8: null pointer or negative size");
     return kBadArg;
@@ -240,9 +252,9 @@ int tessera_sm100_quantize_fp8_device(const void* x, long long n, int dtype, voi
                                : reinterpret_cast<unsigned int*>(scale_out + 2);
   const bool have = amax_in != nullptr;
   switch (dtype) {
-    case TESSERA_SM100_F32: return quant::quantize_t<float>(x, n, q, scale_out, bits, have, st);
-    case TESSERA_SM100_BF16: return quant::quantize_t<__nv_bfloat16>(x, n, q, scale_out, bits, have, st);
-    case TESSERA_SM100_F16: return quant::quantize_t<__half>(x, n, q, scale_out, bits, have, st);
+    case TESSERA_SM100_F32: return quant::quantize_t<float>(x, n, q, scale_out, bits, have, st, fmt);
+    case TESSERA_SM100_BF16: return quant::quantize_t<__nv_bfloat16>(x, n, q, scale_out, bits, have, st, fmt);
+    case TESSERA_SM100_F16: return quant::quantize_t<__half>(x, n, q, scale_out, bits, have, st, fmt);
     default: break;
   }
   set_last_error("quantize_fp8: unsupported dtype %d", dtype);
@@ -253,6 +265,14 @@ int tessera_sm100_quantize_fp8_device(const void* x, long long n, int dtype, voi
 // scales, [E, 2E) amax, [2E, 3E) scratch.
 int tessera_sm100_quantize_fp8_weights_device(const void* w, int E, int K, int N, int dtype,
                                               void* q_t, float* scales, void* stream) {
+  return tessera_sm100_quantize_fp8_weights_fmt_device(w, E, K, N, dtype, TESSERA_SM100_FP8_E4M3, q_t, scales, stream);
+}
+int tessera_sm100_quantize_fp8_weights_fmt_device(const void* w, int E, int K, int N, int dtype, int fmt,
+                                                  void* q_t, float* scales, void* stream) {
+  if (fmt != TESSERA_SM100_FP8_E4M3 && fmt != TESSERA_SM100_FP8_E5M2) {
+    set_last_error("quantize_fp8_weights: format must be 0 (e4m3) or 1 (e5m2), got %d", fmt);
+    return kBadArg;
+  }
   if (!w || !q_t || !scales || E <= 0 || K <= 0 || N <= 0) {
     set_last_error("quantize_fp8_weights: null pointer or non-positive size");
     return kBadArg;
@@ -260,9 +280,9 @@ int tessera_sm100_quantize_fp8_weights_device(const void* w, int E, int K, int N
   if (int rc = ensure_device()) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
-    case TESSERA_SM100_F32: return quant::quantize_weights_t<float>(w, E, K, N, q_t, scales, st);
-    case TESSERA_SM100_BF16: return quant::quantize_weights_t<__nv_bfloat16>(w, E, K, N, q_t, scales, st);
-    case TESSERA_SM100_F16: return quant::quantize_weights_t<__half>(w, E, K, N, q_t, scales, st);
+    case TESSERA_SM100_F32: return quant::quantize_weights_t<float>(w, E, K, N, q_t, scales, st, fmt);
+    case TESSERA_SM100_BF16: return quant::quantize_weights_t<__nv_bfloat16>(w, E, K, N, q_t, scales, st, fmt);
+    case TESSERA_SM100_F16: return quant::quantize_weights_t<__half>(w, E, K, N, q_t, scales, st, fmt);
     default: break;
   }
   set_last_error("quantize_fp8_weights: unsupported dtype %d", dtype);
@@ -331,17 +351,18 @@ int tessera_sm100_dequantize_nvfp4_device(const void* codes, const void* scales,
   return kOk;
 }
 
-// e4m3 bytes -> bf16 holding the same values (the activation operand of the fp8 x fp4 GEMM).
-int tessera_sm100_fp8_to_bf16_device(const void* q, long long n, void* out, void* stream) {
-  if (!q || !out || n < 0) {
-    set_last_error("fp8_to_bf16: null pointer or negative size");
+// 8-bit floats (fmt 0 = e4m3, 1 = e5m2) -> bf16 holding the same values (the activation operand of
+// the fp8 x fp4 GEMM).
+int tessera_sm100_fp8_to_bf16_device(const void* q, long long n, int fmt, void* out, void* stream) {
+  if (!q || !out || n < 0 || (fmt != TESSERA_SM100_FP8_E4M3 && fmt != TESSERA_SM100_FP8_E5M2)) {
+    set_last_error("fp8_to_bf16: null pointer, negative size or unknown format");
     return kBadArg;
   }
   if (n == 0) return kOk;
   if (int rc = ensure_device()) return rc;
   const int blocks = (int)std::min<long long>((n + 255) / 256, 148 * 8);
   quant::fp8_to_bf16_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint8_t*>(q), n, static_cast<__nv_bfloat16*>(out));
+      static_cast<const uint8_t*>(q), n, static_cast<__nv_bfloat16*>(out), fmt);
   TSB_CUDA_OK(cudaGetLastError());
   note_launch();
   return kOk;

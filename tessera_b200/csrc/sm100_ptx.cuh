@@ -242,10 +242,11 @@ __device__ __forceinline__ void umma_f8_ss_parts(uint32_t d_tmem, uint32_t a_lo,
       ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-// Instruction descriptor for kind::f8f6f4 with e4m3 A and B, both K-major, f32 accumulate
-// (format code 0 = e4m3 in the A and B format fields).
-__host__ __device__ constexpr uint32_t make_idesc_f8(int m, int n) {
-  return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+// Instruction descriptor for kind::f8f6f4 with 8-bit A and B of one format, both K-major, f32
+// accumulate. Format codes of the A [7,10) and B [10,13) fields: 0 = e4m3, 1 = e5m2.
+__host__ __device__ constexpr uint32_t make_idesc_f8(int m, int n, int fmt = 0) {
+  return (1u << 4) | (static_cast<uint32_t>(fmt & 7) << 7) | (static_cast<uint32_t>(fmt & 7) << 10) |
+         (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
 // ---------------------------------------------------------------- CTA pairs (cta_group::2)

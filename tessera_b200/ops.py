@@ -474,10 +474,11 @@ def _group_offsets(group_sizes, T: int, op: str) -> np.ndarray:
     return off
 
 
-_FP8_QUANTS = ("fp8", "fp8_e4m3")
-# activation format of the schemes whose weights are NVFP4 (python/tessera/compiler/grouped_layout.py:321-350)
-_FP4_QUANTS = {"nvfp4": "nvfp4", "fp8xfp4": "fp8_e4m3", "fp8_e4m3xnvfp4": "fp8_e4m3"}
-_OTHER_QUANTS = ("fp8_e5m2", "fp8_e5m2xnvfp4")
+# quant names of the reference (python/tessera/compiler/grouped_layout.py:319-350) -> 8-bit format code
+# (tessera_sm100.h: 0 = e4m3, 1 = e5m2), and the activation format of the schemes with NVFP4 weights
+_FP8_QUANTS = {"fp8": 0, "fp8_e4m3": 0, "fp8_e5m2": 1}
+_FP4_QUANTS = {"nvfp4": "nvfp4", "fp8xfp4": 0, "fp8_e4m3xnvfp4": 0, "fp8_e5m2xnvfp4": 1}
+_OTHER_QUANTS = ()
 
 
 def _check_kind(kind: str, alignment, group_sizes, quant, op: str) -> None:
@@ -485,12 +486,9 @@ def _check_kind(kind: str, alignment, group_sizes, quant, op: str) -> None:
         raise ValueError(f"{op}: unknown kind {kind!r}; expected one of {GROUPED_KINDS}")
     if kind not in SUPPORTED_GROUPED_KINDS:
         raise NotImplementedError(f"{op}: kind={kind!r} is not implemented yet")
-    if quant is not None and str(quant).lower() not in _FP8_QUANTS + tuple(_FP4_QUANTS):
-        if str(quant).lower() in _OTHER_QUANTS:
-            raise NotImplementedError(f"{op}: quant={quant!r} is not part of this backend (fp8_e4m3, nvfp4 "
-                                      f"and fp8xfp4 are)")
+    if quant is not None and str(quant).lower() not in tuple(_FP8_QUANTS) + tuple(_FP4_QUANTS):
         raise ValueError(f"{op}: quant {quant!r} has no grouped path; expected one of "
-                         f"{_FP8_QUANTS + tuple(_FP4_QUANTS) + _OTHER_QUANTS}")
+                         f"{tuple(_FP8_QUANTS) + tuple(_FP4_QUANTS)}")
     if alignment is not None:
         gs = np.asarray(group_sizes).astype(np.int64).reshape(-1)
         if np.any(gs % int(alignment)):
@@ -498,32 +496,43 @@ def _check_kind(kind: str, alignment, group_sizes, quant, op: str) -> None:
 
 
 class Fp8Tensor:
-    """e4m3 bytes on the device with their scale(s): ``q`` uint8, ``scales`` float32 device array
-    whose first element(s) are the scale(s) (``tessera_sm100_quantize_fp8*_device`` layouts)."""
+    """8-bit floats (``fmt`` 0 = e4m3, 1 = e5m2) on the device with their scale(s): ``q`` uint8,
+    ``scales`` float32 device array whose first element(s) are the scale(s)
+    (``tessera_sm100_quantize_fp8*_device`` layouts)."""
 
-    def __init__(self, q: DeviceArray, scales: DeviceArray, shape, per_expert: bool):
-        self.q, self.scales, self.shape, self.per_expert = q, scales, tuple(shape), per_expert
+    def __init__(self, q: DeviceArray, scales: DeviceArray, shape, per_expert: bool, fmt: int = 0):
+        self.q, self.scales, self.shape, self.per_expert, self.fmt = q, scales, tuple(shape), per_expert, int(fmt)
 
     def scale_values(self) -> np.ndarray:
         n = self.shape[0] if self.per_expert else 1
         return self.scales.download()[:n]
 
 
-def quantize_fp8_activations(x, *, amax_bits: Optional[DeviceArray] = None, stream=None) -> Fp8Tensor:
-    """Per-tensor e4m3 quantisation of ``x`` (any shape; float32 / float16 / bfloat16) on the
-    device: ``scale = max(amax/448, 1e-12)``, ``q = e4m3(x / scale)``
-    (python/tessera/__init__.py:3340-3374)."""
+def _fp8_fmt(format) -> int:
+    if format in (0, 1):
+        return int(format)
+    try:
+        return {"e4m3": 0, "e5m2": 1}[str(format).lower()]
+    except KeyError:
+        raise ValueError(f"format must be 'e4m3' or 'e5m2'; got {format!r}") from None
+
+
+def quantize_fp8_activations(x, *, amax_bits: Optional[DeviceArray] = None, format="e4m3", stream=None) -> Fp8Tensor:
+    """Per-tensor 8-bit float quantisation of ``x`` (any shape; float32 / float16 / bfloat16) on the
+    device: ``scale = max(amax/max_normal, 1e-12)`` with ``max_normal`` 448 (e4m3) or 57344 (e5m2),
+    ``q = fp8(x / scale)`` (python/tessera/__init__.py:3340-3374)."""
+    fmt = _fp8_fmt(format)
     xa = _unwrap(x)
     dx = xa if isinstance(xa, DeviceArray) else DeviceArray.from_host(np.ascontiguousarray(xa), pooled=True)
     q = DeviceArray(dx.shape, np.uint8)
     scales = DeviceArray((3,), np.float32)
-    _lib.call("tessera_sm100_quantize_fp8_device", dx.ptr, int(dx.size), device.dtype_code(dx.dtype), q.ptr,
+    _lib.call("tessera_sm100_quantize_fp8_fmt_device", dx.ptr, int(dx.size), device.dtype_code(dx.dtype), fmt, q.ptr,
               scales.ptr, amax_bits.ptr if amax_bits is not None else None, device._stream_handle(stream))
-    return Fp8Tensor(q, scales, dx.shape, False)
+    return Fp8Tensor(q, scales, dx.shape, False, fmt)
 
 
-def quantize_fp8_experts(weights, *, stream=None) -> Fp8Tensor:
-    """Per-expert e4m3 quantisation of ``weights`` (E, K, N), stored transposed as (E, N, K) so both
+def quantize_fp8_experts(weights, *, format="e4m3", stream=None) -> Fp8Tensor:
+    """Per-expert 8-bit float quantisation of ``weights`` (E, K, N), stored transposed as (E, N, K) so both
     GEMM operands are K-major (python/tessera/compiler/grouped_layout.py:371-392). Expert weights are
     static: quantise once and pass the result wherever weights are expected."""
     w = _unwrap(weights)
@@ -533,13 +542,18 @@ def quantize_fp8_experts(weights, *, stream=None) -> Fp8Tensor:
     E, K, N = dw.shape
     q = DeviceArray((E, N, K), np.uint8)
     scales = DeviceArray((3 * E,), np.float32)
-    _lib.call("tessera_sm100_quantize_fp8_weights_device", dw.ptr, E, K, N, device.dtype_code(dw.dtype), q.ptr,
-              scales.ptr, device._stream_handle(stream))
-    return Fp8Tensor(q, scales, (E, K, N), True)
+    fmt = _fp8_fmt(format)
+    _lib.call("tessera_sm100_quantize_fp8_weights_fmt_device", dw.ptr, E, K, N, device.dtype_code(dw.dtype), fmt,
+              q.ptr, scales.ptr, device._stream_handle(stream))
+    return Fp8Tensor(q, scales, (E, K, N), True, fmt)
 
 
-def _as_fp8_experts(w, stream) -> Fp8Tensor:
-    return w if isinstance(w, Fp8Tensor) else quantize_fp8_experts(w, stream=stream)
+def _as_fp8_experts(w, fmt, stream) -> Fp8Tensor:
+    if isinstance(w, Fp8Tensor):
+        if w.fmt != fmt:
+            raise ValueError("pre-quantised weights are in a different 8-bit format than the one asked for")
+        return w
+    return quantize_fp8_experts(w, format=fmt, stream=stream)
 
 
 class Nvfp4Tensor:
@@ -587,9 +601,10 @@ def _fp4_operand(x, act: str, stream):
     """x -> (bf16 device array holding the quantised values exactly, device scale or None)."""
     if act == "nvfp4":
         return quantize_nvfp4(x, stream=stream).dequantize(bfloat16, stream=stream), None
-    xq = quantize_fp8_activations(x, stream=stream)
+    xq = quantize_fp8_activations(x, format=act, stream=stream)
     vals = DeviceArray(tuple(xq.q.shape), bfloat16, pooled=True)
-    _lib.call("tessera_sm100_fp8_to_bf16_device", xq.q.ptr, int(xq.q.size), vals.ptr, device._stream_handle(stream))
+    _lib.call("tessera_sm100_fp8_to_bf16_device", xq.q.ptr, int(xq.q.size), xq.fmt, vals.ptr,
+              device._stream_handle(stream))
     return vals, xq.scales
 
 
@@ -659,11 +674,13 @@ def _moe_swiglu_block_fp4(x, w_gate, w_up, w_down, group_sizes, act, stream):
     return out if on_device else _finish(out)
 
 
-def _grouped_gemm_fp8(x, weights, group_sizes, out_dtype, stream):
+def _grouped_gemm_fp8(x, weights, group_sizes, out_dtype, stream, fmt=None):
     xa = _unwrap(x)
     if len(xa.shape) != 2:
         raise ValueError(f"grouped_gemm: x must be (T, K); got {tuple(xa.shape)}")
-    wq = _as_fp8_experts(weights, stream)
+    if fmt is None:
+        fmt = weights.fmt if isinstance(weights, Fp8Tensor) else 0
+    wq = _as_fp8_experts(weights, fmt, stream)
     E, K, N = wq.shape
     T = xa.shape[0]
     if xa.shape[1] != K:
@@ -675,12 +692,12 @@ def _grouped_gemm_fp8(x, weights, group_sizes, out_dtype, stream):
     if K % 16 or N % 8:
         raise ValueError("grouped_gemm: the fp8 path needs K a multiple of 16 and N a multiple of 8")
     on_device = isinstance(xa, DeviceArray)
-    xq = quantize_fp8_activations(xa, stream=stream)
+    xq = quantize_fp8_activations(xa, format=fmt, stream=stream)
     odt = np.dtype(out_dtype) if out_dtype is not None else np.dtype(xa.dtype)
     out = DeviceArray((T, N), odt)      # group sizes sum to T: every row is written
     doff = DeviceArray.from_host(off, pooled=True)
-    _lib.call("tessera_sm100_grouped_gemm_fp8_device", xq.q.ptr, wq.q.ptr, doff.ptr, out.ptr, T, K, N, E,
-              xq.scales.ptr, wq.scales.ptr, device.dtype_code(odt), device._stream_handle(stream))
+    _lib.call("tessera_sm100_grouped_gemm_fp8_fmt_device", xq.q.ptr, wq.q.ptr, doff.ptr, out.ptr, T, K, N, E,
+              xq.scales.ptr, wq.scales.ptr, device.dtype_code(odt), fmt, device._stream_handle(stream))
     return out if on_device else _finish(out)
 
 
@@ -693,10 +710,11 @@ def grouped_gemm(x, weights, group_sizes, *, kind="contiguous", alignment=None, 
     an :class:`Fp8Tensor` from :func:`quantize_fp8_experts`."""
     _check_kind(kind, alignment, group_sizes, quant, "grouped_gemm")
     if isinstance(weights, Nvfp4Tensor) or (quant is not None and str(quant).lower() in _FP4_QUANTS):
-        act = _FP4_QUANTS[str(quant).lower()] if quant is not None else "fp8_e4m3"
+        act = _FP4_QUANTS[str(quant).lower()] if quant is not None else 0
         return _grouped_gemm_fp4(x, weights, group_sizes, act, out_dtype, stream)
     if quant is not None or isinstance(weights, Fp8Tensor):
-        return _grouped_gemm_fp8(x, weights, group_sizes, out_dtype, stream)
+        return _grouped_gemm_fp8(x, weights, group_sizes, out_dtype, stream,
+                                 _FP8_QUANTS[str(quant).lower()] if quant is not None else None)
     x, w = _unwrap(x), _unwrap(weights)
     if x.ndim != 2:
         raise ValueError(f"grouped_gemm: x must be (T, K); got {x.shape}")
@@ -746,10 +764,11 @@ def moe_swiglu_block(x, w_gate, w_up, w_down, group_sizes, *, kind="contiguous",
     kernel, then the down grouped GEMM (python/tessera/__init__.py:592-616)."""
     _check_kind(kind, alignment, group_sizes, quant, "moe_swiglu_block")
     if isinstance(w_gate, Nvfp4Tensor) or (quant is not None and str(quant).lower() in _FP4_QUANTS):
-        act = _FP4_QUANTS[str(quant).lower()] if quant is not None else "fp8_e4m3"
+        act = _FP4_QUANTS[str(quant).lower()] if quant is not None else 0
         return _moe_swiglu_block_fp4(x, w_gate, w_up, w_down, group_sizes, act, stream)
     if quant is not None or isinstance(w_gate, Fp8Tensor):
-        return _moe_swiglu_block_fp8(x, w_gate, w_up, w_down, group_sizes, stream)
+        return _moe_swiglu_block_fp8(x, w_gate, w_up, w_down, group_sizes, stream,
+                                     _FP8_QUANTS[str(quant).lower()] if quant is not None else None)
     x, wg, wu, wd = _unwrap(x), _unwrap(w_gate), _unwrap(w_up), _unwrap(w_down)
     if x.ndim != 2 or wg.ndim != 3 or wu.shape != wg.shape or wd.ndim != 3:
         raise ValueError("moe_swiglu_block: expected x (T,K), w_gate/w_up (E,K,F), w_down (E,F,N)")
@@ -777,14 +796,16 @@ def moe_swiglu_block(x, w_gate, w_up, w_down, group_sizes, *, kind="contiguous",
     return out if on_device else _finish(out)
 
 
-def _moe_swiglu_block_fp8(x, w_gate, w_up, w_down, group_sizes, stream):
+def _moe_swiglu_block_fp8(x, w_gate, w_up, w_down, group_sizes, stream, fmt=None):
     """fp8 expert FFN: x quantised once, gate and up GEMMs fused with silu_mul (16-bit hidden plus its
     amax from the epilogue), hidden quantised per tensor, down GEMM — the reference applies ``quant``
     to every grouped GEMM of the block (python/tessera/__init__.py:592-616)."""
     xa = _unwrap(x)
     if len(xa.shape) != 2:
         raise ValueError("moe_swiglu_block: expected x (T,K)")
-    gq, uq, dq = (_as_fp8_experts(w, stream) for w in (w_gate, w_up, w_down))
+    if fmt is None:
+        fmt = w_gate.fmt if isinstance(w_gate, Fp8Tensor) else 0
+    gq, uq, dq = (_as_fp8_experts(w, fmt, stream) for w in (w_gate, w_up, w_down))
     E, K, F = gq.shape
     if uq.shape != gq.shape or dq.shape[0] != E or dq.shape[1] != F or xa.shape[1] != K:
         raise ValueError(f"moe_swiglu_block: shape mismatch x {tuple(xa.shape)}, w_gate {gq.shape}, "
@@ -802,16 +823,16 @@ def _moe_swiglu_block_fp8(x, w_gate, w_up, w_down, group_sizes, stream):
     # it to 16 bits first would move about one element in 32 across a quantisation boundary.
     hdt = np.dtype(np.float32)
     sh = device._stream_handle(stream)
-    xq = quantize_fp8_activations(xa, stream=stream)
+    xq = quantize_fp8_activations(xa, format=fmt, stream=stream)
     doff = DeviceArray.from_host(off, pooled=True)
     hidden = DeviceArray((T, F), hdt, pooled=True)
     amax = DeviceArray.zeros((1,), np.uint32)
-    _lib.call("tessera_sm100_grouped_swiglu_fp8_device", xq.q.ptr, gq.q.ptr, uq.q.ptr, doff.ptr, hidden.ptr, T, K,
-              F, E, xq.scales.ptr, gq.scales.ptr, uq.scales.ptr, device.dtype_code(hdt), amax.ptr, sh)
-    hq = quantize_fp8_activations(hidden, amax_bits=amax, stream=stream)
+    _lib.call("tessera_sm100_grouped_swiglu_fp8_fmt_device", xq.q.ptr, gq.q.ptr, uq.q.ptr, doff.ptr, hidden.ptr, T,
+              K, F, E, xq.scales.ptr, gq.scales.ptr, uq.scales.ptr, device.dtype_code(hdt), amax.ptr, fmt, sh)
+    hq = quantize_fp8_activations(hidden, amax_bits=amax, format=fmt, stream=stream)
     out = DeviceArray((T, N), odt)
-    _lib.call("tessera_sm100_grouped_gemm_fp8_device", hq.q.ptr, dq.q.ptr, doff.ptr, out.ptr, T, F, N, E,
-              hq.scales.ptr, dq.scales.ptr, device.dtype_code(odt), sh)
+    _lib.call("tessera_sm100_grouped_gemm_fp8_fmt_device", hq.q.ptr, dq.q.ptr, doff.ptr, out.ptr, T, F, N, E,
+              hq.scales.ptr, dq.scales.ptr, device.dtype_code(odt), fmt, sh)
     return out if on_device else _finish(out)
 
 

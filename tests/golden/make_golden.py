@@ -283,7 +283,9 @@ def quant4():
     wu = rt(rng.standard_normal((E, K, F)) / 8, bf16)
     wd = rt(rng.standard_normal((E, F, N)) / 9, bf16)
     out.update(g_x=xs, g_w=w, g_wg=wg, g_wu=wu, g_wd=wd, g_sizes=sizes)
-    for q in ("nvfp4", "fp8xfp4"):
+    dq5, sc5 = tessera.ops.quantize_fp8(x, format="e5m2")
+    out.update(e5_dq=np.asarray(dq5, np.float32), e5_scale=np.float32(sc5))
+    for q in ("nvfp4", "fp8xfp4", "fp8_e5m2", "fp8_e5m2xnvfp4"):
         out[f"gg_{q}"] = np.asarray(tessera.ops.grouped_gemm(xs, w, sizes, quant=q), np.float32)
         out[f"blk_{q}"] = np.asarray(tessera.ops.moe_swiglu_block(xs, wg, wu, wd, sizes, quant=q), np.float32)
     np.savez_compressed(os.path.join(HERE, "quant4.npz"), **out)

@@ -52,7 +52,7 @@ def test_e2m1_grid_ties_and_saturation():
     np.testing.assert_array_equal(vals, want)
 
 
-@pytest.mark.parametrize("quant", ["nvfp4", "fp8xfp4"])
+@pytest.mark.parametrize("quant", ["nvfp4", "fp8xfp4", "fp8_e5m2xnvfp4"])
 def test_fixture_grouped_gemm_and_block(golden_dir, quant):
     g = np.load(os.path.join(golden_dir, "quant4.npz"))
     x = g["g_x"].astype(bfloat16)
@@ -64,7 +64,7 @@ def test_fixture_grouped_gemm_and_block(golden_dir, quant):
     no_device_error()
 
 
-@pytest.mark.parametrize("quant", ["nvfp4", "fp8xfp4"])
+@pytest.mark.parametrize("quant", ["nvfp4", "fp8xfp4", "fp8_e5m2xnvfp4"])
 def test_larger_ragged_groups_and_prequantised_weights(quant):
     rng = np.random.default_rng(12)
     T, K, N, E = 700, 512, 384, 5

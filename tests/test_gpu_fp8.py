@@ -81,11 +81,31 @@ def test_grouped_fp8_against_oracle(sizes, K, N):
 
 def test_unsupported_quant_names():
     x, w = np.zeros((8, 16), np.float32), np.zeros((1, 16, 8), np.float32)
-    with pytest.raises(NotImplementedError):
-        tessera.ops.grouped_gemm(x, w, [8], quant="fp8_e5m2")
     with pytest.raises(ValueError):          # the reference's message: NVFP4 blocks of 16 along N
         tessera.ops.grouped_gemm(x, w, [8], quant="nvfp4")
     with pytest.raises(ValueError):
         tessera.ops.grouped_gemm(x, w, [8], quant="int3")
     with pytest.raises(ValueError):
         tessera.ops.grouped_gemm(np.zeros((8, 24), np.float32), np.zeros((1, 24, 8), np.float32), [8], quant="fp8")
+
+
+def test_e5m2_quantisation_and_grouped_gemm(golden_dir):
+    """quant="fp8_e5m2": the same kernels with the e5m2 format code (scale = amax / 57344)."""
+    g = np.load(os.path.join(golden_dir, "quant4.npz"))
+    t = tessera.ops.quantize_fp8_activations(g["n_x"], format="e5m2")
+    scale = t.scale_values()[0]
+    assert scale == g["e5_scale"]
+    np.testing.assert_array_equal(t.q.download().view(ml_dtypes.float8_e5m2).astype(np.float32) * scale, g["e5_dq"])
+    x, w, wg, wu, wd = (_bf(g[k]) for k in ("g_x", "g_w", "g_wg", "g_wu", "g_wd"))
+    got = tessera.ops.grouped_gemm(x, w, g["g_sizes"], quant="fp8_e5m2", out_dtype=np.float32)
+    assert rel_err(got, g["gg_fp8_e5m2"]) < 1e-5
+    blk = tessera.ops.moe_swiglu_block(x, wg, wu, wd, g["g_sizes"], quant="fp8_e5m2")
+    assert rel_err(blk, g["blk_fp8_e5m2"]) < TOL
+    # larger, ragged, CTA-pair sizes against the oracle
+    rng = np.random.default_rng(3)
+    sizes = np.array([300, 0, 777, 100, 871])
+    xs = _bf(rng.standard_normal((int(sizes.sum()), 272)))
+    ws = _bf(rng.standard_normal((5, 272, 2576)) / 16)
+    got = tessera.ops.grouped_gemm(xs, ws, sizes, quant="fp8_e5m2", out_dtype=np.float32)
+    assert rel_err(got, orc.grouped_gemm_fp8(xs, ws, sizes, "e5m2")) < 1e-5
+    no_device_error()

@@ -252,7 +252,14 @@ def test_nvfp4_quantisation_and_grouped_gemms_match_reference(golden_dir):
     np.testing.assert_array_equal(dq, g["n_dq"])
     np.testing.assert_array_equal(sc, g["n_scales"])
     assert not dq[5, :16].any() and g["n_x"][5, :16].any()      # scale rounded to zero: block reads as 0
-    for q in ("nvfp4", "fp8xfp4"):
+    dq5, sc5 = orc.quantize_fp8(g["n_x"], "e5m2")
+    np.testing.assert_array_equal(dq5, g["e5_dq"])
+    assert sc5 == g["e5_scale"]
+    np.testing.assert_allclose(orc.grouped_gemm_fp8(g["g_x"], g["g_w"], g["g_sizes"], "e5m2"), g["gg_fp8_e5m2"],
+                               rtol=1e-6, atol=1e-6)
+    np.testing.assert_allclose(orc.moe_swiglu_block_fp8(g["g_x"], g["g_wg"], g["g_wu"], g["g_wd"], g["g_sizes"], "e5m2"),
+                               g["blk_fp8_e5m2"], rtol=1e-5, atol=1e-6)
+    for q in ("nvfp4", "fp8xfp4", "fp8_e5m2xnvfp4"):
         np.testing.assert_allclose(orc.grouped_gemm_fp4(g["g_x"], g["g_w"], g["g_sizes"], q), g[f"gg_{q}"],
                                    rtol=1e-6, atol=1e-6)
         np.testing.assert_allclose(orc.moe_swiglu_block_fp4(g["g_x"], g["g_wg"], g["g_wu"], g["g_wd"], g["g_sizes"], q),

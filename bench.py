@@ -524,12 +524,24 @@ def bench_moe(ranks, args, peaks, peak_kind):
                                              parallel.GpuMoeBackend(dwg, dwu, dwd))
             fn = lambda: moe.forward(dxl, ll)
     times = timed_steps(ranks, device, fn, max(2, args.steps // 2), min(args.warmup, 3))
+    ms = statistics.mean(times)
+    pipelined = None
+    if W > 1 and ep_mode == "device":
+        # the same layer over micro-batches, exchange overlapping the expert GEMMs
+        try:
+            pm = parallel.PipelinedExpertParallelMoE(comm, ranks.gather, dwg, dwu, dwd, Tl, k, E, micro_batches=2)
+            fnp = lambda: pm.forward(dxl, dll, out=out_l)
+            pipelined = {"micro_batches": 2,
+                         "ms_per_step": statistics.mean(timed_steps(ranks, device, fnp, max(2, args.steps // 2),
+                                                                    min(args.warmup, 3)))}
+            pm.close()
+        except Exception as exc:
+            pipelined = {"error": f"{type(exc).__name__}: {exc}"}
     if comm:
         comm.close()
-    ms = statistics.mean(times)
     ach = flops / W / ms / 1e9
     return {"metric": "MoE FFN layer TFLOP/s (routed slots, unpadded)", "value": flops / ms / 1e9,
-            "unit": "TFLOP/s", "ms_per_step": ms,
+            "unit": "TFLOP/s", "ms_per_step": ms, "pipelined": pipelined,
             "config": f"T={T} H={H} F={F} E={E} top-{k} bf16, " + ("single GPU" if W == 1 else f"expert-parallel /{W}, exchange: {ep_mode}"),
             "roofline": {"bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops_sustained"],
                          "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops_sustained"],

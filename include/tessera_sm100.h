@@ -63,6 +63,7 @@ int tessera_sm100_device_synchronize(void);
 int tessera_sm100_event_create(void** out);
 int tessera_sm100_event_destroy(void* event);
 int tessera_sm100_event_record(void* event, void* stream);
+int tessera_sm100_stream_wait_event(void* stream, void* event);
 int tessera_sm100_event_synchronize(void* event);
 int tessera_sm100_event_elapsed_ms(void* start, void* stop, float* ms);
 /* Writes `bytes` of a scratch buffer (device memory) to evict the L2 cache between timed runs. */

@@ -60,6 +60,7 @@ _SIGNATURES = {
     "tessera_sm100_event_create": (c_int, [POINTER(_VP)]),
     "tessera_sm100_event_destroy": (c_int, [_VP]),
     "tessera_sm100_event_record": (c_int, [_VP, _VP]),
+    "tessera_sm100_stream_wait_event": (c_int, [_VP, _VP]),
     "tessera_sm100_event_synchronize": (c_int, [_VP]),
     "tessera_sm100_event_elapsed_ms": (c_int, [_VP, _VP, POINTER(c_float)]),
     "tessera_sm100_flush_l2": (c_int, [_VP]),

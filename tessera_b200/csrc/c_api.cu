@@ -160,6 +160,12 @@ int tessera_sm100_event_record(void* event, void* stream) {
   TSB_CUDA_OK(cudaEventRecord(static_cast<cudaEvent_t>(event), static_cast<cudaStream_t>(stream)));
   return kOk;
 }
+// Work enqueued on `stream` after this call waits for `event` (recorded on another stream).
+int tessera_sm100_stream_wait_event(void* stream, void* event) {
+  if (!event) return kBadArg;
+  TSB_CUDA_OK(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), static_cast<cudaEvent_t>(event), 0));
+  return kOk;
+}
 int tessera_sm100_event_synchronize(void* event) {
   if (!event) return kBadArg;
   TSB_CUDA_OK(cudaEventSynchronize(static_cast<cudaEvent_t>(event)));

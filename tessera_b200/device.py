@@ -77,6 +77,10 @@ class Stream:
     def synchronize(self) -> None:
         _lib.call("tessera_sm100_stream_synchronize", self.handle)
 
+    def wait_event(self, event: "Event") -> None:
+        """Work enqueued on this stream from now on waits for ``event``."""
+        _lib.call("tessera_sm100_stream_wait_event", self.handle, event.handle)
+
     def close(self) -> None:
         if self.handle:
             _lib.call("tessera_sm100_stream_destroy", self.handle)

@@ -338,41 +338,51 @@ class DeviceExpertParallelMoE:
         self._recv_ptrs = exchange(self.recv)
         self._y_ptrs = exchange(self.y)
 
-    def _barrier(self, sh) -> None:
-        """Stream-ordered rendezvous of all ranks (a 4-int all-reduce)."""
-        self.comm.all_reduce(self.flag, self.flag_out, "sum", self.stream)
-
-    def forward(self, x_local, logits_local, out=None):
-        """``x_local`` (Tl, H) and ``logits_local`` (Tl, E) fp32 DeviceArrays; returns a (Tl, H)
-        DeviceArray. Everything is enqueued on one stream; the caller synchronises."""
+    # The forward in three stages, each on the stream it is given: exchange in, experts, exchange out.
+    def _stage_dispatch(self, x_local, logits_local, stream) -> None:
         from . import _lib, device
-        from .device import DeviceArray
-        sh = device._stream_handle(self.stream)
-        Tl, k, E, H, F = self.Tl, self.k, self.E, self.H, self.F
-        if out is None:
-            out = DeviceArray((Tl, H), self.dtype, pooled=True)
-        self._barrier(sh)   # peers are done with the previous call's buffers
+        sh = device._stream_handle(stream)
+        Tl, k, E, H = self.Tl, self.k, self.E, self.H
+        self.comm.all_reduce(self.flag, self.flag_out, "sum", stream)   # peers are done with the previous call's buffers
         _lib.call("tessera_sm100_moe_route_device", logits_local.ptr, Tl, E, k, int(self.normalize),
                   self.assignment.ptr, self.weights.ptr, sh)
         _lib.call("tessera_sm100_moe_permute_device", self.assignment.ptr, self.weights.ptr, Tl, k, E, -1,
                   self.token_of_slot.ptr, self.expert_of_slot.ptr, self.weight_of_slot.ptr,
                   self.group_sizes.ptr, self.my_offsets.ptr, self.slot_of.ptr, sh)
-        self.comm.all_gather(self.group_sizes, self.all_counts, self.stream)
+        self.comm.all_gather(self.group_sizes, self.all_counts, stream)
         _lib.call("tessera_sm100_ep_plan_device", self.all_counts.ptr, self.world, self.rank, E,
                   self.local_offsets.ptr, self.dst_base.ptr, sh)
         _lib.call("tessera_sm100_ep_dispatch_device", x_local.ptr, self.token_of_slot.ptr,
                   self.expert_of_slot.ptr, self.my_offsets.ptr, self.dst_base.ptr, self._recv_ptrs,
                   self.world, E, Tl * k, self.capacity, H, self._code, sh)
-        self._barrier(sh)   # every rank's rows have landed
+        self.comm.all_reduce(self.flag, self.flag_out, "sum", stream)   # every rank's rows have landed
+
+    def _stage_experts(self, stream) -> None:
+        from . import _lib, device
+        sh = device._stream_handle(stream)
         _lib.call("tessera_sm100_grouped_swiglu_device", self.recv.ptr, self.wg.ptr, self.wu.ptr,
-                  self.local_offsets.ptr, self.hidden.ptr, self.capacity, H, F, self.Ep, self._code,
+                  self.local_offsets.ptr, self.hidden.ptr, self.capacity, self.H, self.F, self.Ep, self._code,
                   self._code, sh)
         _lib.call("tessera_sm100_grouped_gemm_device", self.hidden.ptr, self.wd.ptr, self.local_offsets.ptr,
-                  self.y.ptr, self.capacity, F, H, self.Ep, self._code, self._code, sh)
-        self._barrier(sh)   # every rank's expert outputs are complete
+                  self.y.ptr, self.capacity, self.F, self.H, self.Ep, self._code, self._code, sh)
+
+    def _stage_combine(self, out, stream) -> None:
+        from . import _lib, device
+        sh = device._stream_handle(stream)
+        self.comm.all_reduce(self.flag, self.flag_out, "sum", stream)   # every rank's expert outputs are complete
         _lib.call("tessera_sm100_ep_combine_device", self._y_ptrs, self.assignment.ptr, self.slot_of.ptr,
-                  self.weights.ptr, self.my_offsets.ptr, self.dst_base.ptr, out.ptr, Tl, k, self.world, E,
-                  self.capacity, H, self._code, sh)
+                  self.weights.ptr, self.my_offsets.ptr, self.dst_base.ptr, out.ptr, self.Tl, self.k, self.world,
+                  self.E, self.capacity, self.H, self._code, sh)
+
+    def forward(self, x_local, logits_local, out=None):
+        """``x_local`` (Tl, H) and ``logits_local`` (Tl, E) fp32 DeviceArrays; returns a (Tl, H)
+        DeviceArray. Everything is enqueued on one stream; the caller synchronises."""
+        from .device import DeviceArray
+        if out is None:
+            out = DeviceArray((self.Tl, self.H), self.dtype, pooled=True)
+        self._stage_dispatch(x_local, logits_local, self.stream)
+        self._stage_experts(self.stream)
+        self._stage_combine(out, self.stream)
         return out
 
     def close(self) -> None:
@@ -380,3 +390,73 @@ class DeviceExpertParallelMoE:
         for p in self._opened:
             _lib.call("tessera_sm100_ipc_close_handle", p)
         self._opened = []
+
+
+class PipelinedExpertParallelMoE:
+    """The expert-parallel forward over micro-batches of the local tokens, with the exchange of one
+    micro-batch overlapping the expert GEMMs of another — the schedule of the reference's
+    ``megamoe_forward_pipelined`` (python/tessera/distributed/moe.py:767-1025). Every micro-batch
+    has its own exchange buffers (a :class:`DeviceExpertParallelMoE` over ``tokens_per_rank /
+    micro_batches`` tokens); the exchange stages (route, dispatch stores, the rendezvous
+    all-reduces, combine) run on one stream and the grouped GEMMs on another, ordered by events:
+
+        exchange stream:  in(0)  in(1)  out(0)  in(2)  out(1) ...
+        compute stream :         ffn(0)         ffn(1) ...
+
+    Tokens are independent, so the result equals the unpipelined forward row for row. All NCCL
+    calls stay on the one exchange stream (a communicator is not used from two streams at once)."""
+
+    def __init__(self, comm, gather_host, w_gate, w_up, w_down, tokens_per_rank: int, top_k: int,
+                 num_experts: int, micro_batches: int = 2, normalize_weights: bool = True) -> None:
+        from .device import Event, Stream
+        if micro_batches < 1 or tokens_per_rank % micro_batches:
+            raise ValueError("tokens_per_rank must be divisible by micro_batches")
+        self.M, self.Tm = micro_batches, tokens_per_rank // micro_batches
+        self.exchange, self.compute = Stream(), Stream()
+        self.parts = [DeviceExpertParallelMoE(comm, gather_host, w_gate, w_up, w_down, self.Tm, top_k, num_experts,
+                                              normalize_weights, stream=self.exchange) for _ in range(self.M)]
+        self.H, self.E, self.dtype = self.parts[0].H, num_experts, self.parts[0].dtype
+        self._in_done = [Event() for _ in range(self.M)]
+        self._ffn_done = [Event() for _ in range(self.M)]
+        self._start, self._end = Event(), Event()
+
+    def forward(self, x_local, logits_local, out=None, stream=None):
+        """``x_local`` (Tl, H), ``logits_local`` (Tl, E) fp32; returns (Tl, H). The work is ordered
+        after what is already enqueued on ``stream`` and ``stream`` waits for it at the end."""
+        from . import _lib, device
+        from .device import DeviceArray
+        Tl = self.M * self.Tm
+        if out is None:
+            out = DeviceArray((Tl, self.H), self.dtype, pooled=True)
+        self._start.record(stream)
+        self.exchange.wait_event(self._start)
+        self.compute.wait_event(self._start)
+        xs = [x_local.view((self.Tm, self.H), i * self.Tm * self.H) for i in range(self.M)]
+        ls = [logits_local.view((self.Tm, self.E), i * self.Tm * self.E) for i in range(self.M)]
+        os_ = [out.view((self.Tm, self.H), i * self.Tm * self.H) for i in range(self.M)]
+
+        def stage_in(i):
+            self.parts[i]._stage_dispatch(xs[i], ls[i], self.exchange)
+            self._in_done[i].record(self.exchange)
+            self.compute.wait_event(self._in_done[i])
+            self.parts[i]._stage_experts(self.compute)
+            self._ffn_done[i].record(self.compute)
+
+        def stage_out(i):
+            self.exchange.wait_event(self._ffn_done[i])
+            self.parts[i]._stage_combine(os_[i], self.exchange)
+
+        stage_in(0)
+        for i in range(1, self.M):
+            stage_in(i)
+            stage_out(i - 1)
+        stage_out(self.M - 1)
+        self._end.record(self.exchange)
+        _lib.call("tessera_sm100_stream_wait_event", device._stream_handle(stream), self._end.handle)
+        return out
+
+    def close(self) -> None:
+        for part in self.parts:
+            part.close()
+        self.exchange.close()
+        self.compute.close()

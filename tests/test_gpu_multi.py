@@ -99,6 +99,18 @@ def _worker(rank, world, port, q):
         dist.barrier()
         errs["ep_moe_device"] = orc.max_rel_err(yd.download(), ref[sl])
         dist.barrier()
+        # --- and over micro-batches, the exchange of one overlapping the expert GEMMs of another
+        pmoe = parallel.PipelinedExpertParallelMoE(comm, gather, backend.wg, backend.wu, backend.wd, Tl, k, E,
+                                                   micro_batches=4)
+        for _ in range(2):
+            yp = pmoe.forward(dx, dlog)
+        device.synchronize()
+        dist.barrier()
+        errs["ep_moe_pipelined"] = orc.max_rel_err(yp.download(), ref[sl])
+        errs["ep_moe_pipelined_vs_plain"] = float(np.abs(yp.download().astype(np.float32)
+                                                         - yd.download().astype(np.float32)).max())
+        dist.barrier()
+        pmoe.close()
         dmoe.close()
         device.check_device_error("multi-gpu test")
         dist.barrier()
@@ -134,6 +146,7 @@ def test_two_gpu_collectives_tp_gemm_and_ep_moe():
         assert exc is None, f"rank {rank}:\n{exc}"
         assert errs["all_gather"] == 0 and errs["all_reduce"] == 0 and errs["all_to_all_v"] == 0, errs
         assert errs["tp_gemm"] < 1e-2 and errs["tp_gemm_pairs"] < 1e-2 and errs["ep_moe"] < 1e-2 and errs["ep_moe_device"] < 1e-2, errs
+        assert errs["ep_moe_pipelined"] < 1e-2 and errs["ep_moe_pipelined_vs_plain"] == 0.0, errs
 
 
 def _adapter_worker(q):

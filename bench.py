@@ -695,6 +695,15 @@ def profile_case(name: str) -> None:
         fn = lambda: _lib.call("tessera_sm100_paged_attn_decode_device", q.ptr, kp.ptr, vp.ptr, table.ptr,
                                lens.ptr, o.ptr, B, Hq, Hkv, D, L, P, per_seq, S, ctypes.c_float(1 / np.sqrt(D)),
                                ns, scr.ptr, None)
+    elif name == "gemm_fp8":
+        n = 8192
+        a8 = DeviceArray.from_host(rng.integers(0, 120, (n, n), dtype=np.uint8))      # e4m3 bytes, finite values
+        b8 = DeviceArray.from_host(rng.integers(0, 120, (n, n), dtype=np.uint8))      # B given transposed [N, K]
+        sa = DeviceArray.from_host(np.array([1e-3], np.float32))
+        sb = DeviceArray.from_host(np.array([1e-3], np.float32))
+        d = DeviceArray.zeros((n, n), bfloat16)
+        fn = lambda: _lib.call("tessera_sm100_gemm_fp8_device", a8.ptr, b8.ptr, d.ptr, n, n, n, sa.ptr, sb.ptr,
+                               _lib.BF16, None)
     elif name == "attn_backward":
         B, H, S, D = 2, 16, 4096, 128
         q, k, v, g = (dev_normal((B, H, S, D)) for _ in range(4))

@@ -168,8 +168,10 @@ __device__ __forceinline__ uint8_t to_e2m1(float x) {
   return static_cast<uint8_t>(c | (x < 0.f ? 8 : 0));
 }
 __device__ __forceinline__ float from_e2m1(uint8_t c) {
-  const float mag[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
-  const float m = mag[c & 7];
+  // magnitudes 0, 0.5, 1, 1.5, 2, 3, 4, 6: exponent field e = bits 1-2, mantissa bit m = bit 0;
+  // e == 0 is the subnormal pair {0, 0.5}, otherwise (1 + m/2) * 2^(e-1)
+  const int e = (c >> 1) & 3, mb = c & 1;
+  const float m = e ? __int_as_float((126 + e) << 23) * (1.f + 0.5f * mb) : 0.5f * mb;
   return (c & 8) ? -m : m;
 }
 __device__ __forceinline__ float e4m3_to_f32(uint8_t b) {
@@ -183,11 +185,24 @@ __global__ void nvfp4_quantize_kernel(const T* __restrict__ x, long long nblocks
   if (i >= nblocks) return;
   float v[16];
   float amax = 0.f;
+  // a block is 16 consecutive elements: 16-byte loads when the base allows (cols % 16 == 0 keeps
+  // every block 16-element aligned relative to it)
+  if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    constexpr int kPer = 16 / sizeof(T);          // elements per 16-byte load
+    const uint4* src = reinterpret_cast<const uint4*>(x + i * 16);
 #pragma unroll
-  for (int j = 0; j < 16; ++j) {
-    v[j] = to_f32(x[i * 16 + j]);
-    amax = fmaxf(amax, fabsf(v[j]));
+    for (int q = 0; q < 16 / kPer; ++q) {
+      const uint4 w4 = src[q];
+      const T* h = reinterpret_cast<const T*>(&w4);
+#pragma unroll
+      for (int j = 0; j < kPer; ++j) v[q * kPer + j] = to_f32(h[j]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = to_f32(x[i * 16 + j]);
   }
+#pragma unroll
+  for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
   const uint8_t sb = __nv_cvt_float_to_fp8(fmaxf(__fdiv_rn(amax, 6.0f), 1e-30f), __NV_SATFINITE, __NV_E4M3);
   float sf = e4m3_to_f32(sb);
   if (sf == 0.f) sf = 1.f;
@@ -205,10 +220,20 @@ __global__ void nvfp4_dequantize_kernel(const uint8_t* __restrict__ codes, const
   if (i >= nblocks) return;
   const uint2 w = *reinterpret_cast<const uint2*>(codes + i * 8);
   const float sf = e4m3_to_f32(scales[i]);
+  alignas(16) OutT vals[16];
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
     const uint32_t word = j < 8 ? w.x : w.y;
-    out[i * 16 + j] = static_cast<OutT>(from_e2m1((word >> (4 * (j & 7))) & 15u) * sf);
+    vals[j] = static_cast<OutT>(from_e2m1((word >> (4 * (j & 7))) & 15u) * sf);
+  }
+  if ((reinterpret_cast<uintptr_t>(out) & 15) == 0) {   // 16-byte stores
+    uint4* dst = reinterpret_cast<uint4*>(out + i * 16);
+    const uint4* srcv = reinterpret_cast<const uint4*>(vals);
+#pragma unroll
+    for (int q = 0; q < static_cast<int>(sizeof(OutT)) * 16 / 16; ++q) dst[q] = srcv[q];
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) out[i * 16 + j] = vals[j];
   }
 }
 

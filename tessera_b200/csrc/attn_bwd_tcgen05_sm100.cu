@@ -39,7 +39,13 @@ constexpr int SMEM_BAR_OFF = 6 * TILE_BYTES;               // six 32 KB tiles
 constexpr int SMEM_STAT_OFF = SMEM_BAR_OFF + 256;           // lse[2][128], delta[2][128] (dkv only)
 constexpr int SMEM_BYTES = SMEM_STAT_OFF + 4 * BLK * 4;
 constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;
-constexpr int THREADS = 192;
+// dq5_kernel: Q, dO, three K stages, two V stages (seven 32 KB tiles), then barriers
+constexpr int DQ_K_STAGES = 3;
+constexpr int DQ_BAR_OFF = 7 * TILE_BYTES;
+constexpr int DQ_SMEM_ALLOC = DQ_BAR_OFF + 256 + 1024;
+static_assert(DQ_SMEM_ALLOC <= 227 * 1024, "dq5_kernel shared memory");
+constexpr int THREADS = 192;       // dkv5_kernel
+constexpr int THREADS_DQ = 320;    // dq5_kernel: two conversion groups (even / odd tiles), the MMA warp, the TMA warp
 
 struct Params {
   int B, Hq, Hkv, Sq, Sk;
@@ -131,10 +137,11 @@ __device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b2) {
 __device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 
-// accumulator (128 lanes x 128 fp32 columns at t_acc) * mul -> bf16 -> swizzled tile at obuf
-__device__ __forceinline__ void acc_to_smem(uint32_t t_acc, uint32_t obuf, int r, float mul) {
+// accumulator columns [32 c_begin, 32 c_end) of 128 (128 lanes at t_acc) * mul -> bf16 -> swizzled tile at obuf
+__device__ __forceinline__ void acc_to_smem(uint32_t t_acc, uint32_t obuf, int r, float mul, int c_begin = 0,
+                                            int c_end = 4) {
 #pragma unroll 1
-  for (int c = 0; c < 4; ++c) {
+  for (int c = c_begin; c < c_end; ++c) {
     uint32_t v[32];
     tmem_ld_32x32b_x32(t_acc + c * 32, v);
     tmem_ld_wait();
@@ -434,7 +441,7 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
   }
 }
 
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS_DQ, 1)
 dq5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
            const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
            const __grid_constant__ CUtensorMap tmdQ, const Params p) {
@@ -442,20 +449,28 @@ dq5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t sQ = smem_base, sdO = smem_base + TILE_BYTES;
-  const uint32_t sK = smem_base + 2 * TILE_BYTES, sV = smem_base + 4 * TILE_BYTES;
-  const uint32_t bars = smem_base + SMEM_BAR_OFF;
+  const uint32_t sK = smem_base + 2 * TILE_BYTES, sV = smem_base + (2 + DQ_K_STAGES) * TILE_BYTES;
+  const uint32_t bars = smem_base + DQ_BAR_OFF;
   const uint32_t q_full = bars;
-  auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
-  auto kv_empty = [&](int s) { return bars + 8u * (3 + s); };
-  const uint32_t s_full = bars + 8u * 5;     // S formed
+  // K(t) is read by S(t) and, a whole tile later, by dQ(t); its buffer comes back only when dQ(t) has
+  // run, and K(t+2) is wanted right then: three K stages keep that load off the critical path.
+  // V(t) is read by dP(t) alone and released straight after it, so two stages are enough.
+  auto k_full = [&](int s) { return bars + 8u * (1 + s); };
+  auto k_empty = [&](int s) { return bars + 8u * (4 + s); };
+  auto v_full = [&](int s) { return bars + 8u * (7 + s); };
+  auto v_empty = [&](int s) { return bars + 8u * (9 + s); };
+  // Tiles alternate between two conversion groups, so every hand-off barrier exists once per tile
+  // parity: each completes every second tile and a commit for tile t+1 can never run a phase ahead
+  // of a warp still waiting for tile t.
+  auto s_full = [&](int st) { return bars + 8u * (11 + st); };     // S formed
   // dP formed, one barrier per dP buffer (each completes every second tile, so a commit for tile t+1
   // can never run a phase ahead of a warp still waiting for tile t)
-  auto dp_full = [&](int st) { return bars + 8u * (st ? 10 : 6); };
-  const uint32_t s_free = bars + 8u * 7;     // S has been read into registers: the buffer may be overwritten
-  const uint32_t ds_full = bars + 8u * 8;    // dS written over dP
-  const uint32_t o_full = bars + 8u * 9;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + SMEM_BAR_OFF + 128);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + SMEM_BAR_OFF + 132);
+  auto dp_full = [&](int st) { return bars + 8u * (13 + st); };
+  auto s_free = [&](int st) { return bars + 8u * (15 + st); };     // S read into registers: may be overwritten
+  auto ds_full = [&](int st) { return bars + 8u * (17 + st); };    // dS written over dP
+  const uint32_t o_full = bars + 8u * 19;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + DQ_BAR_OFF + 192);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + DQ_BAR_OFF + 196);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = (gridDim.x - 1 - blockIdx.x) * BLK;   // the longest rows first
@@ -468,19 +483,24 @@ dq5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(kv_full(s), 1);
-      mbar_init(kv_empty(s), 1);
+    for (int s = 0; s < DQ_K_STAGES; ++s) {
+      mbar_init(k_full(s), 1);
+      mbar_init(k_empty(s), 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(dp_full(0), 1);
-    mbar_init(dp_full(1), 1);
-    mbar_init(s_free, 4);    // one arrival per softmax warp
-    mbar_init(ds_full, 4);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(v_full(s), 1);
+      mbar_init(v_empty(s), 1);
+    }
+    for (int st = 0; st < 2; ++st) {
+      mbar_init(s_full(st), 1);
+      mbar_init(dp_full(st), 1);
+      mbar_init(s_free(st), 4);    // one arrival per warp of the group that owns the tile
+      mbar_init(ds_full(st), 4);
+    }
     mbar_init(o_full, 1);
     fence_mbar_init();
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
     tmem_relinquish();
   }
@@ -492,7 +512,7 @@ dq5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   const uint32_t tS = tmem_base, tdQ = tmem_base + 256;
   auto tdP = [&](int st) { return tmem_base + static_cast<uint32_t>(st ? 384 : 128); };
 
-  if (warp == 5) {
+  if (warp == 9) {
     if (lane == 0 && iters > 0) {
       tma_prefetch_desc(&tmQ);
       tma_prefetch_desc(&tmdO);
@@ -504,57 +524,69 @@ dq5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       tma_load_4d(sdO, &tmdO, q_full, 0, m0, hq, b);
       tma_load_4d(sdO + HALF_BYTES, &tmdO, q_full, 64, m0, hq, b);
       for (int it = 0; it < iters; ++it) {
-        const int st = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
-        if (!mbar_wait(kv_empty(st), ph ^ 1u, abort_flag, p.err, kErrWaitEmpty, it)) break;
-        mbar_arrive_expect_tx(kv_full(st), 2 * TILE_BYTES);
-        tma_load_4d(sK + st * TILE_BYTES, &tmK, kv_full(st), 0, it * BLK, hk, b);
-        tma_load_4d(sK + st * TILE_BYTES + HALF_BYTES, &tmK, kv_full(st), 64, it * BLK, hk, b);
-        tma_load_4d(sV + st * TILE_BYTES, &tmV, kv_full(st), 0, it * BLK, hk, b);
-        tma_load_4d(sV + st * TILE_BYTES + HALF_BYTES, &tmV, kv_full(st), 64, it * BLK, hk, b);
+        const int ks = it % DQ_K_STAGES, vs = it & 1;
+        const uint32_t kph = (it / DQ_K_STAGES) & 1, vph = (it >> 1) & 1;
+        if (!mbar_wait(k_empty(ks), kph ^ 1u, abort_flag, p.err, kErrWaitEmpty, it)) break;
+        mbar_arrive_expect_tx(k_full(ks), TILE_BYTES);
+        tma_load_4d(sK + ks * TILE_BYTES, &tmK, k_full(ks), 0, it * BLK, hk, b);
+        tma_load_4d(sK + ks * TILE_BYTES + HALF_BYTES, &tmK, k_full(ks), 64, it * BLK, hk, b);
+        if (!mbar_wait(v_empty(vs), vph ^ 1u, abort_flag, p.err, kErrWaitEmpty, 100000 + it)) break;
+        mbar_arrive_expect_tx(v_full(vs), TILE_BYTES);
+        tma_load_4d(sV + vs * TILE_BYTES, &tmV, v_full(vs), 0, it * BLK, hk, b);
+        tma_load_4d(sV + vs * TILE_BYTES + HALF_BYTES, &tmV, v_full(vs), 64, it * BLK, hk, b);
       }
     }
-  } else if (warp == 4) {
+  } else if (warp == 8) {
     if (lane == 0 && iters > 0) {
       const uint32_t idesc_ss = make_idesc_f16(true, false, false, BLK, BLK);
       const uint32_t idesc_ts = make_idesc_f16(true, false, true, BLK, D);
       const uint32_t desc_hi = smem_desc_hi(1024);
       const uint32_t q_lo = smem_desc_lo(sQ, 16), g_lo = smem_desc_lo(sdO, 16);
-      const uint32_t k_lo[2] = {smem_desc_lo(sK, 16), smem_desc_lo(sK + TILE_BYTES, 16)};
       const uint32_t v_lo[2] = {smem_desc_lo(sV, 16), smem_desc_lo(sV + TILE_BYTES, 16)};
-      const uint32_t kn_lo[2] = {smem_desc_lo(sK, HALF_BYTES), smem_desc_lo(sK + TILE_BYTES, HALF_BYTES)};
       bool ok = mbar_wait(q_full, 0, abort_flag, p.err, kErrWaitFull, 1000);
-      if (ok) ok = mbar_wait(kv_full(0), 0, abort_flag, p.err, kErrWaitFull, 0);
+      if (ok) ok = mbar_wait(k_full(0), 0, abort_flag, p.err, kErrWaitFull, 0);
       if (ok) {
         tc_fence_after();
-        issue_rows_x_rows(tS, q_lo, k_lo[0], desc_hi, idesc_ss);        // S(0)  = Q K^T
-        umma_commit(s_full);
+        issue_rows_x_rows(tS, q_lo, smem_desc_lo(sK, 16), desc_hi, idesc_ss);   // S(0)  = Q K^T
+        umma_commit(s_full(0));
+      }
+      if (ok) ok = mbar_wait(v_full(0), 0, abort_flag, p.err, kErrWaitFull, 100000);
+      if (ok) {
+        tc_fence_after();
         issue_rows_x_rows(tdP(0), g_lo, v_lo[0], desc_hi, idesc_ss);    // dP(0) = dO V^T
+        umma_commit(v_empty(0));
         umma_commit(dp_full(0));
       }
       for (int it = 0; it < iters && ok; ++it) {
         const int st = it & 1, nst = st ^ 1;
         if (it + 1 < iters) {
           // the softmax warps hold P(t) in registers: S(t+1) and dP(t+1) are formed while they work on dS(t)
-          if (!(ok = mbar_wait(s_free, it & 1, abort_flag, p.err, kErrWaitOther, 2000 + it))) break;
-          if (!(ok = mbar_wait(kv_full(nst), ((it + 1) >> 1) & 1, abort_flag, p.err, kErrWaitFull, it + 1))) break;
+          if (!(ok = mbar_wait(s_free(st), (it >> 1) & 1, abort_flag, p.err, kErrWaitOther, 2000 + it))) break;
+          const int ksn = (it + 1) % DQ_K_STAGES;
+          if (!(ok = mbar_wait(k_full(ksn), ((it + 1) / DQ_K_STAGES) & 1, abort_flag, p.err, kErrWaitFull, it + 1))) break;
           tc_fence_after();
-          issue_rows_x_rows(tS, q_lo, k_lo[nst], desc_hi, idesc_ss);
-          umma_commit(s_full);
+          issue_rows_x_rows(tS, q_lo, smem_desc_lo(sK + ksn * TILE_BYTES, 16), desc_hi, idesc_ss);
+          umma_commit(s_full(nst));
+          if (!(ok = mbar_wait(v_full(nst), ((it + 1) >> 1) & 1, abort_flag, p.err, kErrWaitFull, 100001 + it))) break;
+          tc_fence_after();
           issue_rows_x_rows(tdP(nst), g_lo, v_lo[nst], desc_hi, idesc_ss);
+          umma_commit(v_empty(nst));
           umma_commit(dp_full(nst));
         }
-        if (!(ok = mbar_wait(ds_full, it & 1, abort_flag, p.err, kErrWaitOther, 3000 + it))) break;
+        if (!(ok = mbar_wait(ds_full(st), (it >> 1) & 1, abort_flag, p.err, kErrWaitOther, 3000 + it))) break;
         tc_fence_after();
-        issue_tmem_x_tile(tdQ, tdP(st), kn_lo[st], desc_hi, idesc_ts, it > 0);   // dQ += dS K
-        umma_commit(kv_empty(st));
+        const int ks = it % DQ_K_STAGES;
+        issue_tmem_x_tile(tdQ, tdP(st), smem_desc_lo(sK + ks * TILE_BYTES, HALF_BYTES), desc_hi, idesc_ts,
+                          it > 0);   // dQ += dS K
+        umma_commit(k_empty(ks));
         if (it + 1 == iters) umma_commit(o_full);
       }
     }
   } else {
-    // softmax warps: thread = query row
-    const int r = warp * 32 + lane;
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    // conversion groups: thread = query row; group g (warps 4g .. 4g+3) converts the tiles of parity g
+    const int g = warp >> 2;
+    const int r = (warp & 3) * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const int m = m0 + r;
     const long long row = (static_cast<long long>(b) * p.Hq + hq) * p.Sq + m;
     const float lse = m < p.Sq ? p.lse2[row] : INFINITY;
@@ -563,12 +595,12 @@ dq5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     const uint64_t scale2 = pack2f(p.scale_log2, p.scale_log2);
     const uint64_t nlse2 = pack2f(-lse, -lse), ndel2 = pack2f(-del, -del);
     bool ok = true;
-    for (int it = 0; it < iters && ok; ++it) {
+    for (int it = g; it < iters && ok; it += 2) {
       const int nb = it * BLK;
       const bool tile_legal = nb + BLK - 1 <= (p.causal ? min(m0 + p.shift, p.Sk - 1) : p.Sk - 1);
       uint32_t pk[64];   // bf16 P of this query row
       // ---- phase 1: P = exp2(scale * S - lse) into registers, then the S buffer is handed back
-      if (!(ok = mbar_wait(s_full, it & 1, abort_flag, p.err, kErrWaitTmemFull, it))) break;
+      if (!(ok = mbar_wait(s_full(g), (it >> 1) & 1, abort_flag, p.err, kErrWaitTmemFull, it))) break;
       tc_fence_after();
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -578,7 +610,7 @@ dq5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         if (c == 3) {
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(s_free);
+          if (lane == 0) mbar_arrive(s_free(g));
         }
         if (tile_legal) {   // no mask anywhere in this tile (uniform over the CTA)
 #pragma unroll
@@ -601,24 +633,24 @@ dq5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         }
       }
       // ---- phase 2: dS = P (dP - delta), written over dP; dQ's MMAs may start
-      if (!(ok = mbar_wait(dp_full(it & 1), (it >> 1) & 1, abort_flag, p.err, kErrWaitTmemFull, 500 + it))) break;
+      if (!(ok = mbar_wait(dp_full(g), (it >> 1) & 1, abort_flag, p.err, kErrWaitTmemFull, 500 + it))) break;
       tc_fence_after();
-      const uint32_t t_dp = tdP(it & 1) + lane_base;
+      const uint32_t t_dp = tdP(g) + lane_base;
 #pragma unroll
       for (int cp = 0; cp < 2; ++cp) {
         uint32_t dk[32];
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           const int c = 2 * cp + half;
-          uint32_t g[32];
-          tmem_ld_32x32b_x32(t_dp + 32 * c, g);
+          uint32_t dpv[32];
+          tmem_ld_32x32b_x32(t_dp + 32 * c, dpv);
           tmem_ld_wait();
 #pragma unroll
           for (int k = 0; k < 32; k += 2) {
             const uint32_t pw = pk[16 * c + (k >> 1)];
             const uint64_t pp = pack2f(bf16lo(pw), bf16hi(pw));
             float d0, d1;   // p * dp + p * (-delta)
-            unpack2f(ffma2(pp, pack2f(__uint_as_float(g[k]), __uint_as_float(g[k + 1])), fmul2(pp, ndel2)), d0, d1);
+            unpack2f(ffma2(pp, pack2f(__uint_as_float(dpv[k]), __uint_as_float(dpv[k + 1])), fmul2(pp, ndel2)), d0, d1);
             dk[16 * half + (k >> 1)] = PACK_PROB(d0, d1);
           }
         }
@@ -627,20 +659,20 @@ dq5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(ds_full);
+      if (lane == 0) mbar_arrive(ds_full(g));
     }
     if (iters > 0) {
       if (ok) ok = mbar_wait(o_full, 0, abort_flag, p.err, kErrWaitTmemFull, 9000);
       tc_fence_after();
-      acc_to_smem(tdQ + lane_base, sK, r, p.scale);
+      acc_to_smem(tdQ + lane_base, sK, r, p.scale, 2 * g, 2 * g + 2);   // d columns [64 g, 64 g + 64)
     } else {
-      zeros_to_smem(sK, r);
+      for (int ch = 0; ch < 8; ++ch)
+        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(sK + g * HALF_BYTES + swz128(r, ch)), "r"(0) : "memory");
     }
     fence_proxy_async_smem();
-    asm volatile("bar.sync 1, 128;" ::: "memory");
+    asm volatile("bar.sync %0, 128;" ::"r"(1 + g) : "memory");
     if (r == 0 && ok) {
-      tma_store_4d(&tmdQ, sK, 0, m0, hq, b);
-      tma_store_4d(&tmdQ, sK + HALF_BYTES, 64, m0, hq, b);
+      tma_store_4d(&tmdQ, sK + g * HALF_BYTES, 64 * g, m0, hq, b);
       tma_store_commit();
       tma_store_wait<0>();
     }
@@ -651,7 +683,7 @@ dq5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     for (int k = 0; k < 64; ++k) __nanosleep(10000);
     __syncthreads();
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
@@ -691,10 +723,10 @@ int launch(const void* dO, const void* Q, const void* K, const void* V, void* dQ
   p.delta = delta;
   p.err = device_err_word();
   if (!p.err) return kDeviceFailed;
-  TSB_CUDA_OK(cudaFuncSetAttribute(dq5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));
+  TSB_CUDA_OK(cudaFuncSetAttribute(dq5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM_ALLOC));
   TSB_CUDA_OK(cudaFuncSetAttribute(dkv5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));
   dim3 g1((Sq + BLK - 1) / BLK, Hq, B);
-  dq5_kernel<<<g1, THREADS, SMEM_ALLOC, st>>>(tQ, tdO, tK, tV, tdQ, p);
+  dq5_kernel<<<g1, THREADS_DQ, DQ_SMEM_ALLOC, st>>>(tQ, tdO, tK, tV, tdQ, p);
   TSB_CUDA_OK(cudaGetLastError());
   note_launch();
   dim3 g2((Sk + BLK - 1) / BLK, Hkv, B);

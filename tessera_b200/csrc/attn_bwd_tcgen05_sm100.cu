@@ -44,7 +44,7 @@ constexpr int DQ_K_STAGES = 3;
 constexpr int DQ_BAR_OFF = 7 * TILE_BYTES;
 constexpr int DQ_SMEM_ALLOC = DQ_BAR_OFF + 256 + 1024;
 static_assert(DQ_SMEM_ALLOC <= 227 * 1024, "dq5_kernel shared memory");
-constexpr int THREADS = 192;       // dkv5_kernel
+constexpr int THREADS = 320;       // dkv5_kernel: two conversion groups (query columns 0-63 / 64-127), the MMA warp, the TMA warp
 constexpr int THREADS_DQ = 320;    // dq5_kernel: two conversion groups (even / odd tiles), the MMA warp, the TMA warp
 
 struct Params {
@@ -106,12 +106,15 @@ __device__ __forceinline__ void issue_rows_x_rows(uint32_t d_tmem, uint32_t a_lo
 }
 // d_tmem[128 x 128 d] (+)= A (bf16 in TMEM, 128 lanes x 128 contraction) . B (smem tile whose 128
 // rows are the contraction and whose 128 d are contiguous: MN-major, halves HALF_BYTES apart)
+// kSplitA: the packed A operand lies in two 32-column pieces, k 0-63 at a_tmem and k 64-127 at
+// a_tmem + 64 (each conversion group packs its 64 fp32 columns in place).
+template <bool kSplitA = false>
 __device__ __forceinline__ void issue_tmem_x_tile(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
                                                   uint32_t desc_hi, uint32_t idesc, bool accumulate) {
 #pragma unroll
   for (int ks = 0; ks < BLK / 16; ++ks)
-    umma_f16_ts_parts(d_tmem, a_tmem + 8u * ks, b_lo + ((ks * 2048) >> 4), desc_hi, idesc,
-                      (accumulate || ks > 0) ? 1u : 0u);
+    umma_f16_ts_parts(d_tmem, a_tmem + 8u * ks + ((kSplitA && ks >= BLK / 32) ? 32u : 0u), b_lo + ((ks * 2048) >> 4),
+                      desc_hi, idesc, (accumulate || ks > 0) ? 1u : 0u);
 }
 __device__ __forceinline__ uint64_t pack2f(float lo, float hi) {
   uint64_t d;
@@ -191,7 +194,7 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BLK, hk = blockIdx.y, b = blockIdx.z;
 #ifdef TESSERA_BWD_TRACE
-  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp == 0 || warp == 4);
+  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp == 0 || warp == 8);
 #endif
   const int ratio = p.Hq / p.Hkv;
   const int nqb = (p.Sq + BLK - 1) / BLK;
@@ -210,12 +213,12 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     }
     mbar_init(s_full, 1);
     mbar_init(dp_full, 1);
-    mbar_init(p_full, 4);    // one arrival per softmax warp
-    mbar_init(ds_full, 4);
+    mbar_init(p_full, 8);    // one arrival per softmax warp
+    mbar_init(ds_full, 8);
     mbar_init(o_full, 1);
     fence_mbar_init();
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512);
     tmem_relinquish();
   }
@@ -225,7 +228,7 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdV = tmem_base + 256, tdK = tmem_base + 384;
 
-  if (warp == 5) {
+  if (warp == 9) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0 && iters > 0) {
       tma_prefetch_desc(&tmQ);
@@ -249,7 +252,7 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         tma_load_4d(sdO + st * TILE_BYTES + HALF_BYTES, &tmdO, q_full(st), 64, m0, hq, b);
       }
     }
-  } else if (warp == 4) {
+  } else if (warp == 8) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0 && iters > 0) {
       const uint32_t idesc_ss = make_idesc_f16(true, false, false, BLK, BLK);   // rows x rows over d
@@ -276,7 +279,7 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         if (!(ok = mbar_wait(p_full, it & 1, abort_flag, p.err, kErrWaitOther, 2000 + it))) break;
         BW_TRACE(1, it * 8 + 1);
         tc_fence_after();
-        issue_tmem_x_tile(tdV, tS, gn_lo[st], desc_hi, idesc_ts, it > 0);       // dV += P^T dO
+        issue_tmem_x_tile<true>(tdV, tS, gn_lo[st], desc_hi, idesc_ts, it > 0);       // dV += P^T dO
         BW_TRACE(1, it * 8 + 2);
         if (more) {
           // the S^T buffer is free once dV's MMAs (issued just above, executed in order) have read P^T
@@ -289,7 +292,7 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         if (!(ok = mbar_wait(ds_full, it & 1, abort_flag, p.err, kErrWaitOther, 3000 + it))) break;
         BW_TRACE(1, it * 8 + 4);
         tc_fence_after();
-        issue_tmem_x_tile(tdK, tdP, qn_lo[st], desc_hi, idesc_ts, it > 0);      // dK += dS^T Q
+        issue_tmem_x_tile<true>(tdK, tdP, qn_lo[st], desc_hi, idesc_ts, it > 0);      // dK += dS^T Q
         umma_commit(q_empty(st));
         BW_TRACE(1, it * 8 + 5);
         if (more) {
@@ -302,14 +305,18 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax warps: thread = key
-    const int r = warp * 32 + lane;
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    // ------- softmax groups: thread = key; group g (warps 4g .. 4g+3) converts query columns [64 g, 64 g + 64)
+    // and packs them in place (P^T at columns 64 g .. 64 g + 31 of S^T, dS^T likewise over dP^T), so
+    // neither group ever writes a column the other still has to read
+    const int g = warp >> 2;
+    const int r = (warp & 3) * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const int key = n0 + r;
     const bool key_ok = key < p.Sk;
     bool ok = true;
     float lse_n = INFINITY, del_n = 0.f;
-    auto fetch_stats = [&](int it) {   // this thread's COLUMN (query row m0 + r) of tile `it`
+    auto fetch_stats = [&](int it) {   // group 0: this thread's COLUMN (query row m0 + r) of tile `it`
+      if (g != 0) return;
       const int m = m0_of(it) + r;
       const long long row = (static_cast<long long>(b) * p.Hq + head_of(it)) * p.Sq + m;
       lse_n = m < p.Sq ? p.lse2[row] : INFINITY;   // a row that does not exist: p = 0
@@ -320,16 +327,18 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     // (`ok` only gates the work): a thread that left early would leave the others at the barrier.
     for (int it = 0; it < iters; ++it) {
       const int sl = (it & 1) * BLK;
-      s_lse[sl + r] = -lse_n;   // negated: x = s * scale - lse and dp - delta become packed fmas
-      s_del[sl + r] = -del_n;
+      if (g == 0) {
+        s_lse[sl + r] = -lse_n;   // negated: x = s * scale - lse and dp - delta become packed fmas
+        s_del[sl + r] = -del_n;
+      }
       if (it + 1 < iters) fetch_stats(it + 1);
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 1, 256;" ::: "memory");
       const int m0 = m0_of(it);
       // query rows of this tile the key is legal for: m >= key - shift (causal)
       const int m_first = p.causal ? key - p.shift : -0x40000000;
       const bool tile_legal = n0 + BLK <= p.Sk && (!p.causal || m0 >= n0 + BLK - 1 - p.shift);
       const uint64_t scale2 = pack2f(p.scale_log2, p.scale_log2);
-      uint32_t pk[64];   // bf16 P^T of this key row, kept for the dS^T phase
+      uint32_t pk[32];   // bf16 P^T of this key row and this group's columns, kept for the dS^T phase
       // ---- phase 1: P^T = exp2(scale * S^T - lse), written over S^T; dV's MMAs may start
       BW_TRACE(0, it * 8 + 0);
       if (ok) ok = mbar_wait(s_full, it & 1, abort_flag, p.err, kErrWaitTmemFull, it);
@@ -337,7 +346,8 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       if (ok) {
         tc_fence_after();
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int half = 0; half < 2; ++half) {
+          const int c = 2 * g + half;   // 32-column chunk of S^T
           uint32_t sv[32];
           tmem_ld_32x32b_x32(tS + lane_base + 32 * c, sv);
           tmem_ld_wait();
@@ -347,7 +357,7 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
               const uint64_t nl = *reinterpret_cast<const uint64_t*>(s_lse + sl + 32 * c + k);
               float x0, x1;
               unpack2f(ffma2(pack2f(__uint_as_float(sv[k]), __uint_as_float(sv[k + 1])), scale2, nl), x0, x1);
-              pk[16 * c + (k >> 1)] = PACK_PROB(ex2(x0), ex2(x1));
+              pk[16 * half + (k >> 1)] = PACK_PROB(ex2(x0), ex2(x1));
             }
           } else {
 #pragma unroll
@@ -359,14 +369,11 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
                 const bool legal = key_ok && (m0 + col >= m_first);
                 pe[e] = legal ? ex2(__uint_as_float(sv[k + e]) * p.scale_log2 + s_lse[sl + col]) : 0.f;
               }
-              pk[16 * c + (k >> 1)] = PACK_PROB(pe[0], pe[1]);
+              pk[16 * half + (k >> 1)] = PACK_PROB(pe[0], pe[1]);
             }
           }
-          if (c & 1) {   // 64 fp32 columns consumed -> their 32 packed columns
-            uint32_t (&half)[32] = *reinterpret_cast<uint32_t (*)[32]>(&pk[32 * (c >> 1)]);
-            tmem_st_32x32b_x32(tS + lane_base + 32 * (c >> 1), half);
-          }
         }
+        tmem_st_32x32b_x32(tS + lane_base + 64 * g, pk);   // 64 fp32 columns consumed -> their 32 packed columns
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
@@ -378,27 +385,26 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       BW_TRACE(0, it * 8 + 3);
       if (ok) {
         tc_fence_after();
-#pragma unroll
-        for (int cp = 0; cp < 2; ++cp) {
+        {
           uint32_t dk[32];
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
-            const int c = 2 * cp + half;
-            uint32_t g[32];
-            tmem_ld_32x32b_x32(tdP + lane_base + 32 * c, g);
+            const int c = 2 * g + half;
+            uint32_t dpv[32];
+            tmem_ld_32x32b_x32(tdP + lane_base + 32 * c, dpv);
             tmem_ld_wait();
 #pragma unroll
             for (int k = 0; k < 32; k += 2) {
-              const uint32_t pw = pk[16 * c + (k >> 1)];
+              const uint32_t pw = pk[16 * half + (k >> 1)];
               const uint64_t nd = *reinterpret_cast<const uint64_t*>(s_del + sl + 32 * c + k);
               const uint64_t pp = pack2f(bf16lo(pw), bf16hi(pw));
               // p * dp + p * (-delta)
               float d0, d1;
-              unpack2f(ffma2(pp, pack2f(__uint_as_float(g[k]), __uint_as_float(g[k + 1])), fmul2(pp, nd)), d0, d1);
+              unpack2f(ffma2(pp, pack2f(__uint_as_float(dpv[k]), __uint_as_float(dpv[k + 1])), fmul2(pp, nd)), d0, d1);
               dk[16 * half + (k >> 1)] = PACK_PROB(d0, d1);
             }
           }
-          tmem_st_32x32b_x32(tdP + lane_base + 32 * cp, dk);
+          tmem_st_32x32b_x32(tdP + lane_base + 64 * g, dk);
         }
         tmem_st_wait();
         tc_fence_before();
@@ -411,19 +417,17 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     if (iters > 0) {
       if (ok) ok = mbar_wait(o_full, 0, abort_flag, p.err, kErrWaitTmemFull, 9000);
       tc_fence_after();
-      acc_to_smem(tdV + lane_base, sQ, r, 1.0f);
-      acc_to_smem(tdK + lane_base, sQ + TILE_BYTES, r, p.scale);
+      if (g == 0) acc_to_smem(tdV + lane_base, sQ, r, 1.0f);                  // group 0 stores dV,
+      else acc_to_smem(tdK + lane_base, sQ + TILE_BYTES, r, p.scale);         // group 1 dK
     } else {
-      zeros_to_smem(sQ, r);
-      zeros_to_smem(sQ + TILE_BYTES, r);
+      zeros_to_smem(sQ + g * TILE_BYTES, r);
     }
     fence_proxy_async_smem();
-    asm volatile("bar.sync 1, 128;" ::: "memory");
+    asm volatile("bar.sync %0, 128;" ::"r"(2 + g) : "memory");
     if (r == 0 && ok) {
-      tma_store_4d(&tmdV, sQ, 0, n0, hk, b);
-      tma_store_4d(&tmdV, sQ + HALF_BYTES, 64, n0, hk, b);
-      tma_store_4d(&tmdK, sQ + TILE_BYTES, 0, n0, hk, b);
-      tma_store_4d(&tmdK, sQ + TILE_BYTES + HALF_BYTES, 64, n0, hk, b);
+      const CUtensorMap* tmo = g == 0 ? &tmdV : &tmdK;
+      tma_store_4d(tmo, sQ + g * TILE_BYTES, 0, n0, hk, b);
+      tma_store_4d(tmo, sQ + g * TILE_BYTES + HALF_BYTES, 64, n0, hk, b);
       tma_store_commit();
       tma_store_wait<0>();
     }
@@ -435,7 +439,7 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
     for (int k = 0; k < 64; ++k) __nanosleep(10000);
     __syncthreads();
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }

@@ -127,6 +127,28 @@ __device__ __forceinline__ void unpack2f(uint64_t v, float& lo, float& hi) {
   lo = __uint_as_float(a);
   hi = __uint_as_float(b2);
 }
+// 2^x for a pair on the FMA pipe (the special-function pipe, 4 lanes per cycle and scheduler, bounds the
+// P^T conversion of the dK/dV kernel): round x to an integer n with the 1.5 * 2^23 trick, a cubic for
+// 2^f on f = x - n in [-0.5, 0.5] (relative error 7.5e-5, a thirtieth of the bf16 rounding that follows),
+// then n added into the exponent field. x is clamped at -125 (2^-125 instead of 0 below that) and is
+// expected <= 0 up to rounding, as it is for a log-sum-exp that belongs to the scores.
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b2, uint64_t c);
+__device__ __forceinline__ void ex2_poly2(float x0, float x1, float& y0, float& y1) {
+  const uint64_t one2 = pack2f(1.f, 1.f), mone2 = pack2f(-1.f, -1.f);
+  const uint64_t magic2 = pack2f(12582912.f, 12582912.f), nmagic2 = pack2f(-12582912.f, -12582912.f);
+  const uint64_t xx = pack2f(fmaxf(x0, -125.f), fmaxf(x1, -125.f));
+  const uint64_t t = ffma2(xx, one2, magic2);     // low mantissa bits = n
+  const uint64_t n = ffma2(t, one2, nmagic2);
+  const uint64_t f = ffma2(n, mone2, xx);
+  uint64_t q = ffma2(pack2f(0.0551716648f, 0.0551716648f), f, pack2f(0.2426111251f, 0.2426111251f));
+  q = ffma2(q, f, pack2f(0.6932609677f, 0.6932609677f));
+  q = ffma2(q, f, pack2f(0.9999280572f, 0.9999280572f));
+  float t0, t1, q0, q1;
+  unpack2f(t, t0, t1);
+  unpack2f(q, q0, q1);
+  y0 = __uint_as_float(__float_as_uint(t0) * 0x800000u + __float_as_uint(q0));
+  y1 = __uint_as_float(__float_as_uint(t1) * 0x800000u + __float_as_uint(q1));
+}
 __device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b2, uint64_t c) {
   uint64_t d;
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b2), "l"(c));
@@ -357,7 +379,13 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
               const uint64_t nl = *reinterpret_cast<const uint64_t*>(s_lse + sl + 32 * c + k);
               float x0, x1;
               unpack2f(ffma2(pack2f(__uint_as_float(sv[k]), __uint_as_float(sv[k + 1])), scale2, nl), x0, x1);
-              pk[16 * half + (k >> 1)] = PACK_PROB(ex2(x0), ex2(x1));
+              if (k & 2) {   // every second pair on the FMA pipe
+                float y0, y1;
+                ex2_poly2(x0, x1, y0, y1);
+                pk[16 * half + (k >> 1)] = PACK_PROB(y0, y1);
+              } else {
+                pk[16 * half + (k >> 1)] = PACK_PROB(ex2(x0), ex2(x1));
+              }
             }
           } else {
 #pragma unroll

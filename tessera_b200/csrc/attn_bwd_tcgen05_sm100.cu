@@ -6,9 +6,10 @@
 // dkv5_kernel: one CTA per 128 keys of one KV head. K and V stay in shared memory; the Q and dO
 // tiles (128 query rows) of every query head of the group stream through a two-deep TMA ring.
 // Per tile the MMA warp forms the TRANSPOSED products S^T = K Q^T and dP^T = V dO^T into TMEM
-// (keys on the 128 lanes, query rows along the columns), the four softmax warps (thread = key)
-// turn them in place into bf16 P^T and dS^T, and the MMA warp accumulates dV += P^T dO and
-// dK += dS^T Q with the A operand read straight from TMEM. TMEM: S^T | dP^T | dV | dK, 128 fp32
+// (keys on the 128 lanes, query rows along the columns), two groups of four softmax warps
+// (thread = key; group g owns query columns 64 g .. 64 g + 63 and packs them in place, so neither
+// group writes a column the other still reads) turn them into bf16 P^T and dS^T, and the MMA warp
+// accumulates dV += P^T dO and dK += dS^T Q with the A operand read straight from TMEM. TMEM: S^T | dP^T | dV | dK, 128 fp32
 // columns each, all four products at full width (a 128 x 64 shared-shared MMA is bound by operand
 // delivery, measured). The overlap comes from handing the two score buffers over separately:
 //   softmax:  P^T(t) from S^T(t) (kept packed in registers too) | dS^T(t) from dP^T(t) and P^T(t) | P^T(t+1) ...
@@ -18,8 +19,11 @@
 // dP = dO V^T; thread = query row, so lse and delta are per-thread scalars. P is only needed in
 // registers, so the S buffer is handed back as soon as it has been read (S(t+1) is formed while
 // dS(t) = P(t) (dP(t) - delta) is computed), and dQ += dS K. TMEM: S | dP (even tiles) | dQ | dP (odd tiles).
-// Warps 0-3 softmax + epilogue (TMEM lane = 32 * warp + lane), warp 4 MMA issuer and TMEM owner,
-// warp 5 TMA producer. Every wait is bounded (error word + abort flag), as in the forward kernel.
+// Its two conversion groups take alternate tiles; K has three shared-memory stages (K(t) is read by
+// S(t) and, a tile later, by dQ(t)), V two, released straight after dP.
+// Both kernels: warps 0-7 conversion + epilogue (TMEM lane = 32 * (warp & 3) + lane), warp 8 MMA
+// issuer and TMEM owner, warp 9 TMA producer. Every wait is bounded (error word + abort flag), as in
+// the forward kernel.
 #include <cuda_bf16.h>
 
 #include <cmath>

@@ -134,8 +134,13 @@ TsrStatus tsrGetArtifactTarget(tsrArtifact artifact, const char** out);
 TsrStatus tsrGetKernel(tsrArtifact artifact, const char* name, tsrKernel* out);
 TsrStatus tsrDestroyKernel(tsrKernel kernel);
 /* args[0] = const tsrGpuLaunchParams*; nargs >= 1. Routed to the registered launcher;
- * TSR_STATUS_UNIMPLEMENTED when none handles (target, kernel name). */
+ * TSR_STATUS_UNIMPLEMENTED when none handles (target, kernel name). The built-in launcher
+ * enqueues the work on `s` (NULL = the default stream), so tsrStreamSynchronize(s),
+ * tsrRecordEvent(e, s) and tsrWaitEvent(e, s) order with it. */
 TsrStatus tsrLaunchKernel(tsrStream s, tsrKernel kernel, void** args, size_t nargs);
+/* The launcher signature carries no stream: a launcher registered with tsrRegisterGpuLauncher reads
+ * the cudaStream_t of the tsrLaunchKernel call that is running it here (NULL = default stream). */
+void* tessera_sm100_current_launch_stream(void);
 TsrStatus tsrRegisterGpuLauncher(tsrGpuLauncherFn fn, void* user);
 /* The library's own launcher for target "nvidia_sm100" (kernel names tessera.sm100.*), exported
  * so that a runtime with the same registry, such as the reference's libtessera_runtime

@@ -43,9 +43,14 @@ long long tessera_sm100_launch_count(void);
  * (tessera_nvidia_gemm.cpp:617-697). */
 int tessera_sm100_device_alloc(void** out, size_t bytes);
 int tessera_sm100_device_free(void* ptr);
-/* Caching device allocator (blocks are recycled without cudaFree; stream-ordered reuse). */
+/* Caching device allocator: blocks are recycled without cudaFree. A block may be freed as soon as
+ * the work that uses it has been ENQUEUED; it is handed out again only when that work has finished:
+ * pool_free orders the reuse after everything queued so far on the legacy default stream and on
+ * every stream made by tessera_sm100_stream_create / tsrCreateStream, pool_free_async after the one
+ * given stream (cheaper; the form for a stream this library did not create). */
 int tessera_sm100_pool_alloc(void** out, size_t bytes);
 int tessera_sm100_pool_free(void* ptr);
+int tessera_sm100_pool_free_async(void* ptr, void* stream);
 int tessera_sm100_pool_release(void);
 int tessera_sm100_device_memset(void* ptr, int value, size_t bytes, void* stream);
 int tessera_sm100_device_upload(void* dst, const void* src, size_t bytes, void* stream);
@@ -111,7 +116,10 @@ int tessera_sm100_gemm_epilogue_device(const void* A, const void* B, void* D, in
  * multiplies columns [r*N/world, (r+1)*N/world) of the full B[K,N] and TMA-stores every output
  * tile into all `world` copies of Y. Y_ptrs[i] is rank i's Y base (a CUDA-IPC-mapped peer pointer
  * for i != rank, see tessera_sm100_ipc_*). Each copy is complete once every rank's kernel has
- * finished, so ranks synchronise their streams and then meet at a host barrier. world <= 8. */
+ * finished, so ranks synchronise their streams and then meet at a host barrier. world <= 8.
+ * From 16 k-blocks of 64 on, the K loop of every tile is split over two neighbouring CTA pairs
+ * (fp32 partial sums through a workspace taken from the library's pool for the duration of the
+ * launch), so the first stores leave after half a tile time. */
 int tessera_sm100_gemm_allgather_device(const void* A, const void* B, void* const* Y_ptrs, int world,
                                         int rank, int M, int N_total, int K, int in_dtype,
                                         int out_dtype, void* stream);

@@ -45,6 +45,7 @@ _SIGNATURES = {
     "tessera_sm100_device_free": (c_int, [_VP]),
     "tessera_sm100_pool_alloc": (c_int, [POINTER(_VP), c_size_t]),
     "tessera_sm100_pool_free": (c_int, [_VP]),
+    "tessera_sm100_pool_free_async": (c_int, [_VP, _VP]),
     "tessera_sm100_pool_release": (c_int, []),
     "tessera_sm100_device_memset": (c_int, [_VP, c_int, c_size_t, _VP]),
     "tessera_sm100_device_upload": (c_int, [_VP, _VP, c_size_t, _VP]),

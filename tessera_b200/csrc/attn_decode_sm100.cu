@@ -1289,7 +1289,7 @@ int tessera_sm100_flash_attn_strided_device(const void* Q, const void* K, const 
   const int rc = attn_decode::launch(Q, K, V, O, B, Hq, Hkv, Sk, D, scale, std::max(splits, 1),
                                      scratch, static_cast<cudaStream_t>(stream), q_strides,
                                      k_strides, v_strides, o_strides);
-  if (scratch) pool_free(scratch);  // recycled in stream order, like the dense dispatcher's
+  if (scratch) pool_free_after(scratch, static_cast<cudaStream_t>(stream));  // reusable once this launch is done
   return rc;
 }
 

@@ -63,8 +63,10 @@ int tessera_sm100_device_free(void* ptr) {
 }
 // Caching allocator shared with the host-pointer entry points: freed blocks are kept and handed
 // out again, so steady-state loops make no cudaMalloc/cudaFree calls (each of which synchronises
-// the device). A block may be reused as soon as it is freed: free it only after the work that
-// uses it has been enqueued, and use one stream per pool block chain.
+// the device). Free a block once the work that uses it has been ENQUEUED: pool_free orders its
+// reuse after everything queued so far on the legacy default stream and on every stream made by
+// tessera_sm100_stream_create / tsrCreateStream; pool_free_async after one given stream only
+// (cheaper, and the form for a stream this library did not create).
 int tessera_sm100_pool_alloc(void** out, size_t bytes) {
   if (!out) return kBadArg;
   if (int rc = ensure_device()) return rc;
@@ -72,7 +74,11 @@ int tessera_sm100_pool_alloc(void** out, size_t bytes) {
   return *out ? kOk : kDeviceFailed;
 }
 int tessera_sm100_pool_free(void* ptr) {
-  pool_free(ptr);
+  pool_free_after_all(ptr);
+  return kOk;
+}
+int tessera_sm100_pool_free_async(void* ptr, void* stream) {
+  pool_free_after(ptr, static_cast<cudaStream_t>(stream));
   return kOk;
 }
 int tessera_sm100_pool_release(void) {
@@ -126,11 +132,13 @@ int tessera_sm100_stream_create(void** out) {
   if (int rc = ensure_device()) return rc;
   cudaStream_t s;
   TSB_CUDA_OK(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+  pool_note_stream(s, true);
   *out = s;
   return kOk;
 }
 int tessera_sm100_stream_destroy(void* stream) {
   if (!stream) return kOk;
+  pool_note_stream(static_cast<cudaStream_t>(stream), false);
   TSB_CUDA_OK(cudaStreamDestroy(static_cast<cudaStream_t>(stream)));
   return kOk;
 }

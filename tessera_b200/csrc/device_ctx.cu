@@ -14,11 +14,19 @@ namespace tsb {
 namespace {
 thread_local std::string g_last_error;
 
+// A cached block and the events that must have completed before it may be handed out again
+// (none: free for any stream).
+struct FreeBlock {
+  void* ptr = nullptr;
+  std::vector<cudaEvent_t> pending;
+};
 struct DeviceState {
   int* err_word = nullptr;
   int sm_count = 0;
-  std::multimap<size_t, void*> free_blocks;   // size -> block
-  std::map<void*, size_t> live_blocks;        // block -> size
+  std::multimap<size_t, FreeBlock> free_blocks;  // size -> block
+  std::map<void*, size_t> live_blocks;           // block -> size
+  std::vector<cudaEvent_t> spare_events;         // recycled (timing disabled)
+  std::vector<cudaStream_t> streams;             // streams the library created on this device
 };
 std::mutex g_mu;
 std::atomic<long long> g_launches{0};
@@ -120,6 +128,21 @@ int consume_device_err(int out[4]) {
   return host[0];
 }
 
+namespace {
+// True once every pending event of the block has completed; completed events are recycled.
+bool block_ready_locked(DeviceState& s, FreeBlock& b) {
+  while (!b.pending.empty()) {
+    if (cudaEventQuery(b.pending.back()) != cudaSuccess) {
+      cudaGetLastError();  // cudaErrorNotReady is not sticky, but clear it anyway
+      return false;
+    }
+    s.spare_events.push_back(b.pending.back());
+    b.pending.pop_back();
+  }
+  return true;
+}
+}  // namespace
+
 void* pool_alloc(size_t bytes) {
   if (bytes == 0) bytes = 256;
   bytes = (bytes + 255) & ~size_t(255);
@@ -127,10 +150,11 @@ void* pool_alloc(size_t bytes) {
   {
     std::lock_guard<std::mutex> lk(g_mu);
     DeviceState& s = state_locked(dev);
-    auto it = s.free_blocks.lower_bound(bytes);
-    // Reuse a cached block unless it would waste more than half of itself.
-    if (it != s.free_blocks.end() && it->first <= 2 * bytes) {
-      void* p = it->second;
+    // Reuse a cached block unless it would waste more than half of itself; skip blocks whose
+    // last use has not finished on the stream it was freed on.
+    for (auto it = s.free_blocks.lower_bound(bytes); it != s.free_blocks.end() && it->first <= 2 * bytes; ++it) {
+      if (!block_ready_locked(s, it->second)) continue;
+      void* p = it->second.ptr;
       s.live_blocks[p] = it->first;
       s.free_blocks.erase(it);
       return p;
@@ -153,27 +177,83 @@ void* pool_alloc(size_t bytes) {
   return p;
 }
 
-void pool_free(void* p) {
+namespace {
+// Moves a live block to the free list; `streams` are the streams whose queued work may still use it.
+void pool_free_on(void* p, const cudaStream_t* streams, int n, bool all_known) {
   if (!p) return;
   int dev = current_device();
   std::lock_guard<std::mutex> lk(g_mu);
   DeviceState& s = state_locked(dev);
   auto it = s.live_blocks.find(p);
   if (it == s.live_blocks.end()) return;
-  s.free_blocks.emplace(it->second, p);
+  FreeBlock b;
+  b.ptr = p;
+  auto mark = [&](cudaStream_t st) {
+    cudaEvent_t ev = nullptr;
+    if (!s.spare_events.empty()) {
+      ev = s.spare_events.back();
+      s.spare_events.pop_back();
+    } else if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) {
+      cudaGetLastError();
+      ev = nullptr;
+    }
+    if (ev && cudaEventRecord(ev, st) == cudaSuccess) {
+      b.pending.push_back(ev);
+    } else {
+      // No event to order the reuse by: wait for the stream here instead.
+      cudaGetLastError();
+      if (ev) s.spare_events.push_back(ev);
+      cudaStreamSynchronize(st);
+    }
+  };
+  for (int i = 0; i < n; ++i) mark(streams[i]);
+  if (all_known) {
+    mark(nullptr);  // the legacy default stream (it also waits for every blocking stream)
+    for (cudaStream_t st : s.streams) mark(st);
+  }
+  s.free_blocks.emplace(it->second, std::move(b));
   s.live_blocks.erase(it);
+}
+}  // namespace
+
+void pool_free(void* p) { pool_free_on(p, nullptr, 0, false); }
+void pool_free_after(void* p, cudaStream_t stream) { pool_free_on(p, &stream, 1, false); }
+void pool_free_after_all(void* p) { pool_free_on(p, nullptr, 0, true); }
+
+void pool_note_stream(cudaStream_t stream, bool created) {
+  int dev = current_device();
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto& v = state_locked(dev).streams;
+  if (created) {
+    v.push_back(stream);
+  } else {
+    for (auto& kv : g_devices) {
+      auto& w = kv.second.streams;
+      for (size_t i = 0; i < w.size(); ++i)
+        if (w[i] == stream) {
+          w.erase(w.begin() + i);
+          break;
+        }
+    }
+  }
 }
 
 void pool_release_all() {
   int dev = current_device();
-  std::vector<void*> victims;
+  std::vector<FreeBlock> victims;
   {
     std::lock_guard<std::mutex> lk(g_mu);
     DeviceState& s = state_locked(dev);
-    for (auto& kv : s.free_blocks) victims.push_back(kv.second);
+    for (auto& kv : s.free_blocks) victims.push_back(std::move(kv.second));
     s.free_blocks.clear();
   }
-  for (void* p : victims) cudaFree(p);
+  for (FreeBlock& b : victims) {
+    for (cudaEvent_t ev : b.pending) {
+      cudaEventSynchronize(ev);
+      cudaEventDestroy(ev);
+    }
+    cudaFree(b.ptr);
+  }
 }
 
 bool encode_tmap(CUtensorMap* out, CUtensorMapDataType dtype, int rank, const void* base,

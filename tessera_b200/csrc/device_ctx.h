@@ -31,9 +31,18 @@ int* device_err_word();
 // Reads and clears the word (synchronises the device). Returns the code.
 int consume_device_err(int out[4]);
 
-// Caching allocator: blocks are kept for reuse until pool_release_all().
+// Caching allocator: blocks are kept for reuse until pool_release_all(). A freed block carries
+// the events after which it may be handed out again, so freeing right after enqueueing the work
+// that uses it is safe on any stream:
+//   pool_free(p)            nothing queued uses p any more (the caller synchronised)
+//   pool_free_after(p, s)   work queued on stream s may still use p
+//   pool_free_after_all(p)  the stream is not known: ordered after the legacy default stream and
+//                           every stream this library created on the device (pool_note_stream)
 void* pool_alloc(size_t bytes);
 void pool_free(void* p);
+void pool_free_after(void* p, cudaStream_t stream);
+void pool_free_after_all(void* p);
+void pool_note_stream(cudaStream_t stream, bool created);
 void pool_release_all();
 
 // rank <= 5. dims[0] is the innermost extent (elements); strides_bytes[i] is the byte stride

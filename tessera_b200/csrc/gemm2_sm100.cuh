@@ -20,8 +20,6 @@
 // only its valid rows, as the single-CTA kernel does for partial tiles. In the SwiGLU mode the B
 // halves are the two weight matrices: the even CTA loads the 128 gate columns, the odd CTA the
 // matching 128 up columns, and every CTA's accumulator holds gate | up for its own rows.
-// With `num_peers` > 0 the epilogue stores every piece through the per-rank output maps (the
-// all-gather of the column-parallel GEMM), as the single-CTA kernel does.
 // Both CTAs allocate TMEM with cta_group::2 from the same warp index, and free it only after
 // a cluster barrier; a second cluster barrier after barrier initialisation keeps either CTA
 // from signalling a barrier the other has not initialised yet.
@@ -119,7 +117,7 @@ template <typename OutT, int kMode, bool kFp8 = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
              const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmD,
-             const __grid_constant__ gemm::PeerMaps peers, const Params p) {
+             const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -353,13 +351,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
           __syncwarp();
           if (lane == 0) {
             const int d_b = (kMode == kPlain) ? tile.b : 0;
-            if (kMode == kPlain && p.num_peers > 0) {
-              // Column-parallel GEMM: the same piece into every rank's Y (plain TMA stores over
-              // NVLink; this rank's own copy is one of the maps). One bulk group covers them all.
-              for (int i = 0; i < p.num_peers; ++i) tma_store_3d(&peers.m[i], buf, col0, row0, d_b);
-            } else {
-              tma_store_3d(&tmD, buf, col0, row0, d_b);
-            }
+            tma_store_3d(&tmD, buf, col0, row0, d_b);
             tma_store_commit();
           }
         } else {

@@ -1,6 +1,7 @@
 // Host side of the tcgen05 GEMM: tensor-map construction, launch, and the C entry points.
 #include "gemm_sm100.cuh"
 #include "gemm2_sm100.cuh"
+#include "gemm_ag_sm100.cuh"
 
 #include <algorithm>
 #include <cstdlib>
@@ -18,13 +19,12 @@ size_t out_size(int out_dtype) { return out_dtype == TESSERA_SM100_F32 ? 4 : 2; 
 
 template <typename OutT, int kMode>
 int launch_kernel(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2,
-                  const CUtensorMap& tD, const PeerMaps& peers, const Params& p, int grid,
-                  cudaStream_t stream) {
+                  const CUtensorMap& tD, const Params& p, int grid, cudaStream_t stream) {
   // The attribute is per device; setting it on every call is cheap and keeps multi-device
   // processes correct.
   TSB_CUDA_OK(cudaFuncSetAttribute(gemm_kernel<OutT, kMode>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));
-  gemm_kernel<OutT, kMode><<<grid, NUM_THREADS, SMEM_ALLOC, stream>>>(tA, tB, tB2, tD, peers, p);
+  gemm_kernel<OutT, kMode><<<grid, NUM_THREADS, SMEM_ALLOC, stream>>>(tA, tB, tB2, tD, p);
   TSB_CUDA_OK(cudaGetLastError());
   note_launch();
   return kOk;
@@ -32,15 +32,15 @@ int launch_kernel(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMa
 
 template <int kMode>
 int dispatch_out(int out_dtype, const CUtensorMap& tA, const CUtensorMap& tB,
-                 const CUtensorMap& tB2, const CUtensorMap& tD, const PeerMaps& peers,
-                 const Params& p, int grid, cudaStream_t stream) {
+                 const CUtensorMap& tB2, const CUtensorMap& tD, const Params& p, int grid,
+                 cudaStream_t stream) {
   switch (out_dtype) {
     case TESSERA_SM100_F32:
-      return launch_kernel<float, kMode>(tA, tB, tB2, tD, peers, p, grid, stream);
+      return launch_kernel<float, kMode>(tA, tB, tB2, tD, p, grid, stream);
     case TESSERA_SM100_BF16:
-      return launch_kernel<__nv_bfloat16, kMode>(tA, tB, tB2, tD, peers, p, grid, stream);
+      return launch_kernel<__nv_bfloat16, kMode>(tA, tB, tB2, tD, p, grid, stream);
     case TESSERA_SM100_F16:
-      return launch_kernel<__half, kMode>(tA, tB, tB2, tD, peers, p, grid, stream);
+      return launch_kernel<__half, kMode>(tA, tB, tB2, tD, p, grid, stream);
     default:
       break;
   }
@@ -51,8 +51,8 @@ int dispatch_out(int out_dtype, const CUtensorMap& tA, const CUtensorMap& tB,
 // CTA-pair kernel: cluster of two, as many clusters as the device can hold at once.
 template <typename OutT, int kMode>
 int launch_pair_kernel(const CUtensorMap& tA, const CUtensorMap& tB, const CUtensorMap& tB2,
-                       const CUtensorMap& tD, const PeerMaps& peers, const Params& p,
-                       long long pair_tiles, cudaStream_t stream) {
+                       const CUtensorMap& tD, const Params& p, long long pair_tiles,
+                       cudaStream_t stream) {
   TSB_CUDA_OK(cudaFuncSetAttribute(gemm2::gemm2_kernel<OutT, kMode>,
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, gemm2::SMEM_ALLOC));
   cudaLaunchConfig_t cfg{};
@@ -81,7 +81,65 @@ int launch_pair_kernel(const CUtensorMap& tA, const CUtensorMap& tB, const CUten
   }
   const int clusters = (int)std::min<long long>(pair_tiles, mc);
   cfg.gridDim = dim3(2 * clusters);
-  TSB_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm2::gemm2_kernel<OutT, kMode>, tA, tB, tB2, tD, peers, p));
+  TSB_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm2::gemm2_kernel<OutT, kMode>, tA, tB, tB2, tD, p));
+  note_launch();
+  return kOk;
+}
+
+// The all-gather GEMM: 256 x 256 pair tiles, every piece stored into all copies of the output,
+// K split in two when the K loop is long enough (workspace from the pool, reusable once this
+// launch has finished on `stream`).
+template <typename OutT>
+int launch_ag_kernel(const CUtensorMap& tA, const CUtensorMap& tB, const PeerMaps& peers,
+                     Params p, long long tiles, cudaStream_t stream) {
+  TSB_CUDA_OK(cudaFuncSetAttribute(gemm_ag::gemm_ag_kernel<OutT>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, gemm_ag::SMEM_ALLOC));
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(gemm_ag::NUM_THREADS);
+  cfg.dynamicSmemBytes = gemm_ag::SMEM_ALLOC;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  static int max_clusters[64] = {};
+  const int dev = current_device();
+  int mc = (dev >= 0 && dev < 64) ? max_clusters[dev] : 0;
+  if (mc == 0) {
+    cfg.gridDim = dim3(2 * (sm_count() / 2));
+    if (cudaOccupancyMaxActiveClusters(&mc, gemm_ag::gemm_ag_kernel<OutT>, &cfg) != cudaSuccess || mc <= 0) {
+      cudaGetLastError();
+      mc = sm_count() / 2;
+    }
+    if (dev >= 0 && dev < 64) max_clusters[dev] = mc;
+  }
+  void* ws = nullptr;
+  if (p.ksplit == 2) {
+    const size_t partial_bytes = (size_t)tiles * gemm_ag::PARTIAL_BYTES_PER_TILE;
+    const size_t flag_bytes = (size_t)tiles * gemm_ag::FLAGS_PER_TILE * sizeof(int);
+    ws = pool_alloc(partial_bytes + flag_bytes);
+    if (!ws) return kDeviceFailed;
+    p.partial = static_cast<float*>(ws);
+    p.flags = reinterpret_cast<int*>(static_cast<char*>(ws) + partial_bytes);
+    if (cudaMemsetAsync(p.flags, 0, flag_bytes, stream) != cudaSuccess) {
+      set_last_error("gemm_allgather: clearing the flags failed: %s", cudaGetErrorString(cudaGetLastError()));
+      pool_free_after(ws, stream);
+      return kDeviceFailed;
+    }
+  }
+  // The two halves of a tile run on neighbouring clusters in the same wave: an even cluster count.
+  int clusters = (int)std::min<long long>(tiles * p.ksplit, mc);
+  if (p.ksplit == 2) clusters &= ~1;
+  cfg.gridDim = dim3(2 * clusters);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_ag::gemm_ag_kernel<OutT>, tA, tB, peers, p);
+  if (ws) pool_free_after(ws, stream);
+  if (e != cudaSuccess) {
+    set_last_error("gemm_allgather: launch failed: %s", cudaGetErrorString(e));
+    return kDeviceFailed;
+  }
   note_launch();
   return kOk;
 }
@@ -113,7 +171,8 @@ int launch_plain(const void* A, const void* B, void* D, int batch, int M, int N,
                  long long lda, long long ldb, long long ldd, long long sA, long long sB,
                  long long sD, int in_dtype, int out_dtype, cudaStream_t stream,
                  void* const* peer_D = nullptr, int num_peers = 0, const float* bias = nullptr,
-                 const void* residual = nullptr, long long ldr = 0, int activation = 0) {
+                 const void* residual = nullptr, long long ldr = 0, int activation = 0,
+                 int peer_first = 0) {
   if (!A || !B || !D || batch <= 0 || M <= 0 || N <= 0 || K <= 0) {
     set_last_error("gemm: null pointer or non-positive size (batch %d M %d N %d K %d)", batch, M,
                    N, K);
@@ -161,31 +220,26 @@ int launch_plain(const void* A, const void* B, void* D, int batch, int M, int N,
   const long long pair_tiles =
       (long long)(((M + BM - 1) / BM + 1) / 2) * ((N + BN - 1) / BN) * batch;
   const bool use_pairs = pair_kernel_enabled() && M >= 2 * BM && pair_tiles >= sm_count() / 2;
-  static PeerMaps no_peers{};
   PeerMaps peer_maps;
-  const PeerMaps* peers = &no_peers;
   if (num_peers > 0) {
-    if (num_peers > MAX_PEERS || !peer_D) {
-      set_last_error("gemm: at most %d output copies are supported", MAX_PEERS);
+    // Column-parallel GEMM with the all-gather in the epilogue: one output map per copy of Y.
+    if (num_peers > MAX_PEERS || !peer_D || batch != 1 || bias || residual || activation) {
+      set_last_error("gemm: at most %d output copies, one batch and no fused epilogue", MAX_PEERS);
       return kBadArg;
     }
     uint64_t dims[3] = {(uint64_t)N, (uint64_t)M, (uint64_t)batch};
     uint64_t str[2] = {(uint64_t)ldd * osz, (uint64_t)sD * osz};
-    // 16-bit outputs on the single-CTA kernel take the wide epilogue: 128-column (256-byte)
-    // rows, unswizzled staging. The CTA-pair kernel stores swizzled 128-byte rows.
-    const bool wide = (osz == 2) && !use_pairs;
-    uint32_t box[3] = {wide ? 128u : (uint32_t)(128 / osz), 32, 1};
+    uint32_t box[3] = {(uint32_t)(128 / osz), 32, 1};
     for (int i = 0; i < num_peers; ++i) {
       if (!peer_D[i] || !aligned16(peer_D[i])) {
         set_last_error("gemm: output copy %d is null or not 16-byte aligned", i);
         return kBadArg;
       }
       if (!encode_tmap(&peer_maps.m[i], tm_dtype(out_dtype), 3, peer_D[i], dims, str, box,
-                       wide ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B))
+                       CU_TENSOR_MAP_SWIZZLE_128B))
         return kBadArg;
     }
     for (int i = num_peers; i < MAX_PEERS; ++i) peer_maps.m[i] = peer_maps.m[0];
-    peers = &peer_maps;
   }
   Params p{};
   p.M = M;
@@ -206,21 +260,35 @@ int launch_plain(const void* A, const void* B, void* D, int batch, int M, int N,
   p.err = device_err_word();
   if (!p.err) return kDeviceFailed;
   const long long total = (long long)p.m_tiles * p.n_tiles * batch;
+  if (num_peers > 0) {
+    Params pa = p;
+    pa.idesc = make_idesc_f16(in_dtype == TESSERA_SM100_BF16, false, true, 2 * BM, BN);
+    pa.peer_first = peer_first;
+    // Split K once the K loop has at least 16 k-blocks (each half still fills the TMA ring).
+    pa.ksplit = ((K + BK - 1) / BK >= 16) ? 2 : 1;
+    const long long ag_tiles = (long long)((p.m_tiles + 1) / 2) * p.n_tiles;
+    switch (out_dtype) {
+      case TESSERA_SM100_F32: return launch_ag_kernel<float>(tA, tB, peer_maps, pa, ag_tiles, stream);
+      case TESSERA_SM100_BF16: return launch_ag_kernel<__nv_bfloat16>(tA, tB, peer_maps, pa, ag_tiles, stream);
+      case TESSERA_SM100_F16: return launch_ag_kernel<__half>(tA, tB, peer_maps, pa, ag_tiles, stream);
+      default: break;
+    }
+  }
   if (use_pairs) {
     Params p2 = p;
     p2.idesc = make_idesc_f16(in_dtype == TESSERA_SM100_BF16, false, true, 2 * BM, BN);
     switch (out_dtype) {
       case TESSERA_SM100_F32:
-        return launch_pair_kernel<float, kPlain>(tA, tB, tB, tD, *peers, p2, pair_tiles, stream);
+        return launch_pair_kernel<float, kPlain>(tA, tB, tB, tD, p2, pair_tiles, stream);
       case TESSERA_SM100_BF16:
-        return launch_pair_kernel<__nv_bfloat16, kPlain>(tA, tB, tB, tD, *peers, p2, pair_tiles, stream);
+        return launch_pair_kernel<__nv_bfloat16, kPlain>(tA, tB, tB, tD, p2, pair_tiles, stream);
       case TESSERA_SM100_F16:
-        return launch_pair_kernel<__half, kPlain>(tA, tB, tB, tD, *peers, p2, pair_tiles, stream);
+        return launch_pair_kernel<__half, kPlain>(tA, tB, tB, tD, p2, pair_tiles, stream);
       default: break;
     }
   }
   const int grid = (int)std::min<long long>(total, sm_count());
-  return dispatch_out<kPlain>(out_dtype, tA, tB, tB, tD, *peers, p, grid, stream);
+  return dispatch_out<kPlain>(out_dtype, tA, tB, tB, tD, p, grid, stream);
 }
 
 // Ragged grouped GEMM on device pointers. x[T,K] rows sorted by group, w[E,K,N] (and w2 for
@@ -291,7 +359,6 @@ int launch_grouped(const void* x, const void* w, const void* w2, const int* offs
   // Upper bound on the number of tiles: every group may add one partial m-tile.
   const long long max_tiles = ((long long)(T + BM - 1) / BM + E) * p.n_tiles;
   const int grid = (int)std::min<long long>(max_tiles, sm_count());
-  static PeerMaps no_peers{};
   // Enough rows for at least one wave of 256-row pair tiles: the CTA-pair kernel.
   const long long max_pair_tiles = ((long long)(T + 2 * BM - 1) / (2 * BM) + E) * p.n_tiles;
   if (pair_kernel_enabled() && (long long)(T / (2 * BM)) * p.n_tiles >= sm_count() / 2) {
@@ -299,29 +366,29 @@ int launch_grouped(const void* x, const void* w, const void* w2, const int* offs
     p2.idesc = make_idesc_f16(in_dtype == TESSERA_SM100_BF16, false, true, 2 * BM, BN);
     if (swiglu) {
       if (out_dtype == TESSERA_SM100_F32)
-        return launch_pair_kernel<float, kGroupedSwiGLU>(tA, tB, tB2, tD, no_peers, p2, max_pair_tiles,
+        return launch_pair_kernel<float, kGroupedSwiGLU>(tA, tB, tB2, tD, p2, max_pair_tiles,
                                                          stream);
       if (out_dtype == TESSERA_SM100_BF16)
-        return launch_pair_kernel<__nv_bfloat16, kGroupedSwiGLU>(tA, tB, tB2, tD, no_peers, p2,
+        return launch_pair_kernel<__nv_bfloat16, kGroupedSwiGLU>(tA, tB, tB2, tD, p2,
                                                                  max_pair_tiles, stream);
       if (out_dtype == TESSERA_SM100_F16)
-        return launch_pair_kernel<__half, kGroupedSwiGLU>(tA, tB, tB2, tD, no_peers, p2,
+        return launch_pair_kernel<__half, kGroupedSwiGLU>(tA, tB, tB2, tD, p2,
                                                           max_pair_tiles, stream);
     } else {
       if (out_dtype == TESSERA_SM100_F32)
-        return launch_pair_kernel<float, kGrouped>(tA, tB, tB2, tD, no_peers, p2, max_pair_tiles,
+        return launch_pair_kernel<float, kGrouped>(tA, tB, tB2, tD, p2, max_pair_tiles,
                                                    stream);
       if (out_dtype == TESSERA_SM100_BF16)
-        return launch_pair_kernel<__nv_bfloat16, kGrouped>(tA, tB, tB2, tD, no_peers, p2,
+        return launch_pair_kernel<__nv_bfloat16, kGrouped>(tA, tB, tB2, tD, p2,
                                                            max_pair_tiles, stream);
       if (out_dtype == TESSERA_SM100_F16)
-        return launch_pair_kernel<__half, kGrouped>(tA, tB, tB2, tD, no_peers, p2, max_pair_tiles,
+        return launch_pair_kernel<__half, kGrouped>(tA, tB, tB2, tD, p2, max_pair_tiles,
                                                     stream);
     }
   }
   if (swiglu)
-    return dispatch_out<kGroupedSwiGLU>(out_dtype, tA, tB, tB2, tD, no_peers, p, grid, stream);
-  return dispatch_out<kGrouped>(out_dtype, tA, tB, tB2, tD, no_peers, p, grid, stream);
+    return dispatch_out<kGroupedSwiGLU>(out_dtype, tA, tB, tB2, tD, p, grid, stream);
+  return dispatch_out<kGrouped>(out_dtype, tA, tB, tB2, tD, p, grid, stream);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -584,7 +651,6 @@ template <typename OutT, int kMode>
 int launch_fp8_kernel(bool pairs, const CUtensorMap& tA, const CUtensorMap& tB,
                       const CUtensorMap& tB2, const CUtensorMap& tD, const Params& p,
                       long long tiles, cudaStream_t stream) {
-  static PeerMaps no_peers{};
   if (pairs) {
     TSB_CUDA_OK(cudaFuncSetAttribute(gemm2::gemm2_kernel<OutT, kMode, true>,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -602,14 +668,12 @@ int launch_fp8_kernel(bool pairs, const CUtensorMap& tA, const CUtensorMap& tB,
     cfg.numAttrs = 1;
     const int clusters = (int)std::min<long long>(tiles, sm_count() / 2);
     cfg.gridDim = dim3(2 * clusters);
-    TSB_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm2::gemm2_kernel<OutT, kMode, true>, tA, tB, tB2, tD,
-                                   no_peers, p));
+    TSB_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm2::gemm2_kernel<OutT, kMode, true>, tA, tB, tB2, tD, p));
   } else {
     TSB_CUDA_OK(cudaFuncSetAttribute(gemm_kernel<OutT, kMode, true>,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ALLOC));
     const int grid = (int)std::min<long long>(tiles, sm_count());
-    gemm_kernel<OutT, kMode, true><<<grid, NUM_THREADS, SMEM_ALLOC, stream>>>(tA, tB, tB2, tD,
-                                                                               no_peers, p);
+    gemm_kernel<OutT, kMode, true><<<grid, NUM_THREADS, SMEM_ALLOC, stream>>>(tA, tB, tB2, tD, p);
     TSB_CUDA_OK(cudaGetLastError());
   }
   note_launch();
@@ -833,7 +897,8 @@ int tessera_sm100_gemm_allgather_device(const void* A, const void* B, void* cons
   }
   const char* Bblk = static_cast<const char*>(B) + (size_t)rank * nb * 2;
   return gemm::launch_plain(A, Bblk, outs[rank], 1, M, nb, K, K, N_total, N_total, 0, 0, 0, in_dtype,
-                            out_dtype, static_cast<cudaStream_t>(stream), outs, world);
+                            out_dtype, static_cast<cudaStream_t>(stream), outs, world, nullptr, nullptr, 0, 0,
+                            rank + 1);
 }
 // D = act(A*B + bias + residual): the GEMM with the reference's fused_epilogue applied in the
 // kernel epilogue. bias is fp32 [N] or null; residual is [M,N] in the output dtype or null;

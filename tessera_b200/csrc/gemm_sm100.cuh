@@ -61,7 +61,14 @@ struct Params {
   const int* group_offsets;  // grouped modes: batch + 1 row offsets (device memory)
   void* D;                   // grouped modes: output base for masked stores
   long long ldd;             // grouped modes: output leading dimension (elements)
-  int num_peers;             // plain mode: > 0 = store each tile through peers.m[0..num_peers)
+  // all-gather kernel only (gemm_ag_sm100.cuh): number of output copies, where this rank's
+  // rotation over them starts, and the split of the K loop in two (fp32 partial sums and one flag
+  // per epilogue warp and tile in a device workspace, flags zeroed before the launch)
+  int num_peers;
+  int peer_first;
+  int ksplit;
+  float* partial;
+  int* flags;
   // plain mode, optional fused epilogue: D = act(A*B + bias[col] + residual[row, col])
   const float* bias;         // [N] fp32 or null
   const void* residual;      // [M, N] in the output dtype, leading dimension ldr, or null
@@ -77,8 +84,8 @@ struct Params {
   int* err;
 };
 
-// Output tensor maps of the other ranks (column-parallel GEMM whose epilogue stores every tile
-// into each rank's copy of Y: the all-gather fused into the GEMM).
+// Output tensor maps of every rank's copy of Y, for the column-parallel GEMM whose epilogue is the
+// all-gather (gemm_ag_sm100.cuh).
 constexpr int MAX_PEERS = 8;
 struct PeerMaps {
   CUtensorMap m[MAX_PEERS];
@@ -213,7 +220,7 @@ template <typename OutT, int kMode, bool kFp8 = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmD,
-            const __grid_constant__ PeerMaps peers, const Params p) {
+            const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -400,61 +407,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         sc = sc2 = __ldg(p.scale_a);
       }
       (void)sc2;
-      bool wide_done = false;
-      if constexpr (kMode == kPlain && sizeof(OutT) == 2) {
-        if (p.num_peers > 0) {
-          // Fused all-gather: 128 output columns (256-byte rows) per store, unswizzled staging
-          // (the warp's two 4 KB buffers used as one 8 KB buffer), one TMA store per rank.
-          // Wider rows make better NVLink packets; the bank conflicts of the unswizzled writes
-          // cost a few hundred cycles per tile against a main loop of tens of thousands.
-          wide_done = true;
-          const uint32_t buf = sEpi + static_cast<uint32_t>(warp * 2 * EPI_BUF_BYTES);
 #pragma unroll 1
-          for (int c = 0; c < 2; ++c) {
-            const int col0 = tile.n0 + c * 128;
-            if (col0 >= p.N || !warp_has_rows) break;
-            if (lane == 0) tma_store_wait_read<0>();
-            __syncwarp();
-#pragma unroll
-            for (int h = 0; h < 4; ++h) {
-              uint32_t r[32];
-              tmem_ld_32x32b_x32(t_acc + c * 128 + h * 32, r);
-              tmem_ld_wait();
-              uint32_t w[16];
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                if constexpr (std::is_same<OutT, __nv_bfloat16>::value) {
-                  __nv_bfloat162 v2 = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-                  w[j] = *reinterpret_cast<uint32_t*>(&v2);
-                } else {
-                  __half2 v2 = __floats2half2_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-                  w[j] = *reinterpret_cast<uint32_t*>(&v2);
-                }
-              }
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const uint32_t addr = buf + lane * 256u + static_cast<uint32_t>(h * 4 + j) * 16u;
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * j]),
-                             "r"(w[4 * j + 1]), "r"(w[4 * j + 2]), "r"(w[4 * j + 3])
-                             : "memory");
-              }
-            }
-            if (c == 1 || col0 + 128 >= p.N) {
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(tempty_bar(acc));
-            }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              for (int i = 0; i < p.num_peers; ++i) tma_store_3d(&peers.m[i], buf, col0, row0, tile.b);
-              tma_store_commit();
-            }
-          }
-        }
-      }
-#pragma unroll 1
-      for (int c = 0; c < kChunks && !wide_done; ++c) {
+      for (int c = 0; c < kChunks; ++c) {
         const int col0 = tile.n0 + c * kChunk;
         if (col0 >= p.N || !warp_has_rows) break;
         const uint32_t buf = sEpi + static_cast<uint32_t>((warp * 2 + sbuf) * EPI_BUF_BYTES);
@@ -505,13 +459,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           __syncwarp();
           if (lane == 0) {
             const int d_b = (kMode == kPlain) ? tile.b : 0;
-            if (kMode == kPlain && p.num_peers > 0) {
-              // Same tile into every rank's Y (this rank's own copy is one of the maps); plain
-              // TMA stores, no multicast. One bulk group covers all of them.
-              for (int i = 0; i < p.num_peers; ++i) tma_store_3d(&peers.m[i], buf, col0, row0, d_b);
-            } else {
-              tma_store_3d(&tmD, buf, col0, row0, d_b);
-            }
+            tma_store_3d(&tmD, buf, col0, row0, d_b);
             tma_store_commit();
           }
         } else {

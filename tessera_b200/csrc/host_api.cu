@@ -18,7 +18,7 @@ size_t esize(int dt) { return dt == TESSERA_SM100_F32 ? 4 : 2; }
 struct PoolBuf {
   void* p = nullptr;
   explicit PoolBuf(size_t bytes) : p(pool_alloc(bytes)) {}
-  ~PoolBuf() { pool_free(p); }
+  ~PoolBuf() { pool_free_after_all(p); }  // safe on early exits that leave work queued
   PoolBuf(const PoolBuf&) = delete;
   PoolBuf& operator=(const PoolBuf&) = delete;
 };

@@ -127,7 +127,14 @@ std::string normalize_target(const std::string& t) {
   return t;
 }
 
-// Built-in launcher: kernel name -> op entry point. buffers/dims follow each op's own ABI.
+// The CUDA stream of the tsrLaunchKernel call in progress on this thread. The launcher signature
+// (target, kernel, params, user) carries no stream, so tsrLaunchKernel publishes it here and the
+// built-in launcher enqueues on it; a launcher registered by someone else reads it through
+// tessera_sm100_current_launch_stream().
+thread_local void* t_launch_stream = nullptr;
+
+// Built-in launcher: kernel name -> op entry point. buffers/dims follow each op's own ABI. The
+// work is enqueued on the stream given to tsrLaunchKernel.
 TsrStatus builtin_launcher(const char* target, const char* name, const tsrGpuLaunchParams* p,
                            void* /*user*/) {
   if (normalize_target(target ? target : "") != "nvidia_sm100") return TSR_STATUS_NOT_FOUND;
@@ -143,12 +150,12 @@ TsrStatus builtin_launcher(const char* target, const char* name, const tsrGpuLau
                                    (int)p->dims[1], (int)p->dims[2],
                                    k == "tessera.sm100.gemm.bf16" ? TESSERA_SM100_BF16
                                                                   : TESSERA_SM100_F16,
-                                   TESSERA_SM100_F32, nullptr);
+                                   TESSERA_SM100_F32, t_launch_stream);
   } else if (k == "tessera.sm100.gemm.bf16.bf16out") {
     if (!need(3, 3)) return fail(TSR_STATUS_INVALID_ARGUMENT, "%s wants 3 buffers and 3 dims", name);
     rc = tessera_sm100_gemm_device(p->buffers[0], p->buffers[1], p->buffers[2], 1, (int)p->dims[0],
                                    (int)p->dims[1], (int)p->dims[2], TESSERA_SM100_BF16,
-                                   TESSERA_SM100_BF16, nullptr);
+                                   TESSERA_SM100_BF16, t_launch_stream);
   } else if (k == "tessera.sm100.flash_attn.bf16") {
     // buffers {Q, K, V, O}, dims {B, Hq, Hkv, Sq, Sk, D, causal}; scale = 1/sqrt(D)
     if (!need(4, 7)) return fail(TSR_STATUS_INVALID_ARGUMENT, "%s wants 4 buffers and 7 dims", name);
@@ -156,7 +163,7 @@ TsrStatus builtin_launcher(const char* target, const char* name, const tsrGpuLau
     rc = tessera_sm100_flash_attn_device(p->buffers[0], p->buffers[1], p->buffers[2], p->buffers[3],
                                          (int)p->dims[0], (int)p->dims[1], (int)p->dims[2],
                                          (int)p->dims[3], (int)p->dims[4], (int)p->dims[5], scale,
-                                         (int)p->dims[6], nullptr);
+                                         (int)p->dims[6], t_launch_stream);
   } else if (k == "tessera.sm100.grouped_gemm.bf16") {
     // buffers {x, w, offsets(int32[E+1]), out}, dims {T, K, N, E}
     if (!need(4, 4)) return fail(TSR_STATUS_INVALID_ARGUMENT, "%s wants 4 buffers and 4 dims", name);
@@ -164,7 +171,7 @@ TsrStatus builtin_launcher(const char* target, const char* name, const tsrGpuLau
                                            static_cast<const int*>(p->buffers[2]), p->buffers[3],
                                            (int)p->dims[0], (int)p->dims[1], (int)p->dims[2],
                                            (int)p->dims[3], TESSERA_SM100_BF16, TESSERA_SM100_BF16,
-                                           nullptr);
+                                           t_launch_stream);
   } else {
     return TSR_STATUS_NOT_FOUND;
   }
@@ -286,6 +293,7 @@ TsrStatus tsrCreateStream(tsrDevice dev, tsrStream* out) {
   cudaStream_t s = nullptr;
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking);
   if (e != cudaSuccess) return cuda_fail(e, "stream creation");
+  tsb::pool_note_stream(s, true);
   *out = new tsrStream_t{s, dev->ordinal};
   g_live_streams.fetch_add(1);
   emit(TSR_PROFILE_RUNTIME_API, "tsrCreateStream", t, TSR_STATUS_SUCCESS);
@@ -293,6 +301,7 @@ TsrStatus tsrCreateStream(tsrDevice dev, tsrStream* out) {
 }
 TsrStatus tsrDestroyStream(tsrStream s) {
   if (!s) return TSR_STATUS_SUCCESS;
+  tsb::pool_note_stream(s->stream, false);
   cudaStreamDestroy(s->stream);
   delete s;
   g_live_streams.fetch_sub(1);
@@ -547,6 +556,10 @@ TsrStatus tessera_sm100_gpu_launcher(const char* target, const char* kernel_name
   return builtin_launcher(target, kernel_name, params, user);
 }
 
+// The cudaStream_t of the tsrLaunchKernel call that is running the calling launcher (NULL = the
+// default stream, also outside a launch).
+void* tessera_sm100_current_launch_stream(void) { return t_launch_stream; }
+
 TsrStatus tsrRegisterGpuLauncher(tsrGpuLauncherFn fn, void* user) {
   std::lock_guard<std::mutex> lk(g_mu);
   g_launcher = fn ? fn : (g_init ? builtin_launcher : nullptr);
@@ -570,8 +583,10 @@ TsrStatus tsrLaunchKernel(tsrStream s, tsrKernel kernel, void** args, size_t nar
     st = fail(TSR_STATUS_UNIMPLEMENTED, "no GPU launcher is registered (call tsrInit)");
   } else {
     if (s) cudaSetDevice(s->device);
+    t_launch_stream = s ? static_cast<void*>(s->stream) : nullptr;
     st = fn(kernel->target.c_str(), kernel->name.c_str(),
             static_cast<const tsrGpuLaunchParams*>(args[0]), user);
+    t_launch_stream = nullptr;
     if (st == TSR_STATUS_NOT_FOUND)
       st = fail(TSR_STATUS_UNIMPLEMENTED, "no launcher handles kernel %s on target %s",
                 kernel->name.c_str(), kernel->target.c_str());

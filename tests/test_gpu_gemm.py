@@ -170,24 +170,32 @@ def test_cta_pair_kernel_shapes(batch, M, N, K, out_dt):
     no_device_error()
 
 
-@pytest.mark.parametrize("M,N,K,out_dt", [(2048, 8192, 264, bfloat16), (384, 1024, 512, bfloat16),
-                                          (2304, 8192, 128, np.float32)])
-def test_fused_all_gather_epilogue_with_local_copies(lib, M, N, K, out_dt):
-    """The column-parallel GEMM's epilogue stores each tile into every rank's Y. Here the two
-    "ranks" run one after the other on one GPU with both Y copies local, which exercises the
-    per-copy stores of both kernels (CTA pairs for the large shapes, single CTA for the small
-    one); every copy must hold the complete product."""
+@pytest.mark.parametrize("M,N,K,out_dt,world", [(2048, 8192, 264, bfloat16, 2), (384, 1024, 512, bfloat16, 2),
+                                                (2304, 8192, 128, np.float32, 2), (200, 1088, 72, bfloat16, 8),
+                                                (1000, 2112, 520, np.float16, 4), (129, 48, 64, np.float32, 3),
+                                                (512, 1024, 1088, bfloat16, 2), (2304, 2048, 2048, np.float32, 4),
+                                                (200, 1088, 1032, bfloat16, 8), (4096, 4096, 4096, bfloat16, 4)])
+def test_fused_all_gather_epilogue_with_local_copies(lib, M, N, K, out_dt, world):
+    """The column-parallel GEMM's epilogue stores each finished piece into every rank's Y. Here the
+    "ranks" run one after the other on one GPU with all Y copies local, which exercises the per-copy
+    stores and the rotation over the copies (ragged M, column blocks that are not a multiple of the
+    tile width, an odd number of 128-row tiles, 2 to 8 ranks, 16-bit and fp32 outputs) and, from 16
+    k-blocks on, the split of the K loop over neighbouring clusters (an odd number of k-blocks, a
+    ragged last one, several waves of units); every copy must hold the complete product."""
     from tessera_b200 import _lib, device
     from tessera_b200.device import DeviceArray
     rng = np.random.default_rng(M + K)
-    A, B = _rand(rng, (M, K), bfloat16, 1 / np.sqrt(K)), _rand(rng, (K, N), bfloat16)
+    dt = np.float16 if out_dt == np.float16 else bfloat16
+    A, B = _rand(rng, (M, K), dt, 1 / np.sqrt(K)), _rand(rng, (K, N), dt)
     dA, dB = DeviceArray.from_host(A), DeviceArray.from_host(B)
-    ys = [DeviceArray.zeros((M, N), out_dt) for _ in range(2)]
-    ptrs = (ctypes.c_void_p * 2)(ys[0].ptr, ys[1].ptr)
-    for rank in range(2):
-        _lib.call("tessera_sm100_gemm_allgather_device", dA.ptr, dB.ptr, ptrs, 2, rank, M, N, K, 1,
-                  device.dtype_code(out_dt), None)
+    ys = [DeviceArray.zeros((M, N), out_dt) for _ in range(world)]
+    ptrs = (ctypes.c_void_p * world)(*[y.ptr for y in ys])
+    for rank in range(world):
+        _lib.call("tessera_sm100_gemm_allgather_device", dA.ptr, dB.ptr, ptrs, world, rank, M, N, K,
+                  device.dtype_code(dt), device.dtype_code(out_dt), None)
     ref = orc.gemm(A, B)
-    for y in ys:
-        assert rel_err(y.download(), ref) < (1e-4 if out_dt == np.float32 else TOL)
+    first = ys[0].download()
+    assert rel_err(first, ref) < (1e-4 if out_dt == np.float32 else TOL)
+    for y in ys[1:]:
+        np.testing.assert_array_equal(y.download(), first)
     no_device_error()

@@ -62,3 +62,43 @@ def test_runtime_objects_and_named_gemm_launch():
     for b in (bA, bB, bD):
         rt.free(b)
     rt.close()
+
+
+def test_named_launch_runs_on_the_stream_it_is_given():
+    """tsrLaunchKernel(s, ...) enqueues on `s`: synchronising `s` alone makes the result readable
+    through the buffer's device pointer, and events recorded on `s` bracket the kernel (a GEMM
+    large enough that its device time cannot be mistaken for an empty interval)."""
+    from tessera_b200.device import DeviceArray
+    rt = tsr.TesseraRuntime()
+    l = tsr.lib()
+    dev = rt.device(0)
+    rng = np.random.default_rng(1)
+    M = N = K = 4096
+    A = (rng.standard_normal((M, K), dtype=np.float32) / 64).astype(bfloat16)
+    B = rng.standard_normal((K, N), dtype=np.float32).astype(bfloat16)
+    bA, bB, bD = rt.malloc(dev, A.nbytes), rt.malloc(dev, B.nbytes), rt.malloc(dev, M * N * 4)
+    rt.upload(bA, A)
+    rt.upload(bB, B)
+    stream, e0, e1 = c_void_p(), c_void_p(), c_void_p()
+    assert l.tsrCreateStream(dev, ctypes.byref(stream)) == 0
+    assert l.tsrCreateEvent(dev, ctypes.byref(e0)) == 0 and l.tsrCreateEvent(dev, ctypes.byref(e1)) == 0
+    rt.launch("nvidia_sm100", "tessera.sm100.gemm.bf16", [bA, bB, bD], [M, N, K], stream=stream)   # warm-up
+    assert l.tsrStreamSynchronize(stream) == 0
+    assert l.tsrRecordEvent(e0, stream) == 0
+    rt.launch("nvidia_sm100", "tessera.sm100.gemm.bf16", [bA, bB, bD], [M, N, K], stream=stream)
+    assert l.tsrRecordEvent(e1, stream) == 0
+    assert l.tsrStreamSynchronize(stream) == 0          # this stream only: no device-wide synchronise
+    ms = c_float(-1)
+    assert l.tsrEventElapsedMs(e0, e1, ctypes.byref(ms)) == 0
+    assert ms.value > 0.05, f"events on the launch stream bracket {ms.value} ms: the kernel ran elsewhere"
+    # read through the raw device pointer with an asynchronous copy on the same stream
+    out = DeviceArray((M, N), np.float32, ptr=rt.pointer(bD)).download(stream=stream.value)
+    rows = [0, 1234, M - 1]
+    ref = A[rows].astype(np.float32) @ B.astype(np.float32)
+    assert orc.max_rel_err(out[rows], ref) < 1e-4
+    for h in (e0, e1):
+        l.tsrDestroyEvent(h)
+    l.tsrDestroyStream(stream)
+    for b in (bA, bB, bD):
+        rt.free(b)
+    rt.close()

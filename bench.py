@@ -31,12 +31,41 @@ import sys
 import threading
 import time
 
-import numpy as np
+
+def _all_host_threads_before_numpy():
+    """The CPU legs (the reference arm, and the baselines of a single-GPU run) use every host core.
+    torch.distributed.run exports OMP_NUM_THREADS=1 to its children, which would leave numpy's BLAS
+    with one thread, so the thread counts are set here, before numpy is imported."""
+    reference = any(a == "reference" or a == "--impl=reference" for a in sys.argv)
+    if reference or int(os.environ.get("WORLD_SIZE", "1")) == 1:
+        for var in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+            os.environ[var] = str(os.cpu_count() or 1)
+
+
+_all_host_threads_before_numpy()
+
+import numpy as np  # noqa: E402
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+WORKLOAD = "gemm_bf16_8192: A[8192,8192] x B[8192,8192] -> Y bf16, fp32 accumulate"
+PARITY_TOL = 1e-2          # max|y - ref| / max|ref| in fp32, the stated parity tolerance
+# Peer-store bandwidth of SM-issued stores (TMA or st.global, 128- or 256-byte rows alike), measured
+# on this pool with both GPUs of a pair writing at once: the denominator of the exchange floor.
+PEER_STORE_GBS = 650.0
+
+
+def blas_threads():
+    """Threads numpy's BLAS will use, raised to all cores where the library allows it."""
+    try:
+        import threadpoolctl
+        threadpoolctl.threadpool_limits(limits=os.cpu_count())
+        info = threadpoolctl.threadpool_info()
+        return max((int(i.get("num_threads", 1)) for i in info), default=1)
+    except Exception:
+        return int(os.environ.get("OMP_NUM_THREADS", "1"))
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
 # summarised under profiles/. The GEMM capture is the benchmark size itself; the attention and MoE
@@ -249,6 +278,19 @@ def bench_gemm(ranks, args, peaks, peak_kind, sampler):
     times = timed_steps(ranks, device, step, args.steps, args.warmup)
     m1 = sampler.mark()
     launches = (device.launch_count() - l0) * args.steps // (args.steps + args.warmup)
+    # Parity of what was just timed, on EVERY rank: sampled rows of its gathered Y against the fp32
+    # product of the bf16 operands, over all columns, with the worst column block (one per
+    # producing rank) reported separately.
+    ranks.barrier()
+    rows = [0, 255, 4097 + ranks.rank, n - 1]
+    got = dY.download()[rows].astype(np.float32)
+    ref = A[rows].astype(np.float32) @ B.astype(np.float32)
+    scale = float(np.abs(ref).max())
+    rel = float(np.abs(got - ref).max() / scale)
+    blk = n // W
+    worst_block = max(float(np.abs(got[:, r * blk:(r + 1) * blk] - ref[:, r * blk:(r + 1) * blk]).max() / scale)
+                      for r in range(W))
+    all_rel = ranks.gather(max(rel, worst_block))
     # kernel-only time for the roofline entry: at one GPU the step is the kernel; with several,
     # the GEMM without the exchange, timed the same way (before the clock probe heats the GPU)
     kernel_times = times if W == 1 else timed_steps(ranks, device, gemm_only, args.steps, args.warmup)
@@ -257,48 +299,117 @@ def bench_gemm(ranks, args, peaks, peak_kind, sampler):
     ms = statistics.mean(times)
     k_ms = statistics.mean(kernel_times)
     achieved = flops / W / k_ms / 1e9        # per-GPU kernel TFLOP/s
-    # correctness spot check of what was just timed
-    rows = [0, 4097, n - 1]
-    got = dY.download()[rows].astype(np.float32)
-    ref = A[rows].astype(np.float32) @ B.astype(np.float32)
-    rel = float(np.abs(got - ref).max() / np.abs(ref).max())
 
-    # end to end through the public op with pinned host buffers
+    # End to end through the public host-operand call with pinned buffers. One GPU: ops.gemm on the
+    # whole problem. Several: A is replicated data, so each rank uploads M / W of its rows and its
+    # own column block of W, the rows are all-gathered over NVLink, the fused GEMM runs and the
+    # rank's block of Y comes back (TensorParallelGemm.run_host).
     e2e = None
     try:
-        pA, pB = PinnedArray((n, n), bfloat16), PinnedArray((n, nb), bfloat16)
-        pY = PinnedArray((n, nb), bfloat16)
-        pA.array[...] = A
-        pB.array[...] = B[:, c0:c0 + nb]
         e2e_steps = max(2, min(args.steps, 5))
-        tessera.ops.gemm(pA.array, pB.array, out_dtype=bfloat16, out=pY.array)
+        if W == 1 or fused is None:
+            pA, pB = PinnedArray((n, n), bfloat16), PinnedArray((n, nb), bfloat16)
+            pY = PinnedArray((n, nb), bfloat16)
+            pA.array[...] = A
+            pB.array[...] = B[:, c0:c0 + nb]
+            run = lambda: tessera.ops.gemm(pA.array, pB.array, out_dtype=bfloat16, out=pY.array)
+            api = "tessera_b200.ops.gemm(host, host) -> tessera_sm100_gemm"
+            note = "per rank: upload A and its column block of W, GEMM, download its block of Y"
+            h2d = int(pA.nbytes + pB.nbytes)
+        else:
+            mb = n // W
+            pA, pB = PinnedArray((mb, n), bfloat16), PinnedArray((n, nb), bfloat16)
+            pY = PinnedArray((n, nb), bfloat16)
+            pA.array[...] = A[ranks.rank * mb:(ranks.rank + 1) * mb]
+            pB.array[...] = B[:, c0:c0 + nb]
+            run = lambda: fused.run_host(pA.array, pB.array, pY.array, comm)
+            api = "tessera_b200.parallel.TensorParallelGemm.run_host(host rows of A, host block of W) -> host block of Y"
+            note = (f"per rank: upload M/{W} rows of A and its column block of W, all-gather A over NVLink (NCCL), "
+                    f"fused GEMM + all-gather of Y, download its block of Y; bytes are the sum over ranks")
+            h2d = int(pA.nbytes + pB.nbytes) * W
+        run()
         ranks.barrier()
         t0 = time.perf_counter()
         for _ in range(e2e_steps):
-            tessera.ops.gemm(pA.array, pB.array, out_dtype=bfloat16, out=pY.array)
+            run()
         device.synchronize()
         dt = (time.perf_counter() - t0) / e2e_steps
         dt = max(ranks.gather(dt))
-        e2e = {"value": flops / dt / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": int(pA.nbytes + pB.nbytes),
-               "d2h_bytes_per_step": int(pY.nbytes), "ms_per_step": dt * 1e3,
-               "api": "tessera_b200.ops.gemm(host, host) -> tessera_sm100_gemm",
-               "note": "per rank: upload A and its column block of W, GEMM, download its block of Y"}
+        e2e_got = pY.array[rows].astype(np.float32)
+        e2e_rel = float(np.abs(e2e_got - ref[:, c0:c0 + nb]).max() / scale)
+        e2e = {"value": flops / dt / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": int(pY.nbytes) * (W if fused is not None and W > 1 else 1),
+               "ms_per_step": dt * 1e3, "api": api, "note": note,
+               "check_max_rel_err": max(ranks.gather(e2e_rel))}
     except Exception as exc:  # keep the headline even if pinned allocation fails
         e2e = {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
-               "error": str(exc)}
+               "error": f"{type(exc).__name__}: {exc}"}
     if comm:
         comm.close()
+    roof = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"],
+            "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
+            "traffic": NCU_TRAFFIC_BYTES["gemm_8192"], "peak_kind": f"burst cuBLAS bf16, of {peak_kind}",
+            "kernel_ms": k_ms, "kernel": ("gemm2_kernel<bf16> (tcgen05 cta_group::2, 256x256x64 per CTA pair, 6-stage TMA)"
+                       if (n // 256) * (-(-nb // 256)) >= 74 else
+                       "gemm_kernel<bf16,plain> (tcgen05 128x256x64, 4-stage TMA)")}
+    if W > 1:
+        # Every rank has to take in the other ranks' column blocks of Y over its NVLink ingress.
+        ingress = (W - 1) / W * n * n * 2
+        floor_ms = ingress / (PEER_STORE_GBS * 1e9) * 1e3
+        roof["exchange"] = {"ingress_bytes_per_rank": ingress, "peer_store_gbs": PEER_STORE_GBS,
+                            "exchange_floor_ms": floor_ms, "compute_ms": k_ms,
+                            "floor_ms": max(floor_ms, k_ms), "step_ms": ms,
+                            "efficiency_vs_floor": max(floor_ms, k_ms) / ms,
+                            "fused_kernel": "gemm_ag_kernel<bf16> (cta_group::2 256x256x64, K split over neighbouring "
+                                            "CTA pairs, TMA stores into every rank's Y)" if tp_mode == "fused" else None,
+                            "note": "peer_store_gbs: SM-issued peer stores measured on this pool (both GPUs of a pair "
+                                    "writing at once; a contiguous copy-engine transfer reaches 727)"}
     return {
         "value": flops / ms / 1e9, "ms_per_step": ms, "gpu_launches": int(launches * W),
-        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"],
-                     "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
-                     "traffic": NCU_TRAFFIC_BYTES["gemm_8192"], "peak_kind": f"burst cuBLAS bf16, of {peak_kind}",
-                     "kernel_ms": k_ms, "kernel": ("gemm2_kernel<bf16> (tcgen05 cta_group::2, 256x256x64 per CTA pair, 6-stage TMA)"
-                                if (n // 256) * (-(-nb // 256)) >= 74 else
-                                "gemm_kernel<bf16,plain> (tcgen05 128x256x64, 4-stage TMA)")},
-        "e2e": e2e, "check_max_rel_err": rel, "clock_marks": (m0, m1), "probe_marks": probe_marks,
+        "roofline": roof,
+        "e2e": e2e, "check_max_rel_err": max(all_rel), "check_per_rank": all_rel,
+        "clock_marks": (m0, m1), "probe_marks": probe_marks,
         "tp_mode": tp_mode,
     }
+
+
+def bench_gemm_batched(ranks, args, peaks, peak_kind):
+    """Config 1: A[4,1024,1024] f16 x W[4,1024,1024] f16 -> Y f32, the case the reference runs on its
+    CPU JIT path. Launch-bound on a B200 (3.8 us at the tensor peak): reported with its CPU time,
+    not as a roofline target. With several GPUs every rank runs the same four products."""
+    from oracle import tessera_oracle as orc
+    from tessera_b200 import _lib, device
+    from tessera_b200.device import DeviceArray
+    rng = np.random.default_rng(1001)
+    A = (rng.standard_normal((4, 1024, 1024), dtype=np.float32) / 32).astype(np.float16)
+    Wt = (rng.standard_normal((4, 1024, 1024), dtype=np.float32) / 32).astype(np.float16)
+    dA, dW = DeviceArray.from_host(A), DeviceArray.from_host(Wt)
+    dY = DeviceArray.zeros((4, 1024, 1024), np.float32)
+    fn = lambda: _lib.call("tessera_sm100_gemm_device", dA.ptr, dW.ptr, dY.ptr, 4, 1024, 1024, 1024, _lib.F16,
+                           _lib.F32, None)
+    times = timed_steps(ranks, device, fn, args.steps, args.warmup)
+    ms = statistics.mean(times)
+    flops = 2.0 * 4 * 1024 ** 3
+    out = {"metric": "batched f16 GEMM 4 x 1024^3 -> f32, TFLOP/s", "value": flops / ms / 1e9, "unit": "TFLOP/s",
+           "ms_per_step": ms, "config": "A[4,1024,1024] f16 x W[4,1024,1024] f16 -> Y f32, N(0,1)/sqrt(1024), seed 1001"
+                                        + ("" if ranks.world == 1 else f" (replicated on {ranks.world} GPUs)"),
+           "roofline": {"bound": "tensor", "achieved": flops / ms / 1e9, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                        "frac": flops / ms / 1e9 / peaks["bf16_tflops"], "traffic": None,
+                        "peak_kind": f"burst cuBLAS bf16, of {peak_kind}; launch-bound size, not a roofline target"}}
+    if ranks.rank == 0:
+        blas_threads()
+        ref = orc.gemm(A, Wt)
+        t0 = time.perf_counter()
+        reps = 5
+        for _ in range(reps):
+            orc.gemm(A, Wt)
+        cpu_s = (time.perf_counter() - t0) / reps
+        out["parity"] = {"max_rel_err": float(orc.max_rel_err(dY.download(), ref)), "tolerance": 1e-4}
+        out["cpu_baseline"] = {"value": flops / cpu_s / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+                               "ms_per_step": cpu_s * 1e3,
+                               "sample": f"{reps} x the whole configuration: fp32 matmul of the f16 operands "
+                                         f"(numpy, {blas_threads()} BLAS threads), what the reference's CPU plan executes"}
+    return out
 
 
 def bench_attn_prefill(ranks, args, peaks, peak_kind):
@@ -319,12 +430,31 @@ def bench_attn_prefill(ranks, args, peaks, peak_kind):
     ms = statistics.mean(times)
     flops = 4.0 * B * H * S * S * D / 2
     ach = flops / W / ms / 1e9
-    return {"metric": "causal flash-attention forward TFLOP/s", "value": flops / ms / 1e9, "unit": "TFLOP/s",
-            "ms_per_step": ms, "config": f"B={B} H={H} S={S} D={D} bf16 causal, heads sharded /{W}",
-            "flops_convention": "4*B*H*S^2*D/2",
-            "roofline": {"bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                         "frac": ach / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC_BYTES["attn_prefill"],
-                         "peak_kind": f"burst cuBLAS bf16, of {peak_kind}"}}
+    # parity of what was timed: two (batch, head) slices of this rank against the chunked fp32 reference
+    from oracle import tessera_oracle as orc
+    got = do.download()
+    picks = [(0, 0), (B - 1, Hl - 1)]
+    t0 = time.perf_counter()
+    err = max(orc.max_rel_err(got[b:b + 1, h:h + 1], orc.flash_attn(q[b:b + 1, h:h + 1], k[b:b + 1, h:h + 1],
+                                                                  v[b:b + 1, h:h + 1], causal=True)) for b, h in picks)
+    cpu_s_per_head = (time.perf_counter() - t0) / len(picks)
+    out = {"metric": "causal flash-attention forward TFLOP/s", "value": flops / ms / 1e9, "unit": "TFLOP/s",
+           "ms_per_step": ms, "config": f"B={B} H={H} S={S} D={D} bf16 causal, heads sharded /{W}",
+           "flops_convention": "4*B*H*S^2*D/2",
+           "parity": {"max_rel_err": max(ranks.gather(float(err))), "tolerance": PARITY_TOL,
+                      "sample": "2 (batch, head) slices per rank, all rows"},
+           "roofline": {"bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                        "frac": ach / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC_BYTES["attn_prefill"],
+                        "peak_kind": f"burst cuBLAS bf16, of {peak_kind}"}}
+    if ranks.rank == 0 and W == 1 and not args.no_cpu_baseline:
+        nthreads = blas_threads()
+        out["cpu_baseline"] = {"value": flops / (cpu_s_per_head * B * H) / 1e12, "unit": "TFLOP/s",
+                               "cores": os.cpu_count(), "kind": "port",
+                               "seconds_for_the_whole_config_extrapolated": cpu_s_per_head * B * H,
+                               "sample": f"{len(picks)} of {B * H} (batch, head) slices through the chunked numpy reference "
+                                         f"(the reference's own form materialises a 17 GB score tensor), {nthreads} BLAS "
+                                         f"threads, x{B * H // len(picks)} extrapolation"}
+    return out
 
 
 def bench_attn_backward(ranks, args, peaks, peak_kind):
@@ -392,12 +522,27 @@ def bench_attn_decode(ranks, args, peaks, peak_kind):
     ms = statistics.mean(times)
     nbytes = 2.0 * B * Hkv * S * D * 2
     ach = nbytes / W / ms / 1e6
-    return {"metric": "GQA decode attention GB/s (K+V bytes)", "value": nbytes / ms / 1e6, "unit": "GB/s",
-            "ms_per_step": ms, "config": f"batch={B} Hq={Hq} Hkv={Hkv} KV={S} D={D} bf16, batch sharded /{W}",
-            "splits": ns,
-            "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": ach / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES["attn_decode"],
-                         "peak_kind": f"copy bandwidth, of {peak_kind}"}}
+    from oracle import tessera_oracle as orc
+    got = do.download()
+    picks = [0, Bl - 1]
+    t0 = time.perf_counter()
+    err = max(orc.max_rel_err(got[b:b + 1], orc.gqa_attention(q[b:b + 1], k[b:b + 1], v[b:b + 1], Hq, Hkv)) for b in picks)
+    cpu_s_per_seq = (time.perf_counter() - t0) / len(picks)
+    out = {"metric": "GQA decode attention GB/s (K+V bytes)", "value": nbytes / ms / 1e6, "unit": "GB/s",
+           "ms_per_step": ms, "config": f"batch={B} Hq={Hq} Hkv={Hkv} KV={S} D={D} bf16, batch sharded /{W}",
+           "splits": ns,
+           "parity": {"max_rel_err": max(ranks.gather(float(err))), "tolerance": PARITY_TOL,
+                      "sample": "2 sequences per rank, all heads"},
+           "roofline": {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                        "frac": ach / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES["attn_decode"],
+                        "peak_kind": f"copy bandwidth, of {peak_kind}"}}
+    if ranks.rank == 0 and W == 1 and not args.no_cpu_baseline:
+        out["cpu_baseline"] = {"value": nbytes / (cpu_s_per_seq * B) / 1e9, "unit": "GB/s", "cores": os.cpu_count(),
+                               "kind": "port", "seconds_for_the_whole_config_extrapolated": cpu_s_per_seq * B,
+                               "sample": f"{len(picks)} of {B} sequences through the numpy reference (KV heads repeated x"
+                                         f"{Hq // Hkv}, then attention in fp32), {blas_threads()} BLAS threads, "
+                                         f"x{B // len(picks)} extrapolation"}
+    return out
 
 
 def bench_attn_decode_paged(ranks, args, peaks, peak_kind):
@@ -480,7 +625,9 @@ def bench_attn_decode_int8(ranks, args, peaks, peak_kind):
 
 
 def bench_moe(ranks, args, peaks, peak_kind):
-    from tessera_b200 import _lib, collectives, device, parallel
+    from types import SimpleNamespace
+    from oracle import tessera_oracle as orc
+    from tessera_b200 import _lib, device, parallel
     from tessera_b200.device import DeviceArray, bfloat16
     T, H, F, E, k = 8192, 4096, 14336, 8, 2
     W = ranks.world
@@ -488,65 +635,106 @@ def bench_moe(ranks, args, peaks, peak_kind):
     x = rng.standard_normal((T, H), dtype=np.float32).astype(bfloat16)
     logits = rng.standard_normal((T, E), dtype=np.float32)
     Ep = E // W
-    rngw = np.random.default_rng(2005 + ranks.rank)
-    wg = tiled_normal(rngw, (Ep, H, F), 1, 1 / np.sqrt(H), bfloat16)
-    wu = tiled_normal(rngw, (Ep, H, F), 1, 1 / np.sqrt(H), bfloat16)
-    wd = tiled_normal(rngw, (Ep, F, H), 1, 1 / np.sqrt(F), bfloat16)
-    dwg, dwu, dwd = (DeviceArray.from_host(t) for t in (wg, wu, wd))
+    # Expert e's matrices are one seeded N(0,1)/sqrt(fan-in) draw per kind rolled by 7e columns, so any
+    # rank can rebuild any expert for the parity check without holding all 2.8 GB on the host.
+    wrng = np.random.default_rng(2005)
+    base_g = (wrng.standard_normal((H, F), dtype=np.float32) / np.sqrt(H)).astype(bfloat16)
+    base_u = (wrng.standard_normal((H, F), dtype=np.float32) / np.sqrt(H)).astype(bfloat16)
+    base_d = (wrng.standard_normal((F, H), dtype=np.float32) / np.sqrt(F)).astype(bfloat16)
+    expert = lambda base, e: np.roll(base, 7 * e, axis=1)
+    mine = range(ranks.rank * Ep, (ranks.rank + 1) * Ep)
+    dwg = DeviceArray.from_host(np.stack([expert(base_g, e) for e in mine]))
+    dwu = DeviceArray.from_host(np.stack([expert(base_u, e) for e in mine]))
+    dwd = DeviceArray.from_host(np.stack([expert(base_d, e) for e in mine]))
     flops = 3 * 2.0 * T * k * H * F
-    ep_mode = "single"
+    Tl = T // W
+    sl = slice(ranks.rank * Tl, (ranks.rank + 1) * Tl)
+    moe = None
     if W == 1:
         dx, dl = DeviceArray.from_host(x), DeviceArray.from_host(logits)
         out = DeviceArray.zeros((T, H), bfloat16)
         ws = DeviceArray((_lib.load().tessera_sm100_moe_workspace_bytes(T, H, F, E, k),), np.uint8)
         fn = lambda: _lib.call("tessera_sm100_moe_layer_device", dx.ptr, dl.ptr, dwg.ptr, dwu.ptr, dwd.ptr,
                                out.ptr, T, H, F, E, k, 1, -1, _lib.BF16, _lib.BF16, ws.ptr, None)
-        comm = None
+        mode = "single GPU"
     else:
-        uid = ranks.bcast(collectives.Communicator.unique_id() if ranks.rank == 0 else None)
-        comm = collectives.Communicator.from_unique_id(uid, W, ranks.rank)
-        Tl = T // W
-        sl = slice(ranks.rank * Tl, (ranks.rank + 1) * Tl)
         dxl = DeviceArray.from_host(x[sl])
-        ll = np.ascontiguousarray(logits[sl])
-        ep_mode = "device"
-        try:
-            moe = parallel.DeviceExpertParallelMoE(comm, ranks.gather, dwg, dwu, dwd, Tl, k, E)
-            dll = DeviceArray.from_host(ll)
-            out_l = DeviceArray.zeros((Tl, H), bfloat16)
-            fn = lambda: moe.forward(dxl, dll, out=out_l)
-        except Exception as exc:
-            ep_mode = f"nccl all-to-all (device exchange set-up failed: {exc})"
-        modes = ranks.gather(ep_mode)
-        if any(m != "device" for m in modes):
-            ep_mode = next(m for m in modes if m != "device")
-            moe = parallel.ExpertParallelMoE(E, k, parallel.NcclTransport(comm, ranks.gather),
-                                             parallel.GpuMoeBackend(dwg, dwu, dwd))
-            fn = lambda: moe.forward(dxl, ll)
-    times = timed_steps(ranks, device, fn, max(2, args.steps // 2), min(args.warmup, 3))
+        dll = DeviceArray.from_host(np.ascontiguousarray(logits[sl]))
+        out = DeviceArray.zeros((Tl, H), bfloat16)
+        moe = parallel.DeviceExpertParallelMoE(SimpleNamespace(world=W, rank=ranks.rank), ranks.gather, dwg, dwu,
+                                               dwd, Tl, k, E)
+        fn = lambda: moe.forward(dxl, dll, out=out)
+        mode = (f"expert-parallel /{W}: token rows stored into the owners' buffers and results read back over "
+                f"NVLink by the kernels, ranks ordered by flags in peer memory (no collective)")
+    ranks.barrier()
+    l0 = device.launch_count()
+    steps, warm = max(2, args.steps // 2), min(args.warmup, 3)
+    times = timed_steps(ranks, device, fn, steps, warm)
+    launches = (device.launch_count() - l0) // (steps + warm)
     ms = statistics.mean(times)
-    pipelined = None
-    if W > 1 and ep_mode == "device":
-        # the same layer over micro-batches, exchange overlapping the expert GEMMs
-        try:
-            pm = parallel.PipelinedExpertParallelMoE(comm, ranks.gather, dwg, dwu, dwd, Tl, k, E, micro_batches=2)
-            fnp = lambda: pm.forward(dxl, dll, out=out_l)
-            pipelined = {"micro_batches": 2,
-                         "ms_per_step": statistics.mean(timed_steps(ranks, device, fnp, max(2, args.steps // 2),
-                                                                    min(args.warmup, 3)))}
-            pm.close()
-        except Exception as exc:
-            pipelined = {"error": f"{type(exc).__name__}: {exc}"}
-    if comm:
-        comm.close()
+    # Parity of what was timed, on every rank: routing bit-exact against the reference's router on
+    # the same logits, and sampled tokens against the fp32 reference (hidden activation in bf16).
+    route = orc.route_tokens(logits, k, True)
+    if W == 1:
+        views = [ctypes_void() for _ in range(8)]
+        _lib.call("tessera_sm100_moe_workspace_views", ws.ptr, T, H, F, E, k, *[v_ref(v) for v in views])
+        assign = DeviceArray((T, k), np.int32, ptr=views[0].value).download()
+    else:
+        assign = moe.assignment.download()
+    routing_ok = bool(np.array_equal(assign, route.assignment[sl].astype(np.int32)))
+    got = out.download().astype(np.float32)
+    toks = [0, Tl // 2 + ranks.rank, Tl - 1]
+    ref = np.zeros((len(toks), H), np.float32)
+    xf = x.astype(np.float32)
+    t0 = time.perf_counter()
+    for i, t in enumerate(toks):
+        g = ranks.rank * Tl + t
+        for j in range(k):
+            e = int(route.assignment[g, j])
+            h = orc.silu_mul(xf[g] @ expert(base_g, e).astype(np.float32), xf[g] @ expert(base_u, e).astype(np.float32))
+            h = h.astype(bfloat16).astype(np.float32)
+            ref[i] += route.weights[g, j] * (h @ expert(base_d, e).astype(np.float32))
+    err = float(np.abs(got[toks] - ref).max() / np.abs(ref).max())
+    code = device.consume_device_error()[0]
+    if moe is not None:
+        ranks.barrier()
+        moe.close()
     ach = flops / W / ms / 1e9
-    return {"metric": "MoE FFN layer TFLOP/s (routed slots, unpadded)", "value": flops / ms / 1e9,
-            "unit": "TFLOP/s", "ms_per_step": ms, "pipelined": pipelined,
-            "config": f"T={T} H={H} F={F} E={E} top-{k} bf16, " + ("single GPU" if W == 1 else f"expert-parallel /{W}, exchange: {ep_mode}"),
-            "roofline": {"bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops_sustained"],
-                         "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops_sustained"],
-                         "traffic": NCU_TRAFFIC_BYTES["moe"],
-                         "peak_kind": f"sustained cuBLAS bf16 (two multi-ms GEMMs per step), of {peak_kind}"}}
+    res = {"metric": "MoE FFN layer TFLOP/s (routed slots, unpadded)", "value": flops / ms / 1e9,
+           "unit": "TFLOP/s", "ms_per_step": ms, "gpu_launches_per_step": int(launches), "device_error": code,
+           "config": f"T={T} H={H} F={F} E={E} top-{k} bf16, {mode}",
+           "parity": {"max_rel_err": max(ranks.gather(err)), "routing_bit_exact": all(ranks.gather(routing_ok)),
+                      "tolerance": PARITY_TOL, "sample": "3 tokens per rank, all columns; assignment of every local token"},
+           "roofline": {"bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops_sustained"],
+                        "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops_sustained"],
+                        "traffic": NCU_TRAFFIC_BYTES["moe"],
+                        "peak_kind": f"sustained cuBLAS bf16 (two multi-ms GEMMs per step), of {peak_kind}"}}
+    if ranks.rank == 0 and W == 1 and not args.no_cpu_baseline:
+        # the reference layer on a token subset (every expert still gets ~T/64 rows), extrapolated
+        nthreads = blas_threads()
+        sub = 1024
+        wg_all = np.stack([expert(base_g, e) for e in range(E)]).astype(np.float32)
+        wu_all = np.stack([expert(base_u, e) for e in range(E)]).astype(np.float32)
+        wd_all = np.stack([expert(base_d, e) for e in range(E)]).astype(np.float32)
+        t0 = time.perf_counter()
+        orc.moe_layer_from_logits(xf[:sub], logits[:sub], wg_all, wu_all, wd_all, k)
+        cpu_s = time.perf_counter() - t0
+        res["cpu_baseline"] = {"value": flops * (sub / T) / cpu_s / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(),
+                               "kind": "port", "seconds_for_the_whole_config_extrapolated": cpu_s * T / sub,
+                               "sample": f"the numpy reference layer (route, stable expert sort, three grouped fp32 GEMMs "
+                                         f"per expert, weighted combine) on the first {sub} of {T} tokens, {nthreads} BLAS "
+                                         f"threads, x{T // sub} extrapolation"}
+    return res
+
+
+def ctypes_void():
+    import ctypes
+    return ctypes.c_void_p()
+
+
+def v_ref(v):
+    import ctypes
+    return ctypes.byref(v)
 
 
 def bench_moe_fp8(ranks, args, peaks, peak_kind):
@@ -602,6 +790,7 @@ def bench_moe_fp8(ranks, args, peaks, peak_kind):
 # ------------------------------------------------------------------------------ CPU baseline
 def cpu_gemm_baseline(target_seconds: float = 10.0, max_reps: int = 10):
     from oracle import tessera_oracle as orc
+    nthreads = blas_threads()
     inp = orc.make_inputs("gemm_bf16")
     A, B = inp["A"].astype(np.float32), inp["B"].astype(np.float32)
     t0 = time.perf_counter()
@@ -614,7 +803,8 @@ def cpu_gemm_baseline(target_seconds: float = 10.0, max_reps: int = 10):
     dt = (time.perf_counter() - t0) / reps
     flops = 2.0 * 8192 ** 3
     return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
-            "sample": f"{reps} x full 8192^3 fp32 matmul of bf16-rounded operands (numpy, all host threads), "
+            "blas_threads": nthreads,
+            "sample": f"{reps} x full 8192^3 fp32 matmul of bf16-rounded operands (numpy, {nthreads} BLAS threads), "
                       f"{dt:.2f} s each", "seconds_per_step": dt}
 
 
@@ -623,6 +813,7 @@ def run_reference(args):
     if rank != 0:
         return
     from oracle import tessera_oracle as orc
+    nthreads = blas_threads()
     inp = orc.make_inputs("gemm_bf16")
     A, B = inp["A"].astype(np.float32), inp["B"].astype(np.float32)
     for _ in range(args.warmup):
@@ -635,11 +826,13 @@ def run_reference(args):
     line = {"impl": "reference", "metric": "bf16 GEMM TFLOP/s (M=N=K=8192)", "value": val, "unit": "TFLOP/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic",
-            "config": {"workload": "gemm_bf16_8192: A[8192,8192] x B[8192,8192], bf16 operands, fp32 accumulate"},
+            "data": "synthetic (seeded N(0,1)/sqrt(K) operands)",
+            "config": {"workload": WORKLOAD},
             "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
-                             "sample": "each step = the full 8192^3 product: the reference's tessera.ops.gemm "
-                                       "(np.matmul) on fp32 arrays holding bf16 values, all host threads"},
+                             "blas_threads": nthreads,
+                             "sample": f"each step = the full 8192^3 product: the reference's tessera.ops.gemm "
+                                       f"(np.matmul) on fp32 arrays holding bf16 values, {nthreads} BLAS threads on "
+                                       f"{os.cpu_count()} host cores"},
             "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
@@ -751,8 +944,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="all", choices=["all", "gemm", "attn_prefill", "attn_backward", "attn_decode", "attn_decode_paged", "attn_decode_int8", "moe",
-                             "moe_fp8"])
+    ap.add_argument("--workload", default="all", choices=["all", "gemm", "gemm_batched", "attn_prefill", "attn_backward", "attn_decode",
+                                                          "attn_decode_paged", "attn_decode_int8", "moe", "moe_fp8"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tp-mode", default="fused", choices=["fused", "nccl"],
                     help="N>1 GEMM: all-gather fused into the epilogue (peer TMA stores) or NCCL after it")
@@ -786,19 +979,21 @@ def main():
 
     g = bench_gemm(ranks, args, peaks, peak_kind, sampler)
     extras = {}
-    if args.workload in ("all", "attn_prefill", "attn_backward", "attn_decode", "attn_decode_paged", "attn_decode_int8", "moe",
-                         "moe_fp8"):
-        for name, fn in (("attn_prefill", bench_attn_prefill), ("attn_backward", bench_attn_backward),
-                         ("attn_decode", bench_attn_decode),
-                         ("attn_decode_paged", bench_attn_decode_paged),
-                         ("attn_decode_int8", bench_attn_decode_int8), ("moe", bench_moe),
-                         ("moe_fp8", bench_moe_fp8)):
-            if args.workload not in ("all", name):
-                continue
-            try:
-                extras[name] = fn(ranks, args, peaks, peak_kind)
-            except Exception as exc:
-                extras[name] = {"error": f"{type(exc).__name__}: {exc}"}
+    for name, fn in (("gemm_batched", bench_gemm_batched), ("attn_prefill", bench_attn_prefill),
+                     ("attn_backward", bench_attn_backward), ("attn_decode", bench_attn_decode),
+                     ("attn_decode_paged", bench_attn_decode_paged),
+                     ("attn_decode_int8", bench_attn_decode_int8), ("moe", bench_moe),
+                     ("moe_fp8", bench_moe_fp8)):
+        if args.workload not in ("all", name):
+            continue
+        try:
+            extras[name] = fn(ranks, args, peaks, peak_kind)
+        except Exception as exc:
+            extras[name] = {"error": f"{type(exc).__name__}: {exc}"}
+        # every rank takes part in every workload: if one failed, say so on all of them
+        errors = [e for e in ranks.gather(extras[name].get("error")) if e]
+        if errors and "error" not in extras[name]:
+            extras[name] = {"error": f"another rank failed: {errors[0]}"}
     timed_marks, probe_marks = g.pop("clock_marks"), g.pop("probe_marks")
     clocks = None
     if ranks.rank == 0:
@@ -818,14 +1013,49 @@ def main():
     if ranks.rank == 0 and ranks.world == 1 and not args.no_cpu_baseline:
         cpu = cpu_gemm_baseline()
 
+    # Parity gate: a wrong result makes the run fail, whatever the throughput.
+    parity = {"tp_gemm" if ranks.world > 1 else "gemm": g["check_max_rel_err"]}
+    failures = []
+    if not (g["check_max_rel_err"] < PARITY_TOL):
+        failures.append(f"gemm: max rel err {g['check_max_rel_err']:.3g} on some rank (per rank {g['check_per_rank']})")
+    e2e_err = (g["e2e"] or {}).get("check_max_rel_err")
+    if e2e_err is not None and not (e2e_err < PARITY_TOL):
+        failures.append(f"gemm e2e: max rel err {e2e_err:.3g}")
+    for name, key in (("gemm_batched", "gemm_batched"), ("attn_prefill", "attn_prefill"), ("attn_decode", "attn_decode"),
+                      ("moe", "ep_moe" if ranks.world > 1 else "moe")):
+        w = extras.get(name) or {}
+        if "error" in w:
+            failures.append(f"{name}: {w['error']}")
+        par = w.get("parity")
+        if par:
+            parity[key] = par["max_rel_err"]
+            if not (par["max_rel_err"] < par.get("tolerance", PARITY_TOL)):
+                failures.append(f"{name}: max rel err {par['max_rel_err']:.3g}")
+            if par.get("routing_bit_exact") is False:
+                failures.append(f"{name}: routing differs from the reference router")
+            if "routing_bit_exact" in par:
+                parity[key + "_routing_bit_exact"] = par["routing_bit_exact"]
     if ranks.rank == 0:
         W = ranks.world
+        roof = g["roofline"]
+        roof["parity"] = parity
+        roof["configs"] = {}
+        for cfg, name in (("cfg1_batched_f16_gemm", "gemm_batched"), ("cfg3_causal_prefill", "attn_prefill"),
+                          ("cfg4_gqa_decode", "attn_decode"), ("cfg5_moe_layer", "moe")):
+            w = extras.get(name) or {}
+            if "value" in w:
+                entry = {"value": w["value"], "unit": w["unit"], "ms_per_step": w["ms_per_step"],
+                         "frac": (w.get("roofline") or {}).get("frac"), "bound": (w.get("roofline") or {}).get("bound")}
+                if "cpu_baseline" in w:
+                    entry["cpu_value"] = w["cpu_baseline"]["value"]
+                    entry["cpu_cores"] = w["cpu_baseline"]["cores"]
+                roof["configs"][cfg] = entry
         line = {
             "metric": "bf16 GEMM TFLOP/s (M=N=K=8192)", "value": g["value"], "unit": "TFLOP/s",
             "n_gpus": W, "steps": args.steps, "warmup": args.warmup, "ms_per_step": g["ms_per_step"],
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic (seeded N(0,1)/sqrt(K) operands)",
-            "config": {"workload": "gemm_bf16_8192: A[8192,8192] x B[8192,8192] -> Y bf16, fp32 accumulate",
+            "config": {"workload": WORKLOAD,
                        "parallelism": "single GPU" if W == 1 else (
                            f"column-parallel tp{W}: W split on N, all-gather of Y fused into the GEMM "
                            f"epilogue (TMA stores into every rank's Y over NVLink)" if g["tp_mode"] == "fused"
@@ -833,13 +1063,17 @@ def main():
                                 f"into row-major Y [{g['tp_mode']}]"),
                        "l2": "L2 flushed (256 MiB write) before every timed step, outside the event bracket",
                        "timing": "CUDA events per step on the launching stream, max over ranks, mean of steps"},
-            "roofline": g["roofline"], "e2e": g["e2e"], "gpu_launches": g["gpu_launches"],
-            "clocks": clocks, "check_max_rel_err": g["check_max_rel_err"], "workloads": extras,
+            "roofline": roof, "e2e": g["e2e"], "gpu_launches": g["gpu_launches"],
+            "clocks": clocks, "check_max_rel_err": g["check_max_rel_err"], "parity_failures": failures,
+            "workloads": extras,
         }
         if cpu:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)
     ranks.close()
+    if failures:
+        sys.stderr.write("parity check failed: " + "; ".join(failures) + "\n")
+        sys.exit(3)
 
 
 if __name__ == "__main__":

@@ -38,6 +38,10 @@ int tessera_sm100_sm_count(int* count);
 int tessera_sm100_consume_device_error(int out[4]);
 /* Number of kernels of this library launched by the calling process so far. */
 long long tessera_sm100_launch_count(void);
+/* Self-test of the failure path every kernel shares: one warp waits, through the kernels' bounded
+ * mbarrier wait, on a barrier nobody arrives on; after limit_cycles SM cycles (at most 2^28) it
+ * gives up, records {5, block 0, detail 77} in the error word and the kernel ends normally. */
+int tessera_sm100_selftest_wait_expiry(long long limit_cycles, void* stream);
 
 /* Helpers with the shape of tessera_nvidia_device_alloc ... tessera_nvidia_event_destroy
  * (tessera_nvidia_gemm.cpp:617-697). */
@@ -59,6 +63,9 @@ int tessera_sm100_device_copy(void* dst, const void* src, size_t bytes, void* st
 /* Strided device-to-device copy of `rows` rows of `width_bytes` bytes. */
 int tessera_sm100_device_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
                                  size_t width_bytes, size_t rows, void* stream);
+/* rows x width_bytes from device memory (pitch src_pitch) into host memory (pitch dst_pitch). */
+int tessera_sm100_device_download_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
+                                     size_t width_bytes, size_t rows, void* stream);
 int tessera_sm100_host_alloc(void** out, size_t bytes); /* pinned host memory */
 int tessera_sm100_host_free(void* ptr);
 int tessera_sm100_stream_create(void** out);
@@ -123,6 +130,12 @@ int tessera_sm100_gemm_epilogue_device(const void* A, const void* B, void* D, in
 int tessera_sm100_gemm_allgather_device(const void* A, const void* B, void* const* Y_ptrs, int world,
                                         int rank, int M, int N_total, int K, int in_dtype,
                                         int out_dtype, void* stream);
+/* The same with only this rank's column block resident: B_block is [K, N_total / world] with leading
+ * dimension ldb (elements, a multiple of 8), as ParallelLinear holds its weight shard
+ * (python/tessera/compiler/tensor_parallel.py:87-89). */
+int tessera_sm100_gemm_allgather_block_device(const void* A, const void* B_block, long long ldb,
+                                              void* const* Y_ptrs, int world, int rank, int M, int N_total,
+                                              int K, int in_dtype, int out_dtype, void* stream);
 
 /* ---- MoE grouped GEMM ------------------------------------------------------------------
  * out[T,N] = rows of group e of x[T,K] times w[e] (w is [E,K,N]); offsets[E+1] int32 row
@@ -291,6 +304,44 @@ int tessera_sm100_ep_combine_device(void* const* y_bufs, const int* assignment,
                                     const int* my_offsets, const int* dst_base, void* out, int T,
                                     int top_k, int world, int E, int capacity_rows, int H, int dtype,
                                     void* stream);
+/* The same exchange with the ranks ordered by flags in peer memory instead of collectives: the
+ * form of the reference's planned device-initiated exchange (its mock transport orders the phases
+ * with thread barriers, python/tessera/distributed/moe.py:358-483). Every rank allocates one control
+ * block of tessera_sm100_ep_ctrl_bytes() bytes, ZEROED ONCE, and maps every peer's block
+ * (ctrl_ptrs[i] = rank i's block). `epoch` is 1 on the first forward call and one higher on every
+ * following call, the same on all ranks. Per forward, on one stream:
+ *   ep_route_publish    route + stable expert sort of the Tl local tokens (one launch; outputs as
+ *                       tessera_sm100_moe_route_device + tessera_sm100_moe_permute_device with no
+ *                       capacity drop) and this rank's per-expert counts stored into every rank's
+ *                       control block;
+ *   ep_dispatch_signal  waits for all ranks' counts and for the end of their previous call, writes
+ *                       group_offsets_local[E/world + 1] and dst_base[E] (as ep_plan), stores the token
+ *                       rows into the owners' receive buffers; when the kernel ends every rank's rows
+ *                       for THIS rank have landed, so the grouped GEMMs can follow in the stream;
+ *   ep_combine_signal   (after the GEMMs) announces this rank's outputs, waits for the owners', reads
+ *                       the result rows back and forms the weighted sums; announces the end of the call.
+ * `counter` is one zeroed device int per call site (dispatch and combine each need their own).
+ * Waits give up after wait_limit_ms (<= 0: 10 s) and record code 5 in the device error word
+ * (detail 100+r counts, 200+r previous call, 300+r rows, 400+r outputs of rank r); the kernels then
+ * run to their end without the data. Never run two ranks of one group on the same GPU. */
+size_t tessera_sm100_ep_ctrl_bytes(void);
+int tessera_sm100_ep_route_publish_device(const float* logits, int Tl, int E, int top_k, int normalize,
+                                          int* assignment, float* weights, int* token_of_slot,
+                                          int* expert_of_slot, float* weight_of_slot, int* group_sizes,
+                                          int* my_offsets, int* slot_of_assignment, void* const* ctrl_ptrs,
+                                          int world, int rank, int epoch, void* stream);
+int tessera_sm100_ep_dispatch_signal_device(const void* x, const int* token_of_slot,
+                                            const int* expert_of_slot, const int* my_offsets,
+                                            void* const* ctrl_ptrs, void* const* recv_bufs, int world,
+                                            int rank, int E, int max_slots, int capacity_rows, int H,
+                                            int dtype, int epoch, int* group_offsets_local, int* dst_base,
+                                            int* counter, int wait_limit_ms, void* stream);
+int tessera_sm100_ep_combine_signal_device(void* const* y_bufs, void* const* ctrl_ptrs,
+                                           const int* assignment, const int* slot_of_assignment,
+                                           const float* weights, const int* my_offsets,
+                                           const int* dst_base, void* out, int T, int top_k, int world,
+                                           int rank, int E, int capacity_rows, int H, int dtype, int epoch,
+                                           int* counter, int wait_limit_ms, void* stream);
 
 /* ---- decode attention --------------------------------------------------------------------
  * One query token per sequence against a KV cache: Q,O [B,Hq,1,D], K,V [B,Hkv,Sk,D] bf16,

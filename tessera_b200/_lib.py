@@ -41,6 +41,7 @@ _SIGNATURES = {
     "tessera_sm100_sm_count": (c_int, [POINTER(c_int)]),
     "tessera_sm100_consume_device_error": (c_int, [POINTER(c_int)]),
     "tessera_sm100_launch_count": (c_longlong, []),
+    "tessera_sm100_selftest_wait_expiry": (c_int, [c_longlong, _VP]),
     "tessera_sm100_device_alloc": (c_int, [POINTER(_VP), c_size_t]),
     "tessera_sm100_device_free": (c_int, [_VP]),
     "tessera_sm100_pool_alloc": (c_int, [POINTER(_VP), c_size_t]),
@@ -52,6 +53,7 @@ _SIGNATURES = {
     "tessera_sm100_device_download": (c_int, [_VP, _VP, c_size_t, _VP]),
     "tessera_sm100_device_copy": (c_int, [_VP, _VP, c_size_t, _VP]),
     "tessera_sm100_device_copy_2d": (c_int, [_VP, c_size_t, _VP, c_size_t, c_size_t, c_size_t, _VP]),
+    "tessera_sm100_device_download_2d": (c_int, [_VP, c_size_t, _VP, c_size_t, c_size_t, c_size_t, _VP]),
     "tessera_sm100_host_alloc": (c_int, [POINTER(_VP), c_size_t]),
     "tessera_sm100_host_free": (c_int, [_VP]),
     "tessera_sm100_stream_create": (c_int, [POINTER(_VP)]),
@@ -79,6 +81,8 @@ _SIGNATURES = {
                                                    _VP, c_int, _VP]),
     "tessera_sm100_gemm_allgather_device": (c_int, [_VP, _VP, POINTER(_VP), c_int, c_int, c_int, c_int,
                                                     c_int, c_int, c_int, _VP]),
+    "tessera_sm100_gemm_allgather_block_device": (c_int, [_VP, _VP, c_longlong, POINTER(_VP), c_int, c_int, c_int,
+                                                          c_int, c_int, c_int, c_int, _VP]),
     "tessera_sm100_grouped_gemm_device": (c_int, [_VP, _VP, _VP, _VP, c_int, c_int, c_int, c_int,
                                                   c_int, c_int, _VP]),
     "tessera_sm100_grouped_swiglu_device": (c_int, [_VP, _VP, _VP, _VP, _VP, c_int, c_int, c_int,
@@ -101,6 +105,15 @@ _SIGNATURES = {
                                                  c_int, c_int, c_int, c_int, _VP]),
     "tessera_sm100_ep_combine_device": (c_int, [POINTER(_VP), _VP, _VP, _VP, _VP, _VP, _VP, c_int, c_int,
                                                 c_int, c_int, c_int, c_int, c_int, _VP]),
+    "tessera_sm100_ep_ctrl_bytes": (c_size_t, []),
+    "tessera_sm100_ep_route_publish_device": (c_int, [_VP, c_int, c_int, c_int, c_int, _VP, _VP, _VP, _VP, _VP, _VP,
+                                                      _VP, _VP, POINTER(_VP), c_int, c_int, c_int, _VP]),
+    "tessera_sm100_ep_dispatch_signal_device": (c_int, [_VP, _VP, _VP, _VP, POINTER(_VP), POINTER(_VP), c_int, c_int,
+                                                        c_int, c_int, c_int, c_int, c_int, c_int, _VP, _VP, _VP,
+                                                        c_int, _VP]),
+    "tessera_sm100_ep_combine_signal_device": (c_int, [POINTER(_VP), POINTER(_VP), _VP, _VP, _VP, _VP, _VP, _VP,
+                                                       c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                       c_int, _VP, c_int, _VP]),
     "tessera_sm100_attn_decode_splits": (c_int, [c_int, c_int, c_int, c_int]),
     "tessera_sm100_attn_decode_int8_splits": (c_int, [c_int, c_int, c_int, c_int]),
     "tessera_sm100_attn_decode_scratch_bytes": (c_size_t, [c_int, c_int, c_int]),

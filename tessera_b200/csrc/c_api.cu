@@ -1,6 +1,7 @@
 // Library management and the device / stream / event helpers of the C ABI.
 #include "../../include/tessera_sm100.h"
 #include "device_ctx.h"
+#include "sm100_ptx.cuh"
 
 using namespace tsb;
 
@@ -12,9 +13,43 @@ __global__ void flush_kernel(uint4* buf, size_t n, uint32_t tag) {
        i += (size_t)gridDim.x * blockDim.x)
     buf[i] = make_uint4(tag, tag, tag, tag);
 }
+
+// One warp waits, through the same bounded wait the kernels use, on a barrier that nobody arrives
+// on. When the limit runs out the waiter records the error word and the kernel ends normally.
+__global__ void wait_expiry_kernel(long long limit_cycles, int* err, int* gave_up) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const bool ok = mbar_wait_limit(smem_u32(&bar), 0, &abort_flag, err, kErrWaitOther, 77, limit_cycles);
+    if (gave_up) *gave_up = ok ? 0 : 1;
+  }
+  __syncthreads();
+}
 }  // namespace
 
 extern "C" {
+
+// Self-test of the failure path: a bounded device wait that is certain to run out (at most 2^28
+// cycles, about 0.15 s). Afterwards tessera_sm100_consume_device_error reports {5, 0, 77}.
+int tessera_sm100_selftest_wait_expiry(long long limit_cycles, void* stream) {
+  if (limit_cycles <= 0 || limit_cycles > (1ll << 28)) {
+    set_last_error("selftest_wait_expiry: limit_cycles must be in (0, 2^28]");
+    return kBadArg;
+  }
+  if (int rc = ensure_device()) return rc;
+  int* err = device_err_word();
+  if (!err) return kDeviceFailed;
+  wait_expiry_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(limit_cycles, err, nullptr);
+  TSB_CUDA_OK(cudaGetLastError());
+  note_launch();
+  return kOk;
+}
 
 const char* tessera_sm100_version(void) { return "tessera-sm100 0.1.0 (sm_100a, tcgen05/TMA)"; }
 const char* tessera_sm100_last_error(void) { return last_error(); }
@@ -114,6 +149,15 @@ int tessera_sm100_device_copy_2d(void* dst, size_t dst_pitch, const void* src, s
   if (width_bytes == 0 || rows == 0) return kOk;
   TSB_CUDA_OK(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows,
                                 cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)));
+  return kOk;
+}
+// Rows of `width_bytes` from device memory (pitch src_pitch) into host memory (pitch dst_pitch).
+int tessera_sm100_device_download_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
+                                     size_t width_bytes, size_t rows, void* stream) {
+  if (!dst || !src) return kBadArg;
+  if (width_bytes == 0 || rows == 0) return kOk;
+  TSB_CUDA_OK(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows,
+                                cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
   return kOk;
 }
 int tessera_sm100_host_alloc(void** out, size_t bytes) {

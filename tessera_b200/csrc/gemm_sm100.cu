@@ -264,9 +264,12 @@ int launch_plain(const void* A, const void* B, void* D, int batch, int M, int N,
     Params pa = p;
     pa.idesc = make_idesc_f16(in_dtype == TESSERA_SM100_BF16, false, true, 2 * BM, BN);
     pa.peer_first = peer_first;
-    // Split K once the K loop has at least 16 k-blocks (each half still fills the TMA ring).
-    pa.ksplit = ((K + BK - 1) / BK >= 16) ? 2 : 1;
+    // Split K when there are fewer than four waves of whole tiles (the first tile time and the last
+    // wave's burst of stores then weigh on the step: 8192 x 8192 over 4 or 8 ranks) and the K loop
+    // has at least 16 k-blocks, so that each half still fills the TMA ring. With many waves the
+    // split only adds the partial-sum traffic (two ranks: 0.394 ms with it, 0.375 ms without).
     const long long ag_tiles = (long long)((p.m_tiles + 1) / 2) * p.n_tiles;
+    pa.ksplit = ((K + BK - 1) / BK >= 16 && ag_tiles < 4ll * (sm_count() / 2)) ? 2 : 1;
     switch (out_dtype) {
       case TESSERA_SM100_F32: return launch_ag_kernel<float>(tA, tB, peer_maps, pa, ag_tiles, stream);
       case TESSERA_SM100_BF16: return launch_ag_kernel<__nv_bfloat16>(tA, tB, peer_maps, pa, ag_tiles, stream);
@@ -872,9 +875,9 @@ int tessera_sm100_gemm_strided_device(const void* A, const void* B, void* D, int
 // weight (rank r multiplies its columns [r*nb, (r+1)*nb), nb = N_total / world); Y_ptrs[i] is the
 // base of rank i's [M, N_total] output (peer pointers for i != rank). Every tile is stored into
 // all `world` copies, so when every rank's kernel has finished each copy holds the whole Y.
-int tessera_sm100_gemm_allgather_device(const void* A, const void* B, void* const* Y_ptrs, int world,
-                                        int rank, int M, int N_total, int K, int in_dtype,
-                                        int out_dtype, void* stream) {
+static int gemm_allgather(const void* A, const void* B_block, long long ldb, void* const* Y_ptrs,
+                          int world, int rank, int M, int N_total, int K, int in_dtype, int out_dtype,
+                          void* stream) {
   if (!Y_ptrs || world <= 0 || world > gemm::MAX_PEERS || rank < 0 || rank >= world ||
       N_total % world) {
     set_last_error("gemm_allgather: bad arguments (world %d rank %d N %d; world <= %d, N %% world == 0)",
@@ -883,8 +886,9 @@ int tessera_sm100_gemm_allgather_device(const void* A, const void* B, void* cons
   }
   const int nb = N_total / world;
   const size_t osz = out_dtype == TESSERA_SM100_F32 ? 4 : 2;
-  if (nb % 8) {
-    set_last_error("gemm_allgather: N / world (%d) must be a multiple of 8", nb);
+  if (nb % 8 || ldb < nb) {
+    set_last_error("gemm_allgather: N / world (%d) must be a multiple of 8 and ldb (%lld) at least that", nb,
+                   ldb);
     return kBadArg;
   }
   void* outs[gemm::MAX_PEERS];
@@ -895,10 +899,26 @@ int tessera_sm100_gemm_allgather_device(const void* A, const void* B, void* cons
     }
     outs[i] = static_cast<char*>(Y_ptrs[i]) + (size_t)rank * nb * osz;
   }
-  const char* Bblk = static_cast<const char*>(B) + (size_t)rank * nb * 2;
-  return gemm::launch_plain(A, Bblk, outs[rank], 1, M, nb, K, K, N_total, N_total, 0, 0, 0, in_dtype,
+  return gemm::launch_plain(A, B_block, outs[rank], 1, M, nb, K, K, ldb, N_total, 0, 0, 0, in_dtype,
                             out_dtype, static_cast<cudaStream_t>(stream), outs, world, nullptr, nullptr, 0, 0,
                             rank + 1);
+}
+int tessera_sm100_gemm_allgather_device(const void* A, const void* B, void* const* Y_ptrs, int world,
+                                        int rank, int M, int N_total, int K, int in_dtype,
+                                        int out_dtype, void* stream) {
+  if (!B || world <= 0 || rank < 0 || N_total % world) {
+    set_last_error("gemm_allgather: bad arguments");
+    return kBadArg;
+  }
+  const char* Bblk = static_cast<const char*>(B) + (size_t)rank * (N_total / world) * 2;
+  return gemm_allgather(A, Bblk, N_total, Y_ptrs, world, rank, M, N_total, K, in_dtype, out_dtype, stream);
+}
+// The same with only this rank's column block of B resident: B_block is [K, N_total / world] with
+// leading dimension ldb (elements).
+int tessera_sm100_gemm_allgather_block_device(const void* A, const void* B_block, long long ldb,
+                                              void* const* Y_ptrs, int world, int rank, int M, int N_total,
+                                              int K, int in_dtype, int out_dtype, void* stream) {
+  return gemm_allgather(A, B_block, ldb, Y_ptrs, world, rank, M, N_total, K, in_dtype, out_dtype, stream);
 }
 // D = act(A*B + bias + residual): the GEMM with the reference's fused_epilogue applied in the
 // kernel epilogue. bias is fp32 [N] or null; residual is [M,N] in the output dtype or null;

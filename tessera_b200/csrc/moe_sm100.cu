@@ -29,11 +29,9 @@ constexpr int kMaxTopK = 8;
 // reference's tie rule: among equal values the HIGHER expert index ranks first
 // (np.argsort(...)[:, -k:][:, ::-1]). Weights are the f32 softmax probabilities, renormalised
 // over the selected experts when `normalize` is set and top_k > 1.
-__global__ void route_topk_kernel(const float* __restrict__ logits, int T, int E, int top_k,
-                                  int normalize, int* __restrict__ assignment,
-                                  float* __restrict__ weights) {
-  const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= T) return;
+__device__ __forceinline__ void route_token(const float* __restrict__ logits, int t, int E, int top_k,
+                                            int normalize, int* __restrict__ assignment,
+                                            float* __restrict__ weights) {
   const float* row = logits + (long long)t * E;
   float mx = -FLT_MAX;
   for (int e = 0; e < E; ++e) mx = fmaxf(mx, row[e]);
@@ -67,17 +65,24 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int T, int E
   }
 }
 
+__global__ void route_topk_kernel(const float* __restrict__ logits, int T, int E, int top_k,
+                                  int normalize, int* __restrict__ assignment,
+                                  float* __restrict__ weights) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t < T) route_token(logits, t, E, top_k, normalize, assignment, weights);
+}
+
 // ------------------------------------------------------------------------- permutation
 // Single CTA of 1024 threads: stable counting sort of the token-major slots by expert.
 // Slot s = t * top_k + j. A slot whose rank inside its expert reaches `capacity` is dropped
 // (assignment := -1, weight := 0), which is exactly the reference's token-major fill order.
 // Outputs follow the canonical int32 device ABI of
 // python/tessera/compiler/moe_transport.py:75-134.
-__global__ void __launch_bounds__(1024, 1)
-permute_kernel(int* __restrict__ assignment, float* __restrict__ weights, int S, int E,
-               int capacity, int* __restrict__ token_of_slot, int* __restrict__ expert_of_slot,
-               float* __restrict__ weight_of_slot, int* __restrict__ group_sizes,
-               int* __restrict__ group_offsets, int* __restrict__ slot_of_assignment, int top_k) {
+__device__ void permute_block(int* __restrict__ assignment, float* __restrict__ weights, int S, int E,
+                              int capacity, int* __restrict__ token_of_slot,
+                              int* __restrict__ expert_of_slot, float* __restrict__ weight_of_slot,
+                              int* __restrict__ group_sizes, int* __restrict__ group_offsets,
+                              int* __restrict__ slot_of_assignment, int top_k) {
   __shared__ int s_count[kMaxExperts];       // kept slots per expert
   __shared__ int s_offset[kMaxExperts + 1];  // exclusive scan of s_count
   __shared__ int s_running[kMaxExperts];     // slots of each expert seen in earlier chunks
@@ -149,6 +154,15 @@ permute_kernel(int* __restrict__ assignment, float* __restrict__ weights, int S,
     }
     __syncthreads();
   }
+}
+
+__global__ void __launch_bounds__(1024, 1)
+permute_kernel(int* __restrict__ assignment, float* __restrict__ weights, int S, int E,
+               int capacity, int* __restrict__ token_of_slot, int* __restrict__ expert_of_slot,
+               float* __restrict__ weight_of_slot, int* __restrict__ group_sizes,
+               int* __restrict__ group_offsets, int* __restrict__ slot_of_assignment, int top_k) {
+  permute_block(assignment, weights, S, E, capacity, token_of_slot, expert_of_slot, weight_of_slot,
+                group_sizes, group_offsets, slot_of_assignment, top_k);
 }
 
 // ------------------------------------------------------------------------- dispatch / combine
@@ -312,6 +326,208 @@ __global__ void ep_combine_kernel(PeerPtrs ybufs, const int* __restrict__ assign
     }
 #pragma unroll
     for (int q = 0; q < 8; ++q) out[(long long)t * H + c + q] = from_f32<OT>(acc[q]);
+  }
+}
+
+
+// ---- the same exchange with the ranks ordered by flags in peer memory instead of collectives -----
+// Every rank owns one EpCtrl block that all peers can write (CUDA IPC). A forward call carries an
+// epoch number, the same on all ranks and one higher on every call; a flag is "up" once it has
+// reached the epoch, so nothing is ever reset. Three launches surround the two grouped GEMMs:
+//   ep_route_publish   route + stable expert sort of the local slots (one CTA), then this rank's E
+//                      per-expert counts are stored into counts[rank][] of every rank's block and
+//                      counts_ready[rank] goes up there;
+//   ep_dispatch_signal waits for every source's counts (and for done[] of the previous epoch: the
+//                      peers no longer read the buffers this call overwrites), derives the plan,
+//                      stores the token rows into the owners' receive buffers, and the CTA that
+//                      finishes last raises rows_ready[rank] everywhere and then waits for every
+//                      source's rows_ready, so that the kernel's end means "all my rows are here";
+//   ep_combine_signal  raises y_ready[rank] everywhere (the GEMMs before it in the stream are
+//                      done), waits for every owner's y_ready, reads the result rows back, and the
+//                      CTA that finishes last raises done[rank].
+// Waits are bounded by wall-clock time (%globaltimer); on expiry the error word is set and the
+// kernel carries on to its end without the data, so the context stays usable.
+constexpr int kEpMaxWorld = 8;
+struct EpCtrl {
+  int counts[kEpMaxWorld][kMaxExperts];  // [source rank][global expert], written by the source
+  int counts_ready[32];                  // [source rank] epoch; each flag array on its own line
+  int rows_ready[32];
+  int y_ready[32];
+  int done[32];
+};
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.b32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.b32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ int ld_relaxed_sys(const int* p) {
+  int v;
+  asm volatile("ld.relaxed.sys.global.b32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Waits until *flag has reached `want` (epochs compare by signed difference). Returns false, with
+// the error word set to {kErrWaitOther, block, detail}, when `limit_ns` runs out first.
+__device__ bool ep_wait_flag(const int* flag, int want, unsigned long long limit_ns, int* err,
+                             int detail) {
+  if (ld_acquire_sys(flag) - want >= 0) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (;;) {
+    if (ld_acquire_sys(flag) - want >= 0) return true;
+    if (globaltimer_ns() - t0 > limit_ns) {
+      if (atomicCAS(err, 0, 5 /* kErrWaitOther */) == 0) {
+        err[1] = static_cast<int>(blockIdx.x);
+        err[2] = detail;
+      }
+      __threadfence();
+      return false;
+    }
+    __nanosleep(100);
+  }
+}
+
+__global__ void __launch_bounds__(1024, 1)
+ep_route_publish_kernel(const float* __restrict__ logits, int Tl, int E, int top_k, int normalize,
+                        int* __restrict__ assignment, float* __restrict__ weights,
+                        int* __restrict__ token_of_slot, int* __restrict__ expert_of_slot,
+                        float* __restrict__ weight_of_slot, int* __restrict__ group_sizes,
+                        int* __restrict__ my_offsets, int* __restrict__ slot_of, PeerPtrs ctrl,
+                        int world, int rank, int epoch) {
+  for (int t = threadIdx.x; t < Tl; t += blockDim.x)
+    route_token(logits, t, E, top_k, normalize, assignment, weights);
+  __syncthreads();
+  permute_block(assignment, weights, Tl * top_k, E, -1, token_of_slot, expert_of_slot, weight_of_slot,
+                group_sizes, my_offsets, slot_of, top_k);
+  __syncthreads();
+  for (int i = threadIdx.x; i < world * E; i += blockDim.x) {
+    const int dst = i / E, e = i - dst * E;
+    static_cast<EpCtrl*>(ctrl.p[dst])->counts[rank][e] = group_sizes[e];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < world)
+    st_release_sys(&static_cast<EpCtrl*>(ctrl.p[threadIdx.x])->counts_ready[rank], epoch);
+}
+
+__global__ void ep_dispatch_signal_kernel(const uint4* __restrict__ x, const int* __restrict__ token_of_slot,
+                                          const int* __restrict__ expert_of_slot,
+                                          const int* __restrict__ my_offsets, PeerPtrs ctrl, PeerPtrs recv,
+                                          int world, int rank, int E, int capacity_rows, int vec_per_row,
+                                          int epoch, int* __restrict__ group_offsets_local,
+                                          int* __restrict__ dst_base_out, int* __restrict__ counter,
+                                          unsigned long long limit_ns, int* __restrict__ err) {
+  __shared__ int s_base[kMaxExperts];
+  __shared__ int s_last;
+  const int Ep = E / world;
+  const EpCtrl* mine = static_cast<const EpCtrl*>(ctrl.p[rank]);
+  if (threadIdx.x < world) {
+    ep_wait_flag(&mine->counts_ready[threadIdx.x], epoch, limit_ns, err, 100 + threadIdx.x);
+    ep_wait_flag(&mine->done[threadIdx.x], epoch - 1, limit_ns, err, 200 + threadIdx.x);
+  }
+  __syncthreads();
+  // The plan: for every global expert the first row, in its owner's receive buffer, of the block
+  // this rank contributes (rows arrive expert-major, source-major inside an expert).
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int d = e / Ep;
+    int base = 0;
+    for (int e2 = d * Ep; e2 < e; ++e2)
+      for (int sr = 0; sr < world; ++sr) base += ld_relaxed_sys(&mine->counts[sr][e2]);
+    for (int sr = 0; sr < rank; ++sr) base += ld_relaxed_sys(&mine->counts[sr][e]);
+    s_base[e] = base;
+    if (blockIdx.x == 0) dst_base_out[e] = base;
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    int acc = 0;
+    for (int el = 0; el < Ep; ++el) {
+      group_offsets_local[el] = acc;
+      for (int sr = 0; sr < world; ++sr) acc += ld_relaxed_sys(&mine->counts[sr][rank * Ep + el]);
+    }
+    group_offsets_local[Ep] = acc;
+  }
+  __syncthreads();
+  const int S = my_offsets[E];  // kept slots of this rank
+  const long long total = (long long)S * vec_per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int sl = (int)(i / vec_per_row);
+    const int c = (int)(i - (long long)sl * vec_per_row);
+    const int e = expert_of_slot[sl];
+    const int row = s_base[e] + (sl - my_offsets[e]);
+    if (row < capacity_rows) {
+      uint4* dst = static_cast<uint4*>(recv.p[e / Ep]);
+      dst[(long long)row * vec_per_row + c] = x[(long long)token_of_slot[sl] * vec_per_row + c];
+    }
+  }
+  // The CTA that finishes last tells every rank that this rank's rows have landed.
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(counter, 1) == static_cast<int>(gridDim.x) - 1);
+  __syncthreads();
+  if (s_last) {
+    if (threadIdx.x == 0) *counter = 0;
+    __threadfence_system();
+    if (threadIdx.x < world) {
+      st_release_sys(&static_cast<EpCtrl*>(ctrl.p[threadIdx.x])->rows_ready[rank], epoch);
+      ep_wait_flag(&mine->rows_ready[threadIdx.x], epoch, limit_ns, err, 300 + threadIdx.x);
+    }
+  }
+}
+
+template <typename YT, typename OT>
+__global__ void ep_combine_signal_kernel(PeerPtrs ybufs, PeerPtrs ctrl, const int* __restrict__ assignment,
+                                         const int* __restrict__ slot_of, const float* __restrict__ w,
+                                         const int* __restrict__ my_offsets, const int* __restrict__ dst_base,
+                                         OT* __restrict__ out, int T, int top_k, int world, int rank, int Ep,
+                                         int capacity_rows, int H, int epoch, int* __restrict__ counter,
+                                         unsigned long long limit_ns, int* __restrict__ err) {
+  __shared__ int s_last;
+  const EpCtrl* mine = static_cast<const EpCtrl*>(ctrl.p[rank]);
+  if (threadIdx.x < world) {
+    if (blockIdx.x == 0) {
+      __threadfence_system();
+      st_release_sys(&static_cast<EpCtrl*>(ctrl.p[threadIdx.x])->y_ready[rank], epoch);
+    }
+    ep_wait_flag(&mine->y_ready[threadIdx.x], epoch, limit_ns, err, 400 + threadIdx.x);
+  }
+  __syncthreads();
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
+    float acc[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) acc[q] = 0.f;
+    for (int j = 0; j < top_k; ++j) {
+      const int sl = slot_of[(long long)t * top_k + j];
+      if (sl < 0) continue;
+      const int e = assignment[(long long)t * top_k + j];
+      const int row = dst_base[e] + (sl - my_offsets[e]);
+      if (row >= capacity_rows) continue;
+      const float wj = w[(long long)t * top_k + j];
+      const YT* src = static_cast<const YT*>(ybufs.p[e / Ep]) + (long long)row * H + c;
+      const uint4 v = __ldcg(reinterpret_cast<const uint4*>(src));  // 8 x 16-bit, not through L1
+      const YT* h = reinterpret_cast<const YT*>(&v);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) acc[q] += wj * to_f32<YT>(h[q]);
+    }
+#pragma unroll
+    for (int q = 0; q < 8; ++q) out[(long long)t * H + c + q] = from_f32<OT>(acc[q]);
+  }
+  // The CTA that finishes last tells every rank that this rank no longer reads their buffers.
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(counter, 1) == static_cast<int>(gridDim.x) - 1);
+  __syncthreads();
+  if (s_last) {
+    if (threadIdx.x == 0) *counter = 0;
+    __threadfence_system();
+    if (threadIdx.x < world)
+      st_release_sys(&static_cast<EpCtrl*>(ctrl.p[threadIdx.x])->done[rank], epoch);
   }
 }
 
@@ -647,6 +863,118 @@ int tessera_sm100_ep_combine_device(void* const* y_bufs, const int* assignment,
         T, top_k, Ep, capacity_rows, H);
   else {
     set_last_error("ep_combine: dtype must be bf16 or f16");
+    return kBadArg;
+  }
+  TSB_CUDA_OK(cudaGetLastError());
+  note_launch();
+  return kOk;
+}
+
+// ---- the exchange ordered by flags in peer memory (no collective) ------------------------------
+size_t tessera_sm100_ep_ctrl_bytes(void) { return sizeof(moe::EpCtrl); }
+
+namespace {
+bool ep_peer_ptrs(moe::PeerPtrs& pp, void* const* ptrs, int world, const char* what) {
+  for (int i = 0; i < world; ++i) {
+    if (!ptrs[i]) {
+      set_last_error("%s: pointer %d of a per-rank array is null", what, i);
+      return false;
+    }
+    pp.p[i] = ptrs[i];
+  }
+  return true;
+}
+unsigned long long ep_limit_ns(int wait_limit_ms) {
+  return (unsigned long long)(wait_limit_ms > 0 ? wait_limit_ms : 10000) * 1000000ull;
+}
+}  // namespace
+
+int tessera_sm100_ep_route_publish_device(const float* logits, int Tl, int E, int top_k, int normalize,
+                                          int* assignment, float* weights, int* token_of_slot,
+                                          int* expert_of_slot, float* weight_of_slot, int* group_sizes,
+                                          int* my_offsets, int* slot_of_assignment, void* const* ctrl_ptrs,
+                                          int world, int rank, int epoch, void* stream) {
+  if (!logits || !assignment || !weights || !token_of_slot || !expert_of_slot || !weight_of_slot ||
+      !group_sizes || !my_offsets || !slot_of_assignment || !ctrl_ptrs || Tl <= 0 || E <= 0 ||
+      E > moe::kMaxExperts || top_k <= 0 || top_k > E || top_k > moe::kMaxTopK || world <= 0 ||
+      world > moe::kEpMaxWorld || rank < 0 || rank >= world || E % world) {
+    set_last_error("ep_route_publish: bad arguments (Tl %d E %d top_k %d world %d rank %d)", Tl, E, top_k,
+                   world, rank);
+    return kBadArg;
+  }
+  moe::PeerPtrs cp{};
+  if (!ep_peer_ptrs(cp, ctrl_ptrs, world, "ep_route_publish")) return kBadArg;
+  moe::ep_route_publish_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+      logits, Tl, E, top_k, normalize, assignment, weights, token_of_slot, expert_of_slot, weight_of_slot,
+      group_sizes, my_offsets, slot_of_assignment, cp, world, rank, epoch);
+  TSB_CUDA_OK(cudaGetLastError());
+  note_launch();
+  return kOk;
+}
+
+int tessera_sm100_ep_dispatch_signal_device(const void* x, const int* token_of_slot,
+                                            const int* expert_of_slot, const int* my_offsets,
+                                            void* const* ctrl_ptrs, void* const* recv_bufs, int world,
+                                            int rank, int E, int max_slots, int capacity_rows, int H,
+                                            int dtype, int epoch, int* group_offsets_local, int* dst_base,
+                                            int* counter, int wait_limit_ms, void* stream) {
+  const size_t row_bytes = (size_t)H * moe::dtype_size(dtype);
+  if (!x || !token_of_slot || !expert_of_slot || !my_offsets || !ctrl_ptrs || !recv_bufs ||
+      !group_offsets_local || !dst_base || !counter || world <= 0 || world > moe::kEpMaxWorld ||
+      rank < 0 || rank >= world || E <= 0 || E > moe::kMaxExperts || E % world || (row_bytes % 16) ||
+      max_slots <= 0) {
+    set_last_error("ep_dispatch_signal: bad arguments (rows must be 16-byte multiples, world <= 8)");
+    return kBadArg;
+  }
+  moe::PeerPtrs cp{}, rp{};
+  if (!ep_peer_ptrs(cp, ctrl_ptrs, world, "ep_dispatch_signal") ||
+      !ep_peer_ptrs(rp, recv_bufs, world, "ep_dispatch_signal"))
+    return kBadArg;
+  int* err = device_err_word();
+  if (!err) return kDeviceFailed;
+  const int vec = (int)(row_bytes / 16);
+  const long long total = (long long)max_slots * vec;
+  const int grid = (int)std::min<long long>((total + 255) / 256, 148 * 16);
+  moe::ep_dispatch_signal_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), token_of_slot, expert_of_slot, my_offsets, cp, rp, world, rank, E,
+      capacity_rows, vec, epoch, group_offsets_local, dst_base, counter, ep_limit_ns(wait_limit_ms), err);
+  TSB_CUDA_OK(cudaGetLastError());
+  note_launch();
+  return kOk;
+}
+
+int tessera_sm100_ep_combine_signal_device(void* const* y_bufs, void* const* ctrl_ptrs,
+                                           const int* assignment, const int* slot_of_assignment,
+                                           const float* weights, const int* my_offsets,
+                                           const int* dst_base, void* out, int T, int top_k, int world,
+                                           int rank, int E, int capacity_rows, int H, int dtype, int epoch,
+                                           int* counter, int wait_limit_ms, void* stream) {
+  if (!y_bufs || !ctrl_ptrs || !assignment || !slot_of_assignment || !weights || !my_offsets ||
+      !dst_base || !out || !counter || world <= 0 || world > moe::kEpMaxWorld || rank < 0 ||
+      rank >= world || E % world || (H % 8) || T <= 0) {
+    set_last_error("ep_combine_signal: bad arguments (H must be a multiple of 8, world <= 8, T > 0)");
+    return kBadArg;
+  }
+  moe::PeerPtrs yp{}, cp{};
+  if (!ep_peer_ptrs(yp, y_bufs, world, "ep_combine_signal") ||
+      !ep_peer_ptrs(cp, ctrl_ptrs, world, "ep_combine_signal"))
+    return kBadArg;
+  int* err = device_err_word();
+  if (!err) return kDeviceFailed;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int Ep = E / world;
+  const unsigned long long lim = ep_limit_ns(wait_limit_ms);
+  if (dtype == TESSERA_SM100_BF16)
+    moe::ep_combine_signal_kernel<__nv_bfloat16, __nv_bfloat16><<<T, 128, 0, st>>>(
+        yp, cp, assignment, slot_of_assignment, weights, my_offsets, dst_base,
+        static_cast<__nv_bfloat16*>(out), T, top_k, world, rank, Ep, capacity_rows, H, epoch, counter, lim,
+        err);
+  else if (dtype == TESSERA_SM100_F16)
+    moe::ep_combine_signal_kernel<__half, __half><<<T, 128, 0, st>>>(
+        yp, cp, assignment, slot_of_assignment, weights, my_offsets, dst_base, static_cast<__half*>(out), T,
+        top_k, world, rank, Ep, capacity_rows, H, epoch, counter, lim, err);
+  else {
+    set_last_error("ep_combine_signal: dtype must be bf16 or f16");
     return kBadArg;
   }
   TSB_CUDA_OK(cudaGetLastError());

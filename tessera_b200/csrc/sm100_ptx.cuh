@@ -67,16 +67,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Bounded wait. `abort_flag` lives in shared memory; `err` is a global int[4]
-// {code, blockIdx.x, detail, 0}.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* err, int code, int detail = 0) {
+// {code, blockIdx.x, detail, 0}. `limit` is in SM clock cycles.
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                int* err, int code, int detail, long long limit) {
   if (mbar_try_wait(bar, parity)) return true;
   if (*abort_flag) return false;
   const long long t0 = clock64();
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitLimitCycles) {
+    if (clock64() - t0 > limit) {
       *abort_flag = 1;
       if (atomicCAS(err, 0, code) == 0) {
         err[1] = static_cast<int>(blockIdx.x);
@@ -86,6 +86,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       return false;
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* err, int code, int detail = 0) {
+  return mbar_wait_limit(bar, parity, abort_flag, err, code, detail, kWaitLimitCycles);
 }
 
 // ---------------------------------------------------------------- TMA

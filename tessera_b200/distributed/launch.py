@@ -3,7 +3,11 @@
 
 The reference runs the per-rank calls one after another on the CPU. Here rank ``r`` runs with
 CUDA device ``r mod device_count`` current, so ``ops`` calls inside the kernel body execute on
-that rank's GPU; list-of-ndarray fan-out, scalar broadcast and the length checks are unchanged.
+that rank's GPU, and with more than one GPU the ranks are issued concurrently: one host thread
+per GPU walks that GPU's ranks in order (the C ABI releases the interpreter lock, the current
+device and the error string are per thread), and the call returns when every rank has finished.
+Shards are independent by construction, so the results are those of the sequential loop;
+list-of-ndarray fan-out, scalar broadcast and the length checks are unchanged.
 """
 from __future__ import annotations
 
@@ -60,16 +64,31 @@ class _ShardDispatcher:
                 raise ValueError(f"Shard list {i} has {len(p)} entries but expected {n_ranks} "
                                  f"(from axis {self.axis!r})")
         ndev = _device_count()
-        results = []
-        for r in range(n_ranks):
-            if ndev > 1:
-                from .. import device
-                device.set_device(r % ndev)
-            args = [p[r] if p is not None else shard_lists[i] for i, p in enumerate(lists)]
-            results.append(self._fn(*args))
-        if ndev > 1:
-            from .. import device
-            device.set_device(0)
+
+        def rank_args(r):
+            return [p[r] if p is not None else shard_lists[i] for i, p in enumerate(lists)]
+
+        if ndev <= 1 or n_ranks <= 1:
+            return [self._fn(*rank_args(r)) for r in range(n_ranks)]
+        from concurrent.futures import ThreadPoolExecutor
+        from .. import device
+        results: list = [None] * n_ranks
+        errors: list = [None] * n_ranks
+
+        def run_device(d):
+            device.set_device(d)
+            for r in range(d, n_ranks, ndev):
+                try:
+                    results[r] = self._fn(*rank_args(r))
+                except BaseException as exc:  # reported in rank order below
+                    errors[r] = exc
+
+        used = min(ndev, n_ranks)
+        with ThreadPoolExecutor(max_workers=used) as pool:
+            list(pool.map(run_device, range(used)))
+        for exc in errors:
+            if exc is not None:
+                raise exc
         return results
 
     def __repr__(self) -> str:

@@ -33,10 +33,14 @@ def tp_column_range(n: int, world: int, rank: int) -> tuple:
 
 class TensorParallelGemm:
     """Column-parallel GEMM whose epilogue is the all-gather: rank r multiplies its column block of
-    the full W and stores every output tile into every rank's Y over NVLink
+    W and stores every output tile into every rank's Y over NVLink
     (``tessera_sm100_gemm_allgather_device``). ``gather_host`` exchanges the 64-byte CUDA IPC
     handles of the Y buffers (e.g. ``torch.distributed.all_gather_object`` over gloo). After a
-    call, synchronise the stream and pass a host barrier before reading ``self.Y``."""
+    call, synchronise the stream and pass a host barrier before reading ``self.Y``.
+
+    ``run_host`` is the host-operand form: A is replicated data, so each rank uploads only M / world
+    of its rows (plus its own column block of W), the rows are all-gathered over NVLink into every
+    rank's device copy of A, the fused GEMM runs, and the rank's own block of Y comes back."""
 
     def __init__(self, M: int, N: int, K: int, world: int, rank: int, gather_host, dtype, out_dtype):
         import ctypes
@@ -44,8 +48,10 @@ class TensorParallelGemm:
         from .device import DeviceArray
         tp_column_range(N, world, rank)
         self.M, self.N, self.K, self.world, self.rank = M, N, K, world, rank
+        self.dtype, self.out_dtype = np.dtype(dtype), np.dtype(out_dtype)
         self._in, self._out = device.dtype_code(dtype), device.dtype_code(out_dtype)
         self.Y = DeviceArray.zeros((M, N), out_dtype)
+        self._A = self._Wb = None            # device operands of run_host, made on first use
         device.synchronize()
         handle = ctypes.create_string_buffer(64)
         _lib.call("tessera_sm100_ipc_get_handle", self.Y.ptr, handle)
@@ -66,6 +72,35 @@ class TensorParallelGemm:
         from . import _lib, device
         _lib.call("tessera_sm100_gemm_allgather_device", A.ptr, W_full.ptr, self._ptrs, self.world,
                   self.rank, self.M, self.N, self.K, self._in, self._out, device._stream_handle(stream))
+
+    def run_host(self, A_rows: np.ndarray, W_block: np.ndarray, Y_block: np.ndarray, comm, stream=None) -> None:
+        """``A_rows``: rows [rank*M/world, (rank+1)*M/world) of A, ``W_block``: this rank's (K, N/world)
+        columns of W, ``Y_block``: (M, N/world) host array that receives this rank's columns of Y
+        (page-locked arrays make the copies asynchronous). ``comm`` is a ``collectives.Communicator``.
+        Returns after this rank's block has arrived; the other ranks' blocks of ``self.Y`` are
+        complete once every rank has returned."""
+        from . import _lib, device
+        from .device import DeviceArray
+        M, N, K, W, r = self.M, self.N, self.K, self.world, self.rank
+        if M % W:
+            raise ValueError(f"M={M} is not divisible by the tensor-parallel size {W}")
+        mb, nb = M // W, N // W
+        if A_rows.shape != (mb, K) or W_block.shape != (K, nb) or Y_block.shape != (M, nb):
+            raise ValueError("run_host: operand shapes do not match this rank's shard")
+        if self._A is None:
+            self._A, self._Wb = DeviceArray((M, K), self.dtype), DeviceArray((K, nb), self.dtype)
+        sh = device._stream_handle(stream)
+        isz, osz = self.dtype.itemsize, self.out_dtype.itemsize
+        mine = self._A.view((mb, K), r * mb * K)
+        _lib.call("tessera_sm100_device_upload", mine.ptr, A_rows.ctypes.data, mb * K * isz, sh)
+        _lib.call("tessera_sm100_device_upload", self._Wb.ptr, W_block.ctypes.data, K * nb * isz, sh)
+        if W > 1:
+            comm.all_gather(mine, self._A, stream)            # in place: block r of A is already there
+        _lib.call("tessera_sm100_gemm_allgather_block_device", self._A.ptr, self._Wb.ptr, nb, self._ptrs, W, r,
+                  M, N, K, self._in, self._out, sh)
+        _lib.call("tessera_sm100_device_download_2d", Y_block.ctypes.data, nb * osz, self.Y.ptr + r * nb * osz,
+                  N * osz, nb * osz, M, sh)
+        _lib.call("tessera_sm100_stream_synchronize", sh)
 
     def close(self) -> None:
         from . import _lib
@@ -279,18 +314,22 @@ class GpuMoeBackend:
 class DeviceExpertParallelMoE:
     """Expert-parallel MoE forward with the exchange done by the kernels themselves: token rows are
     stored straight into the owning rank's receive buffer over NVLink, results are read back from
-    the owner's output buffer, and the only NCCL traffic is an all-gather of E int32 counts plus
-    small all-reduces that order the phases. Nothing returns to the host between route and
-    combine. Buffers are sized for the worst case (every slot of every rank on one rank).
+    the owner's output buffer, and the ranks are ordered by flags the kernels raise in each other's
+    memory (``tessera_sm100_ep_{route_publish,dispatch_signal,combine_signal}_device``): no
+    collective, no host round trip, five launches per forward (route + sort + publish, plan +
+    dispatch, the two grouped GEMMs, combine). Buffers are sized for the worst case (every slot of
+    every rank on one rank). Every rank must call ``forward`` the same number of times.
 
-    ``gather_host`` exchanges CUDA IPC handles once at construction."""
+    ``comm`` only supplies ``rank`` and ``world``; ``gather_host`` exchanges CUDA IPC handles once at
+    construction (``torch.distributed.all_gather_object`` over gloo, or a list of one for a single
+    rank). ``wait_limit_ms`` bounds every device-side wait for a peer."""
 
     def __init__(self, comm, gather_host, w_gate, w_up, w_down, tokens_per_rank: int, top_k: int,
-                 num_experts: int, normalize_weights: bool = True, stream=None) -> None:
+                 num_experts: int, normalize_weights: bool = True, stream=None, wait_limit_ms: int = 10000) -> None:
         import ctypes
         from . import _lib, device
         from .device import DeviceArray
-        self.comm, self.world, self.rank = comm, comm.world, comm.rank
+        self.world, self.rank = comm.world, comm.rank
         if num_experts % self.world:
             raise ValueError("num_experts must be divisible by the number of ranks")
         self.E, self.k, self.Tl = num_experts, top_k, tokens_per_rank
@@ -302,6 +341,8 @@ class DeviceExpertParallelMoE:
         self.dtype = w_gate.dtype
         self._code = device.dtype_code(self.dtype)
         self.capacity = self.Tl * self.k * self.world
+        self.wait_limit_ms = int(wait_limit_ms)
+        self.epoch = 0
         S = self.Tl * self.k
         i32, f32 = np.int32, np.float32
         self.assignment = DeviceArray((self.Tl, self.k), i32)
@@ -310,10 +351,9 @@ class DeviceExpertParallelMoE:
         self.weight_of_slot = DeviceArray((S,), f32)
         self.group_sizes, self.my_offsets = DeviceArray((self.E,), i32), DeviceArray((self.E + 1,), i32)
         self.slot_of = DeviceArray((S,), i32)
-        self.all_counts = DeviceArray((self.world, self.E), i32)
         self.local_offsets, self.dst_base = DeviceArray((self.Ep + 1,), i32), DeviceArray((self.E,), i32)
-        self.flag = DeviceArray.zeros((4,), i32)
-        self.flag_out = DeviceArray.zeros((4,), i32)
+        self.counters = DeviceArray.zeros((2,), i32)                             # dispatch, combine
+        self.ctrl = DeviceArray.zeros((int(_lib.load().tessera_sm100_ep_ctrl_bytes()),), np.uint8)   # peers raise flags here
         self.recv = DeviceArray.zeros((self.capacity, self.H), self.dtype)      # peers store here
         self.hidden = DeviceArray((self.capacity, self.F), self.dtype)
         self.y = DeviceArray.zeros((self.capacity, self.H), self.dtype)         # peers read here
@@ -337,25 +377,22 @@ class DeviceExpertParallelMoE:
 
         self._recv_ptrs = exchange(self.recv)
         self._y_ptrs = exchange(self.y)
+        self._ctrl_ptrs = exchange(self.ctrl)
 
     # The forward in three stages, each on the stream it is given: exchange in, experts, exchange out.
     def _stage_dispatch(self, x_local, logits_local, stream) -> None:
         from . import _lib, device
         sh = device._stream_handle(stream)
         Tl, k, E, H = self.Tl, self.k, self.E, self.H
-        self.comm.all_reduce(self.flag, self.flag_out, "sum", stream)   # peers are done with the previous call's buffers
-        _lib.call("tessera_sm100_moe_route_device", logits_local.ptr, Tl, E, k, int(self.normalize),
-                  self.assignment.ptr, self.weights.ptr, sh)
-        _lib.call("tessera_sm100_moe_permute_device", self.assignment.ptr, self.weights.ptr, Tl, k, E, -1,
-                  self.token_of_slot.ptr, self.expert_of_slot.ptr, self.weight_of_slot.ptr,
-                  self.group_sizes.ptr, self.my_offsets.ptr, self.slot_of.ptr, sh)
-        self.comm.all_gather(self.group_sizes, self.all_counts, stream)
-        _lib.call("tessera_sm100_ep_plan_device", self.all_counts.ptr, self.world, self.rank, E,
-                  self.local_offsets.ptr, self.dst_base.ptr, sh)
-        _lib.call("tessera_sm100_ep_dispatch_device", x_local.ptr, self.token_of_slot.ptr,
-                  self.expert_of_slot.ptr, self.my_offsets.ptr, self.dst_base.ptr, self._recv_ptrs,
-                  self.world, E, Tl * k, self.capacity, H, self._code, sh)
-        self.comm.all_reduce(self.flag, self.flag_out, "sum", stream)   # every rank's rows have landed
+        self.epoch += 1
+        _lib.call("tessera_sm100_ep_route_publish_device", logits_local.ptr, Tl, E, k, int(self.normalize),
+                  self.assignment.ptr, self.weights.ptr, self.token_of_slot.ptr, self.expert_of_slot.ptr,
+                  self.weight_of_slot.ptr, self.group_sizes.ptr, self.my_offsets.ptr, self.slot_of.ptr,
+                  self._ctrl_ptrs, self.world, self.rank, self.epoch, sh)
+        _lib.call("tessera_sm100_ep_dispatch_signal_device", x_local.ptr, self.token_of_slot.ptr,
+                  self.expert_of_slot.ptr, self.my_offsets.ptr, self._ctrl_ptrs, self._recv_ptrs, self.world,
+                  self.rank, E, Tl * k, self.capacity, H, self._code, self.epoch, self.local_offsets.ptr,
+                  self.dst_base.ptr, self.counters.ptr, self.wait_limit_ms, sh)
 
     def _stage_experts(self, stream) -> None:
         from . import _lib, device
@@ -369,10 +406,10 @@ class DeviceExpertParallelMoE:
     def _stage_combine(self, out, stream) -> None:
         from . import _lib, device
         sh = device._stream_handle(stream)
-        self.comm.all_reduce(self.flag, self.flag_out, "sum", stream)   # every rank's expert outputs are complete
-        _lib.call("tessera_sm100_ep_combine_device", self._y_ptrs, self.assignment.ptr, self.slot_of.ptr,
-                  self.weights.ptr, self.my_offsets.ptr, self.dst_base.ptr, out.ptr, self.Tl, self.k, self.world,
-                  self.E, self.capacity, self.H, self._code, sh)
+        _lib.call("tessera_sm100_ep_combine_signal_device", self._y_ptrs, self._ctrl_ptrs, self.assignment.ptr,
+                  self.slot_of.ptr, self.weights.ptr, self.my_offsets.ptr, self.dst_base.ptr, out.ptr, self.Tl,
+                  self.k, self.world, self.rank, self.E, self.capacity, self.H, self._code, self.epoch,
+                  self.counters.ptr + 4, self.wait_limit_ms, sh)
 
     def forward(self, x_local, logits_local, out=None):
         """``x_local`` (Tl, H) and ``logits_local`` (Tl, E) fp32 DeviceArrays; returns a (Tl, H)
@@ -390,73 +427,3 @@ class DeviceExpertParallelMoE:
         for p in self._opened:
             _lib.call("tessera_sm100_ipc_close_handle", p)
         self._opened = []
-
-
-class PipelinedExpertParallelMoE:
-    """The expert-parallel forward over micro-batches of the local tokens, with the exchange of one
-    micro-batch overlapping the expert GEMMs of another — the schedule of the reference's
-    ``megamoe_forward_pipelined`` (python/tessera/distributed/moe.py:767-1025). Every micro-batch
-    has its own exchange buffers (a :class:`DeviceExpertParallelMoE` over ``tokens_per_rank /
-    micro_batches`` tokens); the exchange stages (route, dispatch stores, the rendezvous
-    all-reduces, combine) run on one stream and the grouped GEMMs on another, ordered by events:
-
-        exchange stream:  in(0)  in(1)  out(0)  in(2)  out(1) ...
-        compute stream :         ffn(0)         ffn(1) ...
-
-    Tokens are independent, so the result equals the unpipelined forward row for row. All NCCL
-    calls stay on the one exchange stream (a communicator is not used from two streams at once)."""
-
-    def __init__(self, comm, gather_host, w_gate, w_up, w_down, tokens_per_rank: int, top_k: int,
-                 num_experts: int, micro_batches: int = 2, normalize_weights: bool = True) -> None:
-        from .device import Event, Stream
-        if micro_batches < 1 or tokens_per_rank % micro_batches:
-            raise ValueError("tokens_per_rank must be divisible by micro_batches")
-        self.M, self.Tm = micro_batches, tokens_per_rank // micro_batches
-        self.exchange, self.compute = Stream(), Stream()
-        self.parts = [DeviceExpertParallelMoE(comm, gather_host, w_gate, w_up, w_down, self.Tm, top_k, num_experts,
-                                              normalize_weights, stream=self.exchange) for _ in range(self.M)]
-        self.H, self.E, self.dtype = self.parts[0].H, num_experts, self.parts[0].dtype
-        self._in_done = [Event() for _ in range(self.M)]
-        self._ffn_done = [Event() for _ in range(self.M)]
-        self._start, self._end = Event(), Event()
-
-    def forward(self, x_local, logits_local, out=None, stream=None):
-        """``x_local`` (Tl, H), ``logits_local`` (Tl, E) fp32; returns (Tl, H). The work is ordered
-        after what is already enqueued on ``stream`` and ``stream`` waits for it at the end."""
-        from . import _lib, device
-        from .device import DeviceArray
-        Tl = self.M * self.Tm
-        if out is None:
-            out = DeviceArray((Tl, self.H), self.dtype, pooled=True)
-        self._start.record(stream)
-        self.exchange.wait_event(self._start)
-        self.compute.wait_event(self._start)
-        xs = [x_local.view((self.Tm, self.H), i * self.Tm * self.H) for i in range(self.M)]
-        ls = [logits_local.view((self.Tm, self.E), i * self.Tm * self.E) for i in range(self.M)]
-        os_ = [out.view((self.Tm, self.H), i * self.Tm * self.H) for i in range(self.M)]
-
-        def stage_in(i):
-            self.parts[i]._stage_dispatch(xs[i], ls[i], self.exchange)
-            self._in_done[i].record(self.exchange)
-            self.compute.wait_event(self._in_done[i])
-            self.parts[i]._stage_experts(self.compute)
-            self._ffn_done[i].record(self.compute)
-
-        def stage_out(i):
-            self.exchange.wait_event(self._ffn_done[i])
-            self.parts[i]._stage_combine(os_[i], self.exchange)
-
-        stage_in(0)
-        for i in range(1, self.M):
-            stage_in(i)
-            stage_out(i - 1)
-        stage_out(self.M - 1)
-        self._end.record(self.exchange)
-        _lib.call("tessera_sm100_stream_wait_event", device._stream_handle(stream), self._end.handle)
-        return out
-
-    def close(self) -> None:
-        for part in self.parts:
-            part.close()
-        self.exchange.close()
-        self.compute.close()

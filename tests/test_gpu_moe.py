@@ -178,9 +178,12 @@ def test_config5_full_size():
 
 
 def test_device_side_expert_parallel_exchange_on_one_rank():
-    """The peer-memory dispatch/combine kernels with a world of one (own buffers stand in for the
-    peers'): the result must equal the single-device layer, twice in a row (buffers are reused)."""
-    from tessera_b200 import collectives, parallel
+    """The flag-ordered dispatch/combine kernels with a world of one (own buffers stand in for the
+    peers'): the fused route + sort reproduces the reference's routing bit for bit, and the result
+    equals the single-device layer, three times in a row (buffers and flags are reused, the epoch
+    moves on)."""
+    from types import SimpleNamespace
+    from tessera_b200 import parallel
     rng = np.random.default_rng(31)
     T, H, F, E, k = 300, 128, 256, 8, 2
     x = rng.standard_normal((T, H), dtype=np.float32).astype(bfloat16)
@@ -188,15 +191,20 @@ def test_device_side_expert_parallel_exchange_on_one_rank():
     wg = (rng.standard_normal((E, H, F), dtype=np.float32) / 11).astype(bfloat16)
     wu = (rng.standard_normal((E, H, F), dtype=np.float32) / 11).astype(bfloat16)
     wd = (rng.standard_normal((E, F, H), dtype=np.float32) / 16).astype(bfloat16)
-    comm = collectives.Communicator.from_unique_id(collectives.Communicator.unique_id(), 1, 0)
-    moe = parallel.DeviceExpertParallelMoE(comm, lambda h: [h], DA.from_host(wg), DA.from_host(wu),
-                                           DA.from_host(wd), T, k, E)
+    moe = parallel.DeviceExpertParallelMoE(SimpleNamespace(world=1, rank=0), lambda h: [h], DA.from_host(wg),
+                                           DA.from_host(wu), DA.from_host(wd), T, k, E, wait_limit_ms=2000)
     dx, dl = DA.from_host(x), DA.from_host(logits)
-    ref = orc.moe_layer_from_logits(x, logits, wg, wu, wd, k)[0]
-    for _ in range(2):
+    ref, routing, perm = orc.moe_layer_from_logits(x, logits, wg, wu, wd, k)
+    for _ in range(3):
         y = moe.forward(dx, dl)
         device.synchronize()
         assert rel_err(y.download(), ref) < TOL
+    assert moe.epoch == 3
+    np.testing.assert_array_equal(moe.assignment.download(), routing.assignment.astype(np.int32))
+    np.testing.assert_array_equal(moe.token_of_slot.download(), perm.token_of_slot)
+    np.testing.assert_array_equal(moe.expert_of_slot.download(), perm.expert_of_slot)
+    np.testing.assert_array_equal(moe.group_sizes.download(), perm.group_sizes)
+    np.testing.assert_array_equal(moe.local_offsets.download(), perm.group_offsets)
+    np.testing.assert_allclose(moe.weights.download(), routing.weights, rtol=0, atol=1e-6)
     no_device_error()
     moe.close()
-    comm.close()

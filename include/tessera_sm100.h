@@ -365,8 +365,10 @@ int tessera_sm100_attn_decode_device(const void* Q, const void* K, const void* V
  *    splits needs 0.5 MiB; the benchmark shape, batch 64, runs as one split and needs none). splits <= 0 picks the library's split count, lowered
  *    until the partials fit; an explicit split count that does not fit returns 1 with an error
  *    text naming the required and the available bytes.
- *  - The first call on each device resolves the array's device address (with that device
- *    current); issue that first call outside any stream capture.
+ *  - The first call on each device creates the context if none exists yet (a null cudaFree, the only
+ *    allocator call this entry point ever makes, and only then) and resolves the array's device
+ *    address with that device current; issue that first call outside any stream capture. Later
+ *    calls use the cached address and make no such call.
  *  - All calls share the one array. Calls ordered on a stream are safe; calls that overlap on the
  *    GPU (different streams without ordering) race on it. Nothing in it needs clearing between
  *    calls: every partial a launch reads it has written itself.
@@ -422,7 +424,7 @@ int tessera_sm100_flash_attn_bwd(const void* dO, const void* Q, const void* K, c
  * kernel once more to get O and each row's log-sum-exp (into the workspace), then delta = dO.O, a
  * dQ kernel (one CTA per 128 query rows) and a dK/dV kernel (one CTA per 128 keys, over the query
  * heads of the KV head): tcgen05 MMA with TMEM accumulators, no atomics, bit-identical reruns
- * (TESSERA_SM100_ATTN_BWD=mma in the environment selects the earlier mma.sync kernels). workspace: tessera_sm100_flash_attn_bwd_bf16_workspace_bytes(B, Hq, Sq) bytes.
+ * workspace: tessera_sm100_flash_attn_bwd_bf16_workspace_bytes(B, Hq, Sq) bytes.
  * tessera_sm100_flash_attn_fwd_lse_device is that forward pass on its own: O plus lse2[B,Hq,Sq] =
  * log2(sum_n exp2(scale*log2(e)*s_n)) over the legal keys (multiply by ln 2 for the natural-log LSE). */
 size_t tessera_sm100_flash_attn_bwd_bf16_workspace_bytes(int B, int Hq, int Sq);

@@ -6,7 +6,7 @@ that path — ``tessera.jit``, ``tessera.kernel``, ``tessera.index_launch``, ``t
 op executed by hand-written sm_100a kernels through a ctypes C ABI. Nothing here imports
 PyTorch, and there is no CPU fallback.
 """
-from . import cache, collectives, device, nn, ops, runtime
+from . import cache, collectives, device, native_artifact, nn, ops, runtime
 from .distributed import (Block, Cyclic, DistributedArray, MeshSpec, Rect, Region, Replicated,
                           ShardSpec, array, dist, domain, index_launch, kernel)
 from .jit import JitFn, TesseraJitError, jit
@@ -35,7 +35,7 @@ mut_f16 = _DTypeSentinel("mut_f16")
 mut_bf16 = _DTypeSentinel("mut_bf16")
 mut_f32 = _DTypeSentinel("mut_f32")
 
-__all__ = ["ops", "cache", "runtime", "collectives", "device", "nn", "jit", "JitFn", "TesseraJitError",
+__all__ = ["ops", "cache", "runtime", "native_artifact", "collectives", "device", "nn", "jit", "JitFn", "TesseraJitError",
            "kernel", "index_launch", "DistributedArray", "ShardSpec", "MeshSpec", "Rect", "Block",
            "Cyclic", "Replicated", "Region", "domain", "dist", "array", "f16", "bf16", "f32",
            "mut_f16", "mut_bf16", "mut_f32"]

@@ -279,18 +279,19 @@ class PagedKVCache:
         """One new token per sequence: ``k_new``, ``v_new`` ``[B, Hkv, 128]`` (host or device).
         Sequences that start a new page get one from the free list first; the rows are written and
         the lengths bumped by a kernel (KVCacheHandle.append, python/tessera/cache/handle.py:156-215)."""
-        dirty = False
-        for b in range(self.num_seqs):
-            if int(self._lens[b]) >= int(self._owned[b]) * self.page_size:
-                if self._owned[b] >= self.max_pages:
-                    raise ValueError(f"PagedKVCache.append: sequence {b} would exceed its page table "
-                                     f"({self.max_pages} pages of {self.page_size})")
-                if not self._free:
-                    raise ValueError("PagedKVCache.append: no free pages")
-                self._table[b, self._owned[b]] = self._free.pop()
-                self._owned[b] += 1
-                dirty = True
-        if dirty:
+        # Which sequences start a new page: checked for ALL of them before any state changes, so a
+        # refusal leaves the host table, the free list and the device table as they were.
+        need = [b for b in range(self.num_seqs) if int(self._lens[b]) >= int(self._owned[b]) * self.page_size]
+        for b in need:
+            if self._owned[b] >= self.max_pages:
+                raise ValueError(f"PagedKVCache.append: sequence {b} would exceed its page table "
+                                 f"({self.max_pages} pages of {self.page_size})")
+        if len(need) > len(self._free):
+            raise ValueError(f"PagedKVCache.append: no free pages ({len(need)} needed, {len(self._free)} free)")
+        for b in need:
+            self._table[b, self._owned[b]] = self._free.pop()
+            self._owned[b] += 1
+        if need:
             self.page_table.upload(self._table, stream)
         shape = (self.num_seqs, self.num_kv_heads, self.head_dim)
         if self.quantize_bits:

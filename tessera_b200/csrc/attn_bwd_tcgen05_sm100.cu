@@ -1,7 +1,9 @@
 // Attention backward with tcgen05 MMA and TMEM accumulators: bf16, D = Dv = 128, no bias / window /
 // soft-cap, bottom-right causal mask, grouped-query heads. Same mathematics and the same ownership
-// (one CTA per block of gradient rows, fixed summation order, no atomics) as the mma.sync kernels
-// in attn_bwd_tc_sm100.cu; inputs are the forward's row log-sum-exps (base 2) and delta = dO . O.
+// (one CTA per block of gradient rows, fixed summation order, no atomics) as the general CUDA-core
+// kernels in attn_bwd_sm100.cu; inputs are the forward's row log-sum-exps (base 2) and
+// delta = dO . O (delta_kernel below). The entry points at the end of the file run the forward
+// recompute (or take a kept forward state), delta, then the two kernels.
 //
 // dkv5_kernel: one CTA per 128 keys of one KV head. K and V stay in shared memory; the Q and dO
 // tiles (128 query rows) of every query head of the group stream through a two-deep TMA ring.
@@ -33,6 +35,10 @@
 #include "sm100_ptx.cuh"
 
 namespace tsb {
+namespace attn_prefill {
+int launch_with_lse(const void* Q, const void* K, const void* V, void* O, float* lse2, int B, int H,
+                    int Hkv, int Sq, int Sk, int Dh, float scale, int causal, cudaStream_t st);
+}
 namespace attn_bwd5 {
 
 constexpr int D = 128;
@@ -60,20 +66,6 @@ struct Params {
   int* err;
 };
 
-// Optional timeline of one dK/dV CTA (compile with -DTESSERA_BWD_TRACE): clock64 stamps of the hand-offs
-// between the softmax warps and the MMA warp, read back with tessera_sm100_bwd_trace_read. Not part
-// of the normal build.
-#ifdef TESSERA_BWD_TRACE
-__device__ long long g_bwd_trace[2 * 4096];
-#define BW_TRACE(role, idx)                                                              \
-  do {                                                                                   \
-    if (trace_on && (idx) < 4096) g_bwd_trace[(role) * 4096 + (idx)] = clock64();        \
-  } while (0)
-#else
-#define BW_TRACE(role, idx) \
-  do {                      \
-  } while (0)
-#endif
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -219,9 +211,6 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BLK, hk = blockIdx.y, b = blockIdx.z;
-#ifdef TESSERA_BWD_TRACE
-  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (warp == 0 || warp == 8);
-#endif
   const int ratio = p.Hq / p.Hkv;
   const int nqb = (p.Sq + BLK - 1) / BLK;
   const int i_start = p.causal ? max(0, n0 - p.shift) / BLK : 0;   // first block with a legal row
@@ -301,12 +290,9 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       for (int it = 0; it < iters && ok; ++it) {
         const int st = it & 1, nst = st ^ 1;
         const bool more = it + 1 < iters;
-        BW_TRACE(1, it * 8 + 0);
         if (!(ok = mbar_wait(p_full, it & 1, abort_flag, p.err, kErrWaitOther, 2000 + it))) break;
-        BW_TRACE(1, it * 8 + 1);
         tc_fence_after();
         issue_tmem_x_tile<true>(tdV, tS, gn_lo[st], desc_hi, idesc_ts, it > 0);       // dV += P^T dO
-        BW_TRACE(1, it * 8 + 2);
         if (more) {
           // the S^T buffer is free once dV's MMAs (issued just above, executed in order) have read P^T
           if (!(ok = mbar_wait(q_full(nst), ((it + 1) >> 1) & 1, abort_flag, p.err, kErrWaitFull, it + 1))) break;
@@ -314,20 +300,16 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
           issue_rows_x_rows(tS, k_lo, q_lo[nst], desc_hi, idesc_ss);            // S^T(t+1)
           umma_commit(s_full);
         }
-        BW_TRACE(1, it * 8 + 3);
         if (!(ok = mbar_wait(ds_full, it & 1, abort_flag, p.err, kErrWaitOther, 3000 + it))) break;
-        BW_TRACE(1, it * 8 + 4);
         tc_fence_after();
         issue_tmem_x_tile<true>(tdK, tdP, qn_lo[st], desc_hi, idesc_ts, it > 0);      // dK += dS^T Q
         umma_commit(q_empty(st));
-        BW_TRACE(1, it * 8 + 5);
         if (more) {
           issue_rows_x_rows(tdP, v_lo, g_lo[nst], desc_hi, idesc_ss);           // dP^T(t+1)
           umma_commit(dp_full);
         } else {
           umma_commit(o_full);
         }
-        BW_TRACE(1, it * 8 + 6);
       }
     }
   } else {
@@ -366,9 +348,7 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
       const uint64_t scale2 = pack2f(p.scale_log2, p.scale_log2);
       uint32_t pk[32];   // bf16 P^T of this key row and this group's columns, kept for the dS^T phase
       // ---- phase 1: P^T = exp2(scale * S^T - lse), written over S^T; dV's MMAs may start
-      BW_TRACE(0, it * 8 + 0);
       if (ok) ok = mbar_wait(s_full, it & 1, abort_flag, p.err, kErrWaitTmemFull, it);
-      BW_TRACE(0, it * 8 + 1);
       if (ok) {
         tc_fence_after();
 #pragma unroll
@@ -411,10 +391,8 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         __syncwarp();
         if (lane == 0) mbar_arrive(p_full);
       }
-      BW_TRACE(0, it * 8 + 2);
       // ---- phase 2: dS^T = P^T (dP^T - delta), written over dP^T; dK's MMAs may start
       if (ok) ok = mbar_wait(dp_full, it & 1, abort_flag, p.err, kErrWaitTmemFull, 500 + it);
-      BW_TRACE(0, it * 8 + 3);
       if (ok) {
         tc_fence_after();
         {
@@ -443,7 +421,6 @@ dkv5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUt
         __syncwarp();
         if (lane == 0) mbar_arrive(ds_full);
       }
-      BW_TRACE(0, it * 8 + 4);
     }
     // ---- epilogue: dV, scale * dK -> bf16 -> swizzled smem (the Q ring) -> TMA store
     if (iters > 0) {
@@ -726,6 +703,27 @@ dq5_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 }
 
 // dO, Q, dQ [B,Hq,Sq,128]; K, V, dK, dV [B,Hkv,Sk,128] bf16 dense; lse2, delta [B,Hq,Sq] fp32.
+// delta[row] = sum_d dO[row, d] O[row, d], one warp per row.
+__global__ void delta_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
+                             float* __restrict__ delta, long long rows) {
+  const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const uint2 a = *reinterpret_cast<const uint2*>(dO + row * D + lane * 4);
+  const uint2 b = *reinterpret_cast<const uint2*>(O + row * D + lane * 4);
+  const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+  const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const float2 x = __bfloat1622float2(pa[i]), y = __bfloat1622float2(pb[i]);
+    s += x.x * y.x + x.y * y.y;
+  }
+#pragma unroll
+  for (int sh = 16; sh; sh >>= 1) s += __shfl_xor_sync(0xffffffffu, s, sh);
+  if (lane == 0) delta[row] = s;
+}
+
 int launch(const void* dO, const void* Q, const void* K, const void* V, void* dQ, void* dK, void* dV,
            const float* lse2, const float* delta, int B, int Hq, int Hkv, int Sq, int Sk, float scale,
            int causal, cudaStream_t st) {
@@ -775,8 +773,84 @@ int launch(const void* dO, const void* Q, const void* K, const void* V, void* dQ
 }  // namespace attn_bwd5
 }  // namespace tsb
 
-#ifdef TESSERA_BWD_TRACE
-extern "C" int tessera_sm100_bwd_trace_read(long long* out, int n) {
-  return cudaMemcpyFromSymbol(out, tsb::attn_bwd5::g_bwd_trace, sizeof(long long) * n) == cudaSuccess ? 0 : 3;
+using namespace tsb;
+
+extern "C" {
+
+// Workspace of the tensor-core backward: O (bf16), log-sum-exp and delta (fp32) per query row.
+size_t tessera_sm100_flash_attn_bwd_bf16_workspace_bytes(int B, int Hq, int Sq) {
+  if (B <= 0 || Hq <= 0 || Sq <= 0) return 0;
+  const size_t rows = static_cast<size_t>(B) * Hq * Sq;
+  return ((rows * attn_bwd5::D * 2 + 255) & ~size_t(255)) + 2 * ((rows * 4 + 255) & ~size_t(255));
 }
-#endif
+
+// dO, Q, dQ [B,Hq,Sq,128]; K, V, dK, dV [B,Hkv,Sk,128], bf16, dense. causal uses the bottom-right
+// alignment of tessera.ops.flash_attn (identical to the lane's mask when Sq >= Sk).
+static int bwd_bf16_from_state(const void* dO, const void* Q, const void* K, const void* V, const void* O,
+                               const float* lse2, float* delta, void* dQ, void* dK, void* dV, int B, int Hq,
+                               int Hkv, int Sq, int Sk, float scale, int causal, cudaStream_t st);
+
+int tessera_sm100_flash_attn_bwd_bf16_device(const void* dO, const void* Q, const void* K, const void* V,
+                                             void* dQ, void* dK, void* dV, int B, int Hq, int Hkv, int Sq,
+                                             int Sk, float scale, int causal, void* workspace,
+                                             void* stream) {
+  if (!dO || !Q || !K || !V || !dQ || !dK || !dV || !workspace || B <= 0 || Hq <= 0 || Hkv <= 0 ||
+      Hq % Hkv || Sq <= 0 || Sk <= 0 || !(scale > 0.f)) {
+    set_last_error("flash_attn_bwd_bf16: null pointer, non-positive size or scale, or Hq not divisible by Hkv");
+    return kBadArg;
+  }
+  if (int rc = ensure_device()) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t rows = static_cast<size_t>(B) * Hq * Sq;
+  char* ws = static_cast<char*>(workspace);
+  void* O = ws;
+  float* lse2 = reinterpret_cast<float*>(ws + ((rows * attn_bwd5::D * 2 + 255) & ~size_t(255)));
+  float* delta = reinterpret_cast<float*>(reinterpret_cast<char*>(lse2) + ((rows * 4 + 255) & ~size_t(255)));
+  if (int rc = attn_prefill::launch_with_lse(Q, K, V, O, lse2, B, Hq, Hkv, Sq, Sk, attn_bwd5::D, scale,
+                                             causal, st))
+    return rc;
+  return bwd_bf16_from_state(dO, Q, K, V, O, lse2, delta, dQ, dK, dV, B, Hq, Hkv, Sq, Sk, scale, causal, st);
+}
+
+// The backward of a training step that kept the forward's output and row log-sum-exps
+// (tessera_sm100_flash_attn_fwd_lse_device): no forward recompute. delta_scratch: B*Hq*Sq floats.
+int tessera_sm100_flash_attn_bwd_bf16_saved_device(const void* dO, const void* Q, const void* K,
+                                                   const void* V, const void* O, const float* lse2,
+                                                   void* dQ, void* dK, void* dV, int B, int Hq, int Hkv,
+                                                   int Sq, int Sk, float scale, int causal,
+                                                   float* delta_scratch, void* stream) {
+  if (!dO || !Q || !K || !V || !O || !lse2 || !dQ || !dK || !dV || !delta_scratch || B <= 0 || Hq <= 0 ||
+      Hkv <= 0 || Hq % Hkv || Sq <= 0 || Sk <= 0 || !(scale > 0.f)) {
+    set_last_error("flash_attn_bwd_bf16_saved: null pointer, non-positive size or scale, or Hq not divisible by Hkv");
+    return kBadArg;
+  }
+  if (int rc = ensure_device()) return rc;
+  return bwd_bf16_from_state(dO, Q, K, V, O, lse2, delta_scratch, dQ, dK, dV, B, Hq, Hkv, Sq, Sk, scale, causal,
+                             static_cast<cudaStream_t>(stream));
+}
+
+static int bwd_bf16_from_state(const void* dO, const void* Q, const void* K, const void* V, const void* O,
+                               const float* lse2, float* delta, void* dQ, void* dK, void* dV, int B, int Hq,
+                               int Hkv, int Sq, int Sk, float scale, int causal, cudaStream_t st) {
+  const size_t rows = static_cast<size_t>(B) * Hq * Sq;
+  attn_bwd5::delta_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(dO), static_cast<const __nv_bfloat16*>(O), delta,
+      static_cast<long long>(rows));
+  TSB_CUDA_OK(cudaGetLastError());
+  note_launch();
+  return attn_bwd5::launch(dO, Q, K, V, dQ, dK, dV, lse2, delta, B, Hq, Hkv, Sq, Sk, scale, causal, st);
+}
+
+int tessera_sm100_flash_attn_fwd_lse_device(const void* Q, const void* K, const void* V, void* O,
+                                            float* lse2, int B, int Hq, int Hkv, int Sq, int Sk, int D,
+                                            float scale, int causal, void* stream) {
+  if (!lse2) {
+    set_last_error("flash_attn_fwd_lse: lse2 is null");
+    return kBadArg;
+  }
+  if (int rc = ensure_device()) return rc;
+  return attn_prefill::launch_with_lse(Q, K, V, O, lse2, B, Hq, Hkv, Sq, Sk, D, scale, causal,
+                                       static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

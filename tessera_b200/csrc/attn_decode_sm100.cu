@@ -1068,6 +1068,9 @@ int static_slots_for_current_device(StaticSlots* out) {
   std::lock_guard<std::mutex> lk(g_static_mu);
   StaticSlots& s = g_static_slots[dev];
   if (!s.partials) {
+    // First call on this device only: make sure a context exists (this is the one place where the
+    // entry point may touch the allocator; it does so with a null free), then resolve the symbols.
+    if (int rc = ensure_device()) return rc;
     float* pp = nullptr;
     int* pe = nullptr;
     cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&pp), g_static_partials);
@@ -1100,10 +1103,9 @@ int launch_static(const void* Q, const void* K, const void* V, void* O, int B, i
   }
   if ((reinterpret_cast<uintptr_t>(K) & 15) || (reinterpret_cast<uintptr_t>(V) & 15) ||
       (reinterpret_cast<uintptr_t>(Q) & 3)) {
-    set_last_error("attn_decode_static: K and V must be 16-byte aligned");
+    set_last_error("attn_decode_static: K and V must be 16-byte aligned and Q 4-byte aligned");
     return kBadArg;
   }
-  if (int rc = ensure_device()) return rc;
   StaticSlots slots;
   if (int rc = static_slots_for_current_device(&slots)) return rc;
   if (check_previous) {

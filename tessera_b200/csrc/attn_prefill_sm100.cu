@@ -52,20 +52,6 @@ struct Params {
   float* lse2;   // optional [B, H, Sq]: log2-sum-exp2 of scale_log2 * s per row (the backward's input)
 };
 
-// Optional timeline of one CTA (compile with -DTESSERA_PREFILL_TRACE): clock64 stamps of the
-// hand-offs between the softmax groups and the MMA warp, read back with
-// tessera_sm100_prefill_trace_read. Not part of the normal build.
-#ifdef TESSERA_PREFILL_TRACE
-__device__ long long g_trace[3 * 4096];
-#define PF_TRACE(role, idx)                                                        \
-  do {                                                                             \
-    if (trace_on && (idx) < 4096) g_trace[(role) * 4096 + (idx)] = clock64();      \
-  } while (0)
-#else
-#define PF_TRACE(role, idx) \
-  do {                      \
-  } while (0)
-#endif
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -176,9 +162,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     }
   }
   const int n_iter = max(nblk[0], nblk[1]);
-#ifdef TESSERA_PREFILL_TRACE
-  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0;
-#endif
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -290,13 +273,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         bool next_k_ready = false;
         for (int i = 0; i < 2 && ok; ++i) {
           if (j >= nblk[i]) continue;
-          PF_TRACE(2, (j * 2 + i) * 4 + 0);
           if (!(ok = mbar_wait(p_half(i), j & 1, abort_flag, p.err, kErrWaitOther, 6000 + j))) break;
-          PF_TRACE(2, (j * 2 + i) * 4 + 1);
           tc_fence_after();
           issue_pv(i, st, j > 0, 0);
           if (!(ok = mbar_wait(p_full(i), j & 1, abort_flag, p.err, kErrWaitOther, 4000 + j))) break;
-          PF_TRACE(2, (j * 2 + i) * 4 + 2);
           tc_fence_after();
           issue_pv(i, st, true, BKV / 32);
           if (j == nblk[i] - 1) umma_commit(o_full(i));
@@ -308,7 +288,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
             }
             issue_s(i, nst);
           }
-          PF_TRACE(2, (j * 2 + i) * 4 + 3);
         }
         if (!ok) break;
         umma_commit(v_empty(st));
@@ -327,9 +306,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
     float l = 0.f;
     bool ok = true;
     for (int j = 0; j < nblk[i] && ok; ++j) {
-      if ((warp & 3) == 0) PF_TRACE(i, j * 8 + 0);
       if (!(ok = mbar_wait(s_full(i), j & 1, abort_flag, p.err, kErrWaitTmemFull, j))) break;
-      if ((warp & 3) == 0) PF_TRACE(i, j * 8 + 1);
       tc_fence_after();
       const int kv0 = j * BKV;
       const bool need_mask = (kv0 + BKV - 1 > qi0 + shift && p.causal) || (kv0 + BKV > p.Sk);
@@ -342,7 +319,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       tmem_ld_32x32b_x32(t_s + 64, s2);
       tmem_ld_32x32b_x32(t_s + 96, s3);
       tmem_ld_wait();
-      if ((warp & 3) == 0) PF_TRACE(i, j * 8 + 2);
       if (need_mask) {
         constexpr uint32_t kNegInf = 0xff800000u;
 #pragma unroll
@@ -396,7 +372,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       // two-wide fp32 instructions; each batch of 32 columns is laid out as independent work
       // (16 packed FMAs, 32 exponentials, 16 packed adds, 16 packs) so that the single warp a tile
       // has on each scheduler can issue back to back.
-      if ((warp & 3) == 0) PF_TRACE(i, j * 8 + 3);
       const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
       const uint64_t negm2 = pack_f32x2(-m_used, -m_used);
       uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};
@@ -429,7 +404,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(p_half(i));
-          if ((warp & 3) == 0) PF_TRACE(i, j * 8 + 4);
         }
       }
       tmem_st_32x32b_x32(t_s + 32, pkb);
@@ -442,7 +416,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
       // One arrival per warp: 128 arrivals on a single shared-memory word would serialise.
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full(i));
-      if ((warp & 3) == 0) PF_TRACE(i, j * 8 + 5);
     }
     // ---- epilogue: O / l -> bf16 -> swizzled smem (the Q tile's buffer) -> TMA store
     if (ok && nblk[i] > 0) ok = mbar_wait(o_full(i), 0, abort_flag, p.err, kErrWaitTmemFull, 9000);
@@ -583,11 +556,6 @@ int launch_with_lse(const void* Q, const void* K, const void* V, void* O, float*
 
 using namespace tsb;
 
-#ifdef TESSERA_PREFILL_TRACE
-extern "C" int tessera_sm100_prefill_trace_read(long long* out, int n) {
-  return cudaMemcpyFromSymbol(out, tsb::attn_prefill::g_trace, sizeof(long long) * n) == cudaSuccess ? 0 : 3;
-}
-#endif
 
 extern "C" int tessera_sm100_flash_attn_fwd_strided_device(
     const void* Q, const void* K, const void* V, void* O, int B, int Hq, int Hkv, int Sq, int Sk,

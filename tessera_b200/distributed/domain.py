@@ -51,10 +51,6 @@ class Distribution:
     def make_shard_spec(self, domain: Domain) -> ShardSpec:
         raise NotImplementedError
 
-    def to_ir_attr(self) -> str:
-        raise NotImplementedError
-
-
 def _check_axes(mesh_axes, what: str) -> Tuple[str, ...]:
     if not mesh_axes:
         raise ValueError(f"{what} distribution requires at least one mesh axis")
@@ -75,9 +71,6 @@ class Block(Distribution):
                              f"{domain.rank}")
         return ShardSpec(partition=tuple(range(len(self.mesh_axes))), mesh_axes=self.mesh_axes)
 
-    def to_ir_attr(self) -> str:
-        return f'{{dist = "block", axes = {list(self.mesh_axes)}}}'
-
     def __repr__(self) -> str:
         return f"Block(mesh_axes={self.mesh_axes})"
 
@@ -94,9 +87,6 @@ class Cyclic(Distribution):
                              f"{domain.rank}")
         return ShardSpec.cyclic_shard(tuple(range(len(self.mesh_axes))), self.mesh_axes)
 
-    def to_ir_attr(self) -> str:
-        return f'{{dist = "cyclic", axes = {list(self.mesh_axes)}}}'
-
     def __repr__(self) -> str:
         return f"Cyclic(mesh_axes={self.mesh_axes})"
 
@@ -104,9 +94,6 @@ class Cyclic(Distribution):
 class Replicated(Distribution):
     def make_shard_spec(self, domain: Domain) -> ShardSpec:
         return ShardSpec.replicate()
-
-    def to_ir_attr(self) -> str:
-        return '{dist = "replicated"}'
 
     def __repr__(self) -> str:
         return "Replicated()"

@@ -307,6 +307,44 @@ def _failure(artifact: RuntimeArtifact, status: str, reason: str, meta: Mapping,
             "telemetry": {"event": "runtime.launch", "status": status, "arch": meta.get("target")}}
 
 
+def _launch_native_descriptor(artifact: "RuntimeArtifact", args: Any, stream: Any, t0: int, meta: Mapping) -> dict:
+    """The descriptor seam (python/tessera/runtime.py:30905-30990): the invocation is checked against
+    the descriptor and the image BEFORE the registered ``submit`` hook sees it, so a hook only ever
+    receives buffers whose names, dtypes, ranks, layouts, alignments and guarded extents match."""
+    from .native_artifact import ArtifactContractError, BufferArgument, LaunchDescriptor, NativeImageArtifact
+    image, descriptor = artifact.native_image, artifact.launch_descriptor
+    path = str(meta.get("compiler_path", "canonical_native_descriptor"))
+    base = {"compiler_path": path, "artifact_hash": artifact.artifact_hash}
+    try:
+        if not isinstance(image, NativeImageArtifact) or not isinstance(descriptor, LaunchDescriptor):
+            raise ArtifactContractError("E_LAUNCH_DESCRIPTOR_SCHEMA",
+                                        "native_image / launch_descriptor must be NativeImageArtifact / LaunchDescriptor")
+        values = dict(args) if isinstance(args, Mapping) else _bind_launch_args(args, descriptor.argument_names())
+        buffer_names = {b.name for b in descriptor.buffers}
+        buffers = {k: v for k, v in values.items() if k in buffer_names or hasattr(v, "shape") and getattr(v, "ndim", 0) > 0}
+        scalars = {k: v for k, v in values.items() if k not in buffers}
+        descriptor.validate_invocation(image, {k: BufferArgument.of(v) for k, v in buffers.items()}, scalars)
+    except ArtifactContractError as exc:
+        return {"ok": False, "runtime_status": "invalid_artifact", "execution_kind": "artifact_only",
+                "diagnostic_code": exc.code, "reason": str(exc), **base}
+    except Exception as exc:
+        return {"ok": False, "runtime_status": "invalid_artifact", "execution_kind": "artifact_only",
+                "reason": str(exc), **base}
+    base.update(image_digest=image.image_digest, launch_descriptor_digest=descriptor.descriptor_digest)
+    reg = _native_launchers.get(image.target)
+    if reg is None or image.binary_format not in reg.binary_formats:
+        return {"ok": False, "runtime_status": "unimplemented", "execution_kind": "artifact_only",
+                "reason": f"no launcher registered for {image.target} accepts {image.binary_format!r}", **base}
+    try:
+        output = reg.submit(image, descriptor, buffers, scalars, stream)
+    except Exception as exc:  # the submit hook raised
+        return {"ok": False, "runtime_status": "device_error", "execution_kind": "native", "reason": str(exc), **base}
+    ms = (time.perf_counter_ns() - t0) / 1e6
+    return {"ok": True, "runtime_status": "success", "execution_kind": "native_gpu", "execution_mode": "descriptor",
+            "output": output, "telemetry": {"event": "runtime.launch", "status": "ok"},
+            "profile": {"launch_overhead_ms": ms, "kernel_elapsed_ms": ms, "cpu_wall_ms": None}, **base}
+
+
 def launch(kernel: Any, args: Any, stream: Any = None) -> dict:
     """Run an executable artifact on the B200 backend, or return a structured non-success result."""
     global _last_profile
@@ -315,23 +353,7 @@ def launch(kernel: Any, args: Any, stream: Any = None) -> dict:
     meta = artifact.metadata or {}
     target = normalize_target(meta.get("target", "cpu"))
     if artifact.launch_descriptor is not None:
-        reg = _native_launchers.get(target)
-        if reg is None:
-            return _failure(artifact, "missing_backend", f"no native launcher registered for {target}",
-                            meta, gate="runtime_abi")
-        try:
-            values = dict(args) if isinstance(args, Mapping) else _bind_launch_args(
-                args, list(meta.get("arg_names") or []))
-            buffers = {k: v for k, v in values.items() if hasattr(v, "shape")}
-            scalars = {k: v for k, v in values.items() if not hasattr(v, "shape")}
-            output = reg.submit(artifact.native_image, artifact.launch_descriptor, buffers, scalars, stream)
-        except Exception as exc:  # the submit hook raised
-            return _failure(artifact, "device_error", str(exc), meta)
-        return {"ok": True, "runtime_status": "success", "execution_kind": "native_gpu",
-                "compiler_path": str(meta.get("compiler_path", "native_descriptor")),
-                "execution_mode": "native_descriptor", "artifact_hash": artifact.artifact_hash,
-                "output": output, "telemetry": {"event": "runtime.launch", "status": "ok"},
-                "profile": {"cpu_wall_ms": (time.perf_counter_ns() - t0) / 1e6}}
+        return _launch_native_descriptor(artifact, args, stream, t0, meta)
     if target != TARGET:
         cap = backend_capabilities(target)
         status = "unimplemented" if cap.available else "missing_backend"

@@ -201,28 +201,3 @@ def test_backward_from_saved_forward_state_is_bit_identical():
     no_device_error()
 
 
-def test_mma_sync_kernels_stay_correct():
-    """The earlier mma.sync kernels are selected by an environment variable read once per process."""
-    import subprocess
-    import sys
-    code = (
-        "import numpy as np\n"
-        "import tessera_b200 as tessera\n"
-        "from tessera_b200.device import bfloat16\n"
-        "from oracle import tessera_oracle as orc\n"
-        "rng = np.random.default_rng(5)\n"
-        "q = rng.standard_normal((1, 4, 150, 128), dtype=np.float32).astype(bfloat16)\n"
-        "k = rng.standard_normal((1, 2, 220, 128), dtype=np.float32).astype(bfloat16)\n"
-        "v = rng.standard_normal((1, 2, 220, 128), dtype=np.float32).astype(bfloat16)\n"
-        "g = rng.standard_normal((1, 4, 150, 128), dtype=np.float32).astype(bfloat16)\n"
-        "s = 128 ** -0.5\n"
-        "got = tessera.ops.flash_attn_backward(g, q, k, v, scale=s, causal=True, causal_alignment='bottom_right')\n"
-        "ref = orc.attention_lane_backward(g, q, k, v, scale=s, causal=True, causal_shift=70)\n"
-        "err = max(orc.max_rel_err(a.astype(np.float32), e) for a, e in zip(got, ref))\n"
-        "assert err < 2e-2, err\n"
-        "print('ok', err)\n")
-    env = dict(os.environ, TESSERA_SM100_ATTN_BWD="mma")
-    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
-    res = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=300)
-    assert res.returncode == 0 and "ok" in res.stdout, res.stdout + res.stderr

@@ -120,6 +120,40 @@ def test_append_then_decode():
             cache.append(kn, vn)
 
 
+def test_refused_append_changes_nothing():
+    """Three sequences need a new page and two pages are free: the append is refused BEFORE any
+    bookkeeping changes, so the host table, the free list and the device table still agree, and
+    after a page is released the same append works and decodes correctly."""
+    rng = np.random.default_rng(23)
+    B, Hq, Hkv, L = 3, 4, 4, 8
+    S0 = np.array([8, 8, 8])                      # every sequence sits exactly on a page edge
+    K = _bf(rng.standard_normal((B, 16, Hkv, 128)))
+    V = _bf(rng.standard_normal((B, 16, Hkv, 128)))
+    cache = pk.PagedKVCache.from_dense(K, V, page_size=L, seq_lens=S0, num_pages=5, max_pages_per_seq=2)
+    assert len(cache._free) == 2
+    table0, owned0, free0 = cache._table.copy(), cache._owned.copy(), list(cache._free)
+    kn = np.stack([K[b, S0[b]] for b in range(B)])
+    vn = np.stack([V[b, S0[b]] for b in range(B)])
+    with pytest.raises(ValueError, match="no free pages"):
+        cache.append(kn, vn)
+    np.testing.assert_array_equal(cache._table, table0)
+    np.testing.assert_array_equal(cache._owned, owned0)
+    assert list(cache._free) == free0
+    np.testing.assert_array_equal(cache.page_table.download(), table0)
+    np.testing.assert_array_equal(cache.seq_lens.download(), S0)
+    cache.release(2)                              # sequence 2 gives its page back: three free pages
+    assert len(cache._free) == 3
+    cache.append(kn, vn)                          # 0 and 1 grow onto new pages, 2 restarts with one token
+    np.testing.assert_array_equal(cache.seq_lens.download(), [9, 9, 1])
+    Q = _bf(rng.standard_normal((B, Hq, 128)))
+    got = pk.paged_decode(Q, cache)
+    for b, n in ((0, 9), (1, 9)):
+        ref = orc.flash_attn(Q[b][None, :, None, :], K[b, :n].transpose(1, 0, 2)[None],
+                             V[b, :n].transpose(1, 0, 2)[None])[0, :, 0]
+        assert rel_err(got[b], ref) < TOL
+    no_device_error()
+
+
 def test_device_resident_decode_matches_dense_kernel():
     """Same tokens through the paged kernel and the dense decode kernel: identical arithmetic
     order per tile, so the outputs agree bit for bit when the page size covers whole tiles."""

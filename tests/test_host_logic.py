@@ -115,11 +115,25 @@ def test_launch_reports_structured_failures_and_never_raises():
     assert rt.launch(not_exec, ())["ok"] is False
 
 
+def _image_and_descriptor():
+    from tessera_b200 import native_artifact as na
+    abi = "tessera.nvidia.matmul.a_b_d_m_n_k.bf16.v1"
+    image = na.NativeImageArtifact(target="blackwell", architecture="sm_100a", binary_format="cubin",
+                                   payload=b"\x7fELF-stand-in", entry_points=(na.NativeEntryPoint("gemm_entry", abi),))
+    desc = na.LaunchDescriptor(
+        image_digest=image.image_digest, entry_symbol="gemm_entry", abi_id=abi,
+        buffers=(na.BufferBinding(0, "a", "input", "fp32", 2, "row_major", 16),
+                 na.BufferBinding(1, "d", "output", "fp32", 2, "row_major", 16)),
+        scalars=(na.ScalarArgument(2, "n", "int32"),),
+        shape_guards=(na.ShapeGuard("a", 1, "multiple_of", 8),))
+    return image, desc
+
+
 def test_native_launcher_registry():
     seen = {}
 
     def submit(image, descriptor, buffers, scalars, stream):
-        seen.update(buffers=set(buffers), scalars=dict(scalars))
+        seen.update(buffers=set(buffers), scalars=dict(scalars), symbol=descriptor.entry_symbol)
         return "ran"
 
     rt.register_native_launcher("blackwell", binary_formats=("cubin",), submit=submit, replace=True)
@@ -127,12 +141,68 @@ def test_native_launcher_registry():
         rt.register_native_launcher("sm_100a", binary_formats=("cubin",), submit=submit)
     with pytest.raises(ValueError):
         rt.register_native_launcher("sm_100a", binary_formats=(), submit=submit, replace=True)
-    art = rt.RuntimeArtifact(metadata={"target": "nvidia_sm100", "arg_names": ["x", "n"]},
-                             native_image=object(), launch_descriptor=object())
-    res = rt.launch(art, (np.zeros(3), 5))
-    assert res["ok"] and res["output"] == "ran" and seen["buffers"] == {"x"} and seen["scalars"] == {"n": 5}
+    image, desc = _image_and_descriptor()
+    assert image.target == "nvidia_sm100" and desc.argument_names() == ["a", "d", "n"]
+    art = rt.RuntimeArtifact(metadata={"target": "nvidia_sm100"}, native_image=image, launch_descriptor=desc)
+    a, d = np.zeros((4, 16), np.float32), np.zeros((4, 4), np.float32)
+    res = rt.launch(art, (a, d, 5))
+    assert res["ok"] and res["output"] == "ran" and res["execution_mode"] == "descriptor", res
+    assert seen == {"buffers": {"a", "d"}, "scalars": {"n": 5}, "symbol": "gemm_entry"}
+    assert res["image_digest"] == image.image_digest and res["launch_descriptor_digest"] == desc.descriptor_digest
+    assert rt.launch(art, {"a": a, "d": d, "n": 7})["ok"]
+    # objects that are not descriptor types never reach the hook
+    bad = rt.RuntimeArtifact(metadata={"target": "nvidia_sm100"}, native_image=object(), launch_descriptor=object())
+    assert rt.launch(bad, (a, d, 5))["runtime_status"] == "invalid_artifact"
     rt.unregister_native_launcher("nvidia_sm100")
-    assert rt.launch(art, (np.zeros(3), 5))["runtime_status"] == "missing_backend"
+    assert rt.launch(art, (a, d, 5))["runtime_status"] == "unimplemented"
+
+
+def test_descriptor_invocation_is_validated_before_submission():
+    """LaunchDescriptor.validate_invocation (python/tessera/compiler/native_artifact.py:997-1051):
+    every mismatch is an invalid_artifact result with the reference's diagnostic code, and the
+    submit hook is not called."""
+    from tessera_b200 import native_artifact as na
+    calls = []
+    rt.register_native_launcher("nvidia_sm100", binary_formats=("cubin",),
+                                submit=lambda *a: calls.append(a) or "ran", replace=True)
+    image, desc = _image_and_descriptor()
+    art = rt.RuntimeArtifact(metadata={"target": "nvidia_sm100"}, native_image=image, launch_descriptor=desc)
+    a, d = np.zeros((4, 16), np.float32), np.zeros((4, 4), np.float32)
+
+    def code(args):
+        res = rt.launch(art, args)
+        assert res["ok"] is False and res["runtime_status"] == "invalid_artifact", res
+        return res.get("diagnostic_code")
+
+    assert code({"a": a, "n": 5}) == "E_LAUNCH_BINDING_MISMATCH"                       # a buffer is missing
+    assert code({"a": a, "d": d, "n": 5, "extra": 1}) == "E_LAUNCH_BINDING_MISMATCH"   # an unknown scalar
+    assert code((a.astype(np.float16), d, 5)) == "E_LAUNCH_BINDING_MISMATCH"           # dtype
+    assert code((a[0], d, 5)) == "E_LAUNCH_BINDING_MISMATCH"                           # rank
+    assert code((np.zeros((4, 12), np.float32), d, 5)) == "E_LAUNCH_BINDING_MISMATCH"  # shape guard: 12 % 8
+    assert code((a, d, 2.5)) == "E_LAUNCH_BINDING_MISMATCH"                            # int scalar given a float
+    misaligned = np.zeros(4 * 16 + 1, np.float32)[1:].reshape(4, 16)                   # 4-byte aligned only
+    assert code((misaligned, d, 5)) == "E_LAUNCH_BINDING_MISMATCH"
+    other = na.NativeImageArtifact(target="sm100", architecture="sm_100a", binary_format="cubin", payload=b"other",
+                                   entry_points=image.entry_points)
+    stale = rt.RuntimeArtifact(metadata={"target": "nvidia_sm100"}, native_image=other, launch_descriptor=desc)
+    res = rt.launch(stale, (a, d, 5))
+    assert res["diagnostic_code"] == "E_LAUNCH_STALE_IMAGE"
+    assert calls == []
+    assert rt.launch(art, (a, d, 5))["ok"] and len(calls) == 1
+    # schema errors are raised where the descriptor is built
+    with pytest.raises(na.ArtifactContractError) as info:
+        na.BufferBinding(0, "a", "sideways", "fp32", 2, "row_major")
+    assert info.value.code == "E_LAUNCH_DESCRIPTOR_SCHEMA"
+    with pytest.raises(na.ArtifactContractError):
+        na.BufferBinding(0, "a", "input", "fp32", 2, "row_major", alignment=24)
+    with pytest.raises(na.ArtifactContractError):
+        na.LaunchDescriptor(image.image_digest, "gemm_entry", desc.abi_id,
+                            buffers=(na.BufferBinding(0, "a", "input", "fp32", 2, "row_major"),
+                                     na.BufferBinding(0, "d", "output", "fp32", 2, "row_major")))
+    with pytest.raises(na.ArtifactContractError):
+        na.NativeImageArtifact(target="sm100", architecture="sm_100a", binary_format="tarball", payload=b"x",
+                               entry_points=image.entry_points)
+    rt.unregister_native_launcher("nvidia_sm100")
 
 
 def test_jit_rejects_targets_it_does_not_serve_and_scans_ops():

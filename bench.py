@@ -294,6 +294,11 @@ def bench_gemm(ranks, args, peaks, peak_kind, sampler):
     # kernel-only time for the roofline entry: at one GPU the step is the kernel; with several,
     # the GEMM without the exchange, timed the same way (before the clock probe heats the GPU)
     kernel_times = times if W == 1 else timed_steps(ranks, device, gemm_only, args.steps, args.warmup)
+    # the exchange on its own (every rank storing its column block into the peers' Y, all at once):
+    # the measured floor of the fused step on this machine
+    exchange_ms = None
+    if fused is not None:
+        exchange_ms = statistics.mean(timed_steps(ranks, device, fused.exchange_only, args.steps, args.warmup))
     probe_marks = clock_probe(device, sampler, step)
     flops = 2.0 * n * n * n
     ms = statistics.mean(times)
@@ -353,17 +358,23 @@ def bench_gemm(ranks, args, peaks, peak_kind, sampler):
                        if (n // 256) * (-(-nb // 256)) >= 74 else
                        "gemm_kernel<bf16,plain> (tcgen05 128x256x64, 4-stage TMA)")}
     if W > 1:
-        # Every rank has to take in the other ranks' column blocks of Y over its NVLink ingress.
+        # Every rank has to take in the other ranks' column blocks of Y over its NVLink ingress. The
+        # floor is the exchange timed on its own just above (all ranks storing at once); the constant is
+        # the two-GPU figure of profiles/peer_store_bandwidth_2gpu.md, kept beside it for comparison.
         ingress = (W - 1) / W * n * n * 2
-        floor_ms = ingress / (PEER_STORE_GBS * 1e9) * 1e3
-        roof["exchange"] = {"ingress_bytes_per_rank": ingress, "peer_store_gbs": PEER_STORE_GBS,
+        floor_ms = exchange_ms if exchange_ms else ingress / (PEER_STORE_GBS * 1e9) * 1e3
+        roof["exchange"] = {"ingress_bytes_per_rank": ingress,
+                            "exchange_only_ms": exchange_ms,
+                            "peer_store_gbs_measured": (ingress / exchange_ms / 1e6) if exchange_ms else None,
+                            "peer_store_gbs_two_gpu_probe": PEER_STORE_GBS,
                             "exchange_floor_ms": floor_ms, "compute_ms": k_ms,
                             "floor_ms": max(floor_ms, k_ms), "step_ms": ms,
                             "efficiency_vs_floor": max(floor_ms, k_ms) / ms,
                             "fused_kernel": "gemm_ag_kernel<bf16> (cta_group::2 256x256x64, K split over neighbouring "
-                                            "CTA pairs, TMA stores into every rank's Y)" if tp_mode == "fused" else None,
-                            "note": "peer_store_gbs: SM-issued peer stores measured on this pool (both GPUs of a pair "
-                                    "writing at once; a contiguous copy-engine transfer reaches 727)"}
+                                            "CTA pairs below four waves of tiles, TMA stores into every rank's Y)"
+                                            if tp_mode == "fused" else None,
+                            "note": "floor = max(the exchange alone, the GEMM alone); a perfectly overlapped step would "
+                                    "take that long"}
     return {
         "value": flops / ms / 1e9, "ms_per_step": ms, "gpu_launches": int(launches * W),
         "roofline": roof,
@@ -928,6 +939,25 @@ def profile_case(name: str) -> None:
         ws = DeviceArray((_lib.load().tessera_sm100_moe_workspace_bytes(T, H, F, E, k),), np.uint8)
         fn = lambda: _lib.call("tessera_sm100_moe_layer_device", x.ptr, logits.ptr, wg.ptr, wu.ptr, wd.ptr,
                                out.ptr, T, H, F, E, k, 1, -1, _lib.BF16, _lib.BF16, ws.ptr, None)
+    elif name == "gemm_allgather":
+        # the per-rank shape of the 4-GPU column-parallel GEMM with all four copies of Y on this GPU
+        n, world = 8192, 4
+        a, b = dev_normal((n, n), 1 / np.sqrt(n)), dev_normal((n, n), 1 / np.sqrt(n))
+        ys = [DeviceArray.zeros((n, n), bfloat16) for _ in range(world)]
+        ptrs = (ctypes.c_void_p * world)(*[y.ptr for y in ys])
+        fn = lambda: _lib.call("tessera_sm100_gemm_allgather_device", a.ptr, b.ptr, ptrs, world, 1, n, n, n,
+                               _lib.BF16, _lib.BF16, None)
+    elif name == "mma_rate":
+        # issue rate of tcgen05.mma on resident operands (no kernel of the hot path; prints a table)
+        print("tcgen05.mma kind::f16 bf16, K 16, M 128 per CTA, 4000 MMAs per issuing CTA, all SMs at once")
+        for pair, N, mn in ((0, 256, 1), (0, 128, 1), (0, 64, 1), (1, 256, 1), (1, 128, 1), (0, 256, 0), (0, 128, 0),
+                            (1, 256, 0), (1, 128, 0)):
+            cyc = ctypes.c_double(0)
+            _lib.call("tessera_sm100_probe_mma_rate", pair, N, mn, 1000, ctypes.byref(cyc))
+            print(f"  {'cta_group::2 M256' if pair else 'cta_group::1 M128'} N{N:3d} B {'MN' if mn else 'K '}-major: "
+                  f"{cyc.value:6.1f} cycles per MMA (arithmetic at 4096 FMA/clk/SM: {128 * N * 16 / 4096:5.1f})")
+        device.check_device_error("mma_rate")
+        return
     else:
         raise SystemExit(f"unknown profile case {name}")
     for _ in range(3):

@@ -109,6 +109,17 @@ int tessera_sm100_gemm_strided_device(const void* A, const void* B, void* D, int
                                       int N, int K, long long lda, long long ldb, long long ldd,
                                       long long strideA, long long strideB, long long strideD,
                                       int in_dtype, int out_dtype, void* stream);
+/* The exchange of the column-parallel GEMM on its own: this rank's column block of its copy of the
+ * row-major matrix [rows, N_total] is stored into every other rank's copy with 16-byte SM stores
+ * (copies[i]: base of rank i's copy, a peer pointer for i != rank). What bench.py times, all ranks
+ * at once, to get the exchange floor of the fused kernel on the machine it runs on. */
+int tessera_sm100_allgather_columns_device(void* const* copies, int world, int rank, int rows,
+                                           long long n_total, int elem_bytes, void* stream);
+/* SM cycles per tcgen05.mma (K 16, M 128 per CTA) issued back to back on resident shared-memory
+ * operands, the maximum over the issuing CTAs of one full-GPU launch: the arithmetic rate the GEMM
+ * and attention main loops are measured against. pair != 0: cta_group::2 on clusters of two (M 256).
+ * N: 64, 128 or 256 (128 or 256 for pairs). b_mn_major: layout of the B operand. Synchronous. */
+int tessera_sm100_probe_mma_rate(int pair, int N, int b_mn_major, int reps, double* cycles_per_mma);
 /* D[M,N] = act(A*B + bias[col] + residual[row,col]) with the bias / residual / activation applied in
  * the kernel epilogue: tessera.ops.gemm(A, B, epilogue={...}) -> fused_epilogue
  * (python/tessera/__init__.py:239-248, 2658-2675; the reference's GPU lane for it is the emitted

@@ -81,6 +81,8 @@ _SIGNATURES = {
                                                    _VP, c_int, _VP]),
     "tessera_sm100_gemm_allgather_device": (c_int, [_VP, _VP, POINTER(_VP), c_int, c_int, c_int, c_int,
                                                     c_int, c_int, c_int, _VP]),
+    "tessera_sm100_allgather_columns_device": (c_int, [POINTER(_VP), c_int, c_int, c_int, c_longlong, c_int, _VP]),
+    "tessera_sm100_probe_mma_rate": (c_int, [c_int, c_int, c_int, c_int, POINTER(ctypes.c_double)]),
     "tessera_sm100_gemm_allgather_block_device": (c_int, [_VP, _VP, c_longlong, POINTER(_VP), c_int, c_int, c_int,
                                                           c_int, c_int, c_int, c_int, _VP]),
     "tessera_sm100_grouped_gemm_device": (c_int, [_VP, _VP, _VP, _VP, c_int, c_int, c_int, c_int,

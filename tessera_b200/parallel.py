@@ -73,6 +73,14 @@ class TensorParallelGemm:
         _lib.call("tessera_sm100_gemm_allgather_device", A.ptr, W_full.ptr, self._ptrs, self.world,
                   self.rank, self.M, self.N, self.K, self._in, self._out, device._stream_handle(stream))
 
+    def exchange_only(self, stream=None) -> None:
+        """The all-gather without the GEMM: this rank's column block of ``self.Y`` stored into every other
+        rank's Y by a plain copy kernel. Timed on all ranks at once it gives the exchange floor of the
+        fused kernel on the machine at hand."""
+        from . import _lib, device
+        _lib.call("tessera_sm100_allgather_columns_device", self._ptrs, self.world, self.rank, self.M, self.N,
+                  self.out_dtype.itemsize, device._stream_handle(stream))
+
     def run_host(self, A_rows: np.ndarray, W_block: np.ndarray, Y_block: np.ndarray, comm, stream=None) -> None:
         """``A_rows``: rows [rank*M/world, (rank+1)*M/world) of A, ``W_block``: this rank's (K, N/world)
         columns of W, ``Y_block``: (M, N/world) host array that receives this rank's columns of Y

@@ -22,7 +22,6 @@
 
 #include <algorithm>
 #include <cmath>
-#include <type_traits>
 
 #include "../../include/tessera_sm100.h"
 #include "device_ctx.h"
@@ -105,25 +104,6 @@ __device__ __forceinline__ uint32_t cvt_bf16x2_v(float hi, float lo) {
   uint32_t d;
   asm volatile("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
   return d;
-}
-// exp2 of two values on the FMA pipe instead of the special-function unit: n = round(x) by the
-// 1.5 * 2^23 trick, a cubic in f = x - n on [-0.5, 0.5] (relative error 7.5e-5, a thirtieth of the bf16
-// rounding that follows), n added into the exponent field. x is clamped at -125.
-#ifndef TESSERA_PREFILL_POLY_EVERY
-#define TESSERA_PREFILL_POLY_EVERY 0   // 0: every exponential on the special-function unit; k: every k-th pair here
-#endif
-__device__ __forceinline__ void ex2_poly2(uint64_t x2, float& y0, float& y1) {
-  const uint64_t one2 = pack_f32x2(1.f, 1.f), mone2 = pack_f32x2(-1.f, -1.f);
-  const uint64_t magic2 = pack_f32x2(12582912.f, 12582912.f), nmagic2 = pack_f32x2(-12582912.f, -12582912.f);
-  const uint64_t xx = pack_f32x2(fmaxf(lo_f32(x2), -125.f), fmaxf(hi_f32(x2), -125.f));
-  const uint64_t t = ffma2(xx, one2, magic2);  // low mantissa bits = n
-  const uint64_t n = ffma2(t, one2, nmagic2);
-  const uint64_t f = ffma2(n, mone2, xx);
-  uint64_t q = ffma2(pack_f32x2(0.0551716648f, 0.0551716648f), f, pack_f32x2(0.2426111251f, 0.2426111251f));
-  q = ffma2(q, f, pack_f32x2(0.6932609677f, 0.6932609677f));
-  q = ffma2(q, f, pack_f32x2(0.9999280572f, 0.9999280572f));
-  y0 = __uint_as_float(__float_as_uint(lo_f32(t)) * 0x800000u + __float_as_uint(lo_f32(q)));
-  y1 = __uint_as_float(__float_as_uint(hi_f32(t)) * 0x800000u + __float_as_uint(hi_f32(q)));
 }
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
@@ -404,44 +384,28 @@ prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ 
         return k < 32 ? s0[k & 31] : k < 64 ? s1[k & 31] : k < 96 ? s2[k & 31] : s3[k & 31];
       };
       constexpr int kAhead = 2, kLag = 3;
+      uint64_t xs[64];
+      float ev[128];
       uint32_t pka[32], pkb[32];
-      // kPoly: pair t goes to the FMA pipe when t % TESSERA_PREFILL_POLY_EVERY is its last residue
-      // (blocks that no mask touches only: a masked score is -inf and must give exactly 0).
-      auto exp_loop = [&](auto poly_tag) {
-        constexpr bool kPoly = decltype(poly_tag)::value;
-        uint64_t xs[64];
-        float ev[128];
 #pragma unroll
-        for (int t = -kAhead; t < 64 + kLag; ++t) {
-          const int ta = t + kAhead, tc = t - kLag;
-          constexpr int kEvery = TESSERA_PREFILL_POLY_EVERY;
-          const bool poly = kPoly && kEvery > 0 && t >= 0 && t < 64 && (t % (kEvery > 0 ? kEvery : 1)) == (kEvery > 0 ? kEvery : 1) - 1;
-          if (ta >= 0 && ta < 64) xs[ta] = ffma2_v(pack_u32x2(S(2 * ta), S(2 * ta + 1)), scale2, negm2);
-          if (t >= 0 && t < 64) {
-            if (poly)
-              ex2_poly2(xs[t], ev[2 * t], ev[2 * t + 1]);
-            else
-              ev[2 * t] = ex2_v(lo_f32(xs[t]));
-          }
-          if (tc >= 0 && tc < 64)
-            sum2[tc & 3] = fadd2_v(sum2[tc & 3], pack_f32x2(ev[2 * tc], ev[2 * tc + 1]));
-          if (t >= 0 && t < 64 && !poly) ev[2 * t + 1] = ex2_v(hi_f32(xs[t]));
-          if (tc >= 0 && tc < 32) pka[tc] = cvt_bf16x2_v(ev[2 * tc + 1], ev[2 * tc]);
-          if (tc >= 32 && tc < 64) pkb[tc - 32] = cvt_bf16x2_v(ev[2 * tc + 1], ev[2 * tc]);
-          if (tc == 31) tmem_st_32x32b_x32(t_s, pka);  // kv 0..63 of P
-          if (tc == 47) {
-            // the first half of P has landed: hand it to the MMA warp while the rest is computed
-            tmem_st_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(p_half(i));
-          }
+      for (int t = -kAhead; t < 64 + kLag; ++t) {
+        const int ta = t + kAhead, tc = t - kLag;
+        if (ta >= 0 && ta < 64) xs[ta] = ffma2_v(pack_u32x2(S(2 * ta), S(2 * ta + 1)), scale2, negm2);
+        if (t >= 0 && t < 64) ev[2 * t] = ex2_v(lo_f32(xs[t]));
+        if (tc >= 0 && tc < 64)
+          sum2[tc & 3] = fadd2_v(sum2[tc & 3], pack_f32x2(ev[2 * tc], ev[2 * tc + 1]));
+        if (t >= 0 && t < 64) ev[2 * t + 1] = ex2_v(hi_f32(xs[t]));
+        if (tc >= 0 && tc < 32) pka[tc] = cvt_bf16x2_v(ev[2 * tc + 1], ev[2 * tc]);
+        if (tc >= 32 && tc < 64) pkb[tc - 32] = cvt_bf16x2_v(ev[2 * tc + 1], ev[2 * tc]);
+        if (tc == 31) tmem_st_32x32b_x32(t_s, pka);  // kv 0..63 of P
+        if (tc == 47) {
+          // the first half of P has landed: hand it to the MMA warp while the rest is computed
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(p_half(i));
         }
-      };
-      if (TESSERA_PREFILL_POLY_EVERY > 0 && !need_mask)
-        exp_loop(std::true_type{});
-      else
-        exp_loop(std::false_type{});
+      }
       tmem_st_32x32b_x32(t_s + 32, pkb);
       {
         const uint64_t t2 = fadd2(fadd2(sum2[0], sum2[1]), fadd2(sum2[2], sum2[3]));

@@ -135,9 +135,10 @@ int tessera_sm100_gemm_epilogue_device(const void* A, const void* B, void* D, in
  * tile into all `world` copies of Y. Y_ptrs[i] is rank i's Y base (a CUDA-IPC-mapped peer pointer
  * for i != rank, see tessera_sm100_ipc_*). Each copy is complete once every rank's kernel has
  * finished, so ranks synchronise their streams and then meet at a host barrier. world <= 8.
- * From 16 k-blocks of 64 on, the K loop of every tile is split over two neighbouring CTA pairs
- * (fp32 partial sums through a workspace taken from the library's pool for the duration of the
- * launch), so the first stores leave after half a tile time. */
+ * With at most four ranks, fewer than four waves of tiles and at least 16 k-blocks of 64, the first
+ * wave of work units are half-K units shared by two neighbouring CTA pairs (fp32 partial sums through a workspace taken
+ * from the library's pool for the duration of the launch), so the first stores leave after half a
+ * tile time. */
 int tessera_sm100_gemm_allgather_device(const void* A, const void* B, void* const* Y_ptrs, int world,
                                         int rank, int M, int N_total, int K, int in_dtype,
                                         int out_dtype, void* stream);

@@ -8,16 +8,19 @@
 // and ran the same product in 155 us instead of 104 us).
 //
 // What is specific to the fused exchange:
-//   * Split K. With `ksplit` = 2 a work unit is one HALF of the K loop of a tile. Units 2t and 2t+1
-//     (the two halves of tile t) run at the same time on neighbouring clusters: one of them (the
-//     helper) writes its fp32 partial sums to a workspace and raises one flag per epilogue warp; the
-//     other (the finisher) adds them to its own accumulator, converts, and issues the stores to
-//     every copy; the two swap roles from one unit to the next. The first stores therefore leave
-//     after half a tile time instead of a whole one, the burst of the last wave is half as large,
-//     and twice as many units fit the SM count better (8192 x 2048 per rank: 6.9 waves of half
-//     units instead of 3.5 -> 4 waves of whole tiles).
-//     A finisher only ever waits for the unit with the same position in the neighbour's list, and
-//     helpers wait for nobody, so there is no cycle; the wait is bounded like every other wait.
+//   * Split K in the FIRST wave. With `ksplit` = 2 the first unit of every cluster is one half of
+//     the K loop of a tile: clusters 2t and 2t+1 work on tile t at the same time, the odd one (the
+//     helper) writes its fp32 partial sums to a workspace and raises one flag per epilogue warp, the
+//     even one (the finisher) adds them to its own accumulator, converts, and issues the stores to
+//     every copy. All later units are whole tiles. The first stores therefore leave after half a tile
+//     time instead of a whole one, and the NVLink exchange, which bounds the step from four ranks on,
+//     starts that much earlier. A finisher only waits for the unit its neighbour runs at the same
+//     time and helpers wait for nobody, so there is no cycle; the wait is bounded like every other.
+//     Measured on four GPUs (8192^3): 248 us against 273 us unsplit. The host only asks for the
+//     split with at most four copies: with eight, a CTA has more bytes to store per tile than the
+//     tile takes to compute, what counts is that all CTAs store evenly all the time, and every split
+//     form measured slower there (first wave 465 us, every tile with alternating roles 281 us, every
+//     tile with each cluster finishing half of the columns 296 us, unsplit 250 us).
 //   * The copies are issued in an order that starts at a different rank for every rank, CTA, warp and
 //     piece, so the ranks do not all write to the same peer at the same moment.
 // Barriers as in the general pair kernel: full[s] in the even CTA counts both CTAs' TMA bytes,
@@ -58,21 +61,30 @@ constexpr int FLAGS_PER_TILE = 8;
 
 struct Unit {
   int m0, n0;  // first row of the PAIR, first column
-  int tile;    // tile index (workspace slot)
-  int half;    // which part of the K loop (0 when K is not split)
-  int helper;  // 1: this cluster hands its partial sums to the neighbour; 0: it finishes the tile
+  int tile;    // tile index (workspace slot of a split tile)
+  int split;   // 1: this unit is half of the K loop of its tile
+  int half;    // which half (split units)
+  int helper;  // split units: 1 = hands its partial sums to the neighbour, 0 = finishes the tile
 };
 
 // Static unit list shared by both CTAs of a pair. Tiles are rastered in groups of GROUP_PAIRS row
-// blocks, rows fastest; the `ksplit` units of a tile are consecutive.
+// blocks, rows fastest. With ksplit = 2 (an even number of clusters C) the first unit of cluster c is
+// half (c & 1) of tile c / 2, and its later units are the whole tiles C / 2 + c, C / 2 + c + C, ...
 struct Walker {
-  int u, step;
+  int cluster, step;
   int iter = 0;
-  __device__ Walker(int first, int stride) : u(first), step(stride) {}
+  __device__ Walker(int first, int stride) : cluster(first), step(stride) {}
   __device__ bool next(const Params& p, Unit& out) {
     const int m_pairs = (p.m_tiles + 1) / 2;
     const int tiles = m_pairs * p.n_tiles;
-    const int t = (p.ksplit == 2) ? (u >> 1) : u;
+    int t;
+    if (p.ksplit == 2) {
+      out.split = (iter == 0);
+      t = (iter == 0) ? (cluster >> 1) : (step >> 1) + cluster + (iter - 1) * step;
+    } else {
+      out.split = 0;
+      t = cluster + iter * step;
+    }
     if (t >= tiles) return false;
     const int gspan = GROUP_PAIRS * p.n_tiles;
     const int g = t / gspan;
@@ -82,11 +94,8 @@ struct Walker {
     out.m0 = (first_m + rr % gsz) * 2 * BM;
     out.n0 = (rr / gsz) * BN;
     out.tile = t;
-    out.half = (p.ksplit == 2) ? (u & 1) : 0;
-    // The two clusters of a tile swap roles from one unit to the next, so that both carry the
-    // same share of the conversion and of the stores.
-    out.helper = (p.ksplit == 2) ? ((u + iter) & 1) : 0;
-    u += step;
+    out.half = out.split ? (cluster & 1) : 0;
+    out.helper = out.half;
     ++iter;
     return true;
   }
@@ -136,7 +145,7 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int cluster_id = blockIdx.x >> 1;
   const int num_clusters = gridDim.x >> 1;
   const int num_kb = (p.K + BK - 1) / BK;
-  const int kb_mid = (p.ksplit == 2) ? num_kb / 2 : num_kb;  // half 0: [0, kb_mid), half 1: the rest
+  const int kb_mid = num_kb / 2;  // split units: half 0 is [0, kb_mid), half 1 the rest
   constexpr int kChunk = (sizeof(OutT) == 4) ? 32 : 64;      // output columns per stored piece
 
   if (threadIdx.x == 0) {
@@ -178,8 +187,8 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       while (ok && walk.next(p, unit)) {
         const int my_m0 = unit.m0 + static_cast<int>(rank) * BM;
         const int my_n0 = unit.n0 + static_cast<int>(rank) * (BN / 2);
-        const int kb0 = unit.half ? kb_mid : 0;
-        const int kb1 = unit.half ? num_kb : kb_mid;
+        const int kb0 = (unit.split && unit.half) ? kb_mid : 0;
+        const int kb1 = (unit.split && !unit.half) ? kb_mid : num_kb;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.err, kErrWaitEmpty, kb)) {
             ok = false;
@@ -219,8 +228,8 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-        const int kb0 = unit.half ? kb_mid : 0;
-        const int kb1 = unit.half ? num_kb : kb_mid;
+        const int kb0 = (unit.split && unit.half) ? kb_mid : 0;
+        const int kb1 = (unit.split && !unit.half) ? kb_mid : num_kb;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, abort_flag, p.err, kErrWaitFull, kb)) {
             ok = false;
@@ -267,7 +276,7 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t t_acc = tmem_base + static_cast<uint32_t>(acc * BN) + lane_base;
       const int slot = unit.tile * FLAGS_PER_TILE + static_cast<int>(rank) * 4 + warp;
       float* part = p.partial + static_cast<size_t>(slot) * PARTIAL_FLOATS_PER_WARP + lane * 4;
-      if (unit.helper) {
+      if (unit.split && unit.helper) {
         // Helper: this warp's 32 x 256 fp32 partial sums go to the workspace (each store instruction
         // writes 512 contiguous bytes), then its flag goes up.
 #pragma unroll 1
@@ -289,7 +298,7 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
       } else {
         const bool has_rows = row0 < p.M;
-        if (p.ksplit == 2) {
+        if (unit.split) {
           // Finisher: the neighbour cluster's partial sums of these rows must have landed.
           int seen = 1;
           if (lane == 0) {
@@ -318,7 +327,7 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // fetched while this one is converted.
         constexpr int kSteps = BN / 32;
         constexpr int kStepsPerChunk = kChunk / 32;
-        const bool add_partial = (p.ksplit == 2) && ok;
+        const bool add_partial = unit.split && ok;
         float4 nxt[8];
         if (add_partial) {
 #pragma unroll

@@ -86,8 +86,8 @@ int launch_pair_kernel(const CUtensorMap& tA, const CUtensorMap& tB, const CUten
   return kOk;
 }
 
-// The all-gather GEMM: 256 x 256 pair tiles, every piece stored into all copies of the output,
-// K split in two when the K loop is long enough (workspace from the pool, reusable once this
+// The all-gather GEMM: 256 x 256 pair tiles, every piece stored into all copies of the output; with
+// p.ksplit = 2 the first wave of units are half-K units (workspace from the pool, reusable once this
 // launch has finished on `stream`).
 template <typename OutT>
 int launch_ag_kernel(const CUtensorMap& tA, const CUtensorMap& tB, const PeerMaps& peers,
@@ -116,10 +116,21 @@ int launch_ag_kernel(const CUtensorMap& tA, const CUtensorMap& tB, const PeerMap
     }
     if (dev >= 0 && dev < 64) max_clusters[dev] = mc;
   }
+  // With the first wave split, clusters 2t and 2t+1 share tile t: an even cluster count, and fp32
+  // partial sums plus flags for those clusters / 2 tiles.
+  int clusters = (int)std::min<long long>(tiles * p.ksplit, mc);
+  if (p.ksplit == 2) {
+    clusters &= ~1;
+    if (clusters < 2) {
+      p.ksplit = 1;
+      clusters = (int)std::min<long long>(tiles, mc);
+    }
+  }
   void* ws = nullptr;
   if (p.ksplit == 2) {
-    const size_t partial_bytes = (size_t)tiles * gemm_ag::PARTIAL_BYTES_PER_TILE;
-    const size_t flag_bytes = (size_t)tiles * gemm_ag::FLAGS_PER_TILE * sizeof(int);
+    const size_t split_tiles = (size_t)clusters / 2;
+    const size_t partial_bytes = split_tiles * gemm_ag::PARTIAL_BYTES_PER_TILE;
+    const size_t flag_bytes = split_tiles * gemm_ag::FLAGS_PER_TILE * sizeof(int);
     ws = pool_alloc(partial_bytes + flag_bytes);
     if (!ws) return kDeviceFailed;
     p.partial = static_cast<float*>(ws);
@@ -130,9 +141,6 @@ int launch_ag_kernel(const CUtensorMap& tA, const CUtensorMap& tB, const PeerMap
       return kDeviceFailed;
     }
   }
-  // The two halves of a tile run on neighbouring clusters in the same wave: an even cluster count.
-  int clusters = (int)std::min<long long>(tiles * p.ksplit, mc);
-  if (p.ksplit == 2) clusters &= ~1;
   cfg.gridDim = dim3(2 * clusters);
   const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_ag::gemm_ag_kernel<OutT>, tA, tB, peers, p);
   if (ws) pool_free_after(ws, stream);
@@ -264,12 +272,14 @@ int launch_plain(const void* A, const void* B, void* D, int batch, int M, int N,
     Params pa = p;
     pa.idesc = make_idesc_f16(in_dtype == TESSERA_SM100_BF16, false, true, 2 * BM, BN);
     pa.peer_first = peer_first;
-    // Split K when there are fewer than four waves of whole tiles (the first tile time and the last
-    // wave's burst of stores then weigh on the step: 8192 x 8192 over 4 or 8 ranks) and the K loop
-    // has at least 16 k-blocks, so that each half still fills the TMA ring. With many waves the
-    // split only adds the partial-sum traffic (two ranks: 0.394 ms with it, 0.375 ms without).
+    // Split K in the first wave when (a) there are fewer than four waves of whole tiles, so the first
+    // tile time weighs on the step, (b) the K loop has at least 16 k-blocks, so each half still fills
+    // the TMA ring, and (c) there are at most four copies. With more copies a CTA has more bytes to
+    // store per tile than the tile takes to compute, the step is bound by how evenly the stores are
+    // spread over the SMs, and the split (whose first wave stores from half of the CTAs) loses:
+    // measured on eight GPUs 465 us against 250 us unsplit; on four 248 us against 273 us.
     const long long ag_tiles = (long long)((p.m_tiles + 1) / 2) * p.n_tiles;
-    pa.ksplit = ((K + BK - 1) / BK >= 16 && ag_tiles < 4ll * (sm_count() / 2)) ? 2 : 1;
+    pa.ksplit = ((K + BK - 1) / BK >= 16 && ag_tiles < 4ll * (sm_count() / 2) && num_peers <= 4) ? 2 : 1;
     switch (out_dtype) {
       case TESSERA_SM100_F32: return launch_ag_kernel<float>(tA, tB, peer_maps, pa, ag_tiles, stream);
       case TESSERA_SM100_BF16: return launch_ag_kernel<__nv_bfloat16>(tA, tB, peer_maps, pa, ag_tiles, stream);

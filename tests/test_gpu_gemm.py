@@ -174,16 +174,17 @@ def test_cta_pair_kernel_shapes(batch, M, N, K, out_dt):
                                                 (2304, 8192, 128, np.float32, 2), (200, 1088, 72, bfloat16, 8),
                                                 (1000, 2112, 520, np.float16, 4), (129, 48, 64, np.float32, 3),
                                                 (512, 1024, 1088, bfloat16, 2), (2304, 2048, 2048, np.float32, 4),
-                                                (200, 1088, 1032, bfloat16, 8), (4096, 4096, 4096, bfloat16, 4),
+                                                (200, 1088, 1032, bfloat16, 8), (4096, 4096, 4096, bfloat16, 4), (2048, 3072, 2048, np.float16, 3),
                                                 (4864, 8192, 1024, bfloat16, 2)])
 def test_fused_all_gather_epilogue_with_local_copies(lib, M, N, K, out_dt, world):
     """The column-parallel GEMM's epilogue stores each finished piece into every rank's Y. Here the
     "ranks" run one after the other on one GPU with all Y copies local, which exercises the per-copy
     stores and the rotation over the copies (ragged M, column blocks that are not a multiple of the
-    tile width, an odd number of 128-row tiles, 2 to 8 ranks, 16-bit and fp32 outputs) and, from 16
-    k-blocks on and below four waves of tiles, the split of the K loop over neighbouring clusters
-    (an odd number of k-blocks, a ragged last one, several waves of units; the last case has enough
-    tiles to run unsplit with a long K loop); every copy must hold the complete product."""
+    tile width, an odd number of 128-row tiles, 2 to 8 ranks, 16-bit and fp32 outputs) and, with at
+    most four copies, 16 k-blocks or more and fewer than four waves of tiles, the first wave of
+    units split over the K loop between neighbouring clusters (an odd number of k-blocks, a ragged
+    last one, whole tiles following the split wave; the last case has enough tiles to run unsplit
+    with a long K loop); every copy must hold the complete product."""
     from tessera_b200 import _lib, device
     from tessera_b200.device import DeviceArray
     rng = np.random.default_rng(M + K)

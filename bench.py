@@ -11,11 +11,21 @@ layer), each with its own roofline entry.
 A step is one pass over synthetic inputs that are resident in HBM before the timed region. Every
 timed step is preceded (outside its CUDA-event bracket) by an L2 flush. Times are CUDA events on
 the launching stream; with several ranks the per-step maximum over ranks is what counts.
-``e2e`` is the same GEMM through the public ``tessera_b200.ops.gemm`` call with pinned host
-buffers, host<->device copies inside the timed region.
+``e2e`` is the same GEMM through the public host-operand call with pinned host buffers,
+host<->device copies inside the timed region: ``tessera_b200.ops.gemm`` on one GPU,
+``parallel.TensorParallelGemm.run_host`` on several (each rank uploads M/N rows of A and its block of
+W, A is all-gathered over NVLink, the rank's block of Y comes back).
 
-``--impl reference`` times the reference's CPU implementation of the same configuration (its
-numpy path, restated in oracle/) on the host cores of this machine.
+What was timed is checked: sampled outputs of every workload against the CPU reference on every
+rank (``roofline.parity``); a mismatch is listed in ``parity_failures`` and the process exits 3.
+``roofline.configs`` summarises configurations 1, 3, 4 and 5 (value, time, fraction of the roofline,
+CPU value); with several GPUs ``roofline.exchange`` holds the exchange timed on its own, the GEMM
+on its own and the step against the larger of the two.
+
+``--impl reference`` times the reference's CPU implementation of the headline configuration (its
+numpy path, restated in oracle/) on the host cores of this machine with every core's worth of BLAS
+threads; single-GPU runs also time the CPU path of each configuration on a bounded sample
+(``cpu_baseline`` of every workload).
 
 Multi-GPU runs are launched as ``python -m torch.distributed.run --nproc-per-node N bench.py
 --gpus N ...``; torch.distributed (gloo) is used for rank plumbing only.
@@ -52,9 +62,10 @@ sys.path.insert(0, ROOT)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 WORKLOAD = "gemm_bf16_8192: A[8192,8192] x B[8192,8192] -> Y bf16, fp32 accumulate"
 PARITY_TOL = 1e-2          # max|y - ref| / max|ref| in fp32, the stated parity tolerance
-# Peer-store bandwidth of SM-issued stores (TMA or st.global, 128- or 256-byte rows alike), measured
-# on this pool with both GPUs of a pair writing at once: the denominator of the exchange floor.
-PEER_STORE_GBS = 650.0
+# Peer-store bandwidth of SM-issued stores measured on this pool (633-650 GB/s per direction with all
+# ranks storing at once, profiles/column_exchange_8gpu.md): only the fallback denominator of the
+# exchange floor; a multi-GPU run times the exchange itself.
+PEER_STORE_GBS = 640.0
 
 
 def blas_threads():
@@ -360,18 +371,18 @@ def bench_gemm(ranks, args, peaks, peak_kind, sampler):
     if W > 1:
         # Every rank has to take in the other ranks' column blocks of Y over its NVLink ingress. The
         # floor is the exchange timed on its own just above (all ranks storing at once); the constant is
-        # the two-GPU figure of profiles/peer_store_bandwidth_2gpu.md, kept beside it for comparison.
+        # an earlier measurement on this pool, kept beside it for comparison.
         ingress = (W - 1) / W * n * n * 2
         floor_ms = exchange_ms if exchange_ms else ingress / (PEER_STORE_GBS * 1e9) * 1e3
         roof["exchange"] = {"ingress_bytes_per_rank": ingress,
                             "exchange_only_ms": exchange_ms,
                             "peer_store_gbs_measured": (ingress / exchange_ms / 1e6) if exchange_ms else None,
-                            "peer_store_gbs_two_gpu_probe": PEER_STORE_GBS,
+                            "peer_store_gbs_earlier_measurement": PEER_STORE_GBS,
                             "exchange_floor_ms": floor_ms, "compute_ms": k_ms,
                             "floor_ms": max(floor_ms, k_ms), "step_ms": ms,
                             "efficiency_vs_floor": max(floor_ms, k_ms) / ms,
-                            "fused_kernel": "gemm_ag_kernel<bf16> (cta_group::2 256x256x64, K split over neighbouring "
-                                            "CTA pairs below four waves of tiles, TMA stores into every rank's Y)"
+                            "fused_kernel": "gemm_ag_kernel<bf16> (cta_group::2 256x256x64, TMA stores into every rank's Y; "
+                                            "first wave of units split over K with at most four ranks)"
                                             if tp_mode == "fused" else None,
                             "note": "floor = max(the exchange alone, the GEMM alone); a perfectly overlapped step would "
                                     "take that long"}

@@ -453,18 +453,26 @@ __global__ void ep_dispatch_signal_kernel(const uint4* __restrict__ x, const int
     group_offsets_local[Ep] = acc;
   }
   __syncthreads();
+  // One warp per kept slot: the row's source token and destination are looked up once, then the
+  // lanes copy it with four 16-byte loads in flight each (a row of 4096 bf16 is 512 vectors).
   const int S = my_offsets[E];  // kept slots of this rank
-  const long long total = (long long)S * vec_per_row;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const int sl = (int)(i / vec_per_row);
-    const int c = (int)(i - (long long)sl * vec_per_row);
+  const int lane = threadIdx.x & 31;
+  const int warps_per_cta = blockDim.x >> 5;
+  for (int sl = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); sl < S; sl += gridDim.x * warps_per_cta) {
     const int e = expert_of_slot[sl];
     const int row = s_base[e] + (sl - my_offsets[e]);
-    if (row < capacity_rows) {
-      uint4* dst = static_cast<uint4*>(recv.p[e / Ep]);
-      dst[(long long)row * vec_per_row + c] = x[(long long)token_of_slot[sl] * vec_per_row + c];
+    if (row >= capacity_rows) continue;
+    const uint4* src = x + (long long)token_of_slot[sl] * vec_per_row;
+    uint4* dst = static_cast<uint4*>(recv.p[e / Ep]) + (long long)row * vec_per_row;
+    int c = lane;
+    for (; c + 96 < vec_per_row; c += 128) {
+      const uint4 v0 = src[c], v1 = src[c + 32], v2 = src[c + 64], v3 = src[c + 96];
+      dst[c] = v0;
+      dst[c + 32] = v1;
+      dst[c + 64] = v2;
+      dst[c + 96] = v3;
     }
+    for (; c < vec_per_row; c += 32) dst[c] = src[c];
   }
   // The CTA that finishes last tells every rank that this rank's rows have landed.
   __threadfence_system();
@@ -498,26 +506,52 @@ __global__ void ep_combine_signal_kernel(PeerPtrs ybufs, PeerPtrs ctrl, const in
     ep_wait_flag(&mine->y_ready[threadIdx.x], epoch, limit_ns, err, 400 + threadIdx.x);
   }
   __syncthreads();
+  // The token's k result rows: located once per CTA, then every thread issues all of its 16-byte
+  // peer loads (k per column vector) before it touches the values, so one NVLink round trip covers them.
+  __shared__ const YT* s_row[kMaxTopK];
+  __shared__ float s_w[kMaxTopK];
   const int t = blockIdx.x;
-  for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
-    float acc[8];
-#pragma unroll
-    for (int q = 0; q < 8; ++q) acc[q] = 0.f;
-    for (int j = 0; j < top_k; ++j) {
-      const int sl = slot_of[(long long)t * top_k + j];
-      if (sl < 0) continue;
+  if (threadIdx.x < top_k) {
+    const int j = threadIdx.x;
+    const int sl = slot_of[(long long)t * top_k + j];
+    const YT* rowp = nullptr;
+    if (sl >= 0) {
       const int e = assignment[(long long)t * top_k + j];
       const int row = dst_base[e] + (sl - my_offsets[e]);
-      if (row >= capacity_rows) continue;
-      const float wj = w[(long long)t * top_k + j];
-      const YT* src = static_cast<const YT*>(ybufs.p[e / Ep]) + (long long)row * H + c;
-      const uint4 v = __ldcg(reinterpret_cast<const uint4*>(src));  // 8 x 16-bit, not through L1
-      const YT* h = reinterpret_cast<const YT*>(&v);
+      if (row < capacity_rows) rowp = static_cast<const YT*>(ybufs.p[e / Ep]) + (long long)row * H;
+    }
+    s_row[j] = rowp;
+    s_w[j] = w[(long long)t * top_k + j];
+  }
+  __syncthreads();
+  constexpr int kVecsPerThread = 2;
+  for (int c0 = threadIdx.x * 8; c0 < H; c0 += blockDim.x * 8 * kVecsPerThread) {
+    uint4 v[kVecsPerThread][kMaxTopK];
 #pragma unroll
-      for (int q = 0; q < 8; ++q) acc[q] += wj * to_f32<YT>(h[q]);
+    for (int u = 0; u < kVecsPerThread; ++u) {
+      const int c = c0 + u * blockDim.x * 8;
+#pragma unroll
+      for (int j = 0; j < kMaxTopK; ++j)
+        if (j < top_k && c < H && s_row[j]) v[u][j] = __ldcg(reinterpret_cast<const uint4*>(s_row[j] + c));
     }
 #pragma unroll
-    for (int q = 0; q < 8; ++q) out[(long long)t * H + c + q] = from_f32<OT>(acc[q]);
+    for (int u = 0; u < kVecsPerThread; ++u) {
+      const int c = c0 + u * blockDim.x * 8;
+      if (c >= H) break;
+      float acc[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) acc[q] = 0.f;
+#pragma unroll
+      for (int j = 0; j < kMaxTopK; ++j) {
+        if (j >= top_k || !s_row[j]) continue;
+        const float wj = s_w[j];
+        const YT* hp = reinterpret_cast<const YT*>(&v[u][j]);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[q] += wj * to_f32<YT>(hp[q]);
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q) out[(long long)t * H + c + q] = from_f32<OT>(acc[q]);
+    }
   }
   // The CTA that finishes last tells every rank that this rank no longer reads their buffers.
   __syncthreads();
@@ -933,9 +967,10 @@ int tessera_sm100_ep_dispatch_signal_device(const void* x, const int* token_of_s
   int* err = device_err_word();
   if (!err) return kDeviceFailed;
   const int vec = (int)(row_bytes / 16);
-  const long long total = (long long)max_slots * vec;
-  const int grid = (int)std::min<long long>((total + 255) / 256, 148 * 16);
-  moe::ep_dispatch_signal_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  // one warp per slot, 16 warps per CTA, at most two CTAs per SM (one wave: the flag waits of the
+  // prologue are paid once)
+  const int grid = (int)std::min<long long>(((long long)max_slots + 15) / 16, 2ll * sm_count());
+  moe::ep_dispatch_signal_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(x), token_of_slot, expert_of_slot, my_offsets, cp, rp, world, rank, E,
       capacity_rows, vec, epoch, group_offsets_local, dst_base, counter, ep_limit_ns(wait_limit_ms), err);
   TSB_CUDA_OK(cudaGetLastError());
@@ -965,12 +1000,12 @@ int tessera_sm100_ep_combine_signal_device(void* const* y_bufs, void* const* ctr
   const int Ep = E / world;
   const unsigned long long lim = ep_limit_ns(wait_limit_ms);
   if (dtype == TESSERA_SM100_BF16)
-    moe::ep_combine_signal_kernel<__nv_bfloat16, __nv_bfloat16><<<T, 128, 0, st>>>(
+    moe::ep_combine_signal_kernel<__nv_bfloat16, __nv_bfloat16><<<T, 256, 0, st>>>(
         yp, cp, assignment, slot_of_assignment, weights, my_offsets, dst_base,
         static_cast<__nv_bfloat16*>(out), T, top_k, world, rank, Ep, capacity_rows, H, epoch, counter, lim,
         err);
   else if (dtype == TESSERA_SM100_F16)
-    moe::ep_combine_signal_kernel<__half, __half><<<T, 128, 0, st>>>(
+    moe::ep_combine_signal_kernel<__half, __half><<<T, 256, 0, st>>>(
         yp, cp, assignment, slot_of_assignment, weights, my_offsets, dst_base, static_cast<__half*>(out), T,
         top_k, world, rank, Ep, capacity_rows, H, epoch, counter, lim, err);
   else {

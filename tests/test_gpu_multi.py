@@ -64,6 +64,30 @@ def _worker(rank, world, port, q):
         dist.barrier()
         errs["tp_gemm"] = orc.max_rel_err(tp.Y.download(), orc.gemm(A, Wm))
         dist.barrier()
+        # the exchange on its own: every rank's column block stored into the other rank's Y
+        tp.Y.upload(np.full((M, N), rank + 1, np.float32).astype(bfloat16))
+        device.synchronize()
+        dist.barrier()
+        tp.exchange_only()
+        device.synchronize()
+        dist.barrier()
+        want_y = np.concatenate([np.full((M, N // world), r + 1, np.float32) for r in range(world)], axis=1)
+        errs["exchange_only"] = float(np.abs(tp.Y.download().astype(np.float32) - want_y).max())
+        dist.barrier()
+        # host operands: each rank uploads M / world rows of A and its block of W, A is all-gathered
+        # over NVLink, the fused kernel runs, the rank's block of Y comes back
+        from tessera_b200.device import PinnedArray
+        mb, nb = M // world, N // world
+        pa, pw, py = PinnedArray((mb, K), bfloat16), PinnedArray((K, nb), bfloat16), PinnedArray((M, nb), bfloat16)
+        pa.array[...] = A[rank * mb:(rank + 1) * mb]
+        pw.array[...] = Wm[:, rank * nb:(rank + 1) * nb]
+        for _ in range(2):
+            tp.run_host(pa.array, pw.array, py.array, comm)
+        dist.barrier()
+        full = orc.gemm(A, Wm)
+        errs["tp_run_host_block"] = orc.max_rel_err(py.array, full[:, rank * nb:(rank + 1) * nb])
+        errs["tp_run_host_gathered"] = orc.max_rel_err(tp.Y.download(), full)
+        dist.barrier()
         tp.close()
         # large enough for the CTA-pair kernel to do the per-rank stores
         M, N, K = 2048, 8192, 256
@@ -135,6 +159,7 @@ def test_two_gpu_collectives_tp_gemm_and_ep_moe():
         assert exc is None, f"rank {rank}:\n{exc}"
         assert errs["all_gather"] == 0 and errs["all_reduce"] == 0 and errs["all_to_all_v"] == 0, errs
         assert errs["tp_gemm"] < 1e-2 and errs["tp_gemm_pairs"] < 1e-2 and errs["ep_moe"] < 1e-2 and errs["ep_moe_device"] < 1e-2, errs
+        assert errs["exchange_only"] == 0.0 and errs["tp_run_host_block"] < 1e-2 and errs["tp_run_host_gathered"] < 1e-2, errs
 
 
 def _full_size_worker(rank, world, port, q):

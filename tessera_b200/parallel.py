@@ -96,18 +96,27 @@ class TensorParallelGemm:
         if A_rows.shape != (mb, K) or W_block.shape != (K, nb) or Y_block.shape != (M, nb):
             raise ValueError("run_host: operand shapes do not match this rank's shard")
         if self._A is None:
+            from .device import Event, Stream
             self._A, self._Wb = DeviceArray((M, K), self.dtype), DeviceArray((K, nb), self.dtype)
+            self._Yb = DeviceArray((M, nb), self.out_dtype)          # this rank's block of Y, contiguous
+            self._side, self._w_ready = Stream(), Event()
         sh = device._stream_handle(stream)
         isz, osz = self.dtype.itemsize, self.out_dtype.itemsize
         mine = self._A.view((mb, K), r * mb * K)
+        # the rows of A go up first (the all-gather waits for nothing else); the block of W goes up on a
+        # second stream while the all-gather runs
         _lib.call("tessera_sm100_device_upload", mine.ptr, A_rows.ctypes.data, mb * K * isz, sh)
-        _lib.call("tessera_sm100_device_upload", self._Wb.ptr, W_block.ctypes.data, K * nb * isz, sh)
+        _lib.call("tessera_sm100_device_upload", self._Wb.ptr, W_block.ctypes.data, K * nb * isz, self._side.handle)
+        self._w_ready.record(self._side)
         if W > 1:
             comm.all_gather(mine, self._A, stream)            # in place: block r of A is already there
+        _lib.call("tessera_sm100_stream_wait_event", sh, self._w_ready.handle)
         _lib.call("tessera_sm100_gemm_allgather_block_device", self._A.ptr, self._Wb.ptr, nb, self._ptrs, W, r,
                   M, N, K, self._in, self._out, sh)
-        _lib.call("tessera_sm100_device_download_2d", Y_block.ctypes.data, nb * osz, self.Y.ptr + r * nb * osz,
-                  N * osz, nb * osz, M, sh)
+        # the rank's column block is strided in Y: compact it on the device, then one contiguous copy down
+        _lib.call("tessera_sm100_device_copy_2d", self._Yb.ptr, nb * osz, self.Y.ptr + r * nb * osz, N * osz,
+                  nb * osz, M, sh)
+        _lib.call("tessera_sm100_device_download", Y_block.ctypes.data, self._Yb.ptr, M * nb * osz, sh)
         _lib.call("tessera_sm100_stream_synchronize", sh)
 
     def close(self) -> None:
@@ -115,6 +124,10 @@ class TensorParallelGemm:
         for p in self._opened:
             _lib.call("tessera_sm100_ipc_close_handle", p)
         self._opened = []
+        if self._A is not None:
+            self._side.close()
+            self._w_ready.close()
+            self._A = None
 
 
 # ---------------------------------------------------------------------------- expert parallel

@@ -31,12 +31,34 @@ def _ref(q, k, v, causal):
 PREFILL = [(1, 1, 1, 256, 256, False), (1, 1, 1, 256, 256, True), (1, 2, 2, 128, 128, True),
            (1, 2, 1, 384, 384, True), (2, 4, 2, 512, 512, True), (1, 2, 2, 300, 300, True),
            (1, 2, 2, 300, 300, False), (1, 2, 1, 128, 512, True), (1, 1, 1, 77, 1000, True),
-           (1, 1, 1, 1000, 77, False), (1, 8, 1, 130, 130, True), (1, 1, 1, 5, 3, False)]
+           (1, 1, 1, 1000, 77, False), (1, 8, 1, 130, 130, True), (1, 1, 1, 5, 3, False),
+           # the 64-key block walk: exactly one block, a second tile of one row, more query rows than keys
+           # under the causal mask, and a key sequence long enough for every ring slot to wrap many times
+           (1, 1, 1, 200, 64, True), (1, 2, 1, 257, 65, True), (1, 1, 1, 129, 129, True),
+           (1, 1, 1, 1000, 77, True), (1, 2, 2, 64, 4096, True), (1, 1, 1, 320, 4096, False)]
 
 
 @pytest.mark.parametrize("B,Hq,Hkv,Sq,Sk,causal", PREFILL)
 def test_prefill_matches_oracle(B, Hq, Hkv, Sq, Sk, causal):
     q, k, v = _qkv(np.random.default_rng(Sq * 7 + Sk), B, Hq, Hkv, Sq, Sk)
+    assert rel_err(attn_device(q, k, v, causal), _ref(q, k, v, causal)) < TOL
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_prefill_raises_the_running_maximum_in_every_block(causal):
+    """Scores that keep growing along the key axis (by more than 2^8 per 64 keys, at a rate that differs from
+    row to row) make the kernel raise its running maximum and rescale the output accumulator in TMEM in
+    block after block -- the path random data never takes after the first block."""
+    rng = np.random.default_rng(11)
+    B, H, Sq, Sk, D = 1, 2, 384, 1024, 128
+    u = rng.standard_normal(D).astype(np.float32)
+    u /= np.linalg.norm(u)
+    row_gain = (1.0 + 3.0 * np.arange(Sq, dtype=np.float32) / Sq)[None, None, :, None]
+    key_ramp = (np.arange(Sk, dtype=np.float32) / Sk)[None, None, :, None]
+    q = (u * row_gain + 0.05 * rng.standard_normal((B, H, Sq, D), dtype=np.float32)).astype(bfloat16)
+    k = (u * key_ramp * 424.0 + 0.05 * rng.standard_normal((B, H, Sk, D), dtype=np.float32)).astype(bfloat16)
+    v = rng.standard_normal((B, H, Sk, D), dtype=np.float32).astype(bfloat16)
+    # scale * q.k runs from 0 to about 37..150 over the keys: 3..13 (log2 units) per block of 64
     assert rel_err(attn_device(q, k, v, causal), _ref(q, k, v, causal)) < TOL
 
 

@@ -83,7 +83,7 @@ def blas_threads():
 # captures ran a quarter-size case (heads, batch, experts x slots) and are scaled x4, the traffic
 # of these kernels being proportional to those counts. The MoE figure is the sum of its two
 # grouped GEMM launches.
-NCU_TRAFFIC_BYTES = {"gemm_8192": 1.209e9, "attn_prefill": 1.007e9, "attn_decode": 2.171e9, "attn_decode_paged": 2.166e9,
+NCU_TRAFFIC_BYTES = {"gemm_8192": 1.209e9, "attn_prefill": 1.005e9, "attn_decode": 2.171e9, "attn_decode_paged": 2.166e9,
                      "attn_decode_int8": 1.093e9, "moe": 4.78e9}
 
 
@@ -463,6 +463,9 @@ def bench_attn_prefill(ranks, args, peaks, peak_kind):
     out = {"metric": "causal flash-attention forward TFLOP/s", "value": flops / ms / 1e9, "unit": "TFLOP/s",
            "ms_per_step": ms, "config": f"B={B} H={H} S={S} D={D} bf16 causal, heads sharded /{W}",
            "flops_convention": "4*B*H*S^2*D/2",
+           "value_in_the_reference_benchmark_convention": {
+               "value": 3.0 * B * H * S * S * D / ms / 1e9, "unit": "TFLOP/s",
+               "convention": "3*B*H*S^2*D, what benchmarks/benchmark_attention.py:51-63 counts (no causal halving)"},
            "parity": {"max_rel_err": max(ranks.gather(float(err))), "tolerance": PARITY_TOL,
                       "sample": "2 (batch, head) slices per rank, all rows"},
            "roofline": {"bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
